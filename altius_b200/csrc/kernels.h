@@ -1,0 +1,139 @@
+// Launchers of the sm_100a kernels. Host code (the scheduler) sees only these
+// declarations; each launcher enqueues on the given stream and returns the
+// CUDA status of the launch.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ac {
+
+constexpr int kMaxRank = 8;
+
+// ---- elementwise -----------------------------------------------------------
+enum BinOp { BIN_ADD = 0, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW };
+
+// Broadcast binary op over a collapsed iteration space: dims[rank-1] is the
+// innermost extent; a_str / b_str are element strides (0 = broadcast).
+struct BinaryParams {
+  int op;
+  int rank;
+  int64_t dims[kMaxRank];
+  int64_t a_str[kMaxRank];
+  int64_t b_str[kMaxRank];
+  int64_t n;  // total output elements
+};
+cudaError_t launch_binary(const BinaryParams& p, const float* a, const float* b, float* out,
+                          cudaStream_t st);
+
+enum UnaryOp {
+  UN_RELU = 0, UN_SIGMOID, UN_ERF, UN_GELU, UN_HARDSIGMOID, UN_LEAKYRELU, UN_SQRT, UN_TANH,
+  UN_HARDSWISH,  // x * HardSigmoid(x; alpha, beta): the HardSigmoid -> Mul pair folded
+  UN_SQUARE,     // Pow(x, 2) special case of the reference: x * x
+  UN_COPY
+};
+cudaError_t launch_unary(int op, float alpha, float beta, const float* x, float* out, int64_t n,
+                         cudaStream_t st);
+cudaError_t launch_greater_scalar(const float* x, const float* y_scalar, uint8_t* out, int64_t n,
+                                  cudaStream_t st);
+// mode 0: out = cond ? x[0] : y[i]; mode 1: out = cond[i % inner] ? x[i] : y[0]
+cudaError_t launch_where(int mode, const uint8_t* cond, const float* x, const float* y, float* out,
+                         int64_t n, int64_t inner, cudaStream_t st);
+// from/to: 0 bool, 1 f32, 2 i32, 3 i64
+cudaError_t launch_cast(int from, int to, const void* x, void* out, int64_t n, cudaStream_t st);
+cudaError_t launch_batch_norm(const float* x, const float* scale, const float* bias,
+                              const float* mean, const float* var, float* out, int64_t n,
+                              int64_t c, int64_t hw, float eps, cudaStream_t st);
+
+// ---- row kernels (reductions over the last axis) ----------------------------
+// Softmax(x * scale) with the reference's polynomial exponential. `scale_mode`
+// 0: none, 1: multiply by *scale, 2: divide by *scale (scalar read on device).
+cudaError_t launch_softmax(const float* x, float* out, int64_t rows, int64_t len, int scale_mode,
+                           const float* scale, cudaStream_t st);
+
+// v = x; if (pre_bias) v += pre_bias[col]; if (gelu) v = Gelu(v);
+// if (residual) v = residual_first ? residual + v : v + residual;
+// if (sum_out) sum_out = v;  out = LayerNorm(v) * gamma + beta.
+struct LayerNormParams {
+  const float* x;
+  const float* pre_bias;   // [len] or null
+  const float* residual;   // [rows, len] or null
+  const float* gamma;
+  const float* beta;
+  float* sum_out;          // [rows, len] or null
+  float* out;
+  int64_t rows;
+  int64_t len;
+  float eps;
+  int gelu;
+  int residual_first;
+};
+cudaError_t launch_layer_norm(const LayerNormParams& p, cudaStream_t st);
+
+cudaError_t launch_reduce_mean_last(const float* x, float* out, int64_t rows, int64_t len,
+                                    cudaStream_t st);
+cudaError_t launch_reduce_max_last(const float* x, float* out, int64_t rows, int64_t len,
+                                   cudaStream_t st);
+// Whole-tensor maximum; `partials` is scratch of reduce_max_all_scratch_elems(n) floats.
+int64_t reduce_max_all_scratch_elems(int64_t n);
+cudaError_t launch_reduce_max_all(const float* x, float* out, int64_t n, float* partials,
+                                  cudaStream_t st);
+// out[i] = sum(x[i, 0:hw]) / hw
+cudaError_t launch_gavg_pool(const float* x, float* out, int64_t planes, int64_t hw,
+                             cudaStream_t st);
+
+// ---- data movement ----------------------------------------------------------
+cudaError_t launch_max_pool(const float* x, float* out, int64_t planes, int ih, int iw, int oh,
+                            int ow, int kh, int kw, int sh, int sw, int pad_t, int pad_l,
+                            cudaStream_t st);
+// Generic strided gather: out (contiguous, dims[rank]) <- in at sum(idx[d] * in_str[d]) + in_off.
+// Serves Transpose, Slice, Split, Gather, Concat pieces. elem_bytes 1, 4 or 8.
+struct CopyParams {
+  int rank;
+  int64_t dims[kMaxRank];
+  int64_t in_str[kMaxRank];
+  int64_t out_str[kMaxRank];
+  int64_t in_off;
+  int64_t out_off;
+  int64_t n;
+  int elem_bytes;
+};
+cudaError_t launch_strided_copy(const CopyParams& p, const void* in, void* out, cudaStream_t st);
+// Batched 2-D transpose: in [batch, r, c] -> out [batch, c, r] (f32).
+cudaError_t launch_transpose2d(const float* in, float* out, int64_t batch, int r, int c,
+                               cudaStream_t st);
+
+// ---- convolution ------------------------------------------------------------
+enum Act { ACT_NONE = 0, ACT_RELU, ACT_HARDSIGMOID, ACT_HARDSWISH, ACT_GELU };
+struct ConvParams {
+  int n, c, ih, iw, oc, oh, ow, kh, kw, sh, sw, dh, dw, pad_t, pad_l, group;
+  int act;
+  float act_alpha, act_beta;
+};
+// col[n, c, kh, kw, oh, ow] <- x[n, c, ih, iw]
+cudaError_t launch_im2col(const ConvParams& p, const float* x, float* col, cudaStream_t st);
+// Depthwise (group == c == oc) stencil with bias and activation fused.
+cudaError_t launch_depthwise_conv(const ConvParams& p, const float* x, const float* w,
+                                  const float* bias, float* out, cudaStream_t st);
+
+// ---- GEMM -------------------------------------------------------------------
+// C[b] = act(alpha * op(A[b]) * op(B[b]) + beta * Cin[b] + bias) (+ residual)
+// Row-major operands; trans_a: A stored [K, M]; trans_b: B stored [N, K].
+struct GemmParams {
+  int64_t m, n, k;
+  int64_t batch;
+  const float* a; int64_t lda; int64_t stride_a; int trans_a;
+  const float* b; int64_t ldb; int64_t stride_b; int trans_b;
+  float* c; int64_t ldc; int64_t stride_c;
+  float alpha;
+  float beta;               // applied to c_in (may alias c); 0: c_in not read
+  const float* c_in; int64_t ldc_in; int64_t stride_c_in;
+  const float* bias_n;      // [n] or null; added as bias_scale * bias_n[col]
+  const float* bias_m;      // [m] or null; added as bias_scale * bias_m[row]
+  float bias_scale;         // 1 unless a Gemm node carries beta != 1
+  int act; float act_alpha, act_beta;
+  const float* residual; int64_t ld_res; int64_t stride_res;  // added after act; or null
+  int residual_first;       // residual + v instead of v + residual (same value, kept for clarity)
+};
+cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
+
+}  // namespace ac

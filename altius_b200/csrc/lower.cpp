@@ -1,0 +1,1067 @@
+// Lowering: op graph (after altius's fusion passes and shape inference) ->
+// static schedule of kernel launches over storages.
+//
+//  1. values get storages; Reshape / Flatten / Squeeze / Unsqueeze / Identity
+//     alias their input (the reference shares the buffer too: `copy_data_from`
+//     is an Arc clone, crates/core/src/tensor.rs:340-342);
+//  2. producer/consumer folds are detected (disabled by options.disable_fusion):
+//       MatMul|Gemm|Conv2d -> bias Add -> ReLU|Gelu|HardSigmoid|HardSwish -> residual Add
+//       Mul|Div by a scalar -> Softmax
+//       bias Add -> Gelu -> residual Add -> LayerNormalization
+//       HardSigmoid -> Mul (HardSwish), Transpose(last two) -> MatMul rhs
+//  3. every remaining node becomes one or more kernel launches;
+//  4. steps are ordered by their data dependencies.
+//
+// What each node computes follows `run_node`'s dispatch
+// (crates/session_interpreter/src/session.rs:168-249).
+#include <algorithm>
+#include <cstring>
+#include <set>
+
+#include "session.h"
+
+namespace ac {
+namespace {
+
+struct Ctx {
+  AcSession& s;
+  std::vector<int> producer;                 // value -> node
+  std::vector<std::vector<int>> consumers;   // value -> node ids (one entry per use)
+  std::vector<char> is_output;
+  std::vector<char> absorbed;                // node folded into another node's kernel
+  explicit Ctx(AcSession& s_) : s(s_) {}
+
+  Value& val(int v) { return s.values[v]; }
+  bool single_use(int v) const { return consumers[v].size() == 1 && !is_output[v]; }
+  int only_consumer(int v) const { return consumers[v][0]; }
+  Node& node(int n) { return s.nodes[n]; }
+
+  int new_storage(size_t bytes, bool weight = false, bool pinned = false) {
+    Storage st;
+    st.bytes = std::max<size_t>(bytes, 4);
+    st.weight = weight;
+    st.pinned_live = pinned;
+    s.storages.push_back(st);
+    return (int)s.storages.size() - 1;
+  }
+};
+
+bool same_dims(const Value& a, const Value& b) {
+  if (a.rank != b.rank) return false;
+  for (int i = 0; i < a.rank; ++i)
+    if (a.dims[i] != b.dims[i]) return false;
+  return true;
+}
+
+// True when `v` broadcasts against [.., n] as a vector along the last axis.
+bool is_last_axis_vector(const Value& v, int64_t n) {
+  if (v.rank < 1 || v.numel() != n || v.dims[v.rank - 1] != n) return false;
+  return true;
+}
+// True when `v` is a per-channel vector for an NCHW tensor: [c,1,1] or [1,c,1,1].
+bool is_channel_vector(const Value& v, int64_t c) {
+  if (v.numel() != c) return false;
+  if (v.rank == 3) return v.dims[0] == c;
+  if (v.rank == 4) return v.dims[1] == c;
+  return false;
+}
+
+double f32_bytes(const Value& v) { return (double)v.bytes(); }
+
+// ---- fused-group descriptions ----------------------------------------------------
+struct Epilogue {
+  int bias = -1;          // value id of the bias vector
+  int act = ACT_NONE;
+  float act_alpha = 0, act_beta = 0;
+  int residual = -1;
+  int out = -1;           // final value written
+  int trans_b_src = -1;   // MatMul rhs taken from the input of an absorbed Transpose
+};
+
+struct LnFusion {
+  int x = -1, pre_bias = -1, residual = -1, sum_val = -1;
+  int gelu = 0;
+};
+
+struct Plan {
+  std::map<int, Epilogue> epi;      // base node (MatMul/Gemm/Conv2d) -> epilogue
+  std::map<int, int> softmax_scale; // Softmax node -> Mul/Div node folded in
+  std::map<int, LnFusion> ln;       // LayerNormalization node -> folded producers
+  std::map<int, int> hardswish;     // Mul node -> HardSigmoid node folded in
+};
+
+// Recognises `hs = HardSigmoid(t); m = Mul(t, hs)` hanging off value t whose only
+// uses are those two nodes. Returns the Mul node or -1.
+int match_hardswish_pair(Ctx& c, int t, int* hs_node) {
+  if (c.is_output[t] || c.consumers[t].size() != 2) return -1;
+  for (int k = 0; k < 2; ++k) {
+    const int h = c.consumers[t][k], m = c.consumers[t][1 - k];
+    if (c.absorbed[h] || c.absorbed[m]) continue;
+    if (c.node(h).op != AC_OP_HARDSIGMOID || c.node(m).op != AC_OP_MUL) continue;
+    const int hv = c.node(h).outputs[0];
+    if (!c.single_use(hv) || c.only_consumer(hv) != m) continue;
+    const Node& mul = c.node(m);
+    if (!((mul.inputs[0] == t && mul.inputs[1] == hv) || (mul.inputs[1] == t && mul.inputs[0] == hv)))
+      continue;
+    *hs_node = h;
+    return m;
+  }
+  return -1;
+}
+
+void detect_epilogues(Ctx& c, Plan& plan) {
+  AcSession& s = c.s;
+  for (int nid : s.order) {
+    Node& n = c.node(nid);
+    if (c.absorbed[nid]) continue;
+    if (n.op != AC_OP_MATMUL && n.op != AC_OP_GEMM && n.op != AC_OP_CONV2D) continue;
+    Epilogue e;
+    int cur = n.outputs[0];
+    const Value& ov = c.val(cur);
+    const bool conv = n.op == AC_OP_CONV2D;
+    // rhs Transpose of the last two dims -> read the untransposed operand.
+    if (n.op == AC_OP_MATMUL) {
+      const int bv = n.inputs[1];
+      const int tp = c.producer[bv];
+      if (tp >= 0 && !c.absorbed[tp] && c.node(tp).op == AC_OP_TRANSPOSE && c.single_use(bv) &&
+          !c.val(bv).is_const) {
+        const Node& t = c.node(tp);
+        const int r = (int)t.ints.size();
+        bool swap_last = r >= 2 && t.ints[r - 1] == r - 2 && t.ints[r - 2] == r - 1;
+        for (int i = 0; swap_last && i < r - 2; ++i) swap_last = t.ints[i] == i;
+        if (swap_last) {
+          e.trans_b_src = t.inputs[0];
+          c.absorbed[tp] = 1;
+        }
+      }
+    }
+    // bias Add
+    const bool has_bias_input = (n.op == AC_OP_GEMM || conv) && n.inputs.size() > 2 && n.inputs[2] >= 0;
+    if (!has_bias_input && c.single_use(cur)) {
+      const int an = c.only_consumer(cur);
+      Node& a = c.node(an);
+      if (!c.absorbed[an] && a.op == AC_OP_ADD) {
+        const int other = a.inputs[0] == cur ? a.inputs[1] : a.inputs[0];
+        const Value& bv = c.val(other);
+        const bool ok = conv ? is_channel_vector(bv, ov.dims[1])
+                             : is_last_axis_vector(bv, ov.dims[ov.rank - 1]);
+        if (ok && other != cur && same_dims(c.val(a.outputs[0]), ov)) {
+          e.bias = other;
+          c.absorbed[an] = 1;
+          cur = a.outputs[0];
+        }
+      }
+    }
+    // activation
+    if (c.single_use(cur)) {
+      const int un = c.only_consumer(cur);
+      Node& u = c.node(un);
+      if (!c.absorbed[un]) {
+        if (u.op == AC_OP_RELU) e.act = ACT_RELU;
+        else if (u.op == AC_OP_GELU) e.act = ACT_GELU;
+        else if (u.op == AC_OP_HARDSIGMOID) {
+          e.act = ACT_HARDSIGMOID;
+          e.act_alpha = u.floats.size() > 0 ? u.floats[0] : 0.2f;
+          e.act_beta = u.floats.size() > 1 ? u.floats[1] : 0.5f;
+        }
+        if (e.act != ACT_NONE) {
+          c.absorbed[un] = 1;
+          cur = u.outputs[0];
+        }
+      }
+    } else {
+      int hs = -1;
+      const int mul = match_hardswish_pair(c, cur, &hs);
+      if (mul >= 0) {
+        e.act = ACT_HARDSWISH;
+        e.act_alpha = c.node(hs).floats.size() > 0 ? c.node(hs).floats[0] : 0.2f;
+        e.act_beta = c.node(hs).floats.size() > 1 ? c.node(hs).floats[1] : 0.5f;
+        c.absorbed[hs] = 1;
+        c.absorbed[mul] = 1;
+        cur = c.node(mul).outputs[0];
+      }
+    }
+    // residual Add (same shape, other operand produced outside this chain)
+    if (c.single_use(cur)) {
+      const int an = c.only_consumer(cur);
+      Node& a = c.node(an);
+      if (!c.absorbed[an] && a.op == AC_OP_ADD && a.inputs[0] != a.inputs[1]) {
+        const int other = a.inputs[0] == cur ? a.inputs[1] : a.inputs[0];
+        if (same_dims(c.val(other), c.val(cur)) && same_dims(c.val(a.outputs[0]), c.val(cur))) {
+          e.residual = other;
+          c.absorbed[an] = 1;
+          cur = a.outputs[0];
+        }
+      }
+    }
+    e.out = cur;
+    if (e.bias >= 0 || e.act != ACT_NONE || e.residual >= 0 || e.trans_b_src >= 0) plan.epi[nid] = e;
+  }
+}
+
+void detect_softmax_scale(Ctx& c, Plan& plan) {
+  for (int nid : c.s.order) {
+    Node& n = c.node(nid);
+    if (c.absorbed[nid] || n.op != AC_OP_SOFTMAX) continue;
+    const int x = n.inputs[0];
+    const int p = c.producer[x];
+    if (p < 0 || c.absorbed[p] || !c.single_use(x)) continue;
+    Node& m = c.node(p);
+    if (m.op != AC_OP_MUL && m.op != AC_OP_DIV) continue;
+    const Value& a = c.val(m.inputs[0]);
+    const Value& b = c.val(m.inputs[1]);
+    const bool b_scalar = b.numel() == 1 && same_dims(a, c.val(x));
+    const bool a_scalar = a.numel() == 1 && same_dims(b, c.val(x)) && m.op == AC_OP_MUL;
+    if (!b_scalar && !a_scalar) continue;
+    plan.softmax_scale[nid] = p;
+    c.absorbed[p] = 1;
+  }
+}
+
+void detect_layer_norm(Ctx& c, Plan& plan) {
+  for (int nid : c.s.order) {
+    Node& n = c.node(nid);
+    if (c.absorbed[nid] || n.op != AC_OP_LAYERNORMALIZATION) continue;
+    const Value& xv = c.val(n.inputs[0]);
+    const int64_t len = xv.dims[xv.rank - 1];
+    LnFusion f;
+    int cur = n.inputs[0];
+    // residual Add feeding the LayerNorm (its sum may have other users).
+    {
+      const int p = c.producer[cur];
+      if (p >= 0 && !c.absorbed[p] && c.node(p).op == AC_OP_ADD && !c.val(cur).is_const) {
+        Node& a = c.node(p);
+        const int i0 = a.inputs[0], i1 = a.inputs[1];
+        if (i0 != i1 && same_dims(c.val(i0), xv) && same_dims(c.val(i1), xv)) {
+          // Prefer as the main chain the operand that itself continues into Gelu / bias Add.
+          auto chain_like = [&](int v) {
+            const int q = c.producer[v];
+            if (q < 0 || c.absorbed[q] || !c.single_use(v)) return false;
+            return c.node(q).op == AC_OP_GELU || c.node(q).op == AC_OP_ADD;
+          };
+          int main = i0, res = i1;
+          if (!chain_like(i0) && chain_like(i1)) { main = i1; res = i0; }
+          f.residual = res;
+          if (!c.single_use(cur)) f.sum_val = cur;
+          c.absorbed[p] = 1;
+          cur = main;
+        }
+      }
+    }
+    if (f.residual >= 0) {
+      const int p = c.producer[cur];
+      if (p >= 0 && !c.absorbed[p] && c.node(p).op == AC_OP_GELU && c.single_use(cur)) {
+        f.gelu = 1;
+        c.absorbed[p] = 1;
+        cur = c.node(p).inputs[0];
+      }
+      const int q = c.producer[cur];
+      if (q >= 0 && !c.absorbed[q] && c.node(q).op == AC_OP_ADD && c.single_use(cur)) {
+        Node& a = c.node(q);
+        for (int k = 0; k < 2; ++k) {
+          const int main = a.inputs[k], vec = a.inputs[1 - k];
+          if (main != vec && same_dims(c.val(main), xv) && c.val(vec).rank == 1 &&
+              c.val(vec).dims[0] == len) {
+            f.pre_bias = vec;
+            c.absorbed[q] = 1;
+            cur = main;
+            break;
+          }
+        }
+      }
+    }
+    f.x = cur;
+    if (f.residual >= 0) plan.ln[nid] = f;
+  }
+}
+
+void detect_hardswish(Ctx& c, Plan& plan) {
+  for (int nid : c.s.order) {
+    Node& n = c.node(nid);
+    if (c.absorbed[nid] || n.op != AC_OP_HARDSIGMOID) continue;
+    const int t = n.inputs[0];
+    const int hv = n.outputs[0];
+    if (!c.single_use(hv)) continue;
+    const int m = c.only_consumer(hv);
+    Node& mul = c.node(m);
+    if (c.absorbed[m] || mul.op != AC_OP_MUL) continue;
+    const int other = mul.inputs[0] == hv ? mul.inputs[1] : mul.inputs[0];
+    if (other != t || mul.inputs[0] == mul.inputs[1]) continue;
+    plan.hardswish[m] = nid;
+    c.absorbed[nid] = 1;
+  }
+}
+
+// ---- step construction ------------------------------------------------------------
+struct Emit {
+  Ctx& c;
+  AcSession* s;
+  explicit Emit(Ctx& c_) : c(c_), s(&c_.s) {}
+
+  Step& add(const std::string& kind, int op, std::vector<int> read_vals, std::vector<int> write_vals,
+            double bytes, double flops, std::function<cudaError_t(cudaStream_t)> fn, int launches = 1) {
+    Step st;
+    st.kind = kind;
+    st.op = op;
+    st.fn = std::move(fn);
+    st.bytes = bytes;
+    st.flops = flops;
+    st.launches = launches;
+    bool all_const = true;
+    for (int v : read_vals) {
+      if (v < 0) continue;
+      st.reads.push_back(c.val(v).storage);
+      all_const = all_const && c.val(v).is_const;
+    }
+    for (int v : write_vals) st.writes.push_back(c.val(v).storage);
+    st.const_only = all_const;
+    s->steps.push_back(std::move(st));
+    return s->steps.back();
+  }
+};
+
+void broadcast_strides(const Value& v, const Value& out, int64_t* str) {
+  // crates/core/src/tensor.rs:369-406 `strides_for_broadcasting`
+  int64_t st = 1;
+  for (int i = 0; i < out.rank; ++i) str[i] = 0;
+  for (int i = 0; i < v.rank; ++i) {
+    const int vi = v.rank - 1 - i, oi = out.rank - 1 - i;
+    str[oi] = (v.dims[vi] == 1 && out.dims[oi] != 1) ? 0 : (v.dims[vi] == 1 ? 0 : st);
+    st *= v.dims[vi];
+  }
+}
+
+BinaryParams make_binary(int op, const Value& a, const Value& b, const Value& out) {
+  int64_t as[AC_MAX_RANK], bs[AC_MAX_RANK];
+  broadcast_strides(a, out, as);
+  broadcast_strides(b, out, bs);
+  BinaryParams p{};
+  p.op = op;
+  p.n = out.numel();
+  // Collapse: drop extent-1 dims, merge neighbours whose strides compose.
+  int r = 0;
+  for (int d = 0; d < out.rank; ++d) {
+    const int64_t dim = out.dims[d];
+    if (dim == 1) continue;
+    if (r > 0 && p.a_str[r - 1] == as[d] * dim && p.b_str[r - 1] == bs[d] * dim) {
+      p.dims[r - 1] *= dim;
+      p.a_str[r - 1] = as[d];
+      p.b_str[r - 1] = bs[d];
+    } else {
+      p.dims[r] = dim; p.a_str[r] = as[d]; p.b_str[r] = bs[d]; ++r;
+    }
+  }
+  if (r == 0) { p.dims[0] = 1; p.a_str[0] = 0; p.b_str[0] = 0; r = 1; }
+  p.rank = r;
+  return p;
+}
+
+void require_f32(const Value& v, const char* op) {
+  if (v.elem_ty != AC_F32) fail(AC_ERR_UNSUPPORTED, std::string(op) + ": f32 tensors only");
+}
+
+void lower_binary(Emit& em, int nid, int binop) {
+  Node& n = em.c.node(nid);
+  const int a = n.inputs[0], b = n.inputs[1], o = n.outputs[0];
+  require_f32(em.c.val(a), op_name(n.op));
+  require_f32(em.c.val(b), op_name(n.op));
+  const BinaryParams p = make_binary(binop, em.c.val(a), em.c.val(b), em.c.val(o));
+  AcSession* s = em.s;
+  const double bytes = f32_bytes(em.c.val(a)) + f32_bytes(em.c.val(b)) + f32_bytes(em.c.val(o));
+  em.add("binary_" + std::string(op_name(n.op)), n.op, {a, b}, {o}, bytes, 0,
+         [=](cudaStream_t st) { return launch_binary(p, s->fptr(a), s->fptr(b), s->fptr_mut(o), st); });
+}
+
+void lower_unary(Emit& em, int op, int x, int o, int un, float alpha, float beta) {
+  require_f32(em.c.val(x), op_name(op));
+  AcSession* s = em.s;
+  const int64_t n = em.c.val(x).numel();
+  static const char* names[] = {"relu", "sigmoid", "erf", "gelu", "hard_sigmoid", "leaky_relu",
+                                "sqrt", "tanh", "hard_swish", "square", "copy"};
+  em.add(std::string("unary_") + names[un], op, {x}, {o}, 8.0 * n, 0, [=](cudaStream_t st) {
+    return launch_unary(un, alpha, beta, s->fptr(x), s->fptr_mut(o), n, st);
+  });
+}
+
+struct GemmShape {
+  int64_t m, n, k, batch, lda, ldb, ldc, sa, sb, sc;
+  int ta, tb;
+};
+
+void emit_gemm(Emit& em, int op, const GemmShape& g, int a, int b, int out, int c_in, int bias_n,
+               int bias_m, float alpha, float beta, float bias_scale, const Epilogue* e,
+               int64_t a_off = 0, int64_t b_off = 0, int64_t c_off = 0) {
+  AcSession* s = em.s;
+  const int act = e ? e->act : ACT_NONE;
+  const float aa = e ? e->act_alpha : 0.f, ab = e ? e->act_beta : 0.f;
+  const int res = e ? e->residual : -1;
+  std::vector<int> reads = {a, b, c_in, bias_n, bias_m, res};
+  double bytes = 4.0 * g.batch * (g.m * g.k + g.m * g.n) + 4.0 * (g.sb ? g.batch : 1) * g.k * g.n;
+  if (res >= 0) bytes += 4.0 * g.batch * g.m * g.n;
+  const double flops = 2.0 * g.batch * g.m * g.n * g.k;
+  em.add("gemm_fp32_simt", op, reads, {out}, bytes, flops, [=](cudaStream_t st) {
+    GemmParams p{};
+    p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
+    p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
+    p.b = s->fptr(b) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
+    p.c = s->fptr_mut(out) + c_off; p.ldc = g.ldc; p.stride_c = g.sc;
+    p.alpha = alpha; p.beta = c_in >= 0 ? beta : 0.f;
+    p.c_in = c_in >= 0 ? s->fptr(c_in) + c_off : nullptr; p.ldc_in = g.ldc; p.stride_c_in = g.sc;
+    p.bias_n = bias_n >= 0 ? s->fptr(bias_n) : nullptr;
+    p.bias_m = bias_m >= 0 ? s->fptr(bias_m) : nullptr;
+    p.bias_scale = bias_scale;
+    p.act = act; p.act_alpha = aa; p.act_beta = ab;
+    p.residual = res >= 0 ? s->fptr(res) + c_off : nullptr; p.ld_res = g.ldc; p.stride_res = g.sc;
+    return launch_gemm_simt(p, st);
+  });
+}
+
+void lower_matmul(Emit& em, int nid, const Epilogue* e) {
+  Node& n = em.c.node(nid);
+  const int a = n.inputs[0];
+  const int b = (e && e->trans_b_src >= 0) ? e->trans_b_src : n.inputs[1];
+  const int out = e ? e->out : n.outputs[0];
+  const Value& av = em.c.val(a);
+  const Value& ov = em.c.val(n.outputs[0]);
+  const Value& bv = em.c.val(n.inputs[1]);  // logical rhs [.., k, n]
+  require_f32(av, "MatMul");
+  GemmShape g{};
+  g.k = av.dims[av.rank - 1];
+  g.n = ov.dims[ov.rank - 1];
+  g.ta = 0;
+  g.tb = (e && e->trans_b_src >= 0) ? 1 : 0;
+  g.lda = g.k;
+  g.ldb = g.tb ? g.k : g.n;
+  g.ldc = g.n;
+  if (bv.rank == 2) {  // 2Dx2D and 3Dx2D: one GEMM over the flattened rows (session.rs:653-660)
+    g.m = av.numel() / g.k;
+    g.batch = 1;
+  } else {             // 3Dx3D / 4Dx4D: a batch of GEMMs (session.rs:641-672)
+    g.m = av.dims[av.rank - 2];
+    g.batch = av.numel() / (g.m * g.k);
+    g.sa = g.m * g.k; g.sb = g.k * g.n; g.sc = g.m * g.n;
+  }
+  emit_gemm(em, n.op, g, a, b, out, -1, e ? e->bias : -1, -1, 1.f, 0.f, 1.f, e);
+}
+
+void lower_gemm(Emit& em, int nid, const Epilogue* e) {
+  // compute_gemm, session.rs:684-734: C pre-filled with the bias ([N] tiled or
+  // [M,N]), then C = alpha * op(A) op(B) + beta * C.
+  Node& n = em.c.node(nid);
+  const int a = n.inputs[0], b = n.inputs[1];
+  const int cin = n.inputs.size() > 2 ? n.inputs[2] : -1;
+  const int out = e ? e->out : n.outputs[0];
+  const Value& av = em.c.val(a);
+  const Value& bv = em.c.val(b);
+  require_f32(av, "Gemm");
+  GemmShape g{};
+  g.ta = n.ints[0] != 0; g.tb = n.ints[1] != 0;
+  g.m = g.ta ? av.dims[1] : av.dims[0];
+  g.k = g.ta ? av.dims[0] : av.dims[1];
+  g.n = g.tb ? bv.dims[0] : bv.dims[1];
+  g.lda = av.dims[1]; g.ldb = bv.dims[1]; g.ldc = g.n; g.batch = 1;
+  const float alpha = n.floats.size() > 0 ? n.floats[0] : 1.f;
+  const float beta = n.floats.size() > 1 ? n.floats[1] : 1.f;
+  int bias_n = -1, c_in = -1;
+  if (cin >= 0) {
+    const Value& cv = em.c.val(cin);
+    if (cv.rank == 1 && cv.dims[0] == g.n) bias_n = cin;
+    else if (cv.rank == 2 && cv.dims[0] == g.m && cv.dims[1] == g.n) c_in = cin;
+    else fail(AC_ERR_UNSUPPORTED, "Gemm: C must be [N] or [M,N]");
+  }
+  emit_gemm(em, n.op, g, a, b, out, c_in, bias_n, -1, alpha, beta, beta, e);
+}
+
+void lower_conv(Emit& em, int nid, const Epilogue* e) {
+  Node& n = em.c.node(nid);
+  AcSession* s = em.s;
+  const int x = n.inputs[0], w = n.inputs[1];
+  int bias = n.inputs.size() > 2 ? n.inputs[2] : -1;
+  if (e && e->bias >= 0) bias = e->bias;
+  const int out = e ? e->out : n.outputs[0];
+  const Value& xv = em.c.val(x);
+  const Value& wv = em.c.val(w);
+  const Value& ov = em.c.val(n.outputs[0]);
+  require_f32(xv, "Conv2d");
+  int64_t pads[4];
+  resolve_pads(n, 7, xv.dims[2], xv.dims[3], pads);
+  ConvParams p{};
+  p.n = (int)xv.dims[0]; p.c = (int)xv.dims[1]; p.ih = (int)xv.dims[2]; p.iw = (int)xv.dims[3];
+  p.oc = (int)ov.dims[1]; p.oh = (int)ov.dims[2]; p.ow = (int)ov.dims[3];
+  p.kh = (int)n.ints[0]; p.kw = (int)n.ints[1]; p.sh = (int)n.ints[2]; p.sw = (int)n.ints[3];
+  p.dh = (int)n.ints[4]; p.dw = (int)n.ints[5]; p.group = (int)n.ints[6];
+  p.pad_t = (int)pads[0]; p.pad_l = (int)pads[1];
+  // Conv2d.activation (crates/core/src/op.rs:68-75): applied when present, as
+  // the clang backend does; merged with a folded consumer activation.
+  Epilogue ep = e ? *e : Epilogue{};
+  if (n.ints[8] != 0 && ep.act == ACT_NONE) {
+    ep.act = n.ints[8] == 1 ? ACT_RELU : ACT_HARDSIGMOID;
+    ep.act_alpha = n.floats.size() > 0 ? n.floats[0] : 0.2f;
+    ep.act_beta = n.floats.size() > 1 ? n.floats[1] : 0.5f;
+  } else if (n.ints[8] != 0) {
+    fail(AC_ERR_UNSUPPORTED, "Conv2d: fused activation followed by another activation");
+  }
+  p.act = ep.act; p.act_alpha = ep.act_alpha; p.act_beta = ep.act_beta;
+  if (p.group <= 0 || p.c % p.group || p.oc % p.group || wv.dims[1] != p.c / p.group)
+    fail(AC_ERR_SHAPE, "Conv2d: group does not divide the channels");
+  const int icg = p.c / p.group, ocg = p.oc / p.group;
+  const int64_t ohw = (int64_t)p.oh * p.ow;
+  const int64_t kdim = (int64_t)icg * p.kh * p.kw;
+  const double flops = 2.0 * p.n * p.oc * ohw * kdim;
+
+  if (p.group == p.c && icg == 1 && ocg == 1 && ep.residual < 0) {  // depthwise stencil
+    const double bytes = f32_bytes(xv) + f32_bytes(wv) + f32_bytes(ov);
+    em.add("conv_depthwise", n.op, {x, w, bias}, {out}, bytes, flops, [=](cudaStream_t st) {
+      return launch_depthwise_conv(p, s->fptr(x), s->fptr(w), bias >= 0 ? s->fptr(bias) : nullptr,
+                                   s->fptr_mut(out), st);
+    });
+    return;
+  }
+  // GEMM form: out[n] (ocg x ohw) = W_g (ocg x k) * col[n, g] (k x ohw), bias per row.
+  const bool pointwise = p.kh == 1 && p.kw == 1 && p.sh == 1 && p.sw == 1 && p.pad_t == 0 &&
+                         p.pad_l == 0 && pads[2] == 0 && pads[3] == 0;
+  int bsrc = x;
+  if (!pointwise) {
+    // Scratch column buffer col[n, c, kh, kw, oh, ow] (conv2d.rs:81-143).
+    Value colv;
+    colv.elem_ty = AC_F32;
+    colv.rank = 1;
+    colv.dims[0] = (int64_t)p.n * p.c * p.kh * p.kw * ohw;
+    colv.is_const = false;
+    colv.storage = em.c.new_storage(colv.bytes());
+    s->values.push_back(colv);
+    const int col = (int)s->values.size() - 1;
+    em.c.producer.push_back(-1);
+    em.c.consumers.emplace_back();
+    em.c.is_output.push_back(0);
+    em.add("im2col", n.op, {x}, {col}, f32_bytes(xv) + (double)colv.bytes(), 0,
+           [=](cudaStream_t st) { return launch_im2col(p, s->fptr(x), s->fptr_mut(col), st); });
+    bsrc = col;
+  }
+  for (int gi = 0; gi < p.group; ++gi) {
+    GemmShape g{};
+    g.m = ocg; g.k = kdim; g.n = ohw; g.batch = p.n;
+    g.lda = kdim; g.ldb = ohw; g.ldc = ohw;
+    g.sa = 0; g.sb = (int64_t)p.c * p.kh * p.kw * ohw; g.sc = (int64_t)p.oc * ohw;
+    g.ta = 0; g.tb = 0;
+    Epilogue eg = ep;
+    // bias_m needs the group's slice of the bias: pass through an offset closure below.
+    const int64_t a_off = (int64_t)gi * ocg * kdim, b_off = (int64_t)gi * kdim * ohw,
+                  c_off = (int64_t)gi * ocg * ohw;
+    if (p.group == 1) {
+      emit_gemm(em, n.op, g, w, bsrc, out, -1, -1, bias, 1.f, 0.f, 1.f, &eg, a_off, b_off, c_off);
+    } else {
+      if (bias >= 0 || eg.residual >= 0)
+        fail(AC_ERR_UNSUPPORTED, "Conv2d: grouped (non-depthwise) convolution with bias");
+      emit_gemm(em, n.op, g, w, bsrc, out, -1, -1, -1, 1.f, 0.f, 1.f, &eg, a_off, b_off, c_off);
+    }
+  }
+}
+
+void lower_copy(Emit& em, const std::string& kind, int op, int in, int out, const CopyParams& p) {
+  AcSession* s = em.s;
+  const double bytes = 2.0 * p.n * p.elem_bytes;
+  em.add(kind, op, {in}, {out}, bytes, 0,
+         [=](cudaStream_t st) { return launch_strided_copy(p, s->ptr(in), s->ptr(out), st); });
+}
+
+void contiguous_strides(const int64_t* dims, int rank, int64_t* str) {
+  int64_t st = 1;
+  for (int i = rank - 1; i >= 0; --i) { str[i] = st; st *= dims[i]; }
+}
+
+void lower_node(Emit& em, Plan& plan, int nid) {
+  Ctx& c = em.c;
+  AcSession* s = em.s;
+  Node& n = c.node(nid);
+  auto V = [&](int v) -> Value& { return c.val(v); };
+  switch (n.op) {
+    case AC_OP_IDENTITY: case AC_OP_RESHAPE: case AC_OP_FLATTEN: case AC_OP_SQUEEZE:
+    case AC_OP_UNSQUEEZE:
+      return;  // storage alias, no kernel
+    case AC_OP_SHAPE:
+      return;  // evaluated on the host during shape inference
+    case AC_OP_ADD: return lower_binary(em, nid, BIN_ADD);
+    case AC_OP_SUB: return lower_binary(em, nid, BIN_SUB);
+    case AC_OP_DIV: return lower_binary(em, nid, BIN_DIV);
+    case AC_OP_MUL: {
+      auto it = plan.hardswish.find(nid);
+      if (it != plan.hardswish.end()) {
+        Node& hs = c.node(it->second);
+        return lower_unary(em, n.op, hs.inputs[0], n.outputs[0], UN_HARDSWISH,
+                           hs.floats.size() > 0 ? hs.floats[0] : 0.2f,
+                           hs.floats.size() > 1 ? hs.floats[1] : 0.5f);
+      }
+      return lower_binary(em, nid, BIN_MUL);
+    }
+    case AC_OP_POW: {
+      // compute_pow, session.rs:566-606: same shape, or a scalar exponent with
+      // the b == 2 -> a * a special case.
+      const Value& a = V(n.inputs[0]);
+      const Value& b = V(n.inputs[1]);
+      if (same_dims(a, b)) return lower_binary(em, nid, BIN_POW);
+      if (b.numel() == 1 && b.rank <= 1) {
+        if (b.host && *static_cast<const float*>(b.host) == 2.f)
+          return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_SQUARE, 0, 0);
+        return lower_binary(em, nid, BIN_POW);
+      }
+      fail(AC_ERR_UNSUPPORTED, "Pow: only same-shape operands or a scalar exponent");
+    }
+    case AC_OP_SQRT: return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_SQRT, 0, 0);
+    case AC_OP_RELU: return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_RELU, 0, 0);
+    case AC_OP_GELU: return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_GELU, 0, 0);
+    case AC_OP_SIGMOID: return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_SIGMOID, 0, 0);
+    case AC_OP_ERF: return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_ERF, 0, 0);
+    case AC_OP_TANH: return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_TANH, 0, 0);
+    case AC_OP_LEAKYRELU:
+      return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_LEAKYRELU,
+                         n.floats.size() > 0 ? n.floats[0] : 0.01f, 0);
+    case AC_OP_HARDSIGMOID:
+      return lower_unary(em, n.op, n.inputs[0], n.outputs[0], UN_HARDSIGMOID,
+                         n.floats.size() > 0 ? n.floats[0] : 0.2f,
+                         n.floats.size() > 1 ? n.floats[1] : 0.5f);
+    case AC_OP_GREATER: {
+      const int x = n.inputs[0], y = n.inputs[1], o = n.outputs[0];
+      if (!(V(y).numel() == 1 && V(y).rank <= 1))
+        fail(AC_ERR_UNSUPPORTED, "Greater: only a scalar rhs");  // session.rs:559
+      const int64_t cnt = V(x).numel();
+      em.add("greater", n.op, {x, y}, {o}, 5.0 * cnt, 0, [=](cudaStream_t st) {
+        return launch_greater_scalar(s->fptr(x), s->fptr(y), static_cast<uint8_t*>(s->ptr(o)), cnt, st);
+      });
+      return;
+    }
+    case AC_OP_WHERE: {
+      const int cd = n.inputs[0], x = n.inputs[1], y = n.inputs[2], o = n.outputs[0];
+      const Value& cv = V(cd);
+      const Value& ov = V(o);
+      int mode;
+      int64_t inner = 1;
+      if (same_dims(cv, V(y)) && V(x).numel() == 1 && V(x).rank <= 1) mode = 0;   // session.rs:947
+      else if (V(y).numel() == 1 && V(y).rank <= 1 && V(x).rank == 4 && cv.rank == 4 &&
+               cv.dims[0] == 1 && cv.dims[1] == 1 && cv.dims[2] == ov.dims[2] &&
+               cv.dims[3] == ov.dims[3]) {                                          // session.rs:958-964
+        mode = 1;
+        inner = ov.dims[2] * ov.dims[3];
+      } else {
+        fail(AC_ERR_UNSUPPORTED, "Where: unsupported broadcasting pattern");
+      }
+      const int64_t cnt = ov.numel();
+      em.add("where", n.op, {cd, x, y}, {o}, 9.0 * cnt, 0, [=](cudaStream_t st) {
+        return launch_where(mode, static_cast<const uint8_t*>(s->ptr(cd)), s->fptr(x), s->fptr(y),
+                            s->fptr_mut(o), cnt, inner, st);
+      });
+      return;
+    }
+    case AC_OP_CAST: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const int from = V(x).elem_ty, to = (int)n.ints[0];
+      const bool ok = (from == AC_I32 && to == AC_F32) || (from == AC_I64 && to == AC_I32) ||
+                      (from == AC_I64 && to == AC_F32) || (from == AC_F32 && to == AC_BOOL);
+      if (!ok) fail(AC_ERR_UNSUPPORTED, "Cast: unsupported type pair");  // session.rs:1375-1376
+      const int64_t cnt = V(x).numel();
+      em.add("cast", n.op, {x}, {o}, (double)V(x).bytes() + V(o).bytes(), 0, [=](cudaStream_t st) {
+        return launch_cast(from, to, s->ptr(x), s->ptr(o), cnt, st);
+      });
+      return;
+    }
+    case AC_OP_BATCHNORMALIZATION: {
+      const Value& xv = V(n.inputs[0]);
+      if (xv.rank != 4) fail(AC_ERR_UNSUPPORTED, "Input data rank must be 4.");
+      const int x = n.inputs[0], sc = n.inputs[1], b = n.inputs[2], mu = n.inputs[3], var = n.inputs[4],
+                o = n.outputs[0];
+      const float eps = n.floats.size() > 0 ? n.floats[0] : 1e-5f;
+      const int64_t nb = xv.dims[0], ch = xv.dims[1], hw = xv.dims[2] * xv.dims[3];
+      em.add("batch_norm", n.op, {x, sc, b, mu, var}, {o}, 8.0 * xv.numel(), 0, [=](cudaStream_t st) {
+        return launch_batch_norm(s->fptr(x), s->fptr(sc), s->fptr(b), s->fptr(mu), s->fptr(var),
+                                 s->fptr_mut(o), nb, ch, hw, eps, st);
+      });
+      return;
+    }
+    case AC_OP_SOFTMAX: {
+      const int o = n.outputs[0];
+      int x = n.inputs[0];
+      const Value& xv = V(x);
+      require_f32(xv, "Softmax");
+      const int64_t axis = n.ints.empty() ? -1 : n.ints[0];
+      if (!(axis == -1 || axis == xv.rank - 1))
+        fail(AC_ERR_UNSUPPORTED, "Softmax: last axis only");  // session.rs:999
+      const int64_t len = xv.dims[xv.rank - 1], rows = xv.numel() / std::max<int64_t>(len, 1);
+      int mode = 0, scale = -1;
+      auto it = plan.softmax_scale.find(nid);
+      if (it != plan.softmax_scale.end()) {
+        Node& m = c.node(it->second);
+        const bool b_scalar = V(m.inputs[1]).numel() == 1 && same_dims(V(m.inputs[0]), xv);
+        scale = b_scalar ? m.inputs[1] : m.inputs[0];
+        x = b_scalar ? m.inputs[0] : m.inputs[1];
+        mode = m.op == AC_OP_MUL ? 1 : 2;
+      }
+      em.add(mode ? "softmax_scaled" : "softmax", n.op, {x, scale}, {o}, 8.0 * rows * len, 0,
+             [=](cudaStream_t st) {
+               return launch_softmax(s->fptr(x), s->fptr_mut(o), rows, len, mode,
+                                     scale >= 0 ? s->fptr(scale) : nullptr, st);
+             });
+      return;
+    }
+    case AC_OP_LAYERNORMALIZATION: {
+      const int gamma = n.inputs[1], beta = n.inputs[2], o = n.outputs[0];
+      const Value& xv = V(n.inputs[0]);
+      require_f32(xv, "LayerNormalization");
+      const int64_t axis = n.ints.size() > 0 ? n.ints[0] : -1;
+      const int64_t stash = n.ints.size() > 1 ? n.ints[1] : 1;
+      if (!(axis == -1 || axis == xv.rank - 1))
+        fail(AC_ERR_UNSUPPORTED, "Axis must be the last dimension.");  // session.rs:1444-1447
+      if (stash != 1) fail(AC_ERR_UNSUPPORTED, "Stash type must be 1.");
+      const int64_t len = xv.dims[xv.rank - 1], rows = xv.numel() / std::max<int64_t>(len, 1);
+      if (V(gamma).numel() != len || V(beta).numel() != len)
+        fail(AC_ERR_SHAPE, "LayerNormalization: scale / bias length");
+      const float eps = n.floats.size() > 0 ? n.floats[0] : 1e-5f;
+      LnFusion f;
+      f.x = n.inputs[0];
+      auto it = plan.ln.find(nid);
+      if (it != plan.ln.end()) f = it->second;
+      const int x = f.x, pb = f.pre_bias, res = f.residual, sum = f.sum_val, gelu = f.gelu;
+      std::vector<int> writes = {o};
+      if (sum >= 0) writes.push_back(sum);
+      double bytes = 8.0 * rows * len + 8.0 * len;
+      if (res >= 0 && res != x) bytes += 4.0 * rows * len;
+      if (sum >= 0) bytes += 4.0 * rows * len;
+      const char* kind = res >= 0 ? (gelu || pb >= 0 ? "layer_norm_bias_gelu_residual" : "layer_norm_residual")
+                                  : "layer_norm";
+      em.add(kind, n.op, {x, pb, res, gamma, beta}, writes, bytes, 0, [=](cudaStream_t st) {
+        LayerNormParams p{};
+        p.x = s->fptr(x);
+        p.pre_bias = pb >= 0 ? s->fptr(pb) : nullptr;
+        p.residual = res >= 0 ? s->fptr(res) : nullptr;
+        p.gamma = s->fptr(gamma); p.beta = s->fptr(beta);
+        p.sum_out = sum >= 0 ? s->fptr_mut(sum) : nullptr;
+        p.out = s->fptr_mut(o);
+        p.rows = rows; p.len = len; p.eps = eps; p.gelu = gelu;
+        return launch_layer_norm(p, st);
+      });
+      return;
+    }
+    case AC_OP_REDUCEMEAN: case AC_OP_REDUCEMAX: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      require_f32(xv, op_name(n.op));
+      std::vector<int64_t> axes;
+      for (size_t i = 1; i < n.ints.size(); ++i) axes.push_back(n.ints[i] < 0 ? n.ints[i] + xv.rank : n.ints[i]);
+      const bool last_only = axes.size() == 1 && axes[0] == xv.rank - 1;
+      if (n.op == AC_OP_REDUCEMAX && (axes.empty() || (int)axes.size() == xv.rank)) {
+        // compute_reduce_max, session.rs:1292-1305: all axes -> one scalar.
+        Value sv;
+        sv.elem_ty = AC_F32; sv.rank = 1;
+        sv.dims[0] = reduce_max_all_scratch_elems(xv.numel());
+        sv.storage = c.new_storage(sv.bytes());
+        s->values.push_back(sv);
+        const int scratch = (int)s->values.size() - 1;
+        c.producer.push_back(-1); c.consumers.emplace_back(); c.is_output.push_back(0);
+        const int64_t cnt = xv.numel();
+        em.add("reduce_max_all", n.op, {x}, {o, scratch}, 4.0 * cnt, 0, [=](cudaStream_t st) {
+          return launch_reduce_max_all(s->fptr(x), s->fptr_mut(o), cnt, s->fptr_mut(scratch), st);
+        }, 2);
+        return;
+      }
+      if (!last_only)
+        fail(AC_ERR_UNSUPPORTED, std::string(op_name(n.op)) + ": only the last axis is supported");
+      const int64_t len = xv.dims[xv.rank - 1], rows = xv.numel() / std::max<int64_t>(len, 1);
+      const bool mean = n.op == AC_OP_REDUCEMEAN;
+      em.add(mean ? "reduce_mean" : "reduce_max", n.op, {x}, {o}, 4.0 * rows * len + 4.0 * rows, 0,
+             [=](cudaStream_t st) {
+               return mean ? launch_reduce_mean_last(s->fptr(x), s->fptr_mut(o), rows, len, st)
+                           : launch_reduce_max_last(s->fptr(x), s->fptr_mut(o), rows, len, st);
+             });
+      return;
+    }
+    case AC_OP_GLOBALAVERAGEPOOL: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      require_f32(xv, "GlobalAveragePool");
+      const int64_t planes = xv.dims[0] * xv.dims[1], hw = xv.dims[2] * xv.dims[3];
+      em.add("global_avg_pool", n.op, {x}, {o}, 4.0 * planes * hw + 4.0 * planes, 0,
+             [=](cudaStream_t st) { return launch_gavg_pool(s->fptr(x), s->fptr_mut(o), planes, hw, st); });
+      return;
+    }
+    case AC_OP_MAXPOOL: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      const Value& ov = V(o);
+      require_f32(xv, "MaxPool");
+      int64_t pads[4];
+      resolve_pads(n, 4, xv.dims[2], xv.dims[3], pads);
+      const int64_t planes = xv.dims[0] * xv.dims[1];
+      const int ih = (int)xv.dims[2], iw = (int)xv.dims[3], oh = (int)ov.dims[2], ow = (int)ov.dims[3];
+      const int kh = (int)n.ints[0], kw = (int)n.ints[1], sh = (int)n.ints[2], sw = (int)n.ints[3];
+      const int pt = (int)pads[0], pl = (int)pads[1];
+      em.add("max_pool", n.op, {x}, {o}, f32_bytes(xv) + f32_bytes(ov), 0, [=](cudaStream_t st) {
+        return launch_max_pool(s->fptr(x), s->fptr_mut(o), planes, ih, iw, oh, ow, kh, kw, sh, sw, pt,
+                               pl, st);
+      });
+      return;
+    }
+    case AC_OP_TRANSPOSE: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      const int r = xv.rank;
+      // Batched swap of the last two dims -> tiled shared-memory transpose.
+      bool swap_last = r >= 2 && n.ints[r - 1] == r - 2 && n.ints[r - 2] == r - 1 && xv.elem_ty == AC_F32;
+      for (int i = 0; swap_last && i < r - 2; ++i) swap_last = n.ints[i] == i;
+      const int64_t rows = r >= 2 ? xv.dims[r - 2] : 1, cols = r >= 1 ? xv.dims[r - 1] : 1;
+      const int64_t batch = xv.numel() / std::max<int64_t>(rows * cols, 1);
+      if (swap_last && batch <= 65535 && rows > 1 && cols > 1) {
+        em.add("transpose_tiled", n.op, {x}, {o}, 2.0 * xv.bytes(), 0, [=](cudaStream_t st) {
+          return launch_transpose2d(s->fptr(x), s->fptr_mut(o), batch, (int)rows, (int)cols, st);
+        });
+        return;
+      }
+      CopyParams p{};
+      p.rank = r;
+      int64_t in_str[AC_MAX_RANK];
+      contiguous_strides(xv.dims, r, in_str);
+      for (int i = 0; i < r; ++i) { p.dims[i] = xv.dims[n.ints[i]]; p.in_str[i] = in_str[n.ints[i]]; }
+      contiguous_strides(p.dims, r, p.out_str);
+      p.n = xv.numel();
+      p.elem_bytes = (int)xv.elem_bytes();
+      return lower_copy(em, "transpose_copy", n.op, x, o, p);
+    }
+    case AC_OP_CONCAT: {
+      const int o = n.outputs[0];
+      const Value& ov = V(o);
+      int64_t axis = n.ints[0];
+      if (axis < 0) axis += ov.rank;
+      int64_t out_str[AC_MAX_RANK];
+      contiguous_strides(ov.dims, ov.rank, out_str);
+      int64_t off = 0;
+      for (int x : n.inputs) {
+        const Value& xv = V(x);
+        CopyParams p{};
+        p.rank = xv.rank;
+        for (int i = 0; i < xv.rank; ++i) { p.dims[i] = xv.dims[i]; p.out_str[i] = out_str[i]; }
+        contiguous_strides(xv.dims, xv.rank, p.in_str);
+        p.out_off = off * out_str[axis];
+        p.n = xv.numel();
+        p.elem_bytes = (int)xv.elem_bytes();
+        lower_copy(em, "concat_copy", n.op, x, o, p);
+        off += xv.dims[axis];
+      }
+      return;
+    }
+    case AC_OP_SPLIT: {
+      const int x = n.inputs[0];
+      const Value& xv = V(x);
+      int64_t axis = n.ints[0];
+      if (axis < 0) axis += xv.rank;
+      int64_t in_str[AC_MAX_RANK];
+      contiguous_strides(xv.dims, xv.rank, in_str);
+      int64_t off = 0;
+      for (int o : n.outputs) {
+        const Value& ov = V(o);
+        CopyParams p{};
+        p.rank = ov.rank;
+        for (int i = 0; i < ov.rank; ++i) { p.dims[i] = ov.dims[i]; p.in_str[i] = in_str[i]; }
+        contiguous_strides(ov.dims, ov.rank, p.out_str);
+        p.in_off = off * in_str[axis];
+        p.n = ov.numel();
+        p.elem_bytes = (int)ov.elem_bytes();
+        lower_copy(em, "split_copy", n.op, x, o, p);
+        off += ov.dims[axis];
+      }
+      return;
+    }
+    case AC_OP_SLICE: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      const Value& ov = V(o);
+      const int64_t* starts = static_cast<const int64_t*>(V(n.inputs[1]).host);
+      const int64_t* axes = static_cast<const int64_t*>(V(n.inputs[3]).host);
+      const int64_t na = V(n.inputs[3]).numel();
+      const int64_t* steps = (n.inputs.size() > 4 && n.inputs[4] >= 0)
+                                 ? static_cast<const int64_t*>(V(n.inputs[4]).host) : nullptr;
+      CopyParams p{};
+      p.rank = xv.rank;
+      contiguous_strides(xv.dims, xv.rank, p.in_str);
+      for (int i = 0; i < xv.rank; ++i) p.dims[i] = ov.dims[i];
+      for (int64_t i = 0; i < na; ++i) {
+        const int64_t ax = axes[i] < 0 ? axes[i] + xv.rank : axes[i];
+        p.in_off += starts[i] * p.in_str[ax];
+        p.in_str[ax] *= steps ? steps[i] : 1;
+      }
+      contiguous_strides(ov.dims, ov.rank, p.out_str);
+      p.n = ov.numel();
+      p.elem_bytes = (int)xv.elem_bytes();
+      return lower_copy(em, "slice_copy", n.op, x, o, p);
+    }
+    case AC_OP_GATHER: {
+      const int x = n.inputs[0], idx = n.inputs[1], o = n.outputs[0];
+      const Value& xv = V(x);
+      const Value& iv = V(idx);
+      if (!iv.host || iv.elem_ty != AC_I64)
+        fail(AC_ERR_UNSUPPORTED, "Gather: indices must be a constant i64 tensor");
+      const int64_t* ind = static_cast<const int64_t*>(iv.host);
+      const int64_t axis = n.ints[0];
+      int64_t in_str[AC_MAX_RANK];
+      contiguous_strides(xv.dims, xv.rank, in_str);
+      const bool scalar = iv.rank == 0 || (iv.rank == 1 && iv.dims[0] <= 1);
+      const int64_t cnt = scalar ? 1 : iv.dims[1];
+      if (cnt > 256) fail(AC_ERR_UNSUPPORTED, "Gather: more than 256 indices");
+      // One strided copy per index: out[.., j, ..] = x[.., ind[j], ..].
+      const int64_t slab = xv.numel() / xv.dims[axis];
+      for (int64_t j = 0; j < cnt; ++j) {
+        if (ind[j] < 0 || ind[j] >= xv.dims[axis]) fail(AC_ERR_SHAPE, "Gather: index out of range");
+        CopyParams p{};
+        p.rank = 0;
+        for (int i = 0; i < xv.rank; ++i) {
+          if (i == axis) continue;
+          p.dims[p.rank] = xv.dims[i];
+          p.in_str[p.rank] = in_str[i];
+          ++p.rank;
+        }
+        contiguous_strides(p.dims, p.rank, p.out_str);
+        p.in_off = ind[j] * in_str[axis];
+        p.out_off = j * slab;  // the [1, k] form gathers on axis 0: slabs are consecutive
+        p.n = slab;
+        p.elem_bytes = (int)xv.elem_bytes();
+        lower_copy(em, "gather_copy", n.op, x, o, p);
+      }
+      return;
+    }
+    case AC_OP_MATMUL: {
+      auto it = plan.epi.find(nid);
+      return lower_matmul(em, nid, it == plan.epi.end() ? nullptr : &it->second);
+    }
+    case AC_OP_GEMM: {
+      auto it = plan.epi.find(nid);
+      return lower_gemm(em, nid, it == plan.epi.end() ? nullptr : &it->second);
+    }
+    case AC_OP_CONV2D: {
+      auto it = plan.epi.find(nid);
+      return lower_conv(em, nid, it == plan.epi.end() ? nullptr : &it->second);
+    }
+    default:
+      fail(AC_ERR_UNSUPPORTED, std::string(op_name(n.op)) + ": Kernel not implemented");
+  }
+}
+
+// Orders the steps so that every storage is fully written before it is read;
+// among ready steps the original (topological) order is kept.
+bool order_steps(AcSession& s) {
+  const int n = (int)s.steps.size();
+  std::map<int, std::vector<int>> writers;
+  for (int i = 0; i < n; ++i)
+    for (int w : s.steps[i].writes) writers[w].push_back(i);
+  std::vector<std::set<int>> deps(n);
+  for (int i = 0; i < n; ++i)
+    for (int r : s.steps[i].reads) {
+      auto it = writers.find(r);
+      if (it == writers.end()) continue;
+      for (int w : it->second)
+        if (w != i) deps[i].insert(w);
+    }
+  std::vector<int> done(n, 0), out;
+  for (int placed = 0; placed < n;) {
+    bool progress = false;
+    for (int i = 0; i < n; ++i) {
+      if (done[i]) continue;
+      bool ready = true;
+      for (int d : deps[i]) ready = ready && done[d];
+      if (!ready) continue;
+      done[i] = 1;
+      out.push_back(i);
+      ++placed;
+      progress = true;
+      break;  // restart from the lowest index to keep the original order
+    }
+    if (!progress) return false;
+  }
+  std::vector<Step> sorted;
+  sorted.reserve(n);
+  for (int i : out) sorted.push_back(std::move(s.steps[i]));
+  s.steps.swap(sorted);
+  return true;
+}
+
+}  // namespace
+
+void lower_graph(AcSession& s) {
+  Ctx c(s);
+  const int nv = (int)s.values.size();
+  // Scratch values are appended while lowering; references into `values` must stay valid.
+  s.values.reserve(s.values.size() + 4 * s.nodes.size() + 16);
+  c.producer.assign(nv, -1);
+  c.consumers.assign(nv, {});
+  c.is_output.assign(nv, 0);
+  c.absorbed.assign(s.nodes.size(), 0);
+  for (size_t i = 0; i < s.nodes.size(); ++i) {
+    for (int v : s.nodes[i].inputs)
+      if (v >= 0) c.consumers[v].push_back((int)i);
+    for (int v : s.nodes[i].outputs) c.producer[v] = (int)i;
+  }
+  for (int o : s.outputs) c.is_output[o] = 1;
+
+  // Storages: initializers in the weight blob, inputs and everything computed in the arena.
+  for (int v = 0; v < nv; ++v) {
+    Value& val = s.values[v];
+    if (val.is_init) {
+      val.is_const = true;
+      val.storage = c.new_storage(val.bytes(), /*weight=*/true);
+    }
+  }
+  for (int v : s.inputs) {
+    if (s.values[v].is_init) fail(AC_ERR_INVALID, "a graph input is also an initializer");
+    s.values[v].storage = c.new_storage(s.values[v].bytes(), false, /*pinned=*/true);
+  }
+  for (int nid : s.order) {
+    Node& n = s.nodes[nid];
+    bool all_const = true;
+    for (int v : n.inputs)
+      if (v >= 0) {
+        if (s.values[v].storage < 0 && s.values[v].rank >= 0 && c.producer[v] < 0)
+          fail(AC_ERR_INVALID, std::string(op_name(n.op)) + ": input is neither computed, an input nor an initializer");
+        all_const = all_const && s.values[v].is_const;
+      }
+    const bool alias = n.op == AC_OP_IDENTITY || n.op == AC_OP_RESHAPE || n.op == AC_OP_FLATTEN ||
+                       n.op == AC_OP_SQUEEZE || n.op == AC_OP_UNSQUEEZE;
+    for (int o : n.outputs) {
+      Value& ov = s.values[o];
+      ov.is_const = all_const;
+      if (alias) {
+        const Value& iv = s.values[n.inputs[0]];
+        ov.storage = iv.storage;
+        if (iv.host && !ov.host) ov.host = iv.host;
+      } else {
+        ov.storage = c.new_storage(ov.bytes(), false, all_const);
+      }
+    }
+  }
+  for (int o : s.outputs) s.storages[s.values[o].storage].pinned_live = true;
+
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    const bool fuse = attempt == 0 && !s.opt.disable_fusion;
+    Plan plan;
+    std::fill(c.absorbed.begin(), c.absorbed.end(), 0);
+    s.steps.clear();
+    if (fuse) {
+      detect_epilogues(c, plan);
+      detect_softmax_scale(c, plan);
+      detect_layer_norm(c, plan);
+      detect_hardswish(c, plan);
+    }
+    Emit em(c);
+    for (int nid : s.order)
+      if (!c.absorbed[nid]) lower_node(em, plan, nid);
+    if (order_steps(s)) break;
+    if (!fuse) fail(AC_ERR_INVALID, "kernel schedule has a dependency cycle");
+  }
+
+  // Constant-only steps run once at create(); their results stay resident.
+  std::vector<Step> run;
+  for (Step& st : s.steps) {
+    if (st.const_only) s.init_steps.push_back(std::move(st));
+    else run.push_back(std::move(st));
+  }
+  s.steps.swap(run);
+  s.launches_per_run = 0;
+  for (const Step& st : s.steps) s.launches_per_run += st.launches;
+}
+
+}  // namespace ac

@@ -1,0 +1,378 @@
+// Row kernels: reductions over the last axis. Softmax, LayerNormalization
+// (with its elementwise producers folded in), ReduceMean / ReduceMax,
+// GlobalAveragePool, whole-tensor ReduceMax.
+//
+// One warp owns one row; the row lives in registers between the reduction
+// passes, so every element is read from HBM once and written once. Reductions
+// are warp-shuffle trees. The per-element arithmetic restates the reference
+// (crates/session_interpreter/src/session.rs and fast_math.rs); only the
+// summation order differs (tree instead of 8-lane partial sums).
+#include "kernels.h"
+#include "ref_math.cuh"
+
+namespace ac {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = kWarpsPerBlock * 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFull, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(kFull, v, o));
+  return v;
+}
+
+template <int MODE>
+__device__ __forceinline__ float pre_scale(float x, float s) {
+  if (MODE == 1) return __fmul_rn(x, s);
+  if (MODE == 2) return __fdiv_rn(x, s);
+  return x;
+}
+
+// ---- Softmax -----------------------------------------------------------------
+// compute_softmax, session.rs:990-1026 + fast_sum_exp, fast_math.rs:102-187:
+// m = max(row) ignoring NaN; e = exp_poly(max(x - m, -88.37626)); out = e * (1 / sum e).
+template <int VPT, int MODE>
+__global__ void __launch_bounds__(kThreads) softmax_warp(const float* __restrict__ x,
+                                                         float* __restrict__ out, int64_t rows,
+                                                         int len, const float* __restrict__ scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  const float s = MODE ? __ldg(scale) : 1.f;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    const float* xr = x + row * len;
+    float v[VPT];
+    float m = CUDART_NAN_F;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < len) {
+        v[i] = pre_scale<MODE>(__ldg(xr + c), s);
+        m = fmaxf(v[i], m);
+      }
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < len) {
+        v[i] = exp_poly_softmax(__fsub_rn(v[i], m));
+        sum = __fadd_rn(sum, v[i]);
+      }
+    }
+    sum = warp_sum(sum);
+    const float recip = __fdiv_rn(1.f, sum);
+    float* orow = out + row * len;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < len) orow[c] = __fmul_rn(v[i], recip);
+    }
+  }
+}
+
+// Rows longer than the register path holds: three passes over the row by one
+// warp (the re-reads hit L1/L2).
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) softmax_long(const float* __restrict__ x,
+                                                         float* __restrict__ out, int64_t rows,
+                                                         int64_t len,
+                                                         const float* __restrict__ scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  const float s = MODE ? __ldg(scale) : 1.f;
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    const float* xr = x + row * len;
+    float* orow = out + row * len;
+    float m = CUDART_NAN_F;
+    for (int64_t c = lane; c < len; c += 32) m = fmaxf(pre_scale<MODE>(xr[c], s), m);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int64_t c = lane; c < len; c += 32) {
+      const float e = exp_poly_softmax(__fsub_rn(pre_scale<MODE>(xr[c], s), m));
+      orow[c] = e;
+      sum = __fadd_rn(sum, e);
+    }
+    sum = warp_sum(sum);
+    const float recip = __fdiv_rn(1.f, sum);
+    for (int64_t c = lane; c < len; c += 32) orow[c] = __fmul_rn(orow[c], recip);
+  }
+}
+
+template <int MODE>
+cudaError_t softmax_dispatch(const float* x, float* out, int64_t rows, int64_t len,
+                             const float* scale, cudaStream_t st) {
+  const int64_t blocks64 = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
+  const int vpt = (int)((len + 31) / 32);
+#define AC_SM(V)                                                                         \
+  softmax_warp<V, MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, (int)len, scale)
+  if (vpt <= 1) AC_SM(1);
+  else if (vpt <= 2) AC_SM(2);
+  else if (vpt <= 4) AC_SM(4);
+  else if (vpt <= 7) AC_SM(7);
+  else if (vpt <= 8) AC_SM(8);
+  else if (vpt <= 12) AC_SM(12);
+  else if (vpt <= 16) AC_SM(16);
+  else if (vpt <= 24) AC_SM(24);
+  else if (vpt <= 32) AC_SM(32);
+  else softmax_long<MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, len, scale);
+#undef AC_SM
+  return cudaGetLastError();
+}
+
+// ---- LayerNormalization --------------------------------------------------------
+// compute_layer_normalization, session.rs:1465-1482:
+//   mean = sum(x) * (1/n); o = x - mean; inv = 1 / sqrt(fma(sum(o*o), 1/n, eps));
+//   out = fma(o * inv, gamma, beta)
+// with the elementwise producers of x (bias Add, Gelu, residual Add) evaluated in
+// registers first.
+struct LnDev {
+  const float* x; const float* pre_bias; const float* residual; const float* gamma;
+  const float* beta; float* sum_out; float* out; int64_t rows; int len; float eps; int gelu;
+};
+
+__device__ __forceinline__ float ln_prologue(const LnDev& p, float v, int col, float res) {
+  if (p.pre_bias) v = __fadd_rn(v, __ldg(p.pre_bias + col));
+  if (p.gelu) v = gelu_ref(v);
+  if (p.residual) v = __fadd_rn(v, res);
+  return v;
+}
+
+// Vector path: len % 4 == 0, all pointers 16-byte aligned. NV float4 per lane.
+template <int NV>
+__global__ void __launch_bounds__(kThreads) layer_norm_vec(LnDev p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  const int nvec = p.len >> 2;
+  const float inv_n = __fdiv_rn(1.f, (float)p.len);
+  for (int64_t row = warp; row < p.rows; row += nwarps) {
+    const float4* xr = reinterpret_cast<const float4*>(p.x + row * p.len);
+    const float4* rr = p.residual ? reinterpret_cast<const float4*>(p.residual + row * p.len) : nullptr;
+    float4 v[NV];
+    float4 r[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        v[i] = __ldg(xr + c);
+        if (rr) r[i] = __ldg(rr + c);
+      }
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        const float4 rv = rr ? r[i] : make_float4(0, 0, 0, 0);
+        v[i].x = ln_prologue(p, v[i].x, 4 * c + 0, rv.x);
+        v[i].y = ln_prologue(p, v[i].y, 4 * c + 1, rv.y);
+        v[i].z = ln_prologue(p, v[i].z, 4 * c + 2, rv.z);
+        v[i].w = ln_prologue(p, v[i].w, 4 * c + 3, rv.w);
+        if (p.sum_out) reinterpret_cast<float4*>(p.sum_out + row * p.len)[c] = v[i];
+        sum = __fadd_rn(sum, __fadd_rn(__fadd_rn(v[i].x, v[i].y), __fadd_rn(v[i].z, v[i].w)));
+      }
+    }
+    const float mean = __fmul_rn(warp_sum(sum), inv_n);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        v[i].x = __fsub_rn(v[i].x, mean);
+        v[i].y = __fsub_rn(v[i].y, mean);
+        v[i].z = __fsub_rn(v[i].z, mean);
+        v[i].w = __fsub_rn(v[i].w, mean);
+        sq = __fadd_rn(sq, __fadd_rn(__fadd_rn(__fmul_rn(v[i].x, v[i].x), __fmul_rn(v[i].y, v[i].y)),
+                                     __fadd_rn(__fmul_rn(v[i].z, v[i].z), __fmul_rn(v[i].w, v[i].w))));
+      }
+    }
+    const float var = fmaf(warp_sum(sq), inv_n, p.eps);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(var));
+    float4* orow = reinterpret_cast<float4*>(p.out + row * p.len);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        const float4 g = __ldg(reinterpret_cast<const float4*>(p.gamma) + c);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(p.beta) + c);
+        float4 o;
+        o.x = fmaf(__fmul_rn(v[i].x, inv), g.x, b.x);
+        o.y = fmaf(__fmul_rn(v[i].y, inv), g.y, b.y);
+        o.z = fmaf(__fmul_rn(v[i].z, inv), g.z, b.z);
+        o.w = fmaf(__fmul_rn(v[i].w, inv), g.w, b.w);
+        orow[c] = o;
+      }
+    }
+  }
+}
+
+// Any length / alignment: one warp per row, values recomputed from global
+// memory in each pass (served by L1/L2 after the first).
+__global__ void __launch_bounds__(kThreads) layer_norm_generic(LnDev p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  const float inv_n = __fdiv_rn(1.f, (float)p.len);
+  for (int64_t row = warp; row < p.rows; row += nwarps) {
+    const float* xr = p.x + row * p.len;
+    const float* rr = p.residual ? p.residual + row * p.len : nullptr;
+    float sum = 0.f;
+    for (int c = lane; c < p.len; c += 32) {
+      const float v = ln_prologue(p, xr[c], c, rr ? rr[c] : 0.f);
+      if (p.sum_out) p.sum_out[row * p.len + c] = v;
+      sum = __fadd_rn(sum, v);
+    }
+    const float mean = __fmul_rn(warp_sum(sum), inv_n);
+    float sq = 0.f;
+    for (int c = lane; c < p.len; c += 32) {
+      const float o = __fsub_rn(ln_prologue(p, xr[c], c, rr ? rr[c] : 0.f), mean);
+      sq = __fadd_rn(sq, __fmul_rn(o, o));
+    }
+    const float var = fmaf(warp_sum(sq), inv_n, p.eps);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(var));
+    for (int c = lane; c < p.len; c += 32) {
+      const float o = __fsub_rn(ln_prologue(p, xr[c], c, rr ? rr[c] : 0.f), mean);
+      p.out[row * p.len + c] = fmaf(__fmul_rn(o, inv), __ldg(p.gamma + c), __ldg(p.beta + c));
+    }
+  }
+}
+
+// ---- last-axis reductions ---------------------------------------------------------
+// MODE 0: mean = fast_sum(row) * (1/n)  (compute_reduce_mean, session.rs:1328-1339)
+// MODE 1: max over the row              (ONNX ReduceMax on the last axis)
+// MODE 2: sum / n                       (compute_gavg_pool, session.rs:289-293)
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) reduce_last(const float* __restrict__ x,
+                                                        float* __restrict__ out, int64_t rows,
+                                                        int64_t len) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  const bool vec = (len % 4) == 0 && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  for (int64_t row = warp; row < rows; row += nwarps) {
+    const float* xr = x + row * len;
+    float acc = MODE == 1 ? -CUDART_INF_F : 0.f;
+    if (vec) {
+      const float4* x4 = reinterpret_cast<const float4*>(xr);
+      for (int64_t c = lane; c < (len >> 2); c += 32) {
+        const float4 v = __ldg(x4 + c);
+        if (MODE == 1) acc = fmaxf(fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)), acc);
+        else acc = __fadd_rn(acc, __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w)));
+      }
+    } else {
+      for (int64_t c = lane; c < len; c += 32) {
+        const float v = __ldg(xr + c);
+        acc = MODE == 1 ? fmaxf(v, acc) : __fadd_rn(acc, v);
+      }
+    }
+    acc = MODE == 1 ? warp_max(acc) : warp_sum(acc);
+    if (lane == 0) {
+      if (MODE == 0) out[row] = __fmul_rn(acc, __fdiv_rn(1.0f, (float)len));
+      else if (MODE == 1) out[row] = acc;
+      else out[row] = __fdiv_rn(acc, (float)len);
+    }
+  }
+}
+
+template <int MODE>
+cudaError_t reduce_last_dispatch(const float* x, float* out, int64_t rows, int64_t len,
+                                 cudaStream_t st) {
+  if (rows == 0) return cudaSuccess;
+  const int64_t blocks64 = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
+  reduce_last<MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, len);
+  return cudaGetLastError();
+}
+
+// ---- whole-tensor max (compute_reduce_max, session.rs:1292-1305) ---------------------
+constexpr int kMaxAllBlocks = 148 * 8;
+
+__global__ void __launch_bounds__(kThreads) max_all_stage(const float* __restrict__ x,
+                                                          float* __restrict__ out, int64_t n) {
+  __shared__ float sm[kWarpsPerBlock];
+  float acc = -CUDART_INF_F;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * kThreads)
+    acc = fmaxf(__ldg(x + i), acc);
+  acc = warp_max(acc);
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    acc = threadIdx.x < kWarpsPerBlock ? sm[threadIdx.x] : -CUDART_INF_F;
+    acc = warp_max(acc);
+    if (threadIdx.x == 0) out[blockIdx.x] = acc;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_softmax(const float* x, float* out, int64_t rows, int64_t len, int scale_mode,
+                           const float* scale, cudaStream_t st) {
+  if (rows == 0 || len == 0) return cudaSuccess;
+  if (scale_mode == 1) return softmax_dispatch<1>(x, out, rows, len, scale, st);
+  if (scale_mode == 2) return softmax_dispatch<2>(x, out, rows, len, scale, st);
+  return softmax_dispatch<0>(x, out, rows, len, scale, st);
+}
+
+cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
+  if (q.rows == 0 || q.len == 0) return cudaSuccess;
+  LnDev p{q.x, q.pre_bias, q.residual, q.gamma, q.beta, q.sum_out, q.out, q.rows, (int)q.len,
+          q.eps, q.gelu};
+  const int64_t blocks64 = (q.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
+  auto al = [](const void* ptr) { return ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+  const bool vec = (q.len % 4) == 0 && q.len <= 32 * 4 * 8 && al(q.x) && al(q.residual) &&
+                   al(q.gamma) && al(q.beta) && al(q.sum_out) && al(q.out);
+  if (vec) {
+    const int nv = (int)((q.len / 4 + 31) / 32);
+    if (nv <= 1) layer_norm_vec<1><<<blocks, kThreads, 0, st>>>(p);
+    else if (nv <= 2) layer_norm_vec<2><<<blocks, kThreads, 0, st>>>(p);
+    else if (nv <= 3) layer_norm_vec<3><<<blocks, kThreads, 0, st>>>(p);
+    else if (nv <= 4) layer_norm_vec<4><<<blocks, kThreads, 0, st>>>(p);
+    else if (nv <= 6) layer_norm_vec<6><<<blocks, kThreads, 0, st>>>(p);
+    else layer_norm_vec<8><<<blocks, kThreads, 0, st>>>(p);
+  } else {
+    layer_norm_generic<<<blocks, kThreads, 0, st>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_reduce_mean_last(const float* x, float* out, int64_t rows, int64_t len,
+                                    cudaStream_t st) {
+  return reduce_last_dispatch<0>(x, out, rows, len, st);
+}
+cudaError_t launch_reduce_max_last(const float* x, float* out, int64_t rows, int64_t len,
+                                   cudaStream_t st) {
+  return reduce_last_dispatch<1>(x, out, rows, len, st);
+}
+cudaError_t launch_gavg_pool(const float* x, float* out, int64_t planes, int64_t hw,
+                             cudaStream_t st) {
+  return reduce_last_dispatch<2>(x, out, planes, hw, st);
+}
+
+int64_t reduce_max_all_scratch_elems(int64_t n) {
+  const int64_t blocks = (n + kThreads - 1) / kThreads;
+  return blocks < kMaxAllBlocks ? (blocks > 0 ? blocks : 1) : kMaxAllBlocks;
+}
+
+cudaError_t launch_reduce_max_all(const float* x, float* out, int64_t n, float* partials,
+                                  cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  const int64_t blocks = reduce_max_all_scratch_elems(n);
+  max_all_stage<<<(unsigned)blocks, kThreads, 0, st>>>(x, partials, n);
+  max_all_stage<<<1, kThreads, 0, st>>>(partials, out, blocks);
+  return cudaGetLastError();
+}
+
+}  // namespace ac

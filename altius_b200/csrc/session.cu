@@ -1,0 +1,397 @@
+// C ABI of the CUDA session (include/altius_session_cuda.h): parse the graph
+// description, infer shapes, lower to the kernel schedule, plan one device
+// arena from value lifetimes, upload the weights once, capture the schedule in
+// a CUDA graph and replay it per run.
+//
+// Replaces InterpreterSessionBuilder::build
+// (crates/session_interpreter/src/builder.rs:37-65) and InterpreterSession::run
+// (crates/session_interpreter/src/session.rs:66-134). Where the reference
+// allocates every node output per run (`Tensor::uninit_of_type`, :159-162) and
+// frees by last use (crates/session/src/plan.rs:14-58), the same last-use
+// analysis here assigns fixed arena offsets at build time.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "session.h"
+
+using namespace ac;
+
+namespace {
+
+thread_local std::string g_create_error;
+
+#define AC_CUDA(expr)                                                                     \
+  do {                                                                                    \
+    cudaError_t e__ = (expr);                                                             \
+    if (e__ != cudaSuccess)                                                               \
+      fail(AC_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__));             \
+  } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+void parse_graph(AcSession& s, const AcGraphDesc& g) {
+  if (g.n_values < 0 || g.n_nodes < 0 || (g.n_values && !g.values) || (g.n_nodes && !g.nodes))
+    fail(AC_ERR_INVALID, "malformed graph description");
+  s.opset = g.opset_version;
+  s.values.resize(g.n_values);
+  for (int i = 0; i < g.n_values; ++i) {
+    const AcValueDesc& d = g.values[i];
+    Value& v = s.values[i];
+    if (d.elem_ty < 0 || d.elem_ty > AC_I64) fail(AC_ERR_INVALID, "bad element type");
+    v.elem_ty = d.elem_ty;
+    v.rank = d.rank < 0 ? -1 : d.rank;
+    if (d.rank > AC_MAX_RANK) fail(AC_ERR_SHAPE, "rank above 8 is not supported");
+    for (int k = 0; k < v.rank; ++k) {
+      if (d.dims[k] < 0) fail(AC_ERR_SHAPE, "Must be fixed dimension");  // shape.rs:675
+      v.dims[k] = d.dims[k];
+    }
+  }
+  auto check_val = [&](int v, bool allow_missing) {
+    if (v == -1 && allow_missing) return;
+    if (v < 0 || v >= g.n_values) fail(AC_ERR_INVALID, "value id out of range");
+  };
+  s.nodes.resize(g.n_nodes);
+  for (int i = 0; i < g.n_nodes; ++i) {
+    const AcNodeDesc& d = g.nodes[i];
+    Node& n = s.nodes[i];
+    if (d.op < 0 || d.op >= AC_OP_COUNT) fail(AC_ERR_INVALID, "bad operator code");
+    n.op = d.op;
+    for (int k = 0; k < d.n_inputs; ++k) { check_val(d.inputs[k], true); n.inputs.push_back(d.inputs[k]); }
+    for (int k = 0; k < d.n_outputs; ++k) { check_val(d.outputs[k], false); n.outputs.push_back(d.outputs[k]); }
+    if (n.outputs.empty()) fail(AC_ERR_INVALID, "node without outputs");
+    if (d.n_ints > 0) n.ints.assign(d.ints, d.ints + d.n_ints);
+    if (d.n_floats > 0) n.floats.assign(d.floats, d.floats + d.n_floats);
+    if (d.name) n.name = d.name;
+  }
+  for (int i = 0; i < g.n_inits; ++i) {
+    const AcInitDesc& d = g.inits[i];
+    check_val(d.value, false);
+    Value& v = s.values[d.value];
+    if (v.rank < 0) fail(AC_ERR_SHAPE, "initializer without a static shape");
+    if (d.bytes != v.bytes() || (!d.data && d.bytes)) fail(AC_ERR_INVALID, "initializer size mismatch");
+    v.is_init = true;
+    if (d.location == 0) {
+      v.host = d.data;  // valid during create(); small shape tensors are kept below
+      if (v.elem_ty == AC_I64 || v.numel() <= 16) {
+        v.host_owned.assign(static_cast<const char*>(d.data), static_cast<const char*>(d.data) + d.bytes);
+      }
+    }
+  }
+  for (int i = 0; i < g.n_inputs; ++i) {
+    check_val(g.inputs[i], false);
+    if (s.values[g.inputs[i]].rank < 0) fail(AC_ERR_SHAPE, "graph input without a static shape");
+    s.inputs.push_back(g.inputs[i]);
+  }
+  for (int i = 0; i < g.n_outputs; ++i) { check_val(g.outputs[i], false); s.outputs.push_back(g.outputs[i]); }
+  if (s.outputs.empty()) fail(AC_ERR_INVALID, "graph without outputs");
+}
+
+// Lifetimes by step index, then first-fit placement of the largest buffers
+// first: two storages may share bytes only if their live ranges are disjoint.
+void plan_arena(AcSession& s) {
+  const int nsteps = (int)s.steps.size();
+  for (Storage& st : s.storages) { st.first = 1 << 30; st.last = -1; }
+  auto touch = [&](int sid, int step) {
+    Storage& st = s.storages[sid];
+    st.first = std::min(st.first, step);
+    st.last = std::max(st.last, step);
+  };
+  for (int i = 0; i < nsteps; ++i) {
+    for (int r : s.steps[i].reads) touch(r, i);
+    for (int w : s.steps[i].writes) touch(w, i);
+  }
+  for (const Step& st : s.init_steps) {
+    for (int r : st.reads) s.storages[r].pinned_live = s.storages[r].pinned_live || !s.storages[r].weight;
+    for (int w : st.writes) s.storages[w].pinned_live = true;
+  }
+  size_t woff = 0;
+  std::vector<int> live;
+  for (int i = 0; i < (int)s.storages.size(); ++i) {
+    Storage& st = s.storages[i];
+    if (st.weight) {
+      st.offset = woff;
+      woff += align_up(st.bytes, 256);
+      continue;
+    }
+    if (st.pinned_live) { st.first = -1; st.last = nsteps; }
+    if (st.last < 0) continue;  // never touched
+    live.push_back(i);
+  }
+  s.weight_bytes = woff;
+  std::sort(live.begin(), live.end(), [&](int a, int b) {
+    if (s.storages[a].bytes != s.storages[b].bytes) return s.storages[a].bytes > s.storages[b].bytes;
+    return a < b;
+  });
+  std::vector<int> placed;
+  size_t top = 0;
+  for (int id : live) {
+    Storage& st = s.storages[id];
+    const size_t need = align_up(st.bytes, 256);
+    std::vector<std::pair<size_t, size_t>> busy;
+    for (int o : placed) {
+      const Storage& q = s.storages[o];
+      if (q.first <= st.last && st.first <= q.last) busy.push_back({q.offset, q.offset + align_up(q.bytes, 256)});
+    }
+    std::sort(busy.begin(), busy.end());
+    size_t off = 0;
+    for (auto& b : busy) {
+      if (off + need <= b.first) break;
+      off = std::max(off, b.second);
+    }
+    st.offset = off;
+    top = std::max(top, off + need);
+    placed.push_back(id);
+  }
+  s.arena_bytes = std::max<size_t>(top, 256);
+}
+
+void upload_weights(AcSession& s, const AcGraphDesc& g) {
+  AC_CUDA(cudaMalloc(&s.weights, std::max<size_t>(s.weight_bytes, 256)));
+  for (int i = 0; i < g.n_inits; ++i) {
+    const AcInitDesc& d = g.inits[i];
+    if (!d.bytes) continue;
+    void* dst = s.weights + s.storages[s.values[d.value].storage].offset;
+    AC_CUDA(cudaMemcpyAsync(dst, d.data, d.bytes,
+                            d.location == 1 ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                            s.stream));
+  }
+  AC_CUDA(cudaStreamSynchronize(s.stream));
+  // Host pointers of large initializers belong to the caller: forget them.
+  for (Value& v : s.values)
+    if (v.is_init) v.host = v.host_owned.empty() ? nullptr : v.host_owned.data();
+}
+
+cudaError_t replay(AcSession* s, cudaStream_t st) {
+  for (Step& step : s->steps) {
+    cudaError_t e = step.fn(st);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+int set_err(AcSession* s, int status, const std::string& msg) {
+  if (s) s->err = msg;
+  else g_create_error = msg;
+  return status;
+}
+
+int run_common(AcSession* s, const void* const* ins, void* const* outs, bool device_io) {
+  if (!s || (!ins && !s->inputs.empty()) || !outs) return set_err(s, AC_ERR_INVALID, "null argument");
+  if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
+  cudaError_t e = cudaSetDevice(s->device);
+  if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, cudaGetErrorString(e));
+  const cudaMemcpyKind in_kind = device_io ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+  const cudaMemcpyKind out_kind = device_io ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost;
+  for (size_t i = 0; i < s->inputs.size(); ++i) {
+    if (!ins[i]) return set_err(s, AC_ERR_INVALID, "null input buffer");
+    const Value& v = s->values[s->inputs[i]];
+    e = cudaMemcpyAsync(s->ptr(s->inputs[i]), ins[i], v.bytes(), in_kind, s->stream);
+    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("input copy: ") + cudaGetErrorString(e));
+  }
+  if (s->opt.enable_profiling) {
+    const size_t n = s->steps.size();
+    cudaEventRecord(s->events[0], s->stream);
+    for (size_t i = 0; i < n; ++i) {
+      e = s->steps[i].fn(s->stream);
+      if (e != cudaSuccess)
+        return set_err(s, AC_ERR_CUDA, s->steps[i].kind + ": " + cudaGetErrorString(e));
+      cudaEventRecord(s->events[i + 1], s->stream);
+    }
+  } else if (s->graph_exec) {
+    e = cudaGraphLaunch(s->graph_exec, s->stream);
+    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("graph launch: ") + cudaGetErrorString(e));
+  } else {
+    e = replay(s, s->stream);
+    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+  }
+  for (size_t i = 0; i < s->outputs.size(); ++i) {
+    if (!outs[i]) return set_err(s, AC_ERR_INVALID, "null output buffer");
+    const Value& v = s->values[s->outputs[i]];
+    e = cudaMemcpyAsync(outs[i], s->ptr(s->outputs[i]), v.bytes(), out_kind, s->stream);
+    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("output copy: ") + cudaGetErrorString(e));
+  }
+  e = cudaStreamSynchronize(s->stream);
+  if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("run: ") + cudaGetErrorString(e));
+  if (s->opt.enable_profiling) {
+    for (size_t i = 0; i < s->steps.size(); ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, s->events[i], s->events[i + 1]);
+      ProfileAcc& acc = s->profile[s->steps[i].kind];
+      acc.launches += s->steps[i].launches;
+      acc.ms += ms;
+      acc.bytes += s->steps[i].bytes;
+      acc.flops += s->steps[i].flops;
+    }
+  }
+  return AC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int altius_cuda_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) return -AC_ERR_NO_DEVICE;
+  return n;
+}
+
+int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSession** out) {
+  if (!graph || !out) return set_err(nullptr, AC_ERR_INVALID, "null argument");
+  *out = nullptr;
+  AcSession* s = new AcSession();
+  try {
+    if (options) s->opt = *options;
+    s->device = s->opt.device;
+    if (s->opt.plan_only) {
+      parse_graph(*s, *graph);
+      infer_shapes(*s);
+      lower_graph(*s);
+      plan_arena(*s);
+      *out = s;
+      return AC_OK;
+    }
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+      fail(AC_ERR_NO_DEVICE, "no CUDA device is visible: this backend has no CPU fallback");
+    if (s->device < 0 || s->device >= ndev) fail(AC_ERR_NO_DEVICE, "device ordinal out of range");
+    cudaDeviceProp prop;
+    AC_CUDA(cudaGetDeviceProperties(&prop, s->device));
+    if (prop.major != 10)
+      fail(AC_ERR_NO_DEVICE, "device is not sm_100 (the kernels are built for sm_100a only)");
+    AC_CUDA(cudaSetDevice(s->device));
+    AC_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    parse_graph(*s, *graph);
+    infer_shapes(*s);
+    lower_graph(*s);
+    plan_arena(*s);
+    AC_CUDA(cudaMalloc(&s->arena, s->arena_bytes));
+    upload_weights(*s, *graph);
+    for (Step& st : s->init_steps) AC_CUDA(st.fn(s->stream));
+    AC_CUDA(cudaStreamSynchronize(s->stream));
+    if (s->opt.enable_profiling) {
+      s->events.resize(s->steps.size() + 1);
+      for (cudaEvent_t& ev : s->events) AC_CUDA(cudaEventCreate(&ev));
+    } else if (!s->opt.disable_cuda_graph && !s->steps.empty()) {
+      AC_CUDA(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+      cudaError_t e = replay(s, s->stream);
+      cudaError_t e2 = cudaStreamEndCapture(s->stream, &s->graph);
+      if (e != cudaSuccess) fail(AC_ERR_CUDA, std::string("capture: ") + cudaGetErrorString(e));
+      AC_CUDA(e2);
+      AC_CUDA(cudaGraphInstantiate(&s->graph_exec, s->graph, 0));
+    }
+  } catch (const BuildError& e) {
+    set_err(nullptr, e.status, e.msg);
+    altius_cuda_destroy(s);
+    return e.status;
+  } catch (const std::exception& e) {
+    set_err(nullptr, AC_ERR_INVALID, e.what());
+    altius_cuda_destroy(s);
+    return AC_ERR_INVALID;
+  }
+  *out = s;
+  return AC_OK;
+}
+
+int altius_cuda_run(AcSession* s, const void* const* ins, void* const* outs) {
+  return run_common(s, ins, outs, false);
+}
+
+int altius_cuda_run_device(AcSession* s, const void* const* d_ins, void* const* d_outs) {
+  return run_common(s, d_ins, d_outs, true);
+}
+
+int altius_cuda_num_inputs(const AcSession* s) { return s ? (int)s->inputs.size() : -AC_ERR_INVALID; }
+int altius_cuda_num_outputs(const AcSession* s) { return s ? (int)s->outputs.size() : -AC_ERR_INVALID; }
+int altius_cuda_input_value(const AcSession* s, int32_t i) {
+  return (s && i >= 0 && i < (int)s->inputs.size()) ? s->inputs[i] : -AC_ERR_INVALID;
+}
+int altius_cuda_output_value(const AcSession* s, int32_t i) {
+  return (s && i >= 0 && i < (int)s->outputs.size()) ? s->outputs[i] : -AC_ERR_INVALID;
+}
+
+int altius_cuda_value_info(const AcSession* s, int32_t value, AcValueDesc* out) {
+  if (!s || !out || value < 0 || value >= (int)s->values.size()) return AC_ERR_INVALID;
+  const Value& v = s->values[value];
+  out->elem_ty = v.elem_ty;
+  out->rank = v.rank;
+  for (int i = 0; i < AC_MAX_RANK; ++i) out->dims[i] = i < v.rank ? v.dims[i] : 0;
+  return AC_OK;
+}
+
+int64_t altius_cuda_launches_per_run(const AcSession* s) { return s ? s->launches_per_run : -1; }
+uint64_t altius_cuda_arena_bytes(const AcSession* s) { return s ? s->arena_bytes : 0; }
+
+int altius_cuda_profile(AcSession* s, AcProfileEntry* entries, size_t* n) {
+  if (!s || !n) return AC_ERR_INVALID;
+  const size_t cap = *n;
+  size_t i = 0;
+  for (auto& kv : s->profile) {
+    if (entries && i < cap) {
+      AcProfileEntry& e = entries[i];
+      std::memset(&e, 0, sizeof(e));
+      std::snprintf(e.name, sizeof(e.name), "%s", kv.first.c_str());
+      e.launches = kv.second.launches;
+      e.total_ms = kv.second.ms;
+      e.bytes = kv.second.bytes;
+      e.flops = kv.second.flops;
+    }
+    ++i;
+  }
+  *n = i;
+  return AC_OK;
+}
+
+int altius_cuda_schedule(const AcSession* s, AcProfileEntry* entries, size_t* n) {
+  if (!s || !n) return AC_ERR_INVALID;
+  const size_t cap = *n;
+  for (size_t i = 0; i < s->steps.size() && entries && i < cap; ++i) {
+    AcProfileEntry& e = entries[i];
+    std::memset(&e, 0, sizeof(e));
+    std::snprintf(e.name, sizeof(e.name), "%s", s->steps[i].kind.c_str());
+    e.launches = s->steps[i].launches;
+    e.bytes = s->steps[i].bytes;
+    e.flops = s->steps[i].flops;
+  }
+  *n = s->steps.size();
+  return AC_OK;
+}
+
+int altius_cuda_profile_reset(AcSession* s) {
+  if (!s) return AC_ERR_INVALID;
+  s->profile.clear();
+  return AC_OK;
+}
+
+const char* altius_cuda_last_error(const AcSession* s) {
+  return s ? s->err.c_str() : g_create_error.c_str();
+}
+
+void altius_cuda_destroy(AcSession* s) {
+  if (!s) return;
+  if (s->stream) cudaSetDevice(s->device);
+  if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
+  if (s->graph) cudaGraphDestroy(s->graph);
+  for (cudaEvent_t ev : s->events)
+    if (ev) cudaEventDestroy(ev);
+  if (s->arena) cudaFree(s->arena);
+  if (s->weights) cudaFree(s->weights);
+  if (s->stream) cudaStreamDestroy(s->stream);
+  delete s;
+}
+
+int altius_cuda_host_alloc(size_t bytes, void** out) {
+  if (!out) return AC_ERR_INVALID;
+  cudaError_t e = cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault);
+  if (e != cudaSuccess) return set_err(nullptr, AC_ERR_CUDA, cudaGetErrorString(e));
+  return AC_OK;
+}
+
+int altius_cuda_host_free(void* p) {
+  if (!p) return AC_OK;
+  return cudaFreeHost(p) == cudaSuccess ? AC_OK : AC_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,229 @@
+/*
+ * altius_session_cuda -- C ABI of the B200 (sm_100a) execution backend.
+ *
+ * This is the boundary a Rust `crates/session_cuda` (or any FFI caller) binds.
+ * It replaces, for the CUDA backend, what the reference's backends expose as
+ *
+ *   XSessionBuilder::new(model).with_profiling_enabled(b).build()
+ *       crates/session_interpreter/src/builder.rs:18-65
+ *   XSession::run(&self, Vec<Tensor>) -> Result<Vec<Tensor>, SessionError>
+ *       crates/session_interpreter/src/session.rs:66-134
+ *       trait Session, crates/session/src/lib.rs:43-45
+ *
+ * and follows the shape of the one C ABI the reference already has, the
+ * generated `model.so` of session_clang: `initialize()` once, then
+ * `trampoline(const void **ins, const void **outs)` per inference with
+ * caller-owned, shape-fixed buffers
+ * (crates/session_clang/src/translator.rs:441-444, :499-503;
+ *  crates/session_clang/src/session.rs:32-56).
+ *
+ * All types are plain C; no CUDA or C++ types cross the boundary. Every
+ * function returns 0 on success and a non-zero AcStatus otherwise; the message
+ * is available from altius_cuda_last_error(). Nothing aborts or throws across
+ * the ABI. Unsupported operators or shapes are rejected by
+ * altius_cuda_create(), never in the middle of a run.
+ */
+#ifndef ALTIUS_SESSION_CUDA_H
+#define ALTIUS_SESSION_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+#define AC_MAX_RANK 8
+
+typedef enum AcStatus {
+  AC_OK = 0,
+  AC_ERR_INVALID = 1,     /* null pointer, bad id, malformed description        */
+  AC_ERR_SHAPE = 2,       /* shape inference failed (SessionError::Shape)        */
+  AC_ERR_UNSUPPORTED = 3, /* operator / pattern without a kernel                 */
+  AC_ERR_CUDA = 4,        /* a CUDA runtime call failed                          */
+  AC_ERR_NO_DEVICE = 5    /* no usable sm_100 device                             */
+} AcStatus;
+
+/* Element types: TensorElemType, crates/core/src/tensor.rs:47-53 */
+typedef enum AcElemType { AC_BOOL = 0, AC_F32 = 1, AC_I32 = 2, AC_I64 = 3 } AcElemType;
+
+/* Operator codes, in the order of `enum Op`, crates/core/src/op.rs:8-58 */
+typedef enum AcOp {
+  AC_OP_IDENTITY = 0, AC_OP_CONV2D, AC_OP_ADD, AC_OP_SUB, AC_OP_MUL, AC_OP_DIV, AC_OP_POW,
+  AC_OP_GREATER, AC_OP_SQRT, AC_OP_RELU, AC_OP_GELU, AC_OP_LEAKYRELU, AC_OP_SIGMOID, AC_OP_ERF,
+  AC_OP_TANH, AC_OP_CLIP, AC_OP_WHERE, AC_OP_SOFTMAX, AC_OP_CAST, AC_OP_MAXPOOL,
+  AC_OP_GLOBALAVERAGEPOOL, AC_OP_RESHAPE, AC_OP_FLATTEN, AC_OP_RESIZE, AC_OP_CONCAT,
+  AC_OP_TRANSPOSE, AC_OP_SQUEEZE, AC_OP_UNSQUEEZE, AC_OP_REDUCEMIN, AC_OP_REDUCEMAX,
+  AC_OP_REDUCEMEAN, AC_OP_ROUND, AC_OP_EXP, AC_OP_EXPAND, AC_OP_RANGE, AC_OP_LOOP, AC_OP_TILE,
+  AC_OP_SPLIT, AC_OP_SLICE, AC_OP_GATHER, AC_OP_SHAPE, AC_OP_NONMAXSUPPRESSION, AC_OP_MATMUL,
+  AC_OP_GEMM, AC_OP_BATCHNORMALIZATION, AC_OP_LAYERNORMALIZATION, AC_OP_HARDSIGMOID,
+  AC_OP_CONSTANT, AC_OP_FUSEDELEMWISE, AC_OP_COUNT
+} AcOp;
+
+/* A value of the graph (crates/core/src/value.rs). rank < 0: shape unknown, to
+ * be inferred. Graph inputs and initializers must carry static shapes. */
+typedef struct AcValueDesc {
+  int32_t elem_ty;            /* AcElemType */
+  int32_t rank;
+  int64_t dims[AC_MAX_RANK];
+} AcValueDesc;
+
+/* A node (crates/core/src/node.rs:8-14). Attributes are flattened into an
+ * integer and a float array, laid out per operator as follows
+ * (fields of the structs in crates/core/src/op.rs:60-211):
+ *
+ *   CONV2D   ints  = kh, kw, sh, sw, dh, dw, group, auto_pad (0 none / NOTSET,
+ *                    1 SAME_UPPER), activation (0 none, 1 Relu, 2 HardSigmoid),
+ *                    npads (0, 2 or 4), pads[npads] (top, left[, bottom, right])
+ *            floats = activation alpha, activation beta
+ *   MAXPOOL  ints  = kh, kw, sh, sw, auto_pad, npads, pads[npads]
+ *   HARDSIGMOID floats = alpha, beta      LEAKYRELU floats = alpha
+ *   SOFTMAX  ints = axis                  FLATTEN ints = axis
+ *   CAST     ints = to (AcElemType)       CONCAT  ints = axis
+ *   TRANSPOSE ints = perm[rank]           GATHER  ints = axis
+ *   SQUEEZE / UNSQUEEZE ints = axes[]     (opset >= 13: taken from input 1)
+ *   REDUCEMAX / REDUCEMEAN ints = keep_dims, axes[]
+ *   SPLIT    ints = axis, split[]         (opset >= 13: sizes from input 1)
+ *   GEMM     ints = trans_a, trans_b;  floats = alpha, beta
+ *   BATCHNORMALIZATION floats = epsilon
+ *   LAYERNORMALIZATION ints = axis, stash_type;  floats = epsilon
+ *
+ * An absent optional input is value id -1. */
+typedef struct AcNodeDesc {
+  int32_t op;                /* AcOp */
+  int32_t n_inputs;
+  const int32_t *inputs;
+  int32_t n_outputs;
+  const int32_t *outputs;
+  int32_t n_ints;
+  const int64_t *ints;
+  int32_t n_floats;
+  const float *floats;
+  const char *name;          /* may be NULL */
+} AcNodeDesc;
+
+/* An initializer (Graph::inits, crates/core/src/graph.rs:13). `location` 0:
+ * `data` is host memory, copied to the device once by create(). 1: `data` is
+ * already memory of the session's device (e.g. the landing buffer of an NCCL
+ * broadcast); it is copied device-to-device and not referenced afterwards.
+ * Shape-like initializers (Reshape shapes, Slice starts, Split sizes, Gather
+ * indices) are read on the host and must use location 0. */
+typedef struct AcInitDesc {
+  int32_t value;
+  int32_t location;
+  const void *data;
+  uint64_t bytes;
+} AcInitDesc;
+
+/* A direct serialisation of `Model` (crates/core/src/model.rs:13-17) after
+ * altius's fusion passes. `inputs` are the run-time inputs in positional order
+ * (initializers are not listed, as after crates/core/src/onnx/load.rs:144-148). */
+typedef struct AcGraphDesc {
+  int64_t opset_version;
+  int32_t n_values;
+  const AcValueDesc *values;
+  int32_t n_nodes;
+  const AcNodeDesc *nodes;
+  int32_t n_inits;
+  const AcInitDesc *inits;
+  int32_t n_inputs;
+  const int32_t *inputs;
+  int32_t n_outputs;
+  const int32_t *outputs;
+} AcGraphDesc;
+
+/* Builder options (InterpreterSessionBuilder fields,
+ * crates/session_interpreter/src/builder.rs:12-16; intra_op_num_threads has no
+ * meaning on a GPU and is not carried). Zero-initialise for defaults. */
+typedef struct AcOptions {
+  int32_t device;            /* CUDA device ordinal                               */
+  int32_t enable_profiling;  /* time every kernel with CUDA events                */
+  int32_t disable_cuda_graph;/* 1: launch kernels one by one instead of a graph   */
+  int32_t disable_fusion;    /* 1: one kernel per node, no producer/consumer folds*/
+  int32_t gemm_mode;         /* 0 auto (tcgen05 3xTF32 where shapes allow),
+                                1 CUDA-core fp32 FMA only, 2 tcgen05 1xTF32       */
+  int32_t plan_only;         /* 1: infer shapes, lower and plan the arena without
+                                touching a GPU; run() then fails. For inspecting
+                                the schedule on a machine without a device.      */
+  int32_t reserved[2];
+} AcOptions;
+
+typedef struct AcSession AcSession;
+
+/* One line of the per-kernel profile: what `enable_profiling` logs per op name
+ * in the reference (crates/session_interpreter/src/session.rs:118-125,251-255),
+ * here per kernel kind, with the algorithmic work used for roofline figures. */
+typedef struct AcProfileEntry {
+  char name[48];             /* kernel kind, e.g. "layer_norm", "gemm_tf32x3"    */
+  uint64_t launches;         /* launches accumulated since the last reset        */
+  double total_ms;           /* device time, CUDA events on the session's stream */
+  double bytes;              /* algorithmic bytes moved by those launches        */
+  double flops;              /* algorithmic FLOPs (2*MACs) of those launches     */
+} AcProfileEntry;
+
+/* builder.build(): shape inference, lowering to a static kernel schedule, one
+ * device arena sized from the inferred shapes, weights copied to the device.
+ * Replaces InterpreterSessionBuilder::build, builder.rs:37-65. */
+int altius_cuda_create(const AcGraphDesc *graph, const AcOptions *options, AcSession **out);
+
+/* session.run(inputs): `ins[i]` / `outs[i]` are caller-owned HOST buffers of
+ * the i-th graph input / output, sized by their (inferred) shapes. Copies
+ * inputs to the device, replays the schedule, copies outputs back, and returns
+ * after the outputs are complete. Not re-entrant for one session. Replaces
+ * InterpreterSession::run, session.rs:66-134, in the calling convention of
+ * session_clang's trampoline, translator.rs:499-503. */
+int altius_cuda_run(AcSession *s, const void *const *ins, void *const *outs);
+
+/* Same, with DEVICE buffers on the session's device (inputs already resident
+ * in HBM); returns after the work is complete. */
+int altius_cuda_run_device(AcSession *s, const void *const *d_ins, void *const *d_outs);
+
+/* session.model() surrogate (session.rs:62-64): static facts of the built
+ * session. altius_cuda_value_info fills the inferred type and shape of any
+ * value id of the graph description (crates/core/src/analysis/shape.rs:659-692). */
+int altius_cuda_num_inputs(const AcSession *s);
+int altius_cuda_num_outputs(const AcSession *s);
+int altius_cuda_input_value(const AcSession *s, int32_t i);
+int altius_cuda_output_value(const AcSession *s, int32_t i);
+int altius_cuda_value_info(const AcSession *s, int32_t value, AcValueDesc *out);
+
+/* Kernel launches one run() issues, and the bytes of the device arena. */
+int64_t altius_cuda_launches_per_run(const AcSession *s);
+uint64_t altius_cuda_arena_bytes(const AcSession *s);
+
+/* The static kernel schedule, one entry per step in launch order (total_ms is
+ * 0). On entry *n is the capacity of `entries`; on return the number of steps. */
+int altius_cuda_schedule(const AcSession *s, AcProfileEntry *entries, size_t *n);
+
+/* Profile accumulated by runs of a session created with enable_profiling.
+ * On entry *n is the capacity of `entries`; on return the number of kinds.
+ * Replaces the `Profile: {...}` log of session.rs:118-125. */
+int altius_cuda_profile(AcSession *s, AcProfileEntry *entries, size_t *n);
+int altius_cuda_profile_reset(AcSession *s);
+
+/* Message of the last failure on this session (or, with s == NULL, of the last
+ * failed altius_cuda_create on this thread). Stands in for SessionError's
+ * Display, crates/session/src/lib.rs:14-34. */
+const char *altius_cuda_last_error(const AcSession *s);
+
+void altius_cuda_destroy(AcSession *s);
+
+/* Page-locked host buffers for callers that want run()'s copies to overlap and
+ * run at full PCIe rate. (The reference has no counterpart: its tensors never
+ * leave host memory.) */
+int altius_cuda_host_alloc(size_t bytes, void **out);
+int altius_cuda_host_free(void *p);
+
+/* Number of visible CUDA devices, or a negative AcStatus. */
+int altius_cuda_device_count(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALTIUS_SESSION_CUDA_H */

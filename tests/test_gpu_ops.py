@@ -1,0 +1,254 @@
+"""Parity of every CUDA kernel with the CPU oracle, one node at a time, through
+the C ABI. Shapes are those of the reference's own op tests
+(crates/altius_py/tests/test_ops_*.py, crates/session_interpreter/tests/op_bin.rs)
+plus the benchmark configurations' shapes.
+
+Bars: bit-exact for Add/Sub/Mul/Div, ReLU, LeakyReLU, HardSigmoid, Gelu,
+Sigmoid, Tanh, Sqrt (per-element formulas restated operation by operation),
+MaxPool and all data movement; max relative error 1e-5 for reductions and
+softmax (tree summation order differs from the oracle's 8-lane partial sums);
+rtol 1e-5 + atol 1e-5 for contractions (summation order is unspecified in the
+reference's BLIS)."""
+import numpy as np
+import pytest
+
+from helpers import assert_bit_exact, max_rel_err, run_cuda, run_oracle, single_op_model
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(1234)
+
+
+def both(model, inputs, **opts):
+    return run_cuda(model, inputs, **opts), run_oracle(model, inputs)
+
+
+BIN_SHAPES = [((1, 2), (1, 2)), ((3, 1, 10), (3, 1, 10)), ((1, 2, 3, 4, 5, 6, 7), (1, 2, 3, 4, 5, 6, 7)),
+              ((1, 3, 28, 28), (3, 1, 1)), ((1, 12, 9, 9), (1, 1, 1, 9)), ((4, 1, 2), (3, 1)),
+              ((3, 28, 28), (3, 28, 1)), ((3, 15, 15), (15,)), ((3, 15, 15), (1,)), ((1,), (5, 7)),
+              ((8, 197, 768), (768,)), ((4, 16, 14, 14), (4, 16, 1, 1)), ((2, 197, 768), (1, 197, 768)),
+              ((5, 33), (5, 33)), ((128, 3, 224, 224), (128, 3, 224, 224))]
+
+
+@pytest.mark.parametrize("ashape,bshape", BIN_SHAPES)
+def test_binary_bit_exact(cuda_lib, ashape, bshape):
+    a = RNG.standard_normal(ashape).astype(np.float32)
+    b = (RNG.random(bshape, dtype=np.float32) + np.float32(0.25))
+    for op in ("Add", "Sub", "Mul", "Div"):
+        got, want = both(single_op_model(op, [a, b]), [a, b])
+        assert_bit_exact(got[0], want[0])
+
+
+def test_binary_with_constant_operand_and_specials(cuda_lib):
+    a = RNG.standard_normal((6, 10)).astype(np.float32)
+    a[0, :4] = [np.inf, -np.inf, np.nan, 0.0]
+    c = np.array([0.0, 1.0, -2.0, np.inf, 3.0, 1e-38, 1e38, -0.0, 5.0, 7.0], np.float32)
+    for op in ("Add", "Sub", "Mul", "Div"):
+        got, want = both(single_op_model(op, [a], [c]), [a])
+        assert_bit_exact(got[0], want[0])
+        got, want = both(single_op_model(op, [a], [c], const_first=True), [a])
+        assert_bit_exact(got[0], want[0])
+
+
+def test_pow(cuda_lib):
+    a = (RNG.random((3, 17), dtype=np.float32) + np.float32(0.1))
+    b = RNG.standard_normal((3, 17)).astype(np.float32)
+    got, want = both(single_op_model("Pow", [a, b]), [a, b])
+    assert max_rel_err(got[0], want[0]) < 1e-5
+    got, want = both(single_op_model("Pow", [a], [np.array([2.0], np.float32)]), [a])
+    assert_bit_exact(got[0], want[0])
+    got, want = both(single_op_model("Pow", [a], [np.array([1.7], np.float32)]), [a])
+    assert max_rel_err(got[0], want[0]) < 1e-5
+
+
+@pytest.mark.parametrize("op,attrs", [("ReLU", {}), ("Gelu", {}), ("Sigmoid", {}), ("Tanh", {}),
+                                      ("HardSigmoid", dict(alpha=0.2, beta=0.5)),
+                                      ("HardSigmoid", dict(alpha=1.0 / 6.0, beta=0.5)),
+                                      ("LeakyReLU", dict(alpha=0.1)), ("Sqrt", {})])
+@pytest.mark.parametrize("shape", [(1, 2), (3, 1, 28, 28), (3, 1, 7, 7), (4, 197, 3072)])
+def test_unary_bit_exact(cuda_lib, op, attrs, shape):
+    x = (RNG.standard_normal(shape) * 4).astype(np.float32)
+    if op == "Sqrt":
+        x = np.abs(x)
+    flat = x.reshape(-1)
+    flat[: min(6, flat.size)] = [0.0, 100.0, -100.0, 9.5, -9.5, 1e-20][: min(6, flat.size)]
+    got, want = both(single_op_model(op, [x], **attrs), [x])
+    assert_bit_exact(got[0], want[0])
+
+
+def test_erf_unpinned_tolerance(cuda_lib):
+    # The reference's Erf lives in an un-vendored crate and is tested to atol 1e-1 only.
+    x = RNG.standard_normal((3, 1, 28, 28)).astype(np.float32)
+    got, want = both(single_op_model("Erf", [x]), [x])
+    np.testing.assert_allclose(got[0], want[0], atol=1e-6)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 3), (3, 28, 28), (16, 512, 512), (4, 12, 197, 197), (2, 3, 1500)])
+def test_softmax(cuda_lib, shape):
+    x = (RNG.standard_normal(shape) * 3).astype(np.float32)
+    got, want = both(single_op_model("Softmax", [x], axis=-1), [x])
+    assert max_rel_err(got[0], want[0]) < 1e-5
+
+
+def test_softmax_extremes(cuda_lib):
+    x = np.array([[1000.0, 0.0, -1000.0, 1000.0], [-np.inf, 0.0, 1.0, 2.0]], np.float32)
+    got, want = both(single_op_model("Softmax", [x], axis=-1), [x])
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-30)
+
+
+@pytest.mark.parametrize("shape", [(1, 20, 10), (6, 197, 768), (3, 198, 384), (5, 7, 1000), (2, 3, 5000)])
+def test_layer_norm(cuda_lib, shape):
+    x = RNG.standard_normal(shape).astype(np.float32)
+    g = (1 + 0.02 * RNG.standard_normal(shape[-1])).astype(np.float32)
+    b = (0.02 * RNG.standard_normal(shape[-1])).astype(np.float32)
+    m = single_op_model("LayerNormalization", [x], [g.reshape(1, 1, -1), b.reshape(1, 1, -1)],
+                        axis=-1, epsilon=1e-6, stash_type=1)
+    got, want = both(m, [x])
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-6)
+
+
+def test_reductions(cuda_lib):
+    for shape in ((1, 50, 70), (4, 197, 768), (3, 5, 33)):
+        x = RNG.standard_normal(shape).astype(np.float32)
+        got, want = both(single_op_model("ReduceMean", [x], axes=[-1], keep_dims=True), [x])
+        np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-7)
+        got, want = both(single_op_model("ReduceMax", [x], axes=[-1], keep_dims=True), [x])
+        assert_bit_exact(got[0], want[0])
+        got, want = both(single_op_model("ReduceMax", [x], axes=[], keep_dims=False), [x])
+        assert_bit_exact(got[0], want[0])
+    for shape in ((2, 5, 7, 7), (4, 960, 7, 7), (2, 16, 56, 56)):
+        y = RNG.standard_normal(shape).astype(np.float32)
+        got, want = both(single_op_model("GlobalAveragePool", [y]), [y])
+        np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-7)
+
+
+def test_max_pool_bit_exact(cuda_lib):
+    x = RNG.standard_normal((3, 4, 28, 28)).astype(np.float32)
+    for k, s, p in ((2, 2, 0), (3, 3, 0), (5, 1, 2), (3, 2, 1)):
+        m = single_op_model("MaxPool", [x], kernel_shape=[k, k], strides=[s, s], padding=[p, p, p, p])
+        got, want = both(m, [x])
+        assert_bit_exact(got[0], want[0])
+
+
+def test_data_movement_bit_exact(cuda_lib):
+    x = RNG.standard_normal((2, 3, 4, 5)).astype(np.float32)
+    for perm in ([1, 2, 0, 3], [0, 1, 3, 2], [2, 1, 0, 3], [0, 1, 2, 3], [3, 2, 1, 0], [0, 2, 1, 3]):
+        got, want = both(single_op_model("Transpose", [x], perm=perm), [x])
+        assert_bit_exact(got[0], want[0])
+    big = RNG.standard_normal((4, 197, 12, 64)).astype(np.float32)
+    got, want = both(single_op_model("Transpose", [big], perm=[0, 2, 1, 3]), [big])
+    assert_bit_exact(got[0], want[0])
+    kt = RNG.standard_normal((48, 197, 64)).astype(np.float32)
+    got, want = both(single_op_model("Transpose", [kt], perm=[0, 2, 1]), [kt])
+    assert_bit_exact(got[0], want[0])
+    y = RNG.standard_normal((2, 7, 4, 5)).astype(np.float32)
+    got, want = both(single_op_model("Concat", [x, y], axis=1), [x, y])
+    assert_bit_exact(got[0], want[0])
+    z = RNG.standard_normal((2, 3, 12)).astype(np.float32)
+    m = single_op_model("Split", [z], [np.array([4, 5, 3], np.int64)], n_outputs=3, axis=2)
+    got, want = both(m, [z])
+    for g_, w_ in zip(got, want):
+        assert_bit_exact(g_, w_)
+    m = single_op_model("Slice", [z], [np.array([2], np.int64), np.array([9], np.int64),
+                                       np.array([2], np.int64)])
+    got, want = both(m, [z])
+    assert_bit_exact(got[0], want[0])
+    for axis, idx in ((1, np.array(1, np.int64)), (0, np.array([[1, 0, 1]], np.int64))):
+        got, want = both(single_op_model("Gather", [z], [idx], axis=axis), [z])
+        assert_bit_exact(got[0], want[0])
+    got, want = both(single_op_model("Reshape", [z], [np.array([6, -1], np.int64)]), [z])
+    assert_bit_exact(got[0], want[0])
+    got, want = both(single_op_model("Flatten", [x], axis=1), [x])
+    assert_bit_exact(got[0], want[0])
+
+
+def test_where_greater_cast(cuda_lib):
+    x = RNG.standard_normal((1, 128, 10, 10)).astype(np.float32)
+    got, want = both(single_op_model("Greater", [x], [np.array([0.1], np.float32)]), [x])
+    assert_bit_exact(got[0], want[0])
+    cond = RNG.random((1, 1, 10, 10)) > 0.5
+    m = single_op_model("Where", [cond, x], [np.array([-1.0], np.float32)])
+    got, want = both(m, [cond, x])
+    assert_bit_exact(got[0], want[0])
+    y = RNG.standard_normal((1, 1, 10, 10)).astype(np.float32)
+    m = single_op_model("Where", [cond], [np.array([2.0], np.float32), y])
+    got, want = both(m, [cond])
+    assert_bit_exact(got[0], want[0])
+    i64 = RNG.integers(-1000, 1000, (3, 9)).astype(np.int64)
+    for to in (1, 2):
+        got, want = both(single_op_model("Cast", [i64], to=to), [i64])
+        assert_bit_exact(got[0], want[0])
+    got, want = both(single_op_model("Cast", [x], to=0), [x])
+    assert_bit_exact(got[0], want[0])
+
+
+def test_batch_norm(cuda_lib):
+    x = RNG.standard_normal((2, 6, 9, 9)).astype(np.float32)
+    sc, b, mu = (RNG.standard_normal(6).astype(np.float32) for _ in range(3))
+    var = RNG.random(6, dtype=np.float32) + np.float32(0.5)
+    m = single_op_model("BatchNormalization", [x], [sc, b, mu, var], epsilon=1e-5)
+    got, want = both(m, [x])
+    assert_bit_exact(got[0], want[0])
+
+
+MATMUL_SHAPES = [((4, 8), (8, 3)), ((2, 5, 8), (8, 3)), ((3, 5, 8), (3, 8, 6)), ((1, 2, 5, 8), (1, 2, 8, 6)),
+                 ((1, 256), (256, 10)), ((2, 197, 768), (768, 2304)), ((24, 197, 64), (24, 64, 197)),
+                 ((24, 197, 197), (24, 197, 64)), ((394, 3072), (3072, 768)), ((130, 70), (70, 129))]
+
+
+@pytest.mark.parametrize("ashape,bshape", MATMUL_SHAPES)
+@pytest.mark.parametrize("gemm_mode", [0, 1])
+def test_matmul(cuda_lib, ashape, bshape, gemm_mode):
+    a = RNG.standard_normal(ashape).astype(np.float32)
+    b = RNG.standard_normal(bshape).astype(np.float32)
+    got, want = both(single_op_model("MatMul", [a, b]), [a, b], gemm_mode=gemm_mode)
+    k = ashape[-1]
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5 * np.sqrt(k))
+
+
+@pytest.mark.parametrize("gemm_mode", [0, 1])
+def test_gemm(cuda_lib, gemm_mode):
+    a = RNG.standard_normal((7, 9)).astype(np.float32)
+    for ta, ash in ((False, (7, 9)), (True, (9, 7))):
+        a = RNG.standard_normal(ash).astype(np.float32)
+        for tb, bsh in ((False, (9, 5)), (True, (5, 9))):
+            b = RNG.standard_normal(bsh).astype(np.float32)
+            for c in (RNG.standard_normal(5).astype(np.float32),
+                      RNG.standard_normal((7, 5)).astype(np.float32), None):
+                ins = [a, b] + ([c] if c is not None else [])
+                for alpha, beta in ((1.0, 1.0), (0.5, 2.0)):
+                    m = single_op_model("Gemm", ins, alpha=alpha, beta=beta, trans_a=ta, trans_b=tb)
+                    got, want = both(m, ins, gemm_mode=gemm_mode)
+                    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=2e-5)
+    a = RNG.standard_normal((32, 768)).astype(np.float32)
+    w = (0.02 * RNG.standard_normal((1000, 768))).astype(np.float32)
+    c = RNG.standard_normal(1000).astype(np.float32)
+    m = single_op_model("Gemm", [a], [w, c], alpha=1.0, beta=1.0, trans_a=False, trans_b=True)
+    got, want = both(m, [a], gemm_mode=gemm_mode)
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=2e-5)
+
+
+CONV_CASES = [(1, 1, 28, 8, 5, 1, 2, 1, True), (2, 4, 15, 6, 3, 2, 1, 1, True), (2, 16, 9, 16, 3, 1, 1, 16, True),
+              (2, 16, 9, 16, 3, 1, 1, 16, False), (1, 3, 32, 8, 16, 16, 0, 1, True), (2, 24, 14, 40, 1, 1, 0, 1, True),
+              (2, 32, 14, 32, 5, 2, 2, 32, True), (2, 3, 64, 16, 3, 2, 1, 1, False)]
+
+
+@pytest.mark.parametrize("n,c,h,oc,k,s,p,g,with_bias", CONV_CASES)
+@pytest.mark.parametrize("gemm_mode", [0, 1])
+def test_conv2d(cuda_lib, n, c, h, oc, k, s, p, g, with_bias, gemm_mode):
+    x = RNG.standard_normal((n, c, h, h)).astype(np.float32)
+    w = RNG.standard_normal((oc, c // g, k, k)).astype(np.float32)
+    consts = [w] + ([RNG.standard_normal(oc).astype(np.float32)] if with_bias else [])
+    m = single_op_model("Conv2d", [x], consts, kernel_shape=[k, k], strides=[s, s],
+                        padding=[p, p, p, p], dilations=[1, 1], group=g, auto_pad="")
+    got, want = both(m, [x], gemm_mode=gemm_mode)
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5 * np.sqrt(c // g * k * k) * 4)
+
+
+def test_conv2d_same_upper(cuda_lib):
+    x = RNG.standard_normal((1, 1, 28, 28)).astype(np.float32)
+    w = RNG.standard_normal((8, 1, 5, 5)).astype(np.float32)
+    m = single_op_model("Conv2d", [x], [w], kernel_shape=[5, 5], strides=[1, 1], padding=[],
+                        dilations=[1, 1], group=1, auto_pad="SAME_UPPER")
+    got, want = both(m, [x])
+    assert got[0].shape == (1, 8, 28, 28)
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5)   # ops_conv.rs:41-43
