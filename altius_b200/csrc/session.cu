@@ -303,6 +303,35 @@ int altius_cuda_run_device(AcSession* s, const void* const* d_ins, void* const* 
   return run_common(s, d_ins, d_outs, true);
 }
 
+int altius_cuda_time_device_runs(AcSession* s, const void* const* d_ins, void* const* d_outs,
+                                 int32_t iters, float* elapsed_ms) {
+  if (!s || !elapsed_ms || iters <= 0 || !d_outs || (!d_ins && !s->inputs.empty()))
+    return set_err(s, AC_ERR_INVALID, "bad argument");
+  if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
+  if (s->opt.enable_profiling) return set_err(s, AC_ERR_INVALID, "not available on a profiling session");
+  cudaError_t e = cudaSetDevice(s->device);
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  if (e == cudaSuccess) e = cudaEventCreate(&t0);
+  if (e == cudaSuccess) e = cudaEventCreate(&t1);
+  if (e == cudaSuccess) e = cudaEventRecord(t0, s->stream);
+  for (int it = 0; it < iters && e == cudaSuccess; ++it) {
+    for (size_t i = 0; i < s->inputs.size() && e == cudaSuccess; ++i)
+      e = cudaMemcpyAsync(s->ptr(s->inputs[i]), d_ins[i], s->values[s->inputs[i]].bytes(),
+                          cudaMemcpyDeviceToDevice, s->stream);
+    if (e == cudaSuccess) e = s->graph_exec ? cudaGraphLaunch(s->graph_exec, s->stream) : replay(s, s->stream);
+    for (size_t i = 0; i < s->outputs.size() && e == cudaSuccess; ++i)
+      e = cudaMemcpyAsync(d_outs[i], s->ptr(s->outputs[i]), s->values[s->outputs[i]].bytes(),
+                          cudaMemcpyDeviceToDevice, s->stream);
+  }
+  if (e == cudaSuccess) e = cudaEventRecord(t1, s->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+  if (e == cudaSuccess) e = cudaEventElapsedTime(elapsed_ms, t0, t1);
+  if (t0) cudaEventDestroy(t0);
+  if (t1) cudaEventDestroy(t1);
+  if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("timed runs: ") + cudaGetErrorString(e));
+  return AC_OK;
+}
+
 int altius_cuda_num_inputs(const AcSession* s) { return s ? (int)s->inputs.size() : -AC_ERR_INVALID; }
 int altius_cuda_num_outputs(const AcSession* s) { return s ? (int)s->outputs.size() : -AC_ERR_INVALID; }
 int altius_cuda_input_value(const AcSession* s, int32_t i) {

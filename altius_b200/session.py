@@ -83,7 +83,8 @@ class AcProfileEntry(ctypes.Structure):
 
 # Every symbol include/altius_session_cuda.h declares.
 ABI_SYMBOLS = (
-    "altius_cuda_create", "altius_cuda_run", "altius_cuda_run_device", "altius_cuda_num_inputs",
+    "altius_cuda_create", "altius_cuda_run", "altius_cuda_run_device",
+    "altius_cuda_time_device_runs", "altius_cuda_num_inputs",
     "altius_cuda_num_outputs", "altius_cuda_input_value", "altius_cuda_output_value",
     "altius_cuda_value_info", "altius_cuda_launches_per_run", "altius_cuda_arena_bytes",
     "altius_cuda_schedule", "altius_cuda_profile", "altius_cuda_profile_reset", "altius_cuda_last_error",
@@ -108,6 +109,8 @@ def load_library() -> ctypes.CDLL:
                                        ctypes.POINTER(P)]
     lib.altius_cuda_run.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(P)]
     lib.altius_cuda_run_device.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(P)]
+    lib.altius_cuda_time_device_runs.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(P),
+                                                 ctypes.c_int32, ctypes.POINTER(ctypes.c_float)]
     for name in ("altius_cuda_num_inputs", "altius_cuda_num_outputs"):
         getattr(lib, name).argtypes = [P]
     lib.altius_cuda_input_value.argtypes = [P, ctypes.c_int32]
@@ -305,6 +308,16 @@ class CudaSession:
         ins = (ctypes.c_void_p * max(1, len(in_ptrs)))(*in_ptrs)
         outs = (ctypes.c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
         self._check(self._lib.altius_cuda_run_device(self._handle, ins, outs))
+
+    def time_device_runs(self, in_ptrs: Sequence[int], out_ptrs: Sequence[int], iters: int) -> float:
+        """`iters` back-to-back runs on device buffers; returns the elapsed
+        milliseconds between CUDA events on the session's stream."""
+        ins = (ctypes.c_void_p * max(1, len(in_ptrs)))(*in_ptrs)
+        outs = (ctypes.c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
+        ms = ctypes.c_float()
+        self._check(self._lib.altius_cuda_time_device_runs(self._handle, ins, outs, iters,
+                                                           ctypes.byref(ms)))
+        return float(ms.value)
 
     # -- profiling ---------------------------------------------------------------
     def profile(self) -> Dict[str, dict]:

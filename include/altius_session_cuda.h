@@ -181,6 +181,14 @@ int altius_cuda_run(AcSession *s, const void *const *ins, void *const *outs);
  * in HBM); returns after the work is complete. */
 int altius_cuda_run_device(AcSession *s, const void *const *d_ins, void *const *d_outs);
 
+/* `iters` back-to-back runs with device buffers, timed on the device: CUDA
+ * events recorded on the session's stream before the first and after the last
+ * run; *elapsed_ms receives the time between them. For measurement harnesses
+ * (the reference's counterpart is the `Instant` pair around run(),
+ * session.rs:68,123). */
+int altius_cuda_time_device_runs(AcSession *s, const void *const *d_ins, void *const *d_outs,
+                                 int32_t iters, float *elapsed_ms);
+
 /* session.model() surrogate (session.rs:62-64): static facts of the built
  * session. altius_cuda_value_info fills the inferred type and shape of any
  * value id of the graph description (crates/core/src/analysis/shape.rs:659-692). */
