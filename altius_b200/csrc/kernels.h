@@ -123,6 +123,7 @@ struct GemmParams {
   int64_t batch;
   const float* a; int64_t lda; int64_t stride_a; int trans_a;
   const float* b; int64_t ldb; int64_t stride_b; int trans_b;
+  const float* b_lo;        // tensor-core path only: x - trunc_tf32(x) of B, same layout; or null
   float* c; int64_t ldc; int64_t stride_c;
   float alpha;
   float beta;               // applied to c_in (may alias c); 0: c_in not read
@@ -135,5 +136,14 @@ struct GemmParams {
   int residual_first;       // residual + v instead of v + residual (same value, kept for clarity)
 };
 cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
+
+// tcgen05 / TMEM / TMA path. Needs A row-major with K contiguous (trans_a == 0)
+// and B stored [N, K] (trans_b == 1), 16-byte aligned bases and leading
+// dimensions that are multiples of 4 floats. mode 0: 3xTF32, mode 2: 1xTF32.
+// `err_word` (device memory) receives a non-zero code if a bounded wait expired.
+bool gemm_tc_supported(const GemmParams& p);
+cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStream_t st);
+// lo[i] = x[i] - (x[i] truncated to TF32)
+cudaError_t launch_tf32_remainder(const float* x, float* lo, int64_t n, cudaStream_t st);
 
 }  // namespace ac

@@ -388,22 +388,74 @@ struct GemmShape {
   int ta, tb;
 };
 
-void emit_gemm(Emit& em, int op, const GemmShape& g, int a, int b, int out, int c_in, int bias_n,
+// Appends a scratch / derived value (not part of the caller's graph).
+int new_value(Ctx& c, int64_t numel, bool is_const) {
+  Value v;
+  v.elem_ty = AC_F32;
+  v.rank = 1;
+  v.dims[0] = numel;
+  v.is_const = is_const;
+  v.storage = c.new_storage(v.bytes(), false, /*pinned=*/is_const);
+  c.s.values.push_back(v);
+  c.producer.push_back(-1);
+  c.consumers.emplace_back();
+  c.is_output.push_back(0);
+  return (int)c.s.values.size() - 1;
+}
+
+void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, int c_in, int bias_n,
                int bias_m, float alpha, float beta, float bias_scale, const Epilogue* e,
                int64_t a_off = 0, int64_t b_off = 0, int64_t c_off = 0) {
   AcSession* s = em.s;
+  GemmShape g = g_in;
   const int act = e ? e->act : ACT_NONE;
   const float aa = e ? e->act_alpha : 0.f, ab = e ? e->act_beta : 0.f;
   const int res = e ? e->residual : -1;
-  std::vector<int> reads = {a, b, c_in, bias_n, bias_m, res};
   double bytes = 4.0 * g.batch * (g.m * g.k + g.m * g.n) + 4.0 * (g.sb ? g.batch : 1) * g.k * g.n;
   if (res >= 0) bytes += 4.0 * g.batch * g.m * g.n;
   const double flops = 2.0 * g.batch * g.m * g.n * g.k;
-  em.add("gemm_fp32_simt", op, reads, {out}, bytes, flops, [=](cudaStream_t st) {
+
+  // ---- tensor-core eligibility (static part; alignment is re-checked at launch) ----
+  const int mode = s->opt.gemm_mode;
+  bool tc = mode != 1 && !g.ta && (g.lda % 4) == 0 && (a_off % 4) == 0 && (g.sa % 4) == 0 &&
+            flops >= double(1 << 23) && g.k >= 8;
+  int b_use = b, b_lo = -1;
+  const bool b_const = em.c.val(b).is_const;
+  if (tc) {
+    if (g.tb) {
+      tc = (g.ldb % 4) == 0 && (b_off % 4) == 0 && (g.sb % 4) == 0;
+    } else if (b_const && g.batch == 1 && b_off == 0 && (g.k % 4) == 0) {
+      // Constant rhs stored [K, N]: keep a [N, K] copy made once at load.
+      const int bt = new_value(em.c, g.k * g.n, true);
+      const int64_t kk = g.k, nn = g.n;
+      em.add("weight_transpose", op, {b}, {bt}, 8.0 * kk * nn, 0, [=](cudaStream_t st) {
+        return launch_transpose2d(s->fptr(b), s->fptr_mut(bt), 1, (int)kk, (int)nn, st);
+      });
+      b_use = bt;
+      g.tb = 1;
+      g.ldb = g.k;
+    } else {
+      tc = false;
+    }
+  }
+  if (tc && mode != 2 && em.c.val(b_use).is_const) {
+    // x - trunc_tf32(x) of a constant rhs, prepared once.
+    const int64_t cnt = em.c.val(b_use).numel();
+    b_lo = new_value(em.c, cnt, true);
+    const int src = b_use, dst = b_lo;
+    em.add("weight_tf32_remainder", op, {src}, {dst}, 8.0 * cnt, 0, [=](cudaStream_t st) {
+      return launch_tf32_remainder(s->fptr(src), s->fptr_mut(dst), cnt, st);
+    });
+  }
+  const int bsrc = b_use;
+  std::vector<int> reads = {a, bsrc, b_lo, c_in, bias_n, bias_m, res};
+  const char* kind = !tc ? "gemm_fp32_simt" : (mode == 2 ? "gemm_tf32x1_tcgen05" : "gemm_tf32x3_tcgen05");
+  em.add(kind, op, reads, {out}, bytes, flops, [=](cudaStream_t st) {
     GemmParams p{};
     p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
     p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
-    p.b = s->fptr(b) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
+    p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
+    p.b_lo = b_lo >= 0 ? s->fptr(b_lo) + b_off : nullptr;
     p.c = s->fptr_mut(out) + c_off; p.ldc = g.ldc; p.stride_c = g.sc;
     p.alpha = alpha; p.beta = c_in >= 0 ? beta : 0.f;
     p.c_in = c_in >= 0 ? s->fptr(c_in) + c_off : nullptr; p.ldc_in = g.ldc; p.stride_c_in = g.sc;
@@ -412,6 +464,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g, int a, int b, int out, int 
     p.bias_scale = bias_scale;
     p.act = act; p.act_alpha = aa; p.act_beta = ab;
     p.residual = res >= 0 ? s->fptr(res) + c_off : nullptr; p.ld_res = g.ldc; p.stride_res = g.sc;
+    if (tc && gemm_tc_supported(p)) return launch_gemm_tc(p, mode, s->err_word, st);
     return launch_gemm_simt(p, st);
   });
 }

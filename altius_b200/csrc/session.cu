@@ -212,8 +212,11 @@ int run_common(AcSession* s, const void* const* ins, void* const* outs, bool dev
     e = cudaMemcpyAsync(outs[i], s->ptr(s->outputs[i]), v.bytes(), out_kind, s->stream);
     if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("output copy: ") + cudaGetErrorString(e));
   }
+  cudaMemcpyAsync(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost, s->stream);
   e = cudaStreamSynchronize(s->stream);
   if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("run: ") + cudaGetErrorString(e));
+  if (*s->err_host != 0)
+    return set_err(s, AC_ERR_CUDA, "a kernel gave up a bounded wait (code " + std::to_string(*s->err_host) + ")");
   if (s->opt.enable_profiling) {
     for (size_t i = 0; i < s->steps.size(); ++i) {
       float ms = 0.f;
@@ -263,6 +266,10 @@ int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSes
       fail(AC_ERR_NO_DEVICE, "device is not sm_100 (the kernels are built for sm_100a only)");
     AC_CUDA(cudaSetDevice(s->device));
     AC_CUDA(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    AC_CUDA(cudaMalloc(&s->err_word, sizeof(int)));
+    AC_CUDA(cudaMemset(s->err_word, 0, sizeof(int)));
+    AC_CUDA(cudaHostAlloc(&s->err_host, sizeof(int), cudaHostAllocDefault));
+    *s->err_host = 0;
     parse_graph(*s, *graph);
     infer_shapes(*s);
     lower_graph(*s);
@@ -271,6 +278,8 @@ int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSes
     upload_weights(*s, *graph);
     for (Step& st : s->init_steps) AC_CUDA(st.fn(s->stream));
     AC_CUDA(cudaStreamSynchronize(s->stream));
+    AC_CUDA(cudaMemcpy(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*s->err_host != 0) fail(AC_ERR_CUDA, "a kernel gave up a bounded wait while preparing constants");
     if (s->opt.enable_profiling) {
       s->events.resize(s->steps.size() + 1);
       for (cudaEvent_t& ev : s->events) AC_CUDA(cudaEventCreate(&ev));
@@ -324,7 +333,13 @@ int altius_cuda_time_device_runs(AcSession* s, const void* const* d_ins, void* c
                           cudaMemcpyDeviceToDevice, s->stream);
   }
   if (e == cudaSuccess) e = cudaEventRecord(t1, s->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost, s->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+  if (e == cudaSuccess && *s->err_host != 0) {
+    if (t0) cudaEventDestroy(t0);
+    if (t1) cudaEventDestroy(t1);
+    return set_err(s, AC_ERR_CUDA, "a kernel gave up a bounded wait (code " + std::to_string(*s->err_host) + ")");
+  }
   if (e == cudaSuccess) e = cudaEventElapsedTime(elapsed_ms, t0, t1);
   if (t0) cudaEventDestroy(t0);
   if (t1) cudaEventDestroy(t1);
@@ -405,6 +420,8 @@ void altius_cuda_destroy(AcSession* s) {
   if (s->graph) cudaGraphDestroy(s->graph);
   for (cudaEvent_t ev : s->events)
     if (ev) cudaEventDestroy(ev);
+  if (s->err_word) cudaFree(s->err_word);
+  if (s->err_host) cudaFreeHost(s->err_host);
   if (s->arena) cudaFree(s->arena);
   if (s->weights) cudaFree(s->weights);
   if (s->stream) cudaStreamDestroy(s->stream);

@@ -82,6 +82,8 @@ struct AcSession {
   size_t arena_bytes = 0;
   char* weights = nullptr;
   size_t weight_bytes = 0;
+  int* err_word = nullptr;             // device word written by kernels whose bounded waits expire
+  int* err_host = nullptr;             // page-locked mirror
   cudaStream_t stream = nullptr;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t graph_exec = nullptr;

@@ -252,3 +252,81 @@ def test_conv2d_same_upper(cuda_lib):
     got, want = both(m, [x])
     assert got[0].shape == (1, 8, 28, 28)
     np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5)   # ops_conv.rs:41-43
+
+
+# ---- tensor-core (tcgen05, 3xTF32) path: needs a K-major rhs -------------------------
+TC_SHAPES = [((2, 197, 768), (768, 2304)), ((394, 3072), (3072, 768)), ((1000, 768), (768, 768)),
+             ((3, 130, 100), (100, 72)), ((257, 36), (36, 513)), ((128, 32), (32, 64)), ((640, 8), (8, 256))]
+
+
+@pytest.mark.parametrize("ashape,bshape", TC_SHAPES)
+@pytest.mark.parametrize("gemm_mode", [0, 1])
+def test_matmul_constant_weight(cuda_lib, ashape, bshape, gemm_mode):
+    a = RNG.standard_normal(ashape).astype(np.float32)
+    w = RNG.standard_normal(bshape).astype(np.float32)
+    m = single_op_model("MatMul", [a], [w])
+    got, want = both(m, [a], gemm_mode=gemm_mode)
+    np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5 * np.sqrt(ashape[-1]))
+
+
+def test_matmul_tf32x1_is_looser_but_close(cuda_lib):
+    a = RNG.standard_normal((512, 768)).astype(np.float32)
+    w = RNG.standard_normal((768, 512)).astype(np.float32)
+    m = single_op_model("MatMul", [a], [w])
+    got, want = both(m, [a], gemm_mode=2)
+    err = np.abs(got[0] - want[0]).max()
+    assert 1e-4 < err < 0.2          # one TF32 product per term: ~1e-3 relative
+
+
+def _chain_model(build):
+    from altius_b200 import ir
+    g = ir.Graph()
+    outs = build(g)
+    for i, o in enumerate(outs):
+        g.values[o].name = f"out{i}"
+        g.outputs.append(o)
+    return ir.Model(g, 13)
+
+
+def test_qk_transpose_matmul_scale_softmax(cuda_lib):
+    q = RNG.standard_normal((24, 197, 64)).astype(np.float32)
+    k = RNG.standard_normal((24, 197, 64)).astype(np.float32)
+
+    def build(g):
+        qi, ki = g.add_input("q", q.shape), g.add_input("k", k.shape)
+        kt = g.op("Transpose", ki, perm=[0, 2, 1])
+        s = g.op("MatMul", qi, kt)
+        s = g.op("Mul", s, g.new_init(np.array([0.125], np.float32)))
+        return [g.op("Softmax", s, axis=-1)]
+    m = _chain_model(build)
+    for mode in (0, 1):
+        got, want = both(m, [q, k], gemm_mode=mode)
+        np.testing.assert_allclose(got[0], want[0], rtol=2e-5, atol=1e-7)
+
+
+def test_linear_gelu_residual_epilogue(cuda_lib):
+    x = RNG.standard_normal((4, 197, 768)).astype(np.float32)
+    r = RNG.standard_normal((4, 197, 384)).astype(np.float32)
+    w = (0.05 * RNG.standard_normal((768, 384))).astype(np.float32)
+    b = RNG.standard_normal(384).astype(np.float32)
+
+    def build(g):
+        xi, ri = g.add_input("x", x.shape), g.add_input("r", r.shape)
+        h = g.op("MatMul", xi, g.new_init(w))
+        h = g.op("Add", h, g.new_init(b))
+        h = g.op("Gelu", h)
+        return [g.op("Add", ri, h)]
+    m = _chain_model(build)
+    for opts in (dict(gemm_mode=0), dict(gemm_mode=1), dict(gemm_mode=0, fuse=False)):
+        got, want = both(m, [x, r], **opts)
+        np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=3e-5)
+
+
+def test_gemm_transb_constant_weight(cuda_lib):
+    a = RNG.standard_normal((300, 1280)).astype(np.float32)
+    w = (0.02 * RNG.standard_normal((1000, 1280))).astype(np.float32)
+    c = RNG.standard_normal(1000).astype(np.float32)
+    m = single_op_model("Gemm", [a], [w, c], alpha=1.0, beta=1.0, trans_a=False, trans_b=True)
+    for mode in (0, 1):
+        got, want = both(m, [a], gemm_mode=mode)
+        np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=2e-5)

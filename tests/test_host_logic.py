@@ -85,7 +85,8 @@ def test_flops_of_vit_match_the_published_count():
 
 def test_arena_reuses_memory():
     model, _ = configs.vit_base_16(batch=4, depth=12)
-    s = plan(model)
+    # gemm_mode 1: no transposed / split weight copies live in the arena
+    s = CudaSessionBuilder(model).with_plan_only(True).with_gemm_mode(1).build()
     total = 0
     for v in range(len(model.graph.values)):
         if v in model.graph.inits:
