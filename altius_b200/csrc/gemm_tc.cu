@@ -6,18 +6,19 @@
 //
 // It replaces the cblas_sgemm the reference calls for MatMul / Gemm / Conv2d
 // (crates/session_interpreter/src/gemm.rs:36-51, session.rs:621-794,
-// conv2d.rs:145-209). fp32 inputs are used as they are: the tensor core reads
-// the top 19 bits of each word (x_hi = x truncated to TF32); the remainder
-// x_lo = x - x_hi is exact in fp32 and is fed as a second operand, so each
-// product is evaluated as a_hi*b_hi + a_hi*b_lo + a_lo*b_hi with fp32
-// accumulation in TMEM (the a_lo*b_lo term, < 2^-20 relative, is dropped).
+// conv2d.rs:145-209). Every fp32 operand x is split into x_hi = x rounded to
+// TF32 (round to nearest) and x_lo = (x - x_hi) rounded to TF32; x - x_hi is
+// exact in fp32. Each product is evaluated as a_lo*b_hi + a_hi*b_lo + a_hi*b_hi
+// with fp32 accumulation in TMEM; the dropped a_lo*b_lo term and the rounding
+// of x_lo are each below 2^-22 relative.
 //
 // One CTA computes one 128 x BN tile:
 //   warp 4      TMA producer: one elected thread issues cp.async.bulk.tensor
 //               loads (128B-swizzled boxes of 32 floats along K) into a ring of
 //               stages, completion on an mbarrier per stage;
-//   warps 0-3   splitters: compute x_lo for the A tile (and the B tile when B
-//               is not a constant whose x_lo was prepared at load time), then
+//   warps 0-3   splitters: rewrite the A tile as x_hi in place and write x_lo
+//               beside it (the same for the B tile unless B is a constant whose
+//               split was prepared at load time and arrives by TMA), then
 //               the epilogue: tcgen05.ld of the accumulator, bias / activation
 //               / residual, global stores;
 //   warp 5      one thread issues the tcgen05.mma stream and tcgen05.commit.
@@ -138,14 +139,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
-// x_lo = x - (x truncated to TF32), for 4 packed floats.
-__device__ __forceinline__ float4 tf32_remainder(float4 v) {
-  float4 r;
-  r.x = __fsub_rn(v.x, __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u));
-  r.y = __fsub_rn(v.y, __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u));
-  r.z = __fsub_rn(v.z, __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u));
-  r.w = __fsub_rn(v.w, __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u));
-  return r;
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+// hi = rn_tf32(x), lo = rn_tf32(x - hi), for 4 packed floats.
+__device__ __forceinline__ void tf32_split(float4 v, float4& hi, float4& lo) {
+  hi.x = round_tf32(v.x); lo.x = round_tf32(__fsub_rn(v.x, hi.x));
+  hi.y = round_tf32(v.y); lo.y = round_tf32(__fsub_rn(v.y, hi.y));
+  hi.z = round_tf32(v.z); lo.z = round_tf32(__fsub_rn(v.z, hi.z));
+  hi.w = round_tf32(v.w); lo.w = round_tf32(__fsub_rn(v.w, hi.w));
 }
 
 template <int BN>
@@ -261,17 +265,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t ph = (kb / S) & 1;
         ok = mbar_wait(&full[s], ph);
         if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
-        const float4* src = reinterpret_cast<const float4*>(a_raw(s));
+        float4* src = reinterpret_cast<float4*>(a_raw(s));
         float4* dst = reinterpret_cast<float4*>(a_lo(s));
 #pragma unroll
-        for (int i = 0; i < L::kABytes / 16 / kSplitThreads; ++i)
-          dst[i * kSplitThreads + t] = tf32_remainder(src[i * kSplitThreads + t]);
+        for (int i = 0; i < L::kABytes / 16 / kSplitThreads; ++i) {
+          float4 hi, lo;
+          tf32_split(src[i * kSplitThreads + t], hi, lo);
+          src[i * kSplitThreads + t] = hi;
+          dst[i * kSplitThreads + t] = lo;
+        }
         if (MODE == TC_3X_SPLIT_B) {
-          const float4* sb = reinterpret_cast<const float4*>(b_raw(s));
+          float4* sb = reinterpret_cast<float4*>(b_raw(s));
           float4* dbp = reinterpret_cast<float4*>(b_lo(s));
 #pragma unroll
-          for (int i = 0; i < L::kBBytes / 16 / kSplitThreads; ++i)
-            dbp[i * kSplitThreads + t] = tf32_remainder(sb[i * kSplitThreads + t]);
+          for (int i = 0; i < L::kBBytes / 16 / kSplitThreads; ++i) {
+            float4 hi, lo;
+            tf32_split(sb[i * kSplitThreads + t], hi, lo);
+            sb[i * kSplitThreads + t] = hi;
+            dbp[i * kSplitThreads + t] = lo;
+          }
         }
         fence_proxy_async();
         mbar_arrive(&ready[s]);
@@ -351,12 +363,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   }
 }
 
-// x_lo = x - trunc_tf32(x) for a whole tensor (constant operands, once at load).
-__global__ void tf32_remainder_kernel(const float* __restrict__ x, float* __restrict__ lo, int64_t n) {
+// hi / lo split of a whole tensor (constant operands, once at load).
+__global__ void tf32_split_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                  float* __restrict__ lo, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const float v = __ldg(x + i);
-    lo[i] = __fsub_rn(v, __uint_as_float(__float_as_uint(v) & 0xFFFFE000u));
+    const float h = round_tf32(v);
+    hi[i] = h;
+    lo[i] = round_tf32(__fsub_rn(v, h));
   }
 }
 
@@ -473,9 +488,9 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
 #undef AC_TC
 }
 
-cudaError_t launch_tf32_remainder(const float* x, float* lo, int64_t n, cudaStream_t st) {
+cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st) {
   if (n == 0) return cudaSuccess;
-  tf32_remainder_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, lo, n);
+  tf32_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, hi, lo, n);
   return cudaGetLastError();
 }
 

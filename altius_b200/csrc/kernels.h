@@ -123,7 +123,8 @@ struct GemmParams {
   int64_t batch;
   const float* a; int64_t lda; int64_t stride_a; int trans_a;
   const float* b; int64_t ldb; int64_t stride_b; int trans_b;
-  const float* b_lo;        // tensor-core path only: x - trunc_tf32(x) of B, same layout; or null
+  const float* b_lo;        // tensor-core path only: when set, `b` holds the TF32-rounded values of
+                            // B and `b_lo` the rounded remainders, same layout; or null
   float* c; int64_t ldc; int64_t stride_c;
   float alpha;
   float beta;               // applied to c_in (may alias c); 0: c_in not read
@@ -143,7 +144,7 @@ cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
 // `err_word` (device memory) receives a non-zero code if a bounded wait expired.
 bool gemm_tc_supported(const GemmParams& p);
 cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStream_t st);
-// lo[i] = x[i] - (x[i] truncated to TF32)
-cudaError_t launch_tf32_remainder(const float* x, float* lo, int64_t n, cudaStream_t st);
+// hi[i] = rn_tf32(x[i]); lo[i] = rn_tf32(x[i] - hi[i])
+cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st);
 
 }  // namespace ac

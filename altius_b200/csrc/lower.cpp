@@ -439,13 +439,15 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     }
   }
   if (tc && mode != 2 && em.c.val(b_use).is_const) {
-    // x - trunc_tf32(x) of a constant rhs, prepared once.
+    // TF32 hi / lo split of a constant rhs, prepared once.
     const int64_t cnt = em.c.val(b_use).numel();
+    const int hi = new_value(em.c, cnt, true);
     b_lo = new_value(em.c, cnt, true);
-    const int src = b_use, dst = b_lo;
-    em.add("weight_tf32_remainder", op, {src}, {dst}, 8.0 * cnt, 0, [=](cudaStream_t st) {
-      return launch_tf32_remainder(s->fptr(src), s->fptr_mut(dst), cnt, st);
+    const int src = b_use, lo = b_lo;
+    em.add("weight_tf32_split", op, {src}, {hi, lo}, 12.0 * cnt, 0, [=](cudaStream_t st) {
+      return launch_tf32_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), cnt, st);
     });
+    b_use = hi;
   }
   const int bsrc = b_use;
   std::vector<int> reads = {a, bsrc, b_lo, c_in, bias_n, bias_m, res};

@@ -1,0 +1,67 @@
+"""Per-kernel microbenchmarks through the session's C ABI.
+
+    python -m altius_b200.kernel_bench gemm 6304 768 2304 [--mode 0|1|2] [--iters 10]
+    python -m altius_b200.kernel_bench micrograph [--batch 64] [--no-fuse]
+
+Builds a one-node (or micrograph) session with per-kernel CUDA-event profiling
+and prints, per kernel kind, the mean device time and the achieved algorithmic
+TFLOP/s or GB/s. Inputs live on the device; the weight of `gemm` is a constant
+(the form the models have). Used for the ncu captures under profiles/.
+"""
+import argparse
+import json
+import sys
+
+import numpy as np
+
+from . import configs, ir
+from .session import CudaSessionBuilder
+
+
+def _run(model, feeds, mode, fuse, iters):
+    import torch
+    sess = (CudaSessionBuilder(model).with_gemm_mode(mode).with_fusion(fuse)
+            .with_profiling_enabled(True).build())
+    ins = [torch.from_numpy(np.ascontiguousarray(v)).cuda() for v in feeds]
+    outs = [torch.empty(tuple(shape), dtype=torch.float32, device="cuda") for shape, _ in sess.output_info]
+    for it in range(iters + 2):
+        if it == 2:
+            sess.profile_reset()
+        sess.run_device([t.data_ptr() for t in ins], [t.data_ptr() for t in outs])
+    rows = {}
+    for kind, p in sess.profile().items():
+        us = 1e3 * p["total_ms"] / p["launches"]
+        rows[kind] = {"us": round(us, 2), "launches": p["launches"] // iters,
+                      "GBps": round(p["bytes"] / p["launches"] / us / 1e3, 1),
+                      "TFLOPs": round(p["flops"] / p["launches"] / us / 1e6, 2)}
+    sess.close()
+    return rows
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "micrograph"])
+    ap.add_argument("dims", nargs="*", type=int)
+    ap.add_argument("--mode", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--no-fuse", action="store_true")
+    a = ap.parse_args(argv)
+    rng = np.random.default_rng(0)
+    if a.what == "gemm":
+        m, k, n = a.dims
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        w = (0.02 * rng.standard_normal((k, n))).astype(np.float32)
+        g = ir.Graph()
+        xi = g.add_input("x", x.shape)
+        out = g.op("MatMul", xi, g.new_init(w))
+        g.outputs.append(out)
+        rows = _run(ir.Model(g, 13), [x], a.mode, True, a.iters)
+    else:
+        model, feeds = configs.micrograph(batch=a.batch)
+        rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters)
+    print(json.dumps(rows, indent=1))
+
+
+if __name__ == "__main__":
+    main()
