@@ -14,7 +14,7 @@
 //
 // One CTA computes one 128 x BN tile:
 //   warp 4      TMA producer: one elected thread issues cp.async.bulk.tensor
-//               loads (128B-swizzled boxes of 32 floats along K) into a ring of
+//               loads (64B-swizzled boxes of 16 floats along K) into a ring of
 //               stages, completion on an mbarrier per stage;
 //   warps 0-3   splitters: rewrite the A tile as x_hi in place and write x_lo
 //               beside it (the same for the B tile unless B is a constant whose
@@ -26,6 +26,8 @@
 // error word, drains, frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.h"
@@ -35,7 +37,7 @@ namespace ac {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 32;                       // floats: one 128-byte swizzle row
+constexpr int BK = 16;                       // floats: one 64-byte swizzle row per tile row
 constexpr int kSplitThreads = 128;
 constexpr int kThreads = 192;
 constexpr uint32_t kWaitLimit = 1u << 24;    // polls before a wait gives up
@@ -126,23 +128,24 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes
-// (32 floats), stored row after row with the 128-byte swizzle: 8-row groups are
-// 1024 bytes apart (stride byte offset), the leading byte offset is unused.
+// Shared-memory matrix descriptor for a K-major tile whose rows are 64 bytes
+// (16 floats), stored row after row with the 64-byte swizzle: 8-row groups are
+// 512 bytes apart (stride byte offset), the leading byte offset is unused.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3FFF);        // start address
   d |= (uint64_t)1 << 16;                        // leading byte offset (ignored for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)((8 * BK * 4) >> 4) << 32;      // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                        // descriptor version for this architecture
-  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+  d |= (uint64_t)4 << 61;                        // 64-byte swizzle
   return d;
 }
 
+// Round to nearest (ties away from zero) to TF32's 10 mantissa bits, on the
+// integer ALU: cvt.rna.tf32.f32 gives the same bits but issues on the
+// quarter-rate conversion pipe.
 __device__ __forceinline__ float round_tf32(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 // hi = rn_tf32(x), lo = rn_tf32(x - hi), for 4 packed floats.
 __device__ __forceinline__ void tf32_split(float4 v, float4& hi, float4& lo) {
@@ -152,20 +155,187 @@ __device__ __forceinline__ void tf32_split(float4 v, float4& hi, float4& lo) {
   hi.w = round_tf32(v.w); lo.w = round_tf32(__fsub_rn(v.w, hi.w));
 }
 
+
+// Epilogue of one warp's 32 rows. The accumulator chunk arrives with one thread
+// per row (32 columns each); it goes through a 4 KB shared-memory tile so that
+// each group of 8 lanes then owns one row's 128 contiguous bytes: global loads
+// and stores are full lines. 16-byte chunks are XOR-swizzled by the row, which
+// keeps both the row-wise writes and the transposed reads free of bank conflicts.
+template <int BN>
+__device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
+                                              int warp, int lane, int m0, int n0, int bz) {
+      // The stage ring is idle now (every MMA has completed): each warp uses 4 KB
+      // of it to turn its accumulator chunk (one thread = one row of 32 columns)
+      // into row-contiguous float4s, so that global loads and stores are full
+      // 128-byte lines. 16-byte chunks are XOR-swizzled by the row to keep both
+      // the row-wise writes and the transposed reads free of bank conflicts.
+      float* c = ep.c + (long long)bz * ep.sc;
+      const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
+      const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
+      const bool vec_ok = (ep.ldc % 4) == 0 && ((reinterpret_cast<uintptr_t>(c) & 15) == 0) &&
+                          (!cin || ((ep.ldcin % 4) == 0 && (reinterpret_cast<uintptr_t>(cin) & 15) == 0)) &&
+                          (!res || ((ep.ldres % 4) == 0 && (reinterpret_cast<uintptr_t>(res) & 15) == 0)) &&
+                          (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
+      const int c4 = lane & 7;             // float4 column within the 32-column chunk
+      const int rsub = lane >> 3;          // row within a group of 4
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        const int col0 = n0 + cc * 32;
+        if (col0 >= ep.n) break;           // uniform across the warp
+        uint32_t v[32];
+        tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          stage[lane * 8 + (j ^ (lane & 7))] =
+              make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        __syncwarp();
+        const int col = col0 + 4 * c4;
+        float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ep.bias_n) {
+          if (vec_ok && col + 3 < ep.n) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+          else {
+            if (col < ep.n) bn.x = __ldg(ep.bias_n + col);
+            if (col + 1 < ep.n) bn.y = __ldg(ep.bias_n + col + 1);
+            if (col + 2 < ep.n) bn.z = __ldg(ep.bias_n + col + 2);
+            if (col + 3 < ep.n) bn.w = __ldg(ep.bias_n + col + 3);
+          }
+          if (ep.bias_scale != 1.f) {
+            bn.x = __fmul_rn(ep.bias_scale, bn.x); bn.y = __fmul_rn(ep.bias_scale, bn.y);
+            bn.z = __fmul_rn(ep.bias_scale, bn.z); bn.w = __fmul_rn(ep.bias_scale, bn.w);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rl = 4 * i + rsub;                 // row within the warp's 32
+          const int row = m0 + warp * 32 + rl;
+          const float4 a = stage[rl * 8 + (c4 ^ (rl & 7))];
+          if (row >= ep.m || col >= ep.n) continue;
+          float x[4] = {a.x, a.y, a.z, a.w};
+          const bool full4 = vec_ok && col + 3 < ep.n;
+          float cv[4] = {0.f, 0.f, 0.f, 0.f}, rv[4] = {0.f, 0.f, 0.f, 0.f};
+          if (cin) {
+            if (full4) {
+              const float4 t4 = __ldg(reinterpret_cast<const float4*>(cin + (long long)row * ep.ldcin + col));
+              cv[0] = t4.x; cv[1] = t4.y; cv[2] = t4.z; cv[3] = t4.w;
+            } else {
+              for (int e = 0; e < 4; ++e)
+                if (col + e < ep.n) cv[e] = __ldg(cin + (long long)row * ep.ldcin + col + e);
+            }
+          }
+          if (res) {
+            if (full4) {
+              const float4 t4 = __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col));
+              rv[0] = t4.x; rv[1] = t4.y; rv[2] = t4.z; rv[3] = t4.w;
+            } else {
+              for (int e = 0; e < 4; ++e)
+                if (col + e < ep.n) rv[e] = __ldg(res + (long long)row * ep.ldres + col + e);
+            }
+          }
+          const float bm = ep.bias_m ? (ep.bias_scale == 1.f ? __ldg(ep.bias_m + row)
+                                                             : __fmul_rn(ep.bias_scale, __ldg(ep.bias_m + row)))
+                                     : 0.f;
+          const float bnv[4] = {bn.x, bn.y, bn.z, bn.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float y = x[e];
+            if (ep.alpha != 1.f) y = __fmul_rn(ep.alpha, y);
+            if (cin) y = __fadd_rn(ep.beta == 1.f ? cv[e] : __fmul_rn(ep.beta, cv[e]), y);
+            if (ep.bias_n) y = __fadd_rn(y, bnv[e]);
+            if (ep.bias_m) y = __fadd_rn(y, bm);
+            y = apply_act(ep.act, y, ep.act_alpha, ep.act_beta);
+            if (res) y = __fadd_rn(y, rv[e]);
+            x[e] = y;
+          }
+          float* dst = c + (long long)row * ep.ldc + col;
+          if (full4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (col + e < ep.n) dst[e] = x[e];
+          }
+        }
+      }
+    }
+
+// Same data path for the common epilogues (alpha 1, no C input, no row bias,
+// everything 16-byte aligned, N a multiple of 4), with the options fixed at
+// compile time and the eight rows of a chunk processed as independent streams.
+template <int BN, int ACT, bool HAS_BIAS, bool HAS_RES>
+__device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
+                                              int warp, int lane, int m0, int n0, int bz) {
+  float* c = ep.c + (long long)bz * ep.sc;
+  const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
+  const int c4 = lane & 7, rsub = lane >> 3;
+  const int row_base = m0 + warp * 32 + rsub;
+#pragma unroll 1
+  for (int cc = 0; cc < BN / 32; ++cc) {
+    const int col0 = n0 + cc * 32;
+    if (col0 >= ep.n) break;
+    uint32_t v[32];
+    tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      stage[lane * 8 + (j ^ (lane & 7))] =
+          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+    __syncwarp();
+    const int col = col0 + 4 * c4;
+    const bool col_ok = col < ep.n;   // n % 4 == 0: the whole float4 is in range
+    float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (HAS_BIAS && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+    float4 a[8], r[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rl = 4 * i + rsub;
+      a[i] = stage[rl * 8 + (c4 ^ (rl & 7))];
+      if (HAS_RES) {
+        const int row = row_base + 4 * i;
+        r[i] = (col_ok && row < ep.m)
+                   ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 x = a[i];
+      if (HAS_BIAS) {
+        x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
+        x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
+      }
+      if (ACT != ACT_NONE) {
+        x.x = apply_act(ACT, x.x, 0.f, 0.f); x.y = apply_act(ACT, x.y, 0.f, 0.f);
+        x.z = apply_act(ACT, x.z, 0.f, 0.f); x.w = apply_act(ACT, x.w, 0.f, 0.f);
+      }
+      if (HAS_RES) {
+        x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
+        x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
+      }
+      const int row = row_base + 4 * i;
+      if (col_ok && row < ep.m) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
+    }
+  }
+}
+
 template <int BN>
 struct TcSmem {
   static constexpr int kABytes = BM * BK * 4;
   static constexpr int kBBytes = BN * BK * 4;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+  // Sized so that two CTAs are co-resident on an SM (<= ~113 KB each): the
+  // epilogue and pipeline fill of one overlap the main loop of the other.
   static constexpr int kStages = BN >= 256 ? 2 : (BN >= 128 ? 3 : 4);
   static constexpr int kDynBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(kDynBytes <= 113 * 1024, "two CTAs per SM");
 };
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, int num_kb, int b_batched,
-               int* err) {
+               int* err, int probe) {
   using L = TcSmem<BN>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -180,6 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
+  long long t_start = clock64(), t_setup = 0, t_main = 0, t_epi = 0;
 
   auto a_raw = [&](int s) { return smem + s * L::kStageBytes; };
   auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kABytes; };
@@ -206,13 +377,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  t_setup = clock64();
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const uint32_t bytes = L::kABytes + L::kBBytes + (MODE == TC_3X_BLO_TMA ? L::kBBytes : 0);
       const int bzb = b_batched ? bz : 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      for (int kb = 0; kb < num_kb && !(probe & 1); ++kb) {
         const int s = kb % S;
         const uint32_t ph = (kb / S) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; break; }
@@ -232,7 +404,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % S;
         const uint32_t ph = (kb / S) & 1;
-        ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
+        if (!(probe & 1)) ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
         if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
         tc_fence_after();
         const uint64_t da = make_smem_desc(smem_u32(a_raw(s)));
@@ -240,7 +412,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint64_t db = make_smem_desc(smem_u32(b_raw(s)));
         const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)));
 #pragma unroll
-        for (int kk = 0; kk < BK / 8; ++kk) {
+        for (int kk = 0; kk < BK / 8 && !(probe & 2); ++kk) {
           const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats = 32 bytes along K
           const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
           if (MODE == TC_1X) {
@@ -260,7 +432,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int t = threadIdx.x;  // 0..127
     bool ok = true;
     if (MODE != TC_1X) {
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
+      for (int kb = 0; kb < num_kb && ok && !(probe & 1); ++kb) {
         const int s = kb % S;
         const uint32_t ph = (kb / S) & 1;
         ok = mbar_wait(&full[s], ph);
@@ -292,57 +464,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (ok) ok = mbar_wait(accfull, 0);
     if (!ok) { atomicExch(err, 4); *abort_flag = 1; }
     tc_fence_after();
-    if (ok && *abort_flag == 0) {
-      const int row = m0 + warp * 32 + lane;
-      float* c = ep.c + (long long)bz * ep.sc;
-      const float* cin = ep.cin ? ep.cin + (long long)bz * ep.scin : nullptr;
-      const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
-      const bool vec_ok = (ep.ldc % 4) == 0 && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
-      const float bm = (ep.bias_m && row < ep.m)
-                           ? (ep.bias_scale == 1.f ? __ldg(ep.bias_m + row)
-                                                   : __fmul_rn(ep.bias_scale, __ldg(ep.bias_m + row)))
-                           : 0.f;
-#pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
-        const int col0 = n0 + cc * 32;
-        if (col0 >= ep.n) break;                 // uniform across the warp
-        uint32_t v[32];
-        tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
-        if (row < ep.m) {
-          float o[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            float x = __uint_as_float(v[j]);
-            if (col < ep.n) {
-              if (ep.alpha != 1.f) x = __fmul_rn(ep.alpha, x);
-              if (cin && ep.beta != 0.f) {
-                const float cv = __ldg(cin + (long long)row * ep.ldcin + col);
-                x = __fadd_rn(ep.beta == 1.f ? cv : __fmul_rn(ep.beta, cv), x);
-              }
-              if (ep.bias_n) {
-                const float bv = __ldg(ep.bias_n + col);
-                x = __fadd_rn(x, ep.bias_scale == 1.f ? bv : __fmul_rn(ep.bias_scale, bv));
-              }
-              if (ep.bias_m) x = __fadd_rn(x, bm);
-              x = apply_act(ep.act, x, ep.act_alpha, ep.act_beta);
-              if (res) x = __fadd_rn(x, __ldg(res + (long long)row * ep.ldres + col));
-            }
-            o[j] = x;
-          }
-          float* crow = c + (long long)row * ep.ldc + col0;
-          if (vec_ok && col0 + 32 <= ep.n) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4*>(crow + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < ep.n) crow[j] = o[j];
-          }
-        }
+    t_main = clock64();
+    if (ok && *abort_flag == 0 && !(probe & 4)) {
+      float4* stage = reinterpret_cast<float4*>(smem + warp * 4096);
+      const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
+                          ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 &&
+                          ((reinterpret_cast<uintptr_t>(ep.c + (long long)bz * ep.sc) & 15) == 0) &&
+                          (!ep.res || ((ep.ldres % 4) == 0 &&
+                                       (reinterpret_cast<uintptr_t>(ep.res + (long long)bz * ep.sres) & 15) == 0)) &&
+                          (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
+      const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
+      switch (key) {
+        case 0: epilogue_fast<BN, ACT_NONE, false, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        case 1: epilogue_fast<BN, ACT_NONE, true, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        case 2: epilogue_fast<BN, ACT_NONE, false, true>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        case 3: epilogue_fast<BN, ACT_NONE, true, true>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        case (ACT_GELU << 2) | 1: epilogue_fast<BN, ACT_GELU, true, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        case (ACT_RELU << 2) | 1: epilogue_fast<BN, ACT_RELU, true, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        default: epilogue_generic<BN>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
       }
     }
+    t_epi = clock64();
     tc_fence_before();
   }
 
@@ -357,6 +499,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   }
   __syncthreads();
+  if ((probe & 32) && threadIdx.x == 0 && (blockIdx.x + blockIdx.y * gridDim.x) % 97 == 0)
+    printf("cta %d,%d setup %lld main %lld epi %lld teardown %lld\n", blockIdx.x, blockIdx.y,
+           t_setup - t_start, t_main - t_setup, t_epi - t_main, clock64() - t_epi);
   if (warp == 5) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN));
@@ -394,7 +539,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 3-D map over a row-major [batch, rows, k] f32 tensor: box = 32 floats of K x box_rows rows.
+// 3-D map over a row-major [batch, rows, k] f32 tensor: box = BK floats of K x box_rows rows.
 bool make_map(CUtensorMap* map, const float* base, int64_t k, int64_t rows, int64_t batch, int64_t ld,
               int64_t batch_stride, int box_rows) {
   EncodeTiledFn fn = encode_fn();
@@ -403,9 +548,10 @@ bool make_map(CUtensorMap* map, const float* base, int64_t k, int64_t rows, int6
   cuuint64_t strides[2] = {(cuuint64_t)ld * 4,
                            (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * 4};
   cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
+  static_assert(BK * 4 == 64, "box rows are one 64-byte swizzle span");
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -419,10 +565,15 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::kDynBytes);
     if (e != cudaSuccess) return e;
+    // Ask for the largest shared-memory carve-out so that two CTAs fit on an SM.
+    e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
     attr_set = true;
   }
   dim3 grid((unsigned)((ep.n + BN - 1) / BN), (unsigned)((ep.m + BM - 1) / BM), (unsigned)batch);
-  gemm_tc_kernel<BN, MODE><<<grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, num_kb, b_batched, err);
+  static const int probe = std::getenv("ALTIUS_PROBE") ? atoi(std::getenv("ALTIUS_PROBE")) : 0;
+  gemm_tc_kernel<BN, MODE><<<grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, num_kb, b_batched, err, probe);
   return cudaGetLastError();
 }
 

@@ -15,6 +15,7 @@
 // What each node computes follows `run_node`'s dispatch
 // (crates/session_interpreter/src/session.rs:168-249).
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <set>
 
@@ -438,7 +439,13 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       tc = false;
     }
   }
-  if (tc && mode != 2 && em.c.val(b_use).is_const) {
+  // Debug toggle: ALTIUS_CUDA_SPLIT_B_IN_KERNEL=1 splits constant weights inside the
+  // GEMM kernel too (less L2 traffic, more shared-memory traffic) instead of at load.
+  static const bool split_b_in_kernel = [] {
+    const char* e = std::getenv("ALTIUS_CUDA_SPLIT_B_IN_KERNEL");
+    return e && e[0] == '1';
+  }();
+  if (tc && mode != 2 && em.c.val(b_use).is_const && !split_b_in_kernel) {
     // TF32 hi / lo split of a constant rhs, prepared once.
     const int64_t cnt = em.c.val(b_use).numel();
     const int hi = new_value(em.c, cnt, true);
