@@ -12,22 +12,23 @@
 // with fp32 accumulation in TMEM; the dropped a_lo*b_lo term and the rounding
 // of x_lo are each below 2^-22 relative.
 //
-// One CTA computes one 128 x BN tile:
-//   warp 4      TMA producer: one elected thread issues cp.async.bulk.tensor
+// Persistent CTAs (one per SM) walk the 128 x BN output tiles:
+//   warp 8      TMA producer: one elected thread issues cp.async.bulk.tensor
 //               loads (64B-swizzled boxes of 16 floats along K) into a ring of
 //               stages, completion on an mbarrier per stage;
 //   warps 0-3   splitters: rewrite the A tile as x_hi in place and write x_lo
 //               beside it (the same for the B tile unless B is a constant whose
-//               split was prepared at load time and arrives by TMA), then
-//               the epilogue: tcgen05.ld of the accumulator, bias / activation
-//               / residual, global stores;
-//   warp 5      one thread issues the tcgen05.mma stream and tcgen05.commit.
+//               split was prepared at load time and arrives by TMA);
+//   warp 9      one thread issues the tcgen05.mma stream and tcgen05.commit into
+//               one of two accumulators in tensor memory;
+//   warps 4-7   epilogue of the other accumulator: tcgen05.ld, a shared-memory
+//               transpose to row-contiguous float4s, bias / activation /
+//               residual, full-line global stores.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the
 // error word, drains, frees its tensor memory and returns.
 #include <cuda.h>
 
-#include <cstdio>
-#include <cstdlib>
+#include <algorithm>
 #include <mutex>
 
 #include "kernels.h"
@@ -38,8 +39,9 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;                       // floats: one 64-byte swizzle row per tile row
-constexpr int kSplitThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kSplitWarps = 4;
+constexpr int kSplitThreads = kSplitWarps * 32;
+constexpr int kThreads = (kSplitWarps + 6) * 32;   // + 4 epilogue warps, TMA warp, MMA warp
 constexpr uint32_t kWaitLimit = 1u << 24;    // polls before a wait gives up
 
 enum TcMode { TC_3X_BLO_TMA = 0, TC_3X_SPLIT_B = 1, TC_1X = 2 };
@@ -164,11 +166,6 @@ __device__ __forceinline__ void tf32_split(float4 v, float4& hi, float4& lo) {
 template <int BN>
 __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
                                               int warp, int lane, int m0, int n0, int bz) {
-      // The stage ring is idle now (every MMA has completed): each warp uses 4 KB
-      // of it to turn its accumulator chunk (one thread = one row of 32 columns)
-      // into row-contiguous float4s, so that global loads and stores are full
-      // 128-byte lines. 16-byte chunks are XOR-swizzled by the row to keep both
-      // the row-wise writes and the transposed reads free of bank conflicts.
       float* c = ep.c + (long long)bz * ep.sc;
       const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
       const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
@@ -323,38 +320,45 @@ template <int BN>
 struct TcSmem {
   static constexpr int kABytes = BM * BK * 4;
   static constexpr int kBBytes = BN * BK * 4;
-  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
-  // Sized so that two CTAs are co-resident on an SM (<= ~113 KB each): the
-  // epilogue and pipeline fill of one overlap the main loop of the other.
-  static constexpr int kStages = BN >= 256 ? 2 : (BN >= 128 ? 3 : 4);
-  static constexpr int kDynBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
-  static_assert(kDynBytes <= 113 * 1024, "two CTAs per SM");
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;   // hi + lo of both operands
+  static constexpr int kStages = (200 * 1024) / kStageBytes;      // 4 (BN 256), 6 (BN 128), 8 (BN 64)
+  static constexpr int kEpiBytes = 4 * 4096;                      // one 4 KB transpose tile per epilogue warp
+  static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
+  static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
 };
 
+// Persistent kernel: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x +
+// gridDim.x, ... The accumulator is double-buffered in tensor memory, so the
+// epilogue of one tile overlaps the main loop of the next.
+//   warps 0-3   splitters (hi/lo of the A tile, and of B unless it arrives split)
+//   warps 4-7   epilogue (warp w owns TMEM lanes 32*(w-4) .. +31)
+//   warp  8     TMA producer (one thread)
+//   warp  9     MMA issuer (one thread); allocates and frees tensor memory
 template <int BN, int MODE>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, int num_kb, int b_batched,
-               int* err, int probe) {
+               int tiles_m, int tiles_n, int num_tiles, int* err) {
   using L = TcSmem<BN>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * L::kStageBytes);
-  uint64_t* full = bars;            // TMA bytes landed
-  uint64_t* ready = bars + S;       // remainders written
-  uint64_t* empty = bars + 2 * S;   // MMAs that read the stage have completed
-  uint64_t* accfull = bars + 3 * S; // accumulator complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 1);
+  uint8_t* epi_smem = smem + S * L::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + L::kEpiBytes);
+  uint64_t* full = bars;               // TMA bytes landed
+  uint64_t* ready = bars + S;          // hi/lo written
+  uint64_t* empty = bars + 2 * S;      // MMAs that read the stage have completed
+  uint64_t* acc_full = bars + 3 * S;   // [2] accumulator complete
+  uint64_t* acc_empty = bars + 3 * S + 2;  // [2] accumulator drained by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
-  long long t_start = clock64(), t_setup = 0, t_main = 0, t_epi = 0;
+  constexpr uint32_t kTmemCols = 2 * BN;   // 128, 256 or 512: a power of two
 
-  auto a_raw = [&](int s) { return smem + s * L::kStageBytes; };
+  auto a_hi = [&](int s) { return smem + s * L::kStageBytes; };
   auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kABytes; };
-  auto b_raw = [&](int s) { return smem + s * L::kStageBytes + 2 * L::kABytes; };
+  auto b_hi = [&](int s) { return smem + s * L::kStageBytes + 2 * L::kABytes; };
   auto b_lo = [&](int s) { return smem + s * L::kStageBytes + 2 * L::kABytes + L::kBBytes; };
 
   if (threadIdx.x == 0) {
@@ -363,134 +367,162 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       mbar_init(&ready[s], kSplitThreads);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accfull, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);     // one arrival per epilogue warp
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == kSplitWarps + 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"((uint32_t)BN));
+                 "r"(kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  t_setup = clock64();
 
-  if (warp == 4) {
+  if (warp == kSplitWarps + 4) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const uint32_t bytes = L::kABytes + L::kBBytes + (MODE == TC_3X_BLO_TMA ? L::kBBytes : 0);
-      const int bzb = b_batched ? bz : 0;
-      for (int kb = 0; kb < num_kb && !(probe & 1); ++kb) {
-        const int s = kb % S;
-        const uint32_t ph = (kb / S) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; break; }
-        mbar_arrive_expect_tx(&full[s], bytes);
-        tma_load_3d(a_raw(s), &tm_a, &full[s], kb * BK, m0, bz);
-        tma_load_3d(b_raw(s), &tm_b, &full[s], kb * BK, n0, bzb);
-        if (MODE == TC_3X_BLO_TMA) tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * BK, n0, bzb);
+      int it = 0;   // running K-block count over all of this CTA's tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+        const int bzb = b_batched ? bz : 0;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
+          mbar_arrive_expect_tx(&full[s], bytes);
+          tma_load_3d(a_hi(s), &tm_a, &full[s], kb * BK, tm * BM, bz);
+          tma_load_3d(b_hi(s), &tm_b, &full[s], kb * BK, tn * BN, bzb);
+          if (MODE == TC_3X_BLO_TMA) tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * BK, tn * BN, bzb);
+        }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kSplitWarps + 5) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       // Instruction descriptor: fp32 accumulator, TF32 A and B, both K-major, N = BN, M = 128.
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
+      int it = 0, ti = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % S;
-        const uint32_t ph = (kb / S) & 1;
-        if (!(probe & 1)) ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
-        if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++ti) {
+        const int ab = ti & 1;
+        // The epilogue must have drained this accumulator (two tiles ago).
+        if (!mbar_wait(&acc_empty[ab], ((ti >> 1) & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
         tc_fence_after();
-        const uint64_t da = make_smem_desc(smem_u32(a_raw(s)));
-        const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)));
-        const uint64_t db = make_smem_desc(smem_u32(b_raw(s)));
-        const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)));
+        const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
+          if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_u32(a_hi(s)));
+          const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)));
+          const uint64_t db = make_smem_desc(smem_u32(b_hi(s)));
+          const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)));
 #pragma unroll
-        for (int kk = 0; kk < BK / 8 && !(probe & 2); ++kk) {
-          const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats = 32 bytes along K
-          const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-          if (MODE == TC_1X) {
-            tc_mma_tf32(tmem_base, da + off, db + off, idesc, acc);
-          } else {
-            tc_mma_tf32(tmem_base, dal + off, db + off, idesc, acc);   // a_lo * b_hi
-            tc_mma_tf32(tmem_base, da + off, dbl + off, idesc, 1u);    // a_hi * b_lo
-            tc_mma_tf32(tmem_base, da + off, db + off, idesc, 1u);     // a_hi * b_hi
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats = 32 bytes along K
+            const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+            if (MODE == TC_1X) {
+              tc_mma_tf32(d_tmem, da + off, db + off, idesc, acc);
+            } else {
+              tc_mma_tf32(d_tmem, dal + off, db + off, idesc, acc);   // a_lo * b_hi
+              tc_mma_tf32(d_tmem, da + off, dbl + off, idesc, 1u);    // a_hi * b_lo
+              tc_mma_tf32(d_tmem, da + off, db + off, idesc, 1u);     // a_hi * b_hi
+            }
           }
+          tc_commit(&empty[s]);
         }
-        tc_commit(&empty[s]);
+        if (ok) tc_commit(&acc_full[ab]);
       }
-      tc_commit(accfull);
+    }
+  } else if (warp < kSplitWarps) {
+    // ---------------- splitters ----------------
+    if (MODE != TC_1X) {
+      const int t0 = threadIdx.x;  // 0 .. kSplitThreads-1
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          ok = mbar_wait(&full[s], ph);
+          if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
+          float4* src = reinterpret_cast<float4*>(a_hi(s));
+          float4* dst = reinterpret_cast<float4*>(a_lo(s));
+#pragma unroll
+          for (int i = 0; i < L::kABytes / 16 / kSplitThreads; ++i) {
+            float4 hi, lo;
+            tf32_split(src[i * kSplitThreads + t0], hi, lo);
+            src[i * kSplitThreads + t0] = hi;
+            dst[i * kSplitThreads + t0] = lo;
+          }
+          if (MODE == TC_3X_SPLIT_B) {
+            float4* sb = reinterpret_cast<float4*>(b_hi(s));
+            float4* dbp = reinterpret_cast<float4*>(b_lo(s));
+#pragma unroll
+            for (int i = 0; i < L::kBBytes / 16 / kSplitThreads; ++i) {
+              float4 hi, lo;
+              tf32_split(sb[i * kSplitThreads + t0], hi, lo);
+              sb[i * kSplitThreads + t0] = hi;
+              dbp[i * kSplitThreads + t0] = lo;
+            }
+          }
+          fence_proxy_async();
+          mbar_arrive(&ready[s]);
+        }
+      }
     }
   } else {
-    // ---------------- splitters, then epilogue (warps 0-3) ----------------
-    const int t = threadIdx.x;  // 0..127
-    bool ok = true;
-    if (MODE != TC_1X) {
-      for (int kb = 0; kb < num_kb && ok && !(probe & 1); ++kb) {
-        const int s = kb % S;
-        const uint32_t ph = (kb / S) & 1;
-        ok = mbar_wait(&full[s], ph);
-        if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
-        float4* src = reinterpret_cast<float4*>(a_raw(s));
-        float4* dst = reinterpret_cast<float4*>(a_lo(s));
-#pragma unroll
-        for (int i = 0; i < L::kABytes / 16 / kSplitThreads; ++i) {
-          float4 hi, lo;
-          tf32_split(src[i * kSplitThreads + t], hi, lo);
-          src[i * kSplitThreads + t] = hi;
-          dst[i * kSplitThreads + t] = lo;
-        }
-        if (MODE == TC_3X_SPLIT_B) {
-          float4* sb = reinterpret_cast<float4*>(b_raw(s));
-          float4* dbp = reinterpret_cast<float4*>(b_lo(s));
-#pragma unroll
-          for (int i = 0; i < L::kBBytes / 16 / kSplitThreads; ++i) {
-            float4 hi, lo;
-            tf32_split(sb[i * kSplitThreads + t], hi, lo);
-            sb[i * kSplitThreads + t] = hi;
-            dbp[i * kSplitThreads + t] = lo;
-          }
-        }
-        fence_proxy_async();
-        mbar_arrive(&ready[s]);
-      }
-    }
-    if (ok) ok = mbar_wait(accfull, 0);
-    if (!ok) { atomicExch(err, 4); *abort_flag = 1; }
-    tc_fence_after();
-    t_main = clock64();
-    if (ok && *abort_flag == 0 && !(probe & 4)) {
-      float4* stage = reinterpret_cast<float4*>(smem + warp * 4096);
-      const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
-                          ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 &&
-                          ((reinterpret_cast<uintptr_t>(ep.c + (long long)bz * ep.sc) & 15) == 0) &&
-                          (!ep.res || ((ep.ldres % 4) == 0 &&
-                                       (reinterpret_cast<uintptr_t>(ep.res + (long long)bz * ep.sres) & 15) == 0)) &&
-                          (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
-      const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
+    // ---------------- epilogue (warps 4-7) ----------------
+    const int q = warp - kSplitWarps;   // TMEM lane quarter (kSplitWarps is a multiple of 4)
+    float4* stage = reinterpret_cast<float4*>(epi_smem + q * 4096);
+    const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
+                        ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
+                        (!ep.res || ((ep.ldres % 4) == 0 && (ep.sres % 4) == 0 &&
+                                     (reinterpret_cast<uintptr_t>(ep.res) & 15) == 0)) &&
+                        (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
+    const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
+    int ti = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++ti) {
+      const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+      const int ab = ti & 1;
+      if (!mbar_wait(&acc_full[ab], (ti >> 1) & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
+      tc_fence_after();
+      const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
+      const int m0 = tm * BM, n0 = tn * BN;
       switch (key) {
-        case 0: epilogue_fast<BN, ACT_NONE, false, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
-        case 1: epilogue_fast<BN, ACT_NONE, true, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
-        case 2: epilogue_fast<BN, ACT_NONE, false, true>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
-        case 3: epilogue_fast<BN, ACT_NONE, true, true>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
-        case (ACT_GELU << 2) | 1: epilogue_fast<BN, ACT_GELU, true, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
-        case (ACT_RELU << 2) | 1: epilogue_fast<BN, ACT_RELU, true, false>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
-        default: epilogue_generic<BN>(ep, stage, tmem_base, warp, lane, m0, n0, bz); break;
+        case 0: epilogue_fast<BN, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 1: epilogue_fast<BN, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 2: epilogue_fast<BN, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 3: epilogue_fast<BN, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case (ACT_GELU << 2) | 1: epilogue_fast<BN, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case (ACT_RELU << 2) | 1: epilogue_fast<BN, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        default: epilogue_generic<BN>(ep, stage, acc, q, lane, m0, n0, bz); break;
       }
+      // Every tcgen05.ld of this warp has completed (each is followed by
+      // wait::ld): hand the accumulator back to the MMA warp.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
     }
-    t_epi = clock64();
-    tc_fence_before();
   }
 
   // ---------------- teardown ----------------
+  tc_fence_before();
   __syncthreads();
-  if (*abort_flag != 0 && warp == 4 && lane == 0) {
+  if (*abort_flag != 0 && warp == kSplitWarps + 4 && lane == 0) {
     // Give copies that may still be in flight a bounded time to land before the
     // shared memory is released.
     for (int s = 0; s < S; ++s) {
@@ -499,12 +531,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   }
   __syncthreads();
-  if ((probe & 32) && threadIdx.x == 0 && (blockIdx.x + blockIdx.y * gridDim.x) % 97 == 0)
-    printf("cta %d,%d setup %lld main %lld epi %lld teardown %lld\n", blockIdx.x, blockIdx.y,
-           t_setup - t_start, t_main - t_setup, t_epi - t_main, clock64() - t_epi);
-  if (warp == 5) {
+  if (warp == kSplitWarps + 5) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
   }
 }
 
@@ -555,6 +584,16 @@ bool make_map(CUtensorMap* map, const float* base, int64_t k, int64_t rows, int6
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int MODE>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mbl,
                       const TcEpilogue& ep, int num_kb, int b_batched, int64_t batch, int* err,
@@ -565,15 +604,14 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::kDynBytes);
     if (e != cudaSuccess) return e;
-    // Ask for the largest shared-memory carve-out so that two CTAs fit on an SM.
-    e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
-    if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  dim3 grid((unsigned)((ep.n + BN - 1) / BN), (unsigned)((ep.m + BM - 1) / BM), (unsigned)batch);
-  static const int probe = std::getenv("ALTIUS_PROBE") ? atoi(std::getenv("ALTIUS_PROBE")) : 0;
-  gemm_tc_kernel<BN, MODE><<<grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, num_kb, b_batched, err, probe);
+  const int tiles_n = (ep.n + BN - 1) / BN, tiles_m = (ep.m + BM - 1) / BM;
+  const long long num_tiles = (long long)tiles_n * tiles_m * batch;
+  if (num_tiles > (1ll << 30)) return cudaErrorInvalidValue;
+  const int grid = (int)std::min<long long>(num_tiles, sm_count());
+  gemm_tc_kernel<BN, MODE><<<grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, num_kb, b_batched, tiles_m,
+                                                                 tiles_n, (int)num_tiles, err);
   return cudaGetLastError();
 }
 
@@ -591,14 +629,20 @@ bool gemm_tc_supported(const GemmParams& q) {
 }
 
 int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch) {
-  // Fewest waves over 148 SMs, weighted by the tile's cost; ties go to the wider tile.
+  // Rounds of the persistent CTAs (one per SM) times the cost of one tile. The
+  // cost is the MMA time of the tile in units of 2 clocks per K-step, bounded
+  // below by the shared-memory traffic of the operands (narrow tiles re-read
+  // A), plus a small fixed part; ties go to the wider tile.
   const int cands[3] = {256, 128, 64};
+  const double tile_cost[3] = {134.0, 72.0, 56.0};
+  const int sms = sm_count();
   int best = 256;
   double best_cost = 1e300;
-  for (int bn : cands) {
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cands[i];
     const int64_t tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn) * batch;
-    const double waves = (double)((tiles + 147) / 148);
-    const double cost = waves * (bn + 40);   // + fixed per-tile overhead in the same unit
+    const double rounds = (double)((tiles + sms - 1) / sms);
+    const double cost = rounds * tile_cost[i];
     if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
   }
   return best;
