@@ -65,7 +65,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                 "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -194,7 +194,7 @@ def micrograph_hbm(device, peaks):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemm-mode", type=int, default=0)
@@ -261,10 +261,14 @@ def main():
     for _ in range(args.warmup):
         sess.run_device(in_ptrs, out_ptrs)
     sampler = ClockSampler(local_rank)
-    barrier()
     sampler.start()
+    time.sleep(0.4)                      # let nvidia-smi start sampling
+    sess.run_device(in_ptrs, out_ptrs)   # and put the GPU under load before the first sample counts
+    barrier()
+    n_before = len(sampler.lines)
     ms = sess.time_device_runs(in_ptrs, out_ptrs, args.steps)
     barrier()
+    sampler.lines = sampler.lines[max(n_before - 1, 0):] if len(sampler.lines) > n_before else sampler.lines[-2:]
     clocks = sampler.stop()
     ms = max_over_ranks(ms)
     value = world * PER_GPU_BATCH * args.steps / (ms * 1e-3)
