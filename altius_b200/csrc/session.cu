@@ -171,6 +171,15 @@ cudaError_t replay(AcSession* s, cudaStream_t st) {
   return cudaSuccess;
 }
 
+}  // namespace
+
+namespace ac {
+// Lets other translation units of the library report through altius_cuda_last_error(NULL).
+void set_thread_error(const std::string& msg) { g_create_error = msg; }
+}  // namespace ac
+
+namespace {
+
 int set_err(AcSession* s, int status, const std::string& msg) {
   if (s) s->err = msg;
   else g_create_error = msg;

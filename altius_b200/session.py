@@ -89,7 +89,7 @@ ABI_SYMBOLS = (
     "altius_cuda_value_info", "altius_cuda_launches_per_run", "altius_cuda_arena_bytes",
     "altius_cuda_schedule", "altius_cuda_profile", "altius_cuda_profile_reset", "altius_cuda_last_error",
     "altius_cuda_destroy", "altius_cuda_host_alloc", "altius_cuda_host_free",
-    "altius_cuda_device_count",
+    "altius_cuda_device_count", "altius_cuda_reduce_max_noalloc",
 )
 
 _lib = None
@@ -131,6 +131,7 @@ def load_library() -> ctypes.CDLL:
     lib.altius_cuda_destroy.restype = None
     lib.altius_cuda_host_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(P)]
     lib.altius_cuda_host_free.argtypes = [P]
+    lib.altius_cuda_reduce_max_noalloc.argtypes = [P, ctypes.c_int64, P, P]
     _lib = lib
     return lib
 
@@ -434,6 +435,18 @@ class InferenceSession:
                 raise RuntimeError(f"Input not found: {name}")
             ordered.append(input[name])
         return self.session.run(ordered)
+
+
+def reduce_max_noalloc(x_ptr: int, n: int, out_ptr: int, stream: int = 0) -> None:
+    """Whole-tensor maximum of `n` device floats at `x_ptr` into the device float at
+    `out_ptr`, for callers that may not allocate device memory (see the header):
+    fixed scratch inside the library, at most 67,108,864 elements, calls on one GPU
+    must not overlap. Raises SessionError on refusal."""
+    lib = load_library()
+    rc = lib.altius_cuda_reduce_max_noalloc(x_ptr, n, out_ptr, stream or None)
+    if rc != 0:
+        msg = lib.altius_cuda_last_error(None)
+        raise SessionError(rc, msg.decode() if msg else "reduce_max_noalloc failed")
 
 
 def alloc_pinned(shape, dtype=np.float32) -> np.ndarray:

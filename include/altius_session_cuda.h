@@ -225,6 +225,22 @@ void altius_cuda_destroy(AcSession *s);
 int altius_cuda_host_alloc(size_t bytes, void **out);
 int altius_cuda_host_free(void *p);
 
+/* Maximum of `n` f32 values at device address `d_x`, written to the device float
+ * `d_out`, enqueued on `stream` (a cudaStream_t passed as void*, NULL = the
+ * default stream) of the current device. It has no counterpart in the reference
+ * (whose reductions run inside a session on host memory). It exists for callers
+ * that must not allocate device memory when they need the value -- real-time or
+ * callback code that cannot take cudaMalloc's synchronisation, plug-ins without a
+ * pool of their own, code between allocation-free checkpoints: unlike a session
+ * it calls no cudaMalloc / cudaFree or other allocating routine. Its partial
+ * results live in a fixed 64 KB array inside the library's device image, which
+ * limits `n` to 67,108,864 elements (larger `n`: AC_ERR_INVALID with a message
+ * from altius_cuda_last_error(NULL)) and is shared by every call on that GPU, so
+ * calls that can overlap on one GPU must be serialised by the caller. The first
+ * call on each device also looks up the array's device address; make that call
+ * before starting any stream capture. */
+int altius_cuda_reduce_max_noalloc(const float *d_x, int64_t n, float *d_out, void *stream);
+
 /* Number of visible CUDA devices, or a negative AcStatus. */
 int altius_cuda_device_count(void);
 
