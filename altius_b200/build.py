@@ -23,7 +23,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "--fmad=false", "-Xcompiler", "-fPIC
           "-Xcudafe", "--diag_suppress=177"]
 
 SOURCES = ["session.cu", "shapes.cpp", "lower.cpp", "eltwise.cu", "rowops.cu", "movement.cu",
-           "gemm_simt.cu", "gemm_tc.cu", "noalloc.cu"]
+           "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "noalloc.cu"]
 
 
 def _newer(target, deps):

@@ -13,15 +13,15 @@
 // of x_lo are each below 2^-22 relative.
 //
 // Persistent CTAs (one per SM) walk the 128 x BN output tiles:
-//   warp 8      TMA producer: one elected thread issues cp.async.bulk.tensor
+//   warp 12     TMA producer: one elected thread issues cp.async.bulk.tensor
 //               loads (64B-swizzled boxes of 16 floats along K) into a ring of
 //               stages, completion on an mbarrier per stage;
-//   warps 0-3   splitters: rewrite the A tile as x_hi in place and write x_lo
+//   warps 0-7   splitters (two groups on alternate stages): rewrite the A tile as x_hi in place and write x_lo
 //               beside it (the same for the B tile unless B is a constant whose
 //               split was prepared at load time and arrives by TMA);
-//   warp 9      one thread issues the tcgen05.mma stream and tcgen05.commit into
+//   warp 13     one thread issues the tcgen05.mma stream and tcgen05.commit into
 //               one of two accumulators in tensor memory;
-//   warps 4-7   epilogue of the other accumulator: tcgen05.ld, a shared-memory
+//   warps 8-11  epilogue of the other accumulator: tcgen05.ld, a shared-memory
 //               transpose to row-contiguous float4s, bias / activation /
 //               residual, full-line global stores.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the
@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "kernels.h"
@@ -39,8 +40,9 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 16;                       // floats: one 64-byte swizzle row per tile row
-constexpr int kSplitWarps = 4;
-constexpr int kSplitThreads = kSplitWarps * 32;
+constexpr int kSplitGroups = 2;                 // groups of 4 warps taking alternate stages
+constexpr int kSplitWarps = 4 * kSplitGroups;
+constexpr int kSplitThreads = 128;             // threads working on one stage
 constexpr int kThreads = (kSplitWarps + 6) * 32;   // + 4 epilogue warps, TMA warp, MMA warp
 constexpr uint32_t kWaitLimit = 1u << 24;    // polls before a wait gives up
 
@@ -330,10 +332,11 @@ struct TcSmem {
 // Persistent kernel: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x +
 // gridDim.x, ... The accumulator is double-buffered in tensor memory, so the
 // epilogue of one tile overlaps the main loop of the next.
-//   warps 0-3   splitters (hi/lo of the A tile, and of B unless it arrives split)
-//   warps 4-7   epilogue (warp w owns TMEM lanes 32*(w-4) .. +31)
-//   warp  8     TMA producer (one thread)
-//   warp  9     MMA issuer (one thread); allocates and frees tensor memory
+//   warps 0-7   splitters, two groups of four taking alternate K-blocks (hi/lo of the
+//               A tile, and of B unless it arrives split)
+//   warps 8-11  epilogue (warp w owns TMEM lanes 32*(w-8) .. +31)
+//   warp  12    TMA producer (one thread)
+//   warp  13    MMA issuer (one thread); allocates and frees tensor memory
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -449,11 +452,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   } else if (warp < kSplitWarps) {
     // ---------------- splitters ----------------
     if (MODE != TC_1X) {
-      const int t0 = threadIdx.x;  // 0 .. kSplitThreads-1
+      const int t0 = threadIdx.x & (kSplitThreads - 1);
+      const int group = threadIdx.x / kSplitThreads;   // takes the K-blocks with it % kSplitGroups == group
       int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          if (it % kSplitGroups != group) continue;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           ok = mbar_wait(&full[s], ph);
@@ -628,13 +633,17 @@ bool gemm_tc_supported(const GemmParams& q) {
   return encode_fn() != nullptr;
 }
 
-int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch) {
-  // Rounds of the persistent CTAs (one per SM) times the cost of one tile. The
-  // cost is the MMA time of the tile in units of 2 clocks per K-step, bounded
-  // below by the shared-memory traffic of the operands (narrow tiles re-read
-  // A), plus a small fixed part; ties go to the wider tile.
+int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch, bool b_presplit) {
+  // Debug toggle: ALTIUS_CUDA_TC_BN=64|128|256 forces the tile width.
+  if (const char* e = std::getenv("ALTIUS_CUDA_TC_BN")) {
+    const int v = std::atoi(e);
+    if (v == 64 || v == 128 || v == 256) return v;
+  }
+  // Measured: the main loop is fed from L2 at about 27 bytes per clock per SM
+  // (7 TB/s over the chip) and three TF32 MMAs per K-step of a 128 x BN tile take
+  // 0.75 * BN clocks. A tile shape costs the larger of its rounds of MMA time and
+  // its share of the operand traffic; B arrives as hi + lo when it is a constant.
   const int cands[3] = {256, 128, 64};
-  const double tile_cost[3] = {134.0, 72.0, 56.0};
   const int sms = sm_count();
   int best = 256;
   double best_cost = 1e300;
@@ -642,7 +651,10 @@ int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch) {
     const int bn = cands[i];
     const int64_t tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn) * batch;
     const double rounds = (double)((tiles + sms - 1) / sms);
-    const double cost = rounds * tile_cost[i];
+    const double mma_clk = rounds * (bn == 64 ? 72.0 : 0.75 * bn * 2);        // per 16-float K-block
+    const double bytes = (double)tiles * (BM * 64.0 + bn * 64.0 * (b_presplit ? 2 : 1));
+    const double feed_clk = bytes / (27.0 * sms);
+    const double cost = std::max(mma_clk, feed_clk) + 0.02 * rounds * 16;
     if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
   }
   return best;
@@ -650,7 +662,7 @@ int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch) {
 
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
   if (!gemm_tc_supported(q)) return cudaErrorInvalidValue;
-  const int bn = gemm_tc_pick_bn(q.m, q.n, q.batch);
+  const int bn = gemm_tc_pick_bn(q.m, q.n, q.batch, mode != 2 && q.b_lo != nullptr);
   CUtensorMap ma, mb, mbl;
   const int b_batched = (q.batch > 1 && q.stride_b > 0) ? 1 : 0;
   if (!make_map(&ma, q.a, q.k, q.m, q.batch, q.lda, q.stride_a, BM)) return cudaErrorInvalidValue;

@@ -147,4 +147,18 @@ cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStr
 // hi[i] = rn_tf32(x[i]); lo[i] = rn_tf32(x[i] - hi[i])
 cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st);
 
+// ---- fused attention core ---------------------------------------------------------
+// O[b, t, h*hd + d] = sum_j Softmax_j((Q K^T)[t, j] (*|/) scale) V[j, d], with
+// Q/K/V[b, t, h*hd + d] at q/k/v + b*batch_stride + t*row_stride + h*hd + d.
+struct AttentionParams {
+  const float* q; const float* k; const float* v;
+  int64_t row_stride, batch_stride;
+  float* out; int64_t out_row_stride, out_batch_stride;
+  int batch, heads, tokens, head_dim;
+  const float* scale;   // device scalar or null
+  int scale_mode;       // 1: multiply, 2: divide
+};
+bool attention_supported(const AttentionParams& p);
+cudaError_t launch_attention(const AttentionParams& p, cudaStream_t st);
+
 }  // namespace ac

@@ -84,7 +84,20 @@ struct LnFusion {
   int gelu = 0;
 };
 
+struct HeadView {       // a [B*H, T, hd] operand that is a strided view of a [B, T, C] tensor
+  int src = -1;         // the [B, T, C] value
+  int64_t col = 0;      // first column of this operand inside C
+  int64_t B = 0, H = 0, T = 0, hd = 0, C = 0;
+};
+
+struct AttentionFusion {
+  HeadView q, k, v;
+  int scale = -1, scale_mode = 0;
+  int out = -1;         // the [B, T, H*hd] result
+};
+
 struct Plan {
+  std::map<int, AttentionFusion> attention;  // Softmax node -> whole attention core
   std::map<int, Epilogue> epi;      // base node (MatMul/Gemm/Conv2d) -> epilogue
   std::map<int, int> softmax_scale; // Softmax node -> Mul/Div node folded in
   std::map<int, LnFusion> ln;       // LayerNormalization node -> folded producers
@@ -108,6 +121,140 @@ int match_hardswish_pair(Ctx& c, int t, int* hs_node) {
     return m;
   }
   return -1;
+}
+
+
+// Walks back from a [B*H, T, hd] MatMul operand through
+//   Reshape <- Transpose[0,2,1,3] <- Reshape <- (Split output | plain [B,T,C] value)
+// collecting the nodes; every intermediate must have exactly one user.
+bool trace_head_view(Ctx& c, int v, HeadView* out, std::vector<int>* nodes) {
+  const Value& v3 = c.val(v);
+  if (v3.rank != 3 || !c.single_use(v)) return false;
+  const int r2 = c.producer[v];
+  if (r2 < 0 || c.absorbed[r2] || c.node(r2).op != AC_OP_RESHAPE) return false;
+  const int t1 = c.node(r2).inputs[0];
+  const Value& v4 = c.val(t1);
+  if (v4.rank != 4 || !c.single_use(t1) || v4.dims[0] * v4.dims[1] != v3.dims[0] ||
+      v4.dims[2] != v3.dims[1] || v4.dims[3] != v3.dims[2]) return false;
+  const int tr = c.producer[t1];
+  if (tr < 0 || c.absorbed[tr] || c.node(tr).op != AC_OP_TRANSPOSE) return false;
+  const Node& tn = c.node(tr);
+  if (tn.ints.size() != 4 || tn.ints[0] != 0 || tn.ints[1] != 2 || tn.ints[2] != 1 || tn.ints[3] != 3) return false;
+  const int t0 = tn.inputs[0];
+  if (!c.single_use(t0)) return false;
+  const int r1 = c.producer[t0];
+  if (r1 < 0 || c.absorbed[r1] || c.node(r1).op != AC_OP_RESHAPE) return false;
+  const int s0 = c.node(r1).inputs[0];
+  const Value& sv = c.val(s0);
+  const int64_t B = v4.dims[0], H = v4.dims[1], T = v4.dims[2], hd = v4.dims[3];
+  if (sv.rank != 3 || sv.dims[0] != B || sv.dims[1] != T || sv.dims[2] != H * hd) return false;
+  out->B = B; out->H = H; out->T = T; out->hd = hd;
+  nodes->push_back(r2); nodes->push_back(tr); nodes->push_back(r1);
+  // Optional Split on the last axis: read in place from its input.
+  const int sp = c.producer[s0];
+  if (sp >= 0 && !c.absorbed[sp] && c.node(sp).op == AC_OP_SPLIT && c.single_use(s0)) {
+    const Node& sn = c.node(sp);
+    const Value& in = c.val(sn.inputs[0]);
+    int64_t axis = sn.ints[0] < 0 ? sn.ints[0] + in.rank : sn.ints[0];
+    if (in.rank == 3 && axis == 2 && !in.is_const) {
+      int64_t col = 0;
+      for (int o : sn.outputs) {
+        if (o == s0) break;
+        col += c.val(o).dims[2];
+      }
+      out->src = sn.inputs[0]; out->col = col; out->C = in.dims[2];
+      nodes->push_back(-1 - sp);   // marks the Split: absorbed only if all its outputs are
+      return true;
+    }
+  }
+  out->src = s0; out->col = 0; out->C = sv.dims[2];
+  return true;
+}
+
+// MatMul(q, Transpose(k)) -> [Mul|Div scalar] -> Softmax -> MatMul(., v) -> Reshape ->
+// Transpose[0,2,1,3] -> Reshape, with q, k, v head views of [B,T,C] tensors.
+void detect_attention(Ctx& c, Plan& plan) {
+  for (int nid : c.s.order) {
+    Node& sm = c.node(nid);
+    if (c.absorbed[nid] || sm.op != AC_OP_SOFTMAX) continue;
+    std::vector<int> nodes;
+    AttentionFusion f;
+    int x = sm.inputs[0];
+    if (c.val(x).rank != 3 || !c.single_use(x)) continue;
+    int px = c.producer[x];
+    if (px < 0 || c.absorbed[px]) continue;
+    if (c.node(px).op == AC_OP_MUL || c.node(px).op == AC_OP_DIV) {
+      Node& m = c.node(px);
+      const bool b_scalar = c.val(m.inputs[1]).numel() == 1;
+      const bool a_scalar = c.val(m.inputs[0]).numel() == 1 && m.op == AC_OP_MUL;
+      if (!b_scalar && !a_scalar) continue;
+      f.scale = b_scalar ? m.inputs[1] : m.inputs[0];
+      f.scale_mode = m.op == AC_OP_MUL ? 1 : 2;
+      nodes.push_back(px);
+      x = b_scalar ? m.inputs[0] : m.inputs[1];
+      if (!c.single_use(x)) continue;
+      px = c.producer[x];
+      if (px < 0 || c.absorbed[px]) continue;
+    }
+    if (c.node(px).op != AC_OP_MATMUL) continue;
+    Node& m1 = c.node(px);
+    nodes.push_back(px);
+    // rhs must be Transpose[0,2,1] of k
+    const int kt = m1.inputs[1];
+    const int tp = c.producer[kt];
+    if (tp < 0 || c.absorbed[tp] || c.node(tp).op != AC_OP_TRANSPOSE || !c.single_use(kt)) continue;
+    const Node& tn = c.node(tp);
+    if (tn.ints.size() != 3 || tn.ints[0] != 0 || tn.ints[1] != 2 || tn.ints[2] != 1) continue;
+    nodes.push_back(tp);
+    if (!trace_head_view(c, m1.inputs[0], &f.q, &nodes)) continue;
+    if (!trace_head_view(c, tn.inputs[0], &f.k, &nodes)) continue;
+    // Softmax -> MatMul(P, v)
+    const int pv = sm.outputs[0];
+    if (!c.single_use(pv)) continue;
+    const int m2n = c.only_consumer(pv);
+    Node& m2 = c.node(m2n);
+    if (c.absorbed[m2n] || m2.op != AC_OP_MATMUL || m2.inputs[0] != pv) continue;
+    nodes.push_back(m2n);
+    if (!trace_head_view(c, m2.inputs[1], &f.v, &nodes)) continue;
+    if (f.q.B != f.k.B || f.q.B != f.v.B || f.q.H != f.k.H || f.q.H != f.v.H || f.q.T != f.k.T ||
+        f.q.T != f.v.T || f.q.hd != f.k.hd || f.q.hd != f.v.hd || f.q.C != f.k.C || f.q.C != f.v.C)
+      continue;
+    if (f.q.hd != 64 || f.q.T > 256 || f.q.B * f.q.H > 65535 || (f.q.C % 4) || (f.q.col % 4) ||
+        (f.k.col % 4) || (f.v.col % 4))
+      continue;
+    // O [BH,T,hd] -> Reshape [B,H,T,hd] -> Transpose [0,2,1,3] -> Reshape [B,T,D]
+    const int o3 = m2.outputs[0];
+    if (!c.single_use(o3)) continue;
+    const int r1 = c.only_consumer(o3);
+    if (c.absorbed[r1] || c.node(r1).op != AC_OP_RESHAPE) continue;
+    const int o4 = c.node(r1).outputs[0];
+    const Value& o4v = c.val(o4);
+    if (o4v.rank != 4 || o4v.dims[0] != f.q.B || o4v.dims[1] != f.q.H || o4v.dims[2] != f.q.T ||
+        o4v.dims[3] != f.q.hd || !c.single_use(o4)) continue;
+    const int tr = c.only_consumer(o4);
+    if (c.absorbed[tr] || c.node(tr).op != AC_OP_TRANSPOSE) continue;
+    const Node& otn = c.node(tr);
+    if (otn.ints.size() != 4 || otn.ints[0] != 0 || otn.ints[1] != 2 || otn.ints[2] != 1 || otn.ints[3] != 3) continue;
+    const int o5 = otn.outputs[0];
+    if (!c.single_use(o5)) continue;
+    const int r2 = c.only_consumer(o5);
+    if (c.absorbed[r2] || c.node(r2).op != AC_OP_RESHAPE) continue;
+    const int out = c.node(r2).outputs[0];
+    const Value& ov = c.val(out);
+    if (ov.rank != 3 || ov.dims[0] != f.q.B || ov.dims[1] != f.q.T || ov.dims[2] != f.q.H * f.q.hd) continue;
+    nodes.push_back(r1); nodes.push_back(tr); nodes.push_back(r2);
+    f.out = out;
+    // Commit: absorb the chain. A Split is absorbed when every output of it feeds this core.
+    std::map<int, int> split_uses;
+    for (int id : nodes)
+      if (id < 0) split_uses[-1 - id]++;
+    bool ok = true;
+    for (auto& kv : split_uses)
+      if ((int)c.node(kv.first).outputs.size() != kv.second) ok = false;   // partly used Split: keep it simple
+    if (!ok) continue;
+    for (int id : nodes) c.absorbed[id < 0 ? -1 - id : id] = 1;
+    plan.attention[nid] = f;
+  }
 }
 
 void detect_epilogues(Ctx& c, Plan& plan) {
@@ -740,6 +887,26 @@ void lower_node(Emit& em, Plan& plan, int nid) {
       return;
     }
     case AC_OP_SOFTMAX: {
+      auto at = plan.attention.find(nid);
+      if (at != plan.attention.end()) {
+        const AttentionFusion f = at->second;
+        const int64_t B = f.q.B, H = f.q.H, T = f.q.T, hd = f.q.hd, C = f.q.C;
+        const double bytes = 4.0 * B * T * hd * H * 4;
+        const double flops = 4.0 * B * H * T * T * hd;
+        em.add("attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, {f.out}, bytes, flops,
+               [=](cudaStream_t st) {
+                 AttentionParams p{};
+                 p.q = s->fptr(f.q.src) + f.q.col;
+                 p.k = s->fptr(f.k.src) + f.k.col;
+                 p.v = s->fptr(f.v.src) + f.v.col;
+                 p.row_stride = C; p.batch_stride = T * C;
+                 p.out = s->fptr_mut(f.out); p.out_row_stride = H * hd; p.out_batch_stride = T * H * hd;
+                 p.batch = (int)B; p.heads = (int)H; p.tokens = (int)T; p.head_dim = (int)hd;
+                 p.scale = f.scale >= 0 ? s->fptr(f.scale) : nullptr; p.scale_mode = f.scale_mode;
+                 return launch_attention(p, st);
+               });
+        return;
+      }
       const int o = n.outputs[0];
       int x = n.inputs[0];
       const Value& xv = V(x);
@@ -1103,6 +1270,7 @@ void lower_graph(AcSession& s) {
     std::fill(c.absorbed.begin(), c.absorbed.end(), 0);
     s.steps.clear();
     if (fuse) {
+      detect_attention(c, plan);
       detect_epilogues(c, plan);
       detect_softmax_scale(c, plan);
       detect_layer_norm(c, plan);

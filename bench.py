@@ -102,14 +102,25 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
+def host_threads():
+    """All host cores this process may use (torchrun presets OMP_NUM_THREADS=1, so the
+    OpenMP default cannot be trusted); also lifts numpy's BLAS pool to that count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=n)
+    except Exception:
+        pass
+    return n
+
+
 def time_cpu_port(target_seconds=12.0, batch=2, max_runs=50):
     """The CPU oracle on a bounded sample: forward passes of ViT-B/16 at a small
     batch, repeated for about `target_seconds`; all host threads; OpenBLAS sgemm
     (numpy's) standing in for the reference's BLIS."""
     from altius_b200 import configs
     from oracle import InterpreterSessionBuilder
-    from oracle.interpreter import lib
-    threads = lib().or_max_threads()
+    threads = host_threads()
     model, feeds = configs.vit_base_16(batch=batch)
     sess = (InterpreterSessionBuilder(model).with_intra_op_num_threads(threads)
             .with_sgemm("openblas").build())
@@ -134,8 +145,7 @@ def reference_arm(args, rank):
     batch = 2
     from altius_b200 import configs
     from oracle import InterpreterSessionBuilder
-    from oracle.interpreter import lib
-    threads = lib().or_max_threads()
+    threads = host_threads()
     model, feeds = configs.vit_base_16(batch=batch)
     sess = (InterpreterSessionBuilder(model).with_intra_op_num_threads(threads)
             .with_sgemm("openblas").build())
@@ -285,7 +295,7 @@ def main():
     e2e_s = max_over_ranks(e2e_s)
     e2e = world * PER_GPU_BATCH * args.steps / e2e_s
     logits = np.array(y_host)
-    launches = sess.launches_per_run * args.steps
+    launches = sess.launches_per_run * args.steps * world
     sess.close()
 
     if rank != 0:

@@ -65,7 +65,11 @@ def test_fusion_folds_the_expected_chains():
     model, _ = configs.vit_base_16(batch=2, depth=2)
     kinds = collections.Counter(e["kind"] for e in plan(model).schedule())
     gemms = sum(v for k, v in kinds.items() if k.startswith("gemm"))
-    assert gemms == 2 * 6 + 2          # per layer: qkv, qk^T, av, proj, mlp1, mlp2; patch embed; head
+    assert gemms == 2 * 4 + 2          # per layer: qkv, proj, mlp1, mlp2; patch embed; head
+    assert kinds["attention_fused"] == 2   # Split/Reshape/Transpose/QK^T/scale/Softmax/PV/merge in one kernel
+    assert not any(k in kinds for k in ("split_copy", "transpose_copy", "softmax", "softmax_scaled"))
+    unfused = collections.Counter(e["kind"] for e in plan(model, fuse=False).schedule())
+    assert unfused["split_copy"] == 6 and unfused["softmax"] == 2
     assert kinds["layer_norm"] == 2 * 2 + 1
     assert kinds.get("binary_Add", 0) == 1        # only the position embedding stays a kernel
     assert "unary_gelu" not in kinds
