@@ -2,6 +2,7 @@
 
     python -m altius_b200.kernel_bench gemm 6304 768 2304 [--mode 0|1|2] [--iters 10]
     python -m altius_b200.kernel_bench micrograph [--batch 64] [--no-fuse]
+    python -m altius_b200.kernel_bench attention 32 197 12     # batch, tokens, heads (head dim 64)
 
 Builds a one-node (or micrograph) session with per-kernel CUDA-event profiling
 and prints, per kernel kind, the mean device time and the achieved algorithmic
@@ -40,7 +41,7 @@ def _run(model, feeds, mode, fuse, iters):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "micrograph"])
+    ap.add_argument("what", choices=["gemm", "micrograph", "attention"])
     ap.add_argument("dims", nargs="*", type=int)
     ap.add_argument("--mode", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -57,6 +58,27 @@ def main(argv=None):
         out = g.op("MatMul", xi, g.new_init(w))
         g.outputs.append(out)
         rows = _run(ir.Model(g, 13), [x], a.mode, True, a.iters)
+    elif a.what == "attention":
+        B, T, H = a.dims
+        hd, D = 64, 64 * H
+        qkv = rng.standard_normal((B, T, 3 * D)).astype(np.float32)
+        g = ir.Graph()
+        x = g.add_input("qkv", qkv.shape)
+        i64 = lambda v: g.new_init(np.asarray(v, np.int64))
+        q, k, v = g.add_node("Split", [x, i64([D, D, D])], 3, axis=2)
+
+        def heads(t):
+            t = g.op("Reshape", t, i64([B, T, H, hd]))
+            t = g.op("Transpose", t, perm=[0, 2, 1, 3])
+            return g.op("Reshape", t, i64([B * H, T, hd]))
+        q, k, v = heads(q), heads(k), heads(v)
+        s_ = g.op("MatMul", q, g.op("Transpose", k, perm=[0, 2, 1]))
+        s_ = g.op("Mul", s_, g.new_init(np.array([hd ** -0.5], np.float32)))
+        o = g.op("MatMul", g.op("Softmax", s_, axis=-1), v)
+        o = g.op("Reshape", o, i64([B, H, T, hd]))
+        o = g.op("Transpose", o, perm=[0, 2, 1, 3])
+        g.outputs.append(g.op("Reshape", o, i64([B, T, D])))
+        rows = _run(ir.Model(g, 13), [qkv], a.mode, not a.no_fuse, a.iters)
     else:
         model, feeds = configs.micrograph(batch=a.batch)
         rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters)
