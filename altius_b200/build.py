@@ -19,7 +19,7 @@ LIB = os.path.join(LIBDIR, "libaltius_session_cuda.so")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-COMMON = ["-O3", "-std=c++17", "-lineinfo", "--fmad=false", "-Xcompiler", "-fPIC,-fvisibility=hidden",
+COMMON = (["-DAC_TC_BK=" + os.environ["AC_TC_BK"]] if "AC_TC_BK" in os.environ else []) + ["-O3", "-std=c++17", "-lineinfo", "--fmad=false", "-Xcompiler", "-fPIC,-fvisibility=hidden",
           "-Xcudafe", "--diag_suppress=177"]
 
 SOURCES = ["session.cu", "shapes.cpp", "lower.cpp", "eltwise.cu", "rowops.cu", "movement.cu",

@@ -39,7 +39,10 @@ namespace ac {
 namespace {
 
 constexpr int BM = 128;
-constexpr int BK = 16;                       // floats: one 64-byte swizzle row per tile row
+#ifndef AC_TC_BK
+#define AC_TC_BK 16
+#endif
+constexpr int BK = AC_TC_BK;                 // floats per tile row: 16 (64-byte swizzle) or 32 (128-byte swizzle)
 constexpr int kSplitGroups = 2;                 // groups of 4 warps taking alternate stages
 constexpr int kSplitWarps = 4 * kSplitGroups;
 constexpr int kSplitThreads = 128;             // threads working on one stage
@@ -141,7 +144,7 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   d |= (uint64_t)1 << 16;                        // leading byte offset (ignored for swizzled K-major)
   d |= (uint64_t)((8 * BK * 4) >> 4) << 32;      // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                        // descriptor version for this architecture
-  d |= (uint64_t)4 << 61;                        // 64-byte swizzle
+  d |= (uint64_t)(BK == 32 ? 2 : 4) << 61;       // 128-byte or 64-byte swizzle
   return d;
 }
 
@@ -318,6 +321,77 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
   }
 }
 
+// Unreduced accumulator of a K-slice -> workspace tile [128][BN], same staging
+// as the real epilogues so that the stores are full lines.
+template <int BN>
+__device__ __forceinline__ void epilogue_raw(float* ws_tile, float4* stage, uint32_t tmem_base, int warp,
+                                             int lane) {
+  const int c4 = lane & 7, rsub = lane >> 3;
+#pragma unroll 1
+  for (int cc = 0; cc < BN / 32; ++cc) {
+    uint32_t v[32];
+    tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      stage[lane * 8 + (j ^ (lane & 7))] =
+          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rl = 4 * i + rsub;
+      *reinterpret_cast<float4*>(ws_tile + (size_t)(warp * 32 + rl) * BN + cc * 32 + 4 * c4) =
+          stage[rl * 8 + (c4 ^ (rl & 7))];
+    }
+  }
+}
+
+// Adds the K-slices of the tail tiles in slice order and applies the epilogue.
+__global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ ws, TcEpilogue ep, int bn,
+                                                            int dp_tiles, int parts, int tiles_m, int tiles_n) {
+  const int tt = blockIdx.y;
+  const int t = dp_tiles + tt;
+  const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+  const int e4 = blockIdx.x * 256 + threadIdx.x;          // float4 index inside the tile
+  if (e4 >= BM * bn / 4) return;
+  const int rl = e4 / (bn / 4), cl = (e4 % (bn / 4)) * 4;
+  const int row = tm * BM + rl, col0 = tn * bn + cl;
+  if (row >= ep.m || col0 >= ep.n) return;
+  const float* src = ws + (size_t)tt * parts * BM * bn + (size_t)rl * bn + cl;
+  float4 acc = __ldg(reinterpret_cast<const float4*>(src));
+  for (int p = 1; p < parts; ++p) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(src + (size_t)p * BM * bn));
+    acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+    acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+  }
+  float* c = ep.c + (long long)bz * ep.sc;
+  const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
+  const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
+  const float x[4] = {acc.x, acc.y, acc.z, acc.w};
+  for (int e = 0; e < 4; ++e) {
+    const int col = col0 + e;
+    if (col >= ep.n) break;
+    float y = x[e];
+    if (ep.alpha != 1.f) y = __fmul_rn(ep.alpha, y);
+    if (cin) {
+      const float cv = __ldg(cin + (long long)row * ep.ldcin + col);
+      y = __fadd_rn(ep.beta == 1.f ? cv : __fmul_rn(ep.beta, cv), y);
+    }
+    if (ep.bias_n) {
+      const float bv = __ldg(ep.bias_n + col);
+      y = __fadd_rn(y, ep.bias_scale == 1.f ? bv : __fmul_rn(ep.bias_scale, bv));
+    }
+    if (ep.bias_m) {
+      const float bv = __ldg(ep.bias_m + row);
+      y = __fadd_rn(y, ep.bias_scale == 1.f ? bv : __fmul_rn(ep.bias_scale, bv));
+    }
+    y = apply_act(ep.act, y, ep.act_alpha, ep.act_beta);
+    if (res) y = __fadd_rn(y, __ldg(res + (long long)row * ep.ldres + col));
+    c[(long long)row * ep.ldc + col] = y;
+  }
+}
+
 template <int BN>
 struct TcSmem {
   static constexpr int kABytes = BM * BK * 4;
@@ -328,6 +402,37 @@ struct TcSmem {
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
 };
+
+// Work distribution of the persistent kernel. The first `dp_tiles` tiles (whole
+// rounds of the grid) are taken round-robin, one whole tile at a time. The
+// remaining `num_tiles - dp_tiles` tiles would leave most SMs idle for a full
+// tile time, so each of them is cut along K into `tail_parts` slices, one slice
+// per CTA; a slice's accumulator goes unreduced to a workspace slot (its CTA
+// index) and a second small kernel adds the slices in a fixed order and applies
+// the epilogue. tail_parts < 2: no slicing, dp_tiles == num_tiles.
+struct TcSched {
+  int num_tiles, dp_tiles, tail_parts, num_kb;
+};
+struct TcWork {
+  int tile, k0, k1, raw;   // raw: workspace slot, or -1 for a whole tile with the real epilogue
+};
+__device__ __forceinline__ bool tc_get_work(const TcSched& sc, int w, TcWork* out) {
+  const int c = blockIdx.x, g = gridDim.x;
+  const int n_dp = sc.dp_tiles > c ? (sc.dp_tiles - c + g - 1) / g : 0;
+  if (w < n_dp) {
+    out->tile = c + w * g; out->k0 = 0; out->k1 = sc.num_kb; out->raw = -1;
+    return true;
+  }
+  if (w == n_dp && sc.tail_parts >= 2 && c < (sc.num_tiles - sc.dp_tiles) * sc.tail_parts) {
+    const int part = c % sc.tail_parts;
+    out->tile = sc.dp_tiles + c / sc.tail_parts;
+    out->k0 = (int)((long long)part * sc.num_kb / sc.tail_parts);
+    out->k1 = (int)((long long)(part + 1) * sc.num_kb / sc.tail_parts);
+    out->raw = c;
+    return true;
+  }
+  return false;
+}
 
 // Persistent kernel: one CTA per SM walks tiles t = blockIdx.x, blockIdx.x +
 // gridDim.x, ... The accumulator is double-buffered in tensor memory, so the
@@ -340,8 +445,8 @@ struct TcSmem {
 template <int BN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-               const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, int num_kb, int b_batched,
-               int tiles_m, int tiles_n, int num_tiles, int* err) {
+               const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, TcSched sc, int b_batched,
+               int tiles_m, int tiles_n, float* workspace, int* err) {
   using L = TcSmem<BN>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -394,10 +499,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t bytes = L::kABytes + L::kBBytes + (MODE == TC_3X_BLO_TMA ? L::kBBytes : 0);
       int it = 0;   // running K-block count over all of this CTA's tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      TcWork wk;
+      for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w) {
+        const int t = wk.tile;
         const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
         const int bzb = b_batched ? bz : 0;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
@@ -416,13 +523,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                              ((uint32_t)(BM >> 4) << 24);
       int it = 0, ti = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++ti) {
+      TcWork wk;
+      for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w, ++ti) {
         const int ab = ti & 1;
         // The epilogue must have drained this accumulator (two tiles ago).
         if (!mbar_wait(&acc_empty[ab], ((ti >> 1) & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
@@ -435,7 +543,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
             const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats = 32 bytes along K
-            const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+            const uint32_t acc = (kb > wk.k0 || kk > 0) ? 1u : 0u;
             if (MODE == TC_1X) {
               tc_mma_tf32(d_tmem, da + off, db + off, idesc, acc);
             } else {
@@ -456,8 +564,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int group = threadIdx.x / kSplitThreads;   // takes the K-blocks with it % kSplitGroups == group
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      TcWork wk;
+      for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w) {
+        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           if (it % kSplitGroups != group) continue;
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -500,13 +609,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
     const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
     int ti = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++ti) {
+    TcWork wk;
+    for (int w = 0; tc_get_work(sc, w, &wk); ++w, ++ti) {
+      const int t = wk.tile;
       const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
       const int ab = ti & 1;
       if (!mbar_wait(&acc_full[ab], (ti >> 1) & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
       tc_fence_after();
       const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
       const int m0 = tm * BM, n0 = tn * BN;
+      if (wk.raw >= 0) {
+        epilogue_raw<BN>(workspace + (size_t)wk.raw * BM * BN, stage, acc, q, lane);
+      } else
       switch (key) {
         case 0: epilogue_fast<BN, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
         case 1: epilogue_fast<BN, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
@@ -582,10 +696,10 @@ bool make_map(CUtensorMap* map, const float* base, int64_t k, int64_t rows, int6
   cuuint64_t strides[2] = {(cuuint64_t)ld * 4,
                            (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * 4};
   cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
-  static_assert(BK * 4 == 64, "box rows are one 64-byte swizzle span");
+  static_assert(BK * 4 == 64 || BK * 4 == 128, "box rows are one swizzle span");
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -599,9 +713,44 @@ int sm_count() {
   return n;
 }
 
+// Host-side schedule: whole rounds of the grid are data parallel; a last partial
+// round of `tail` tiles is cut along K into `parts` slices when that keeps more
+// SMs busy (see TcSched).
+struct TcPlan {
+  int grid, tiles_m, tiles_n;
+  TcSched sc;
+  size_t workspace_bytes;
+};
+TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn) {
+  TcPlan pl{};
+  const int sms = sm_count();
+  pl.tiles_n = (int)((n + bn - 1) / bn);
+  pl.tiles_m = (int)((m + BM - 1) / BM);
+  const long long tiles = (long long)pl.tiles_n * pl.tiles_m * batch;
+  const int num_kb = (int)((k + BK - 1) / BK);
+  pl.sc.num_tiles = (int)tiles;
+  pl.sc.num_kb = num_kb;
+  pl.sc.dp_tiles = (int)tiles;
+  pl.sc.tail_parts = 0;
+  pl.grid = (int)std::min<long long>(tiles, sms);
+  const int tail = (int)(tiles % sms);
+  static const bool no_tail = std::getenv("ALTIUS_CUDA_TC_NO_TAIL_SPLIT") != nullptr;   // debug toggle
+  if (tail > 0 && !no_tail) {
+    const int parts = std::min(sms / tail, num_kb / 2);   // at least two K-blocks per slice
+    if (parts >= 2) {
+      pl.sc.dp_tiles = (int)(tiles - tail);
+      pl.sc.tail_parts = parts;
+      pl.grid = std::max(pl.grid, tail * parts);
+      pl.grid = std::min(pl.grid, sms);
+      pl.workspace_bytes = (size_t)tail * parts * BM * bn * sizeof(float);
+    }
+  }
+  return pl;
+}
+
 template <int BN, int MODE>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mbl,
-                      const TcEpilogue& ep, int num_kb, int b_batched, int64_t batch, int* err,
+                      const TcEpilogue& ep, const TcPlan& pl, int b_batched, float* workspace, int* err,
                       cudaStream_t st) {
   using L = TcSmem<BN>;
   static bool attr_set = false;
@@ -611,12 +760,14 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const int tiles_n = (ep.n + BN - 1) / BN, tiles_m = (ep.m + BM - 1) / BM;
-  const long long num_tiles = (long long)tiles_n * tiles_m * batch;
-  if (num_tiles > (1ll << 30)) return cudaErrorInvalidValue;
-  const int grid = (int)std::min<long long>(num_tiles, sm_count());
-  gemm_tc_kernel<BN, MODE><<<grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, num_kb, b_batched, tiles_m,
-                                                                 tiles_n, (int)num_tiles, err);
+  gemm_tc_kernel<BN, MODE><<<pl.grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, pl.sc, b_batched, pl.tiles_m,
+                                                                    pl.tiles_n, workspace, err);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || pl.sc.tail_parts < 2) return e;
+  const int tail = pl.sc.num_tiles - pl.sc.dp_tiles;
+  dim3 grid((BM * BN / 4 + 255) / 256, tail);
+  gemm_tc_fixup_kernel<<<grid, 256, 0, st>>>(workspace, ep, BN, pl.sc.dp_tiles, pl.sc.tail_parts, pl.tiles_m,
+                                             pl.tiles_n);
   return cudaGetLastError();
 }
 
@@ -660,6 +811,11 @@ int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch, bool b_presplit) {
   return best;
 }
 
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, bool b_presplit) {
+  const int bn = gemm_tc_pick_bn(m, n, batch, b_presplit);
+  return make_plan(m, n, k, batch, bn).workspace_bytes;
+}
+
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
   if (!gemm_tc_supported(q)) return cudaErrorInvalidValue;
   const int bn = gemm_tc_pick_bn(q.m, q.n, q.batch, mode != 2 && q.b_lo != nullptr);
@@ -683,12 +839,18 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.bias_n = q.bias_n; ep.bias_m = q.bias_m; ep.bias_scale = q.bias_scale;
   ep.act = q.act; ep.act_alpha = q.act_alpha; ep.act_beta = q.act_beta;
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
-  const int num_kb = (int)((q.k + BK - 1) / BK);
-#define AC_TC(BNV)                                                                                   \
-  (kmode == TC_1X ? launch_tc<BNV, TC_1X>(ma, mb, mbl, ep, num_kb, b_batched, q.batch, err_word, st) \
-   : kmode == TC_3X_BLO_TMA                                                                          \
-       ? launch_tc<BNV, TC_3X_BLO_TMA>(ma, mb, mbl, ep, num_kb, b_batched, q.batch, err_word, st)    \
-       : launch_tc<BNV, TC_3X_SPLIT_B>(ma, mb, mbl, ep, num_kb, b_batched, q.batch, err_word, st))
+  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn);
+  if (pl.sc.tail_parts >= 2 && (!q.workspace || q.workspace_bytes < pl.workspace_bytes)) {
+    // No (or too small a) workspace: fall back to whole tiles only.
+    pl.sc.dp_tiles = pl.sc.num_tiles;
+    pl.sc.tail_parts = 0;
+  }
+  float* ws = q.workspace;
+#define AC_TC(BNV)                                                                              \
+  (kmode == TC_1X ? launch_tc<BNV, TC_1X>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)     \
+   : kmode == TC_3X_BLO_TMA                                                                     \
+       ? launch_tc<BNV, TC_3X_BLO_TMA>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)        \
+       : launch_tc<BNV, TC_3X_SPLIT_B>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st))
   if (bn == 256) return AC_TC(256);
   if (bn == 128) return AC_TC(128);
   return AC_TC(64);

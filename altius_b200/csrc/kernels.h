@@ -135,6 +135,8 @@ struct GemmParams {
   int act; float act_alpha, act_beta;
   const float* residual; int64_t ld_res; int64_t stride_res;  // added after act; or null
   int residual_first;       // residual + v instead of v + residual (same value, kept for clarity)
+  float* workspace;         // tensor-core path: scratch for K-sliced tail tiles, or null
+  size_t workspace_bytes;
 };
 cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
 
@@ -144,6 +146,8 @@ cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
 // `err_word` (device memory) receives a non-zero code if a bounded wait expired.
 bool gemm_tc_supported(const GemmParams& p);
 cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStream_t st);
+// Scratch the tensor-core path wants for this problem (0 when its tiles fill whole rounds).
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, bool b_presplit);
 // hi[i] = rn_tf32(x[i]); lo[i] = rn_tf32(x[i] - hi[i])
 cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st);
 

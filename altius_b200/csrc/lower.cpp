@@ -604,10 +604,21 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     b_use = hi;
   }
   const int bsrc = b_use;
+  // Scratch for the K-sliced tail tiles of the persistent kernel (lives for this step only).
+  int ws = -1;
+  size_t ws_bytes = 0;
+  if (tc) {
+    ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b_lo >= 0);
+    if (ws_bytes) ws = new_value(em.c, (int64_t)(ws_bytes / 4), false);
+  }
   std::vector<int> reads = {a, bsrc, b_lo, c_in, bias_n, bias_m, res};
   const char* kind = !tc ? "gemm_fp32_simt" : (mode == 2 ? "gemm_tf32x1_tcgen05" : "gemm_tf32x3_tcgen05");
-  em.add(kind, op, reads, {out}, bytes, flops, [=](cudaStream_t st) {
+  std::vector<int> writes = {out};
+  if (ws >= 0) writes.push_back(ws);
+  em.add(kind, op, reads, writes, bytes, flops, [=](cudaStream_t st) {
     GemmParams p{};
+    p.workspace = ws >= 0 ? s->fptr_mut(ws) : nullptr;
+    p.workspace_bytes = ws_bytes;
     p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
     p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
     p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
@@ -622,7 +633,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.residual = res >= 0 ? s->fptr(res) + c_off : nullptr; p.ld_res = g.ldc; p.stride_res = g.sc;
     if (tc && gemm_tc_supported(p)) return launch_gemm_tc(p, mode, s->err_word, st);
     return launch_gemm_simt(p, st);
-  });
+  }, ws >= 0 ? 2 : 1);
 }
 
 void lower_matmul(Emit& em, int nid, const Epilogue* e) {

@@ -30,11 +30,16 @@ def _run(model, feeds, mode, fuse, iters):
             sess.profile_reset()
         sess.run_device([t.data_ptr() for t in ins], [t.data_ptr() for t in outs])
     rows = {}
+    steps = {}
+    for e in sess.schedule():
+        steps[e["kind"]] = steps.get(e["kind"], 0) + 1
     for kind, p in sess.profile().items():
-        us = 1e3 * p["total_ms"] / p["launches"]
-        rows[kind] = {"us": round(us, 2), "launches": p["launches"] // iters,
-                      "GBps": round(p["bytes"] / p["launches"] / us / 1e3, 1),
-                      "TFLOPs": round(p["flops"] / p["launches"] / us / 1e6, 2)}
+        n = steps.get(kind, 1) * iters                 # executions of this kind of step
+        us = 1e3 * p["total_ms"] / n
+        rows[kind] = {"us": round(us, 2), "steps_per_run": steps.get(kind, 1),
+                      "launches_per_run": p["launches"] // iters,
+                      "GBps": round(p["bytes"] / n / us / 1e3, 1),
+                      "TFLOPs": round(p["flops"] / n / us / 1e6, 2)}
     sess.close()
     return rows
 

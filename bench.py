@@ -315,7 +315,7 @@ def main():
     prof_sess.close()
     total_ms = sum(p["total_ms"] for p in prof.values())
     kernels = {k: {"share": round(p["total_ms"] / total_ms, 4),
-                   "us_per_launch": round(1e3 * p["total_ms"] / p["launches"], 2),
+                   "ms_per_step": round(p["total_ms"] / 4, 4),
                    "launches_per_step": p["launches"] // 4}
                for k, p in sorted(prof.items(), key=lambda kv: -kv[1]["total_ms"])}
     top = max(prof.items(), key=lambda kv: kv[1]["total_ms"])
