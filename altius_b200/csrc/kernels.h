@@ -111,6 +111,9 @@ struct ConvParams {
 };
 // col[n, c, kh, kw, oh, ow] <- x[n, c, ih, iw]
 cudaError_t launch_im2col(const ConvParams& p, const float* x, float* col, cudaStream_t st);
+// Non-overlapping patches (kernel == stride, no padding): rows[n * oh * ow, c * kh * kw] <- x,
+// one row per patch with the (c, fy, fx) order of the weight's K axis. kw % 4 == 0.
+cudaError_t launch_patchify(const ConvParams& p, const float* x, float* rows, cudaStream_t st);
 // Depthwise (group == c == oc) stencil with bias and activation fused.
 cudaError_t launch_depthwise_conv(const ConvParams& p, const float* x, const float* w,
                                   const float* bias, float* out, cudaStream_t st);

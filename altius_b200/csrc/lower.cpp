@@ -724,6 +724,39 @@ void lower_conv(Emit& em, int nid, const Epilogue* e) {
   p.act = ep.act; p.act_alpha = ep.act_alpha; p.act_beta = ep.act_beta;
   if (p.group <= 0 || p.c % p.group || p.oc % p.group || wv.dims[1] != p.c / p.group)
     fail(AC_ERR_SHAPE, "Conv2d: group does not divide the channels");
+
+  // Patch embedding: Conv2d with kernel == stride and no padding, followed by
+  // Reshape [N, OC, P] -> Transpose [0, 2, 1]. One GEMM over patch rows writes the
+  // [N, P, OC] token tensor directly (bias along N), no NCHW intermediate.
+  if (!s->opt.disable_fusion && p.group == 1 && p.kh == p.sh && p.kw == p.sw && p.dh == 1 && p.dw == 1 &&
+      pads[0] == 0 && pads[1] == 0 && pads[2] == 0 && pads[3] == 0 && p.ih == p.oh * p.kh &&
+      p.iw == p.ow * p.kw && (p.kw % 4) == 0 && (p.iw % 4) == 0 && ep.act == ACT_NONE && ep.residual < 0 &&
+      out == n.outputs[0] && em.c.single_use(out)) {
+    const int rn = em.c.only_consumer(out);
+    if (em.c.node(rn).op == AC_OP_RESHAPE) {
+      const int rv = em.c.node(rn).outputs[0];
+      const Value& rvv = em.c.val(rv);
+      if (rvv.rank == 3 && rvv.dims[0] == p.n && rvv.dims[1] == p.oc && em.c.single_use(rv)) {
+        const int tn = em.c.only_consumer(rv);
+        const Node& tnode = em.c.node(tn);
+        if (tnode.op == AC_OP_TRANSPOSE && tnode.ints.size() == 3 && tnode.ints[0] == 0 &&
+            tnode.ints[1] == 2 && tnode.ints[2] == 1 && !em.c.absorbed[tn]) {
+          const int tokens = tnode.outputs[0];
+          em.c.absorbed[tn] = 1;
+          const int64_t rows = (int64_t)p.n * p.oh * p.ow, kd = (int64_t)p.c * p.kh * p.kw;
+          const int colv = new_value(em.c, rows * kd, false);
+          em.add("patchify", n.op, {x}, {colv}, 2.0 * f32_bytes(xv), 0, [=](cudaStream_t st) {
+            return launch_patchify(p, s->fptr(x), s->fptr_mut(colv), st);
+          });
+          GemmShape g{};
+          g.m = rows; g.k = kd; g.n = p.oc; g.batch = 1;
+          g.lda = kd; g.ldb = kd; g.ldc = p.oc; g.ta = 0; g.tb = 1;   // W is [OC, K]: already K-major
+          emit_gemm(em, n.op, g, colv, w, tokens, -1, bias, -1, 1.f, 0.f, 1.f, nullptr);
+          return;
+        }
+      }
+    }
+  }
   const int icg = p.c / p.group, ocg = p.oc / p.group;
   const int64_t ohw = (int64_t)p.oh * p.ow;
   const int64_t kdim = (int64_t)icg * p.kh * p.kw;

@@ -98,7 +98,32 @@ __global__ void __launch_bounds__(256) im2col_kernel(const float* __restrict__ x
   col[i] = v;
 }
 
+// Patch rows for a convolution whose windows do not overlap (kernel == stride, no
+// padding): the im2col matrix transposed, rows[(n, oy, ox)][(c, fy, fx)], so that the
+// convolution is one GEMM rows x W^T whose output is already [n, tokens, channels].
+__global__ void __launch_bounds__(256) patchify_kernel(const float* __restrict__ x, float* __restrict__ rows,
+                                                       ConvParams p, int64_t total4) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total4) return;
+  const int kw4 = p.kw / 4;
+  const int fx4 = (int)(i % kw4);
+  int64_t r = i / kw4;
+  const int fy = (int)(r % p.kh); r /= p.kh;
+  const int c = (int)(r % p.c); r /= p.c;
+  const int ox = (int)(r % p.ow); r /= p.ow;
+  const int oy = (int)(r % p.oh); r /= p.oh;   // r = image index
+  const float* src = x + ((r * p.c + c) * p.ih + (oy * p.kh + fy)) * (int64_t)p.iw + ox * p.kw + fx4 * 4;
+  reinterpret_cast<float4*>(rows)[i] = __ldg(reinterpret_cast<const float4*>(src));
+}
+
 }  // namespace
+
+cudaError_t launch_patchify(const ConvParams& p, const float* x, float* rows, cudaStream_t st) {
+  const int64_t total4 = (int64_t)p.n * p.oh * p.ow * p.c * p.kh * (p.kw / 4);
+  if (total4 == 0) return cudaSuccess;
+  patchify_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, st>>>(x, rows, p, total4);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_max_pool(const float* x, float* out, int64_t planes, int ih, int iw, int oh,
                             int ow, int kh, int kw, int sh, int sw, int pad_t, int pad_l,

@@ -149,37 +149,57 @@ __device__ __forceinline__ float ln_prologue(const LnDev& p, float v, int col, f
 }
 
 // Vector path: len % 4 == 0, all pointers 16-byte aligned. NV float4 per lane.
-template <int NV>
+// Each warp walks rows warp, warp + nwarps, ...; the next row's loads are issued
+// before the current row is reduced and stored, so reads and writes overlap
+// instead of alternating in phases. FUSED = false compiles the producers out.
+template <int NV, bool FUSED>
+__device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lane, int nvec, float4 (&v)[NV],
+                                            float4 (&r)[NV]) {
+  const float4* xr = reinterpret_cast<const float4*>(p.x + row * p.len);
+  const float4* rr = (FUSED && p.residual) ? reinterpret_cast<const float4*>(p.residual + row * p.len) : nullptr;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      v[i] = __ldg(xr + c);
+      if (FUSED && rr) r[i] = __ldg(rr + c);
+    }
+  }
+}
+
+template <int NV, bool FUSED>
 __global__ void __launch_bounds__(kThreads) layer_norm_vec(LnDev p) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
   const int nvec = p.len >> 2;
   const float inv_n = __fdiv_rn(1.f, (float)p.len);
-  for (int64_t row = warp; row < p.rows; row += nwarps) {
-    const float4* xr = reinterpret_cast<const float4*>(p.x + row * p.len);
-    const float4* rr = p.residual ? reinterpret_cast<const float4*>(p.residual + row * p.len) : nullptr;
-    float4 v[NV];
-    float4 r[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = lane + 32 * i;
-      if (c < nvec) {
-        v[i] = __ldg(xr + c);
-        if (rr) r[i] = __ldg(rr + c);
-      }
+  int64_t row = warp;
+  if (row >= p.rows) return;
+  float4 v[NV], r[FUSED ? NV : 1];
+  float4 nv[NV], nr[FUSED ? NV : 1];
+  if (FUSED) ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
+  else ln_load_row<NV, false>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(v));
+  while (true) {
+    const int64_t next = row + nwarps;
+    const bool has_next = next < p.rows;
+    if (has_next) {
+      if (FUSED) ln_load_row<NV, true>(p, next, lane, nvec, nv, reinterpret_cast<float4(&)[NV]>(nr));
+      else ln_load_row<NV, false>(p, next, lane, nvec, nv, reinterpret_cast<float4(&)[NV]>(nv));
     }
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < nvec) {
-        const float4 rv = rr ? r[i] : make_float4(0, 0, 0, 0);
-        v[i].x = ln_prologue(p, v[i].x, 4 * c + 0, rv.x);
-        v[i].y = ln_prologue(p, v[i].y, 4 * c + 1, rv.y);
-        v[i].z = ln_prologue(p, v[i].z, 4 * c + 2, rv.z);
-        v[i].w = ln_prologue(p, v[i].w, 4 * c + 3, rv.w);
-        if (p.sum_out) reinterpret_cast<float4*>(p.sum_out + row * p.len)[c] = v[i];
+        if (FUSED) {
+          const float4 rv = p.residual ? r[i] : make_float4(0, 0, 0, 0);
+          v[i].x = ln_prologue(p, v[i].x, 4 * c + 0, rv.x);
+          v[i].y = ln_prologue(p, v[i].y, 4 * c + 1, rv.y);
+          v[i].z = ln_prologue(p, v[i].z, 4 * c + 2, rv.z);
+          v[i].w = ln_prologue(p, v[i].w, 4 * c + 3, rv.w);
+          if (p.sum_out) reinterpret_cast<float4*>(p.sum_out + row * p.len)[c] = v[i];
+        }
         sum = __fadd_rn(sum, __fadd_rn(__fadd_rn(v[i].x, v[i].y), __fadd_rn(v[i].z, v[i].w)));
       }
     }
@@ -213,6 +233,13 @@ __global__ void __launch_bounds__(kThreads) layer_norm_vec(LnDev p) {
         o.w = fmaf(__fmul_rn(v[i].w, inv), g.w, b.w);
         orow[c] = o;
       }
+    }
+    if (!has_next) break;
+    row = next;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      v[i] = nv[i];
+      if (FUSED) r[i] = nr[i];
     }
   }
 }
@@ -336,12 +363,22 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
                    al(q.gamma) && al(q.beta) && al(q.sum_out) && al(q.out);
   if (vec) {
     const int nv = (int)((q.len / 4 + 31) / 32);
-    if (nv <= 1) layer_norm_vec<1><<<blocks, kThreads, 0, st>>>(p);
-    else if (nv <= 2) layer_norm_vec<2><<<blocks, kThreads, 0, st>>>(p);
-    else if (nv <= 3) layer_norm_vec<3><<<blocks, kThreads, 0, st>>>(p);
-    else if (nv <= 4) layer_norm_vec<4><<<blocks, kThreads, 0, st>>>(p);
-    else if (nv <= 6) layer_norm_vec<6><<<blocks, kThreads, 0, st>>>(p);
-    else layer_norm_vec<8><<<blocks, kThreads, 0, st>>>(p);
+    const bool fused = q.pre_bias || q.residual || q.gelu || q.sum_out;
+    // Two blocks of 8 warps per SM: several rows per warp, so the prefetch of the next
+    // row overlaps the stores of the current one.
+    const unsigned vblocks = blocks64 > 148 * 2 ? 148 * 2 : (unsigned)blocks64;
+#define AC_LN(NVV)                                                                         \
+  do {                                                                                     \
+    if (fused) layer_norm_vec<NVV, true><<<vblocks, kThreads, 0, st>>>(p);                 \
+    else layer_norm_vec<NVV, false><<<vblocks, kThreads, 0, st>>>(p);                      \
+  } while (0)
+    if (nv <= 1) AC_LN(1);
+    else if (nv <= 2) AC_LN(2);
+    else if (nv <= 3) AC_LN(3);
+    else if (nv <= 4) AC_LN(4);
+    else if (nv <= 6) AC_LN(6);
+    else AC_LN(8);
+#undef AC_LN
   } else {
     layer_norm_generic<<<blocks, kThreads, 0, st>>>(p);
   }
