@@ -27,6 +27,7 @@
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the
 // error word, drains, frees its tensor memory and returns.
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 #include <cstdlib>
@@ -34,22 +35,25 @@
 
 #include "kernels.h"
 #include "ref_math.cuh"
+#include "tc_common.cuh"
 
 namespace ac {
 namespace {
 
+using namespace tc;
+
 constexpr int BM = 128;
-#ifndef AC_TC_BK
-#define AC_TC_BK 16
-#endif
-constexpr int BK = AC_TC_BK;                 // floats per tile row: 16 (64-byte swizzle) or 32 (128-byte swizzle)
+constexpr int BK = 16;                       // floats of K per stage in the TF32 modes (64-byte rows)
+constexpr int BK16 = 32;                     // floats of K per stage in the fp16 mode (64-byte rows of halves)
 constexpr int kSplitGroups = 2;                 // groups of 4 warps taking alternate stages
 constexpr int kSplitWarps = 4 * kSplitGroups;
 constexpr int kSplitThreads = 128;             // threads working on one stage
 constexpr int kThreads = (kSplitWarps + 6) * 32;   // + 4 epilogue warps, TMA warp, MMA warp
-constexpr uint32_t kWaitLimit = 1u << 24;    // polls before a wait gives up
 
-enum TcMode { TC_3X_BLO_TMA = 0, TC_3X_SPLIT_B = 1, TC_1X = 2 };
+// TC_F16X3: operands split into fp16 hi + fp16 (remainder * 2^11); hi*hi goes to one
+// accumulator, the two cross terms (scaled by 2^11) to a second one.
+enum TcMode { TC_3X_BLO_TMA = 0, TC_3X_SPLIT_B = 1, TC_1X = 2, TC_F16X3 = 3 };
+constexpr float kLoScale = 2048.f, kLoUnscale = 1.f / 2048.f;
 
 struct TcEpilogue {
   int m, n;
@@ -61,80 +65,6 @@ struct TcEpilogue {
   const float* res; long long ldres, sres;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-// Bounded wait on the phase with the given parity. Returns false on expiry.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
-                                            int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
-        "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-        "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
-        "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 // Shared-memory matrix descriptor for a K-major tile whose rows are 64 bytes
 // (16 floats), stored row after row with the 64-byte swizzle: 8-row groups are
 // 512 bytes apart (stride byte offset), the leading byte offset is unused.
@@ -142,33 +72,58 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3FFF);        // start address
   d |= (uint64_t)1 << 16;                        // leading byte offset (ignored for swizzled K-major)
-  d |= (uint64_t)((8 * BK * 4) >> 4) << 32;      // stride byte offset: 8 rows
+  d |= (uint64_t)((8 * 64) >> 4) << 32;          // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                        // descriptor version for this architecture
-  d |= (uint64_t)(BK == 32 ? 2 : 4) << 61;       // 128-byte or 64-byte swizzle
+  d |= (uint64_t)4 << 61;                        // 64-byte swizzle
   return d;
 }
 
-// Round to nearest (ties away from zero) to TF32's 10 mantissa bits, on the
-// integer ALU: cvt.rna.tf32.f32 gives the same bits but issues on the
-// quarter-rate conversion pipe.
-__device__ __forceinline__ float round_tf32(float x) {
-  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+// Code left in the error word when an operand does not fit the fp16 split.
+constexpr int kRangeCode = 21;
+
+// |x| > 65504 (the largest fp16), infinities included, NaN excluded.
+__device__ __forceinline__ unsigned beyond_half(float x) {
+  const unsigned ab = __float_as_uint(x) & 0x7FFFFFFFu;
+  return (ab - 0x477FE001u) <= (0x7F800000u - 0x477FE001u) ? 1u : 0u;
 }
-// hi = rn_tf32(x), lo = rn_tf32(x - hi), for 4 packed floats.
-__device__ __forceinline__ void tf32_split(float4 v, float4& hi, float4& lo) {
-  hi.x = round_tf32(v.x); lo.x = round_tf32(__fsub_rn(v.x, hi.x));
-  hi.y = round_tf32(v.y); lo.y = round_tf32(__fsub_rn(v.y, hi.y));
-  hi.z = round_tf32(v.z); lo.z = round_tf32(__fsub_rn(v.z, hi.z));
-  hi.w = round_tf32(v.w); lo.w = round_tf32(__fsub_rn(v.w, hi.w));
+// hi = rn_fp16(x); lo = rn_fp16((x - hi) * 2^11); x - hi is exact in fp32.
+__device__ __forceinline__ void f16_split(float4 x, uint2& hi, uint2& lo) {
+  const __half2 h01 = __floats2half2_rn(x.x, x.y), h23 = __floats2half2_rn(x.z, x.w);
+  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+  const __half2 l01 = __floats2half2_rn(__fmul_rn(__fsub_rn(x.x, f01.x), kLoScale),
+                                        __fmul_rn(__fsub_rn(x.y, f01.y), kLoScale));
+  const __half2 l23 = __floats2half2_rn(__fmul_rn(__fsub_rn(x.z, f23.x), kLoScale),
+                                        __fmul_rn(__fsub_rn(x.w, f23.y), kLoScale));
+  hi.x = *reinterpret_cast<const uint32_t*>(&h01); hi.y = *reinterpret_cast<const uint32_t*>(&h23);
+  lo.x = *reinterpret_cast<const uint32_t*>(&l01); lo.y = *reinterpret_cast<const uint32_t*>(&l23);
 }
 
+// 32 accumulator columns of this warp's rows. D2OFF != 0: the fp16 mode's second
+// accumulator (cross terms, scaled by 2^11) sits D2OFF columns further on.
+template <int D2OFF>
+__device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32]) {
+  tc_ld_32x32(taddr, v);
+  if (D2OFF != 0) {
+    uint32_t w[32];
+    tc_ld_32x32(taddr + (uint32_t)D2OFF, w);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      v[j] = __float_as_uint(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])));
+  }
+}
+
+// Byte offset of 8-byte chunk `c8` (4 halves) of row `row` in a K-major fp16 tile with
+// 64-byte rows and the 64-byte swizzle (16-byte chunks XORed with bits 1-2 of the row).
+__device__ __forceinline__ uint32_t sw64_off8(int row, int c8) {
+  return (uint32_t)((row >> 3) * 512 + (row & 7) * 64 + (((c8 >> 1) ^ ((row & 7) >> 1)) << 4) + (c8 & 1) * 8);
+}
 
 // Epilogue of one warp's 32 rows. The accumulator chunk arrives with one thread
 // per row (32 columns each); it goes through a 4 KB shared-memory tile so that
 // each group of 8 lanes then owns one row's 128 contiguous bytes: global loads
 // and stores are full lines. 16-byte chunks are XOR-swizzled by the row, which
 // keeps both the row-wise writes and the transposed reads free of bank conflicts.
-template <int BN>
+template <int BN, int D2OFF>
 __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
                                               int warp, int lane, int m0, int n0, int bz) {
       float* c = ep.c + (long long)bz * ep.sc;
@@ -185,7 +140,7 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
         const int col0 = n0 + cc * 32;
         if (col0 >= ep.n) break;           // uniform across the warp
         uint32_t v[32];
-        tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+        load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -264,7 +219,7 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
 // Same data path for the common epilogues (alpha 1, no C input, no row bias,
 // everything 16-byte aligned, N a multiple of 4), with the options fixed at
 // compile time and the eight rows of a chunk processed as independent streams.
-template <int BN, int ACT, bool HAS_BIAS, bool HAS_RES>
+template <int BN, int D2OFF, int ACT, bool HAS_BIAS, bool HAS_RES>
 __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
                                               int warp, int lane, int m0, int n0, int bz) {
   float* c = ep.c + (long long)bz * ep.sc;
@@ -276,7 +231,7 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
     const int col0 = n0 + cc * 32;
     if (col0 >= ep.n) break;
     uint32_t v[32];
-    tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -323,14 +278,14 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
 
 // Unreduced accumulator of a K-slice -> workspace tile [128][BN], same staging
 // as the real epilogues so that the stores are full lines.
-template <int BN>
+template <int BN, int D2OFF>
 __device__ __forceinline__ void epilogue_raw(float* ws_tile, float4* stage, uint32_t tmem_base, int warp,
                                              int lane) {
   const int c4 = lane & 7, rsub = lane >> 3;
 #pragma unroll 1
   for (int cc = 0; cc < BN / 32; ++cc) {
     uint32_t v[32];
-    tc_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -348,20 +303,21 @@ __device__ __forceinline__ void epilogue_raw(float* ws_tile, float4* stage, uint
 }
 
 // Adds the K-slices of the tail tiles in slice order and applies the epilogue.
-__global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ ws, TcEpilogue ep, int bn,
-                                                            int dp_tiles, int parts, int tiles_m, int tiles_n) {
+__global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ ws, TcEpilogue ep, int bm,
+                                                            int bn, int dp_tiles, int parts, int tiles_m,
+                                                            int tiles_n) {
   const int tt = blockIdx.y;
   const int t = dp_tiles + tt;
   const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
   const int e4 = blockIdx.x * 256 + threadIdx.x;          // float4 index inside the tile
-  if (e4 >= BM * bn / 4) return;
+  if (e4 >= bm * bn / 4) return;
   const int rl = e4 / (bn / 4), cl = (e4 % (bn / 4)) * 4;
-  const int row = tm * BM + rl, col0 = tn * bn + cl;
+  const int row = tm * bm + rl, col0 = tn * bn + cl;
   if (row >= ep.m || col0 >= ep.n) return;
-  const float* src = ws + (size_t)tt * parts * BM * bn + (size_t)rl * bn + cl;
+  const float* src = ws + (size_t)tt * parts * bm * bn + (size_t)rl * bn + cl;
   float4 acc = __ldg(reinterpret_cast<const float4*>(src));
   for (int p = 1; p < parts; ++p) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(src + (size_t)p * BM * bn));
+    const float4 v = __ldg(reinterpret_cast<const float4*>(src + (size_t)p * bm * bn));
     acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
     acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
   }
@@ -392,15 +348,31 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
   }
 }
 
-template <int BN>
+// Shared-memory stage of the main loop. MT = 128-row sub-tiles per CTA tile.
+// TF32 modes: A arrives by TMA where its hi copy lives (split in place), lo beside it.
+// fp16 mode: A arrives as fp32 rows of 32 floats (no swizzle) in a raw area and the
+// splitters write the fp16 hi / lo tiles; B arrives as fp16 hi / lo by TMA.
+template <int BN, int MT, int MODE>
 struct TcSmem {
-  static constexpr int kABytes = BM * BK * 4;
-  static constexpr int kBBytes = BN * BK * 4;
-  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;   // hi + lo of both operands
-  static constexpr int kStages = (200 * 1024) / kStageBytes;      // 4 (BN 256), 6 (BN 128), 8 (BN 64)
+  static constexpr bool kF16 = MODE == TC_F16X3;
+  static constexpr int kKb = kF16 ? BK16 : BK;                          // floats of K per stage
+  static constexpr int kARaw = kF16 ? MT * BM * kKb * 4 : 0;
+  static constexpr int kABytes = kF16 ? MT * BM * kKb * 2 : MT * BM * kKb * 4;   // one of A hi / lo
+  static constexpr int kBBytes = kF16 ? BN * kKb * 2 : BN * kKb * 4;             // one of B hi / lo
+  static constexpr int kOffAHi = kARaw;
+  static constexpr int kOffALo = kARaw + kABytes;
+  static constexpr int kOffBHi = kARaw + 2 * kABytes;
+  static constexpr int kOffBLo = kOffBHi + kBBytes;
+  static constexpr int kStageBytes = kARaw + 2 * kABytes + 2 * kBBytes;
+  static constexpr int kTxBytes = (kF16 ? kARaw : kABytes) + kBBytes + ((kF16 || MODE == TC_3X_BLO_TMA) ? kBBytes : 0);
+  static constexpr int kStages = (200 * 1024) / kStageBytes;      // TF32: 4 / 6 / 8; fp16: 3 / 4 / 5 (BN 256 / 128 / 64)
   static constexpr int kEpiBytes = 4 * 4096;                      // one 4 KB transpose tile per epilogue warp
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
+  static constexpr int kAccCols = (kF16 ? 2 : 1) * MT * BN;       // tensor-memory columns of one accumulator set
+  static constexpr int kNumAcc = (2 * kAccCols <= 512) ? 2 : 1;   // sets: two when they fit (epilogue overlaps)
+  static constexpr int kD2Off = kF16 ? MT * BN : 0;               // column offset of the cross-term accumulator
   static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
+  static_assert(kAccCols <= 512, "tensor memory");
 };
 
 // Work distribution of the persistent kernel. The first `dp_tiles` tiles (whole
@@ -442,13 +414,16 @@ __device__ __forceinline__ bool tc_get_work(const TcSched& sc, int w, TcWork* ou
 //   warps 8-11  epilogue (warp w owns TMEM lanes 32*(w-8) .. +31)
 //   warp  12    TMA producer (one thread)
 //   warp  13    MMA issuer (one thread); allocates and frees tensor memory
-template <int BN, int MODE>
+template <int BN, int MT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, TcSched sc, int b_batched,
                int tiles_m, int tiles_n, float* workspace, int* err) {
-  using L = TcSmem<BN>;
+  using L = TcSmem<BN, MT, MODE>;
   constexpr int S = L::kStages;
+  constexpr int NACC = L::kNumAcc;      // accumulator sets in tensor memory
+  constexpr int KB = L::kKb;            // floats of K per stage
+  constexpr int D2 = L::kD2Off;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + S * L::kStageBytes;
@@ -462,12 +437,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = 2 * BN;   // 128, 256 or 512: a power of two
+  constexpr uint32_t kTmemCols = NACC * L::kAccCols;   // 128, 256 or 512: a power of two
 
-  auto a_hi = [&](int s) { return smem + s * L::kStageBytes; };
-  auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kABytes; };
-  auto b_hi = [&](int s) { return smem + s * L::kStageBytes + 2 * L::kABytes; };
-  auto b_lo = [&](int s) { return smem + s * L::kStageBytes + 2 * L::kABytes + L::kBBytes; };
+  auto a_raw = [&](int s) { return smem + s * L::kStageBytes; };
+  auto a_hi = [&](int s) { return smem + s * L::kStageBytes + L::kOffAHi; };
+  auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kOffALo; };
+  auto b_hi = [&](int s) { return smem + s * L::kStageBytes + L::kOffBHi; };
+  auto b_lo = [&](int s) { return smem + s * L::kStageBytes + L::kOffBLo; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -496,7 +472,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   if (warp == kSplitWarps + 4) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const uint32_t bytes = L::kABytes + L::kBBytes + (MODE == TC_3X_BLO_TMA ? L::kBBytes : 0);
+      const uint32_t bytes = L::kTxBytes;
       int it = 0;   // running K-block count over all of this CTA's tiles
       bool ok = true;
       TcWork wk;
@@ -509,47 +485,58 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
           mbar_arrive_expect_tx(&full[s], bytes);
-          tma_load_3d(a_hi(s), &tm_a, &full[s], kb * BK, tm * BM, bz);
-          tma_load_3d(b_hi(s), &tm_b, &full[s], kb * BK, tn * BN, bzb);
-          if (MODE == TC_3X_BLO_TMA) tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * BK, tn * BN, bzb);
+          tma_load_3d(a_raw(s), &tm_a, &full[s], kb * KB, tm * (MT * BM), bz);   // TF32 modes: a_raw == a_hi
+          tma_load_3d(b_hi(s), &tm_b, &full[s], kb * KB, tn * BN, bzb);
+          if (MODE == TC_3X_BLO_TMA || MODE == TC_F16X3)
+            tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * KB, tn * BN, bzb);
         }
       }
     }
   } else if (warp == kSplitWarps + 5) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      // Instruction descriptor: fp32 accumulator, TF32 A and B, both K-major, N = BN, M = 128.
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+      // Instruction descriptor: fp32 accumulator, A and B both TF32 (format 2) or both
+      // fp16 (format 0), both K-major, N = BN, M = 128.
+      constexpr uint32_t kFmt = MODE == TC_F16X3 ? 0u : 2u;
+      const uint32_t idesc = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((uint32_t)(BN >> 3) << 17) |
                              ((uint32_t)(BM >> 4) << 24);
       int it = 0, ti = 0;
       bool ok = true;
       TcWork wk;
       for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w, ++ti) {
-        const int ab = ti & 1;
-        // The epilogue must have drained this accumulator (two tiles ago).
-        if (!mbar_wait(&acc_empty[ab], ((ti >> 1) & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
+        const int ab = ti % NACC;
+        // The epilogue must have drained this accumulator (NACC tiles ago).
+        if (!mbar_wait(&acc_empty[ab], ((ti / NACC) & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(ab * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(ab * L::kAccCols);
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
           if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
           tc_fence_after();
-          const uint64_t da = make_smem_desc(smem_u32(a_hi(s)));
-          const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)));
           const uint64_t db = make_smem_desc(smem_u32(b_hi(s)));
           const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)));
 #pragma unroll
-          for (int kk = 0; kk < BK / 8; ++kk) {
-            const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats = 32 bytes along K
+          for (int kk = 0; kk < 2; ++kk) {                  // two K-steps per 64-byte row
+            const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats or 16 halves = 32 bytes along K
             const uint32_t acc = (kb > wk.k0 || kk > 0) ? 1u : 0u;
-            if (MODE == TC_1X) {
-              tc_mma_tf32(d_tmem, da + off, db + off, idesc, acc);
-            } else {
-              tc_mma_tf32(d_tmem, dal + off, db + off, idesc, acc);   // a_lo * b_hi
-              tc_mma_tf32(d_tmem, da + off, dbl + off, idesc, 1u);    // a_hi * b_lo
-              tc_mma_tf32(d_tmem, da + off, db + off, idesc, 1u);     // a_hi * b_hi
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint64_t da = make_smem_desc(smem_u32(a_hi(s) + mt * (BM * 64)));
+              const uint64_t dal = make_smem_desc(smem_u32(a_lo(s) + mt * (BM * 64)));
+              const uint32_t d = d_tmem + (uint32_t)(mt * BN);
+              if (MODE == TC_F16X3) {
+                tc_mma_f16(d, da + off, db + off, idesc, acc);            // a_hi * b_hi
+                tc_mma_f16(d + D2, dal + off, db + off, idesc, acc);      // a_lo' * b_hi  (scaled by 2^11)
+                tc_mma_f16(d + D2, da + off, dbl + off, idesc, 1u);       // a_hi * b_lo'
+              } else if (MODE == TC_1X) {
+                tc_mma_tf32(d, da + off, db + off, idesc, acc);
+              } else {
+                tc_mma_tf32(d, dal + off, db + off, idesc, acc);   // a_lo * b_hi
+                tc_mma_tf32(d, da + off, dbl + off, idesc, 1u);    // a_hi * b_lo
+                tc_mma_tf32(d, da + off, db + off, idesc, 1u);     // a_hi * b_hi
+              }
             }
           }
           tc_commit(&empty[s]);
@@ -564,6 +551,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int group = threadIdx.x / kSplitThreads;   // takes the K-blocks with it % kSplitGroups == group
       int it = 0;
       bool ok = true;
+      unsigned range_bad = 0;
       TcWork wk;
       for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w) {
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
@@ -572,6 +560,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const uint32_t ph = (it / S) & 1;
           ok = mbar_wait(&full[s], ph);
           if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
+          if (MODE == TC_F16X3) {
+            // fp32 rows of 32 floats -> fp16 hi / lo tiles; one float4 (4 consecutive k) per item.
+            const float4* raw = reinterpret_cast<const float4*>(a_raw(s));
+            uint8_t* hi_t = a_hi(s);
+            uint8_t* lo_t = a_lo(s);
+#pragma unroll
+            for (int i = 0; i < L::kARaw / 16 / kSplitThreads; ++i) {
+              const int item = i * kSplitThreads + t0;
+              const float4 x = raw[item];
+              range_bad |= beyond_half(x.x) | beyond_half(x.y) | beyond_half(x.z) | beyond_half(x.w);
+              uint2 hi, lo;
+              f16_split(x, hi, lo);
+              const uint32_t off = sw64_off8(item >> 3, item & 7);
+              *reinterpret_cast<uint2*>(hi_t + off) = hi;
+              *reinterpret_cast<uint2*>(lo_t + off) = lo;
+            }
+          } else {
           float4* src = reinterpret_cast<float4*>(a_hi(s));
           float4* dst = reinterpret_cast<float4*>(a_lo(s));
 #pragma unroll
@@ -580,6 +585,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tf32_split(src[i * kSplitThreads + t0], hi, lo);
             src[i * kSplitThreads + t0] = hi;
             dst[i * kSplitThreads + t0] = lo;
+          }
           }
           if (MODE == TC_3X_SPLIT_B) {
             float4* sb = reinterpret_cast<float4*>(b_hi(s));
@@ -596,6 +602,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           mbar_arrive(&ready[s]);
         }
       }
+      // An element of A too large for fp16: the result is not to be used (the host
+      // re-runs on the TF32 path); a code from a timed-out wait takes precedence.
+      if (MODE == TC_F16X3 && range_bad) atomicCAS(err, 0, kRangeCode);
     }
   } else {
     // ---------------- epilogue (warps 4-7) ----------------
@@ -613,22 +622,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     for (int w = 0; tc_get_work(sc, w, &wk); ++w, ++ti) {
       const int t = wk.tile;
       const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
-      const int ab = ti & 1;
-      if (!mbar_wait(&acc_full[ab], (ti >> 1) & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
+      const int ab = ti % NACC;
+      if (!mbar_wait(&acc_full[ab], (ti / NACC) & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
       tc_fence_after();
-      const uint32_t acc = tmem_base + (uint32_t)(ab * BN);
-      const int m0 = tm * BM, n0 = tn * BN;
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+      const uint32_t acc = tmem_base + (uint32_t)(ab * L::kAccCols + mt * BN);
+      const int m0 = (tm * MT + mt) * BM, n0 = tn * BN;
+      if (m0 >= ep.m) break;                     // uniform: the second sub-tile may lie past M
       if (wk.raw >= 0) {
-        epilogue_raw<BN>(workspace + (size_t)wk.raw * BM * BN, stage, acc, q, lane);
+        epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane);
       } else
       switch (key) {
-        case 0: epilogue_fast<BN, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case 1: epilogue_fast<BN, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case 2: epilogue_fast<BN, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case 3: epilogue_fast<BN, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case (ACT_GELU << 2) | 1: epilogue_fast<BN, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case (ACT_RELU << 2) | 1: epilogue_fast<BN, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        default: epilogue_generic<BN>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        default: epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz); break;
+      }
       }
       // Every tcgen05.ld of this warp has completed (each is followed by
       // wait::ld): hand the accumulator back to the MMA warp.
@@ -668,6 +681,20 @@ __global__ void tf32_split_kernel(const float* __restrict__ x, float* __restrict
   }
 }
 
+// fp16 hi / lo split of a constant [rows, k] operand (row stride ld) into [rows, k8]
+// halves, columns k .. k8-1 zero. An element beyond fp16 leaves kRangeCode in *err.
+__global__ void f16_split_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo,
+                                 int64_t rows, int64_t k, int64_t ld, int64_t k8, int* err) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * k8) return;
+  const int64_t r = i / k8, c = i % k8;
+  const float v = c < k ? __ldg(x + r * ld + c) : 0.f;
+  const __half h = __float2half_rn(v);
+  hi[i] = h;
+  lo[i] = __float2half_rn(__fmul_rn(__fsub_rn(v, __half2float(h)), kLoScale));
+  if (beyond_half(v)) atomicCAS(err, 0, kRangeCode);
+}
+
 // ---- host side ---------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -687,19 +714,21 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 3-D map over a row-major [batch, rows, k] f32 tensor: box = BK floats of K x box_rows rows.
-bool make_map(CUtensorMap* map, const float* base, int64_t k, int64_t rows, int64_t batch, int64_t ld,
-              int64_t batch_stride, int box_rows) {
+// 3-D map over a row-major [batch, rows, k] tensor of f32 (elem_bytes 4) or fp16 (2):
+// box = box_k elements of K x box_rows rows. Swizzled boxes are 64 bytes wide.
+bool make_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t k, int64_t rows, int64_t batch,
+              int64_t ld, int64_t batch_stride, int box_k, int box_rows, bool swizzle64) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(batch, 1)};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 4,
-                           (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * 4};
-  cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1};
-  static_assert(BK * 4 == 64 || BK * 4 == 128, "box rows are one swizzle span");
+  cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes,
+                           (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * elem_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
+  if (swizzle64 && box_k * elem_bytes != 64) return false;
   cuuint32_t estr[3] = {1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, BK == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -721,13 +750,13 @@ struct TcPlan {
   TcSched sc;
   size_t workspace_bytes;
 };
-TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn) {
+TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn, int mt, int kb_floats) {
   TcPlan pl{};
   const int sms = sm_count();
   pl.tiles_n = (int)((n + bn - 1) / bn);
-  pl.tiles_m = (int)((m + BM - 1) / BM);
+  pl.tiles_m = (int)((m + mt * BM - 1) / (mt * BM));
   const long long tiles = (long long)pl.tiles_n * pl.tiles_m * batch;
-  const int num_kb = (int)((k + BK - 1) / BK);
+  const int num_kb = (int)((k + kb_floats - 1) / kb_floats);
   pl.sc.num_tiles = (int)tiles;
   pl.sc.num_kb = num_kb;
   pl.sc.dp_tiles = (int)tiles;
@@ -742,31 +771,31 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn) {
       pl.sc.tail_parts = parts;
       pl.grid = std::max(pl.grid, tail * parts);
       pl.grid = std::min(pl.grid, sms);
-      pl.workspace_bytes = (size_t)tail * parts * BM * bn * sizeof(float);
+      pl.workspace_bytes = (size_t)tail * parts * mt * BM * bn * sizeof(float);
     }
   }
   return pl;
 }
 
-template <int BN, int MODE>
+template <int BN, int MT, int MODE>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mbl,
                       const TcEpilogue& ep, const TcPlan& pl, int b_batched, float* workspace, int* err,
                       cudaStream_t st) {
-  using L = TcSmem<BN>;
+  using L = TcSmem<BN, MT, MODE>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::kDynBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  gemm_tc_kernel<BN, MODE><<<pl.grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, pl.sc, b_batched, pl.tiles_m,
+  gemm_tc_kernel<BN, MT, MODE><<<pl.grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, pl.sc, b_batched, pl.tiles_m,
                                                                     pl.tiles_n, workspace, err);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || pl.sc.tail_parts < 2) return e;
   const int tail = pl.sc.num_tiles - pl.sc.dp_tiles;
-  dim3 grid((BM * BN / 4 + 255) / 256, tail);
-  gemm_tc_fixup_kernel<<<grid, 256, 0, st>>>(workspace, ep, BN, pl.sc.dp_tiles, pl.sc.tail_parts, pl.tiles_m,
+  dim3 grid((MT * BM * BN / 4 + 255) / 256, tail);
+  gemm_tc_fixup_kernel<<<grid, 256, 0, st>>>(workspace, ep, MT * BM, BN, pl.sc.dp_tiles, pl.sc.tail_parts, pl.tiles_m,
                                              pl.tiles_n);
   return cudaGetLastError();
 }
@@ -784,52 +813,78 @@ bool gemm_tc_supported(const GemmParams& q) {
   return encode_fn() != nullptr;
 }
 
-int gemm_tc_pick_bn(int64_t m, int64_t n, int64_t batch, bool b_presplit) {
+namespace {
+struct TcShape { int bn, mt; };
+
+// Tile shape by a cost model in SM clocks, fitted to measurements: TMA fills shared
+// memory at about 28 bytes per clock per SM (8 TB/s over the chip, the L2 -> SM
+// limit), and an MMA of 128 x BN x 32 bytes of K takes about (4096 + 32 BN) / 64 clocks
+// (it is bound by fetching its operands from shared memory). A stage costs the larger
+// of its MMA time and its operand bytes; rounds come from the same plan the launch uses
+// (a K-sliced tail costs 1 / parts of a round); a shape that fills tensor memory with
+// one accumulator set cannot hide its epilogue. variant: 0 TF32 with B arriving split,
+// 1 TF32 with one B copy, 2 fp16 split.
+TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant) {
+  static const TcShape cands[3] = {{256, 1}, {128, 1}, {64, 1}};
   // Debug toggle: ALTIUS_CUDA_TC_BN=64|128|256 forces the tile width.
-  if (const char* e = std::getenv("ALTIUS_CUDA_TC_BN")) {
-    const int v = std::atoi(e);
-    if (v == 64 || v == 128 || v == 256) return v;
-  }
-  // Measured: the main loop is fed from L2 at about 27 bytes per clock per SM
-  // (7 TB/s over the chip) and three TF32 MMAs per K-step of a 128 x BN tile take
-  // 0.75 * BN clocks. A tile shape costs the larger of its rounds of MMA time and
-  // its share of the operand traffic; B arrives as hi + lo when it is a constant.
-  const int cands[3] = {256, 128, 64};
+  const char* ebn = std::getenv("ALTIUS_CUDA_TC_BN");
+  const int fbn = ebn ? std::atoi(ebn) : 0;
   const int sms = sm_count();
-  int best = 256;
+  const bool f16 = variant == 2;
+  const int kbf = f16 ? BK16 : BK;
+  TcShape best = {256, 1};
   double best_cost = 1e300;
   for (int i = 0; i < 3; ++i) {
-    const int bn = cands[i];
-    const int64_t tiles = ((m + BM - 1) / BM) * ((n + bn - 1) / bn) * batch;
-    const double rounds = (double)((tiles + sms - 1) / sms);
-    const double mma_clk = rounds * (bn == 64 ? 72.0 : 0.75 * bn * 2);        // per 16-float K-block
-    const double bytes = (double)tiles * (BM * 64.0 + bn * 64.0 * (b_presplit ? 2 : 1));
-    const double feed_clk = bytes / (27.0 * sms);
-    const double cost = std::max(mma_clk, feed_clk) + 0.02 * rounds * 16;
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+    const TcShape c = cands[i];
+    if (fbn && c.bn != fbn) continue;
+    const TcPlan pl = make_plan(m, n, k, batch, c.bn, c.mt, kbf);
+    double rounds = (double)(pl.sc.dp_tiles / sms) + (pl.sc.dp_tiles % sms ? 1.0 : 0.0);
+    if (pl.sc.tail_parts >= 2) rounds += 1.0 / pl.sc.tail_parts + 0.05;
+    const double mma_clk = c.mt * 6.0 * (4096.0 + 32.0 * c.bn) / 64.0 * (variant == 1 ? 1.0 / 3.0 : 1.0);
+    const double a_bytes = c.mt * BM * kbf * 4.0;
+    const double b_bytes = f16 ? c.bn * kbf * 4.0 : c.bn * kbf * 4.0 * (variant == 0 ? 2 : 1);
+    const double feed_clk = (a_bytes + b_bytes) / 28.0;
+    const int acc_cols = (f16 ? 2 : 1) * c.mt * c.bn;
+    const double epi_clk = 2 * acc_cols <= 512 ? 0.0 : c.mt * c.bn * (f16 ? 24.0 : 18.0);
+    double cost = rounds * (pl.sc.num_kb * std::max(mma_clk, feed_clk) + epi_clk);
+    if (pl.sc.num_tiles < sms) cost += 1.0;   // ties: prefer the shape with more tiles in flight
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = c; }
   }
   return best;
 }
+}  // namespace
 
-size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, bool b_presplit) {
-  const int bn = gemm_tc_pick_bn(m, n, batch, b_presplit);
-  return make_plan(m, n, k, batch, bn).workspace_bytes;
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant) {
+  const TcShape sh = pick_shape(m, n, k, batch, variant);
+  return make_plan(m, n, k, batch, sh.bn, sh.mt, variant == 2 ? BK16 : BK).workspace_bytes;
 }
 
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
   if (!gemm_tc_supported(q)) return cudaErrorInvalidValue;
-  const int bn = gemm_tc_pick_bn(q.m, q.n, q.batch, mode != 2 && q.b_lo != nullptr);
+  // mode 0: fp16 split when B comes with one, else 3xTF32; 2: 1xTF32; 3: 3xTF32.
+  const int kmode = mode == 2 ? TC_1X
+                    : (mode == 0 && q.b16_hi && q.b16_lo) ? TC_F16X3
+                    : (q.b_lo ? TC_3X_BLO_TMA : TC_3X_SPLIT_B);
+  const int variant = kmode == TC_F16X3 ? 2 : (kmode == TC_3X_BLO_TMA ? 0 : 1);
+  const TcShape sh = pick_shape(q.m, q.n, q.k, q.batch, variant);
+  const int bn = sh.bn;
   CUtensorMap ma, mb, mbl;
   const int b_batched = (q.batch > 1 && q.stride_b > 0) ? 1 : 0;
-  if (!make_map(&ma, q.a, q.k, q.m, q.batch, q.lda, q.stride_a, BM)) return cudaErrorInvalidValue;
-  if (!make_map(&mb, q.b, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, bn))
-    return cudaErrorInvalidValue;
-  int kmode = mode == 2 ? TC_1X : (q.b_lo ? TC_3X_BLO_TMA : TC_3X_SPLIT_B);
-  if (kmode == TC_3X_BLO_TMA) {
-    if (!make_map(&mbl, q.b_lo, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, bn))
-      return cudaErrorInvalidValue;
+  if (kmode == TC_F16X3) {
+    if (b_batched || (q.ldb16 % 8) != 0) return cudaErrorInvalidValue;
+    if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK16, sh.mt * BM, false)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, bn, true)) return cudaErrorInvalidValue;
+    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, bn, true)) return cudaErrorInvalidValue;
   } else {
-    mbl = mb;
+    if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK, sh.mt * BM, true)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, true))
+      return cudaErrorInvalidValue;
+    if (kmode == TC_3X_BLO_TMA) {
+      if (!make_map(&mbl, q.b_lo, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, true))
+        return cudaErrorInvalidValue;
+    } else {
+      mbl = mb;
+    }
   }
   TcEpilogue ep;
   ep.m = (int)q.m; ep.n = (int)q.n;
@@ -839,7 +894,7 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.bias_n = q.bias_n; ep.bias_m = q.bias_m; ep.bias_scale = q.bias_scale;
   ep.act = q.act; ep.act_alpha = q.act_alpha; ep.act_beta = q.act_beta;
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
-  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn);
+  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, kmode == TC_F16X3 ? BK16 : BK);
   if (pl.sc.tail_parts >= 2 && (!q.workspace || q.workspace_bytes < pl.workspace_bytes)) {
     // No (or too small a) workspace: fall back to whole tiles only.
     pl.sc.dp_tiles = pl.sc.num_tiles;
@@ -847,14 +902,25 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   }
   float* ws = q.workspace;
 #define AC_TC(BNV)                                                                              \
-  (kmode == TC_1X ? launch_tc<BNV, TC_1X>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)     \
+  (kmode == TC_1X ? launch_tc<BNV, 1, TC_1X>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)     \
+   : kmode == TC_F16X3                                                                          \
+       ? launch_tc<BNV, 1, TC_F16X3>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)           \
    : kmode == TC_3X_BLO_TMA                                                                     \
-       ? launch_tc<BNV, TC_3X_BLO_TMA>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)        \
-       : launch_tc<BNV, TC_3X_SPLIT_B>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st))
+       ? launch_tc<BNV, 1, TC_3X_BLO_TMA>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)      \
+       : launch_tc<BNV, 1, TC_3X_SPLIT_B>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st))
   if (bn == 256) return AC_TC(256);
   if (bn == 128) return AC_TC(128);
   return AC_TC(64);
 #undef AC_TC
+}
+
+cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, int64_t k, int64_t ld, int64_t k8,
+                             int* err_word, cudaStream_t st) {
+  const int64_t n = rows * k8;
+  if (n == 0) return cudaSuccess;
+  f16_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, static_cast<__half*>(hi), static_cast<__half*>(lo),
+                                                               rows, k, ld, k8, err_word);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st) {

@@ -128,6 +128,9 @@ struct GemmParams {
   const float* b; int64_t ldb; int64_t stride_b; int trans_b;
   const float* b_lo;        // tensor-core path only: when set, `b` holds the TF32-rounded values of
                             // B and `b_lo` the rounded remainders, same layout; or null
+  const void* b16_hi;       // tensor-core path only: fp16 split of a constant B, [n, ldb16] halves each:
+  const void* b16_lo;       // hi = rn_fp16(B), lo = rn_fp16((B - hi) * 2^11); or null
+  int64_t ldb16;            // a multiple of 8
   float* c; int64_t ldc; int64_t stride_c;
   float alpha;
   float beta;               // applied to c_in (may alias c); 0: c_in not read
@@ -145,12 +148,21 @@ cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
 
 // tcgen05 / TMEM / TMA path. Needs A row-major with K contiguous (trans_a == 0)
 // and B stored [N, K] (trans_b == 1), 16-byte aligned bases and leading
-// dimensions that are multiples of 4 floats. mode 0: 3xTF32, mode 2: 1xTF32.
-// `err_word` (device memory) receives a non-zero code if a bounded wait expired.
+// dimensions that are multiples of 4 floats. mode 0: the fp16 split (three fp16
+// MMAs per product) when b16_hi / b16_lo are given, else 3xTF32; 2: 1xTF32; 3: 3xTF32.
+// `err_word` (device memory) receives a non-zero code if a bounded wait expired, or
+// kGemmRangeCode if an element of A does not fit the fp16 split (result unusable).
 bool gemm_tc_supported(const GemmParams& p);
 cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStream_t st);
 // Scratch the tensor-core path wants for this problem (0 when its tiles fill whole rounds).
-size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, bool b_presplit);
+// variant: 0 TF32 with B arriving split, 1 TF32 with one copy of B, 2 fp16 split.
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant);
+constexpr int kGemmRangeCode = 21;
+// fp16 split of a constant [rows, k] operand (row stride ld) into [rows, k8] halves
+// (k8 >= k, a multiple of 8, padding zero); leaves kGemmRangeCode in *err_word when an
+// element exceeds the fp16 range.
+cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, int64_t k, int64_t ld, int64_t k8,
+                             int* err_word, cudaStream_t st);
 // hi[i] = rn_tf32(x[i]); lo[i] = rn_tf32(x[i] - hi[i])
 cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st);
 
@@ -164,8 +176,14 @@ struct AttentionParams {
   int batch, heads, tokens, head_dim;
   const float* scale;   // device scalar or null
   int scale_mode;       // 1: multiply, 2: divide
+  int use_tc;           // take the tcgen05 kernel when it supports the shape
+  int* err_word;        // device word for the tcgen05 kernel's bounded waits (or null)
 };
 bool attention_supported(const AttentionParams& p);
+// Dispatches to the tcgen05 kernel (use_tc and attention_tc_supported) or the CUDA-core kernel.
 cudaError_t launch_attention(const AttentionParams& p, cudaStream_t st);
+// tcgen05 kernel: head_dim 64, 64 < tokens <= 256, 3xTF32 products.
+bool attention_tc_supported(const AttentionParams& p);
+cudaError_t launch_attention_tc(const AttentionParams& p, cudaStream_t st);
 
 }  // namespace ac

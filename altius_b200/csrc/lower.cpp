@@ -592,7 +592,21 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     const char* e = std::getenv("ALTIUS_CUDA_SPLIT_B_IN_KERNEL");
     return e && e[0] == '1';
   }();
-  if (tc && mode != 2 && em.c.val(b_use).is_const && !split_b_in_kernel) {
+  // mode 0 with a constant rhs: the fp16 split (hi, remainder * 2^11) prepared once, [N, K8] halves.
+  int b16_hi = -1, b16_lo = -1;
+  int64_t ldb16 = 0;
+  if (tc && mode == 0 && em.c.val(b_use).is_const && g.tb && g.batch == 1 && b_off == 0) {
+    ldb16 = (g.k + 7) / 8 * 8;
+    const int64_t floats = g.n * ldb16 / 2;     // two halves per float of scratch
+    b16_hi = new_value(em.c, floats, true);
+    b16_lo = new_value(em.c, floats, true);
+    const int src = b_use, hi = b16_hi, lo = b16_lo;
+    const int64_t nn = g.n, kk = g.k, ld = g.ldb, k8 = ldb16;
+    em.add("weight_f16_split", op, {src}, {hi, lo}, 4.0 * nn * kk + 4.0 * nn * k8, 0, [=](cudaStream_t st) {
+      return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word, st);
+    });
+  }
+  if (tc && b16_hi < 0 && mode != 2 && em.c.val(b_use).is_const && !split_b_in_kernel) {
     // TF32 hi / lo split of a constant rhs, prepared once.
     const int64_t cnt = em.c.val(b_use).numel();
     const int hi = new_value(em.c, cnt, true);
@@ -608,11 +622,12 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
   int ws = -1;
   size_t ws_bytes = 0;
   if (tc) {
-    ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b_lo >= 0);
+    ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b16_hi >= 0 ? 2 : (b_lo >= 0 ? 0 : 1));
     if (ws_bytes) ws = new_value(em.c, (int64_t)(ws_bytes / 4), false);
   }
-  std::vector<int> reads = {a, bsrc, b_lo, c_in, bias_n, bias_m, res};
-  const char* kind = !tc ? "gemm_fp32_simt" : (mode == 2 ? "gemm_tf32x1_tcgen05" : "gemm_tf32x3_tcgen05");
+  std::vector<int> reads = {a, bsrc, b_lo, b16_hi, b16_lo, c_in, bias_n, bias_m, res};
+  const char* kind = !tc ? "gemm_fp32_simt"
+                     : (mode == 2 ? "gemm_tf32x1_tcgen05" : (b16_hi >= 0 ? "gemm_f16x3_tcgen05" : "gemm_tf32x3_tcgen05"));
   std::vector<int> writes = {out};
   if (ws >= 0) writes.push_back(ws);
   em.add(kind, op, reads, writes, bytes, flops, [=](cudaStream_t st) {
@@ -623,6 +638,9 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
     p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
     p.b_lo = b_lo >= 0 ? s->fptr(b_lo) + b_off : nullptr;
+    p.b16_hi = b16_hi >= 0 ? s->ptr(b16_hi) : nullptr;
+    p.b16_lo = b16_lo >= 0 ? s->ptr(b16_lo) : nullptr;
+    p.ldb16 = ldb16;
     p.c = s->fptr_mut(out) + c_off; p.ldc = g.ldc; p.stride_c = g.sc;
     p.alpha = alpha; p.beta = c_in >= 0 ? beta : 0.f;
     p.c_in = c_in >= 0 ? s->fptr(c_in) + c_off : nullptr; p.ldc_in = g.ldc; p.stride_c_in = g.sc;
@@ -937,7 +955,10 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         const int64_t B = f.q.B, H = f.q.H, T = f.q.T, hd = f.q.hd, C = f.q.C;
         const double bytes = 4.0 * B * T * hd * H * 4;
         const double flops = 4.0 * B * H * T * T * hd;
-        em.add("attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, {f.out}, bytes, flops,
+        // gemm_mode 1 asks for exact fp32 FMA chains: it keeps the CUDA-core kernel.
+        static const bool no_tc_attn = std::getenv("ALTIUS_CUDA_NO_TC_ATTENTION") != nullptr;   // debug toggle
+        const bool tc_attn = s->opt.gemm_mode != 1 && !no_tc_attn && hd == 64 && T > 64 && T <= 256;
+        em.add(tc_attn ? "attention_tcgen05" : "attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, {f.out}, bytes, flops,
                [=](cudaStream_t st) {
                  AttentionParams p{};
                  p.q = s->fptr(f.q.src) + f.q.col;
@@ -947,6 +968,7 @@ void lower_node(Emit& em, Plan& plan, int nid) {
                  p.out = s->fptr_mut(f.out); p.out_row_stride = H * hd; p.out_batch_stride = T * H * hd;
                  p.batch = (int)B; p.heads = (int)H; p.tokens = (int)T; p.head_dim = (int)hd;
                  p.scale = f.scale >= 0 ? s->fptr(f.scale) : nullptr; p.scale_mode = f.scale_mode;
+                 p.use_tc = tc_attn ? 1 : 0; p.err_word = s->err_word;
                  return launch_attention(p, st);
                });
         return;

@@ -87,7 +87,8 @@ def main(argv=None):
     else:
         model, feeds = configs.micrograph(batch=a.batch)
         rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters)
-    print(json.dumps(rows, indent=1))
+    for kind, row in rows.items():
+        print(json.dumps({kind: row}))
 
 
 if __name__ == "__main__":

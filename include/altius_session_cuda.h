@@ -143,8 +143,10 @@ typedef struct AcOptions {
   int32_t enable_profiling;  /* time every kernel with CUDA events                */
   int32_t disable_cuda_graph;/* 1: launch kernels one by one instead of a graph   */
   int32_t disable_fusion;    /* 1: one kernel per node, no producer/consumer folds*/
-  int32_t gemm_mode;         /* 0 auto (tcgen05 3xTF32 where shapes allow),
-                                1 CUDA-core fp32 FMA only, 2 tcgen05 1xTF32       */
+  int32_t gemm_mode;         /* 0 auto (tcgen05: fp16-split products for constant
+                                weights, 3xTF32 otherwise, where shapes allow),
+                                1 CUDA-core fp32 FMA only, 2 tcgen05 1xTF32,
+                                3 tcgen05 3xTF32 only                             */
   int32_t plan_only;         /* 1: infer shapes, lower and plan the arena without
                                 touching a GPU; run() then fails. For inspecting
                                 the schedule on a machine without a device.      */

@@ -196,7 +196,7 @@ MATMUL_SHAPES = [((4, 8), (8, 3)), ((2, 5, 8), (8, 3)), ((3, 5, 8), (3, 8, 6)), 
 
 
 @pytest.mark.parametrize("ashape,bshape", MATMUL_SHAPES)
-@pytest.mark.parametrize("gemm_mode", [0, 1])
+@pytest.mark.parametrize("gemm_mode", [0, 1, 3])
 def test_matmul(cuda_lib, ashape, bshape, gemm_mode):
     a = RNG.standard_normal(ashape).astype(np.float32)
     b = RNG.standard_normal(bshape).astype(np.float32)
@@ -205,7 +205,7 @@ def test_matmul(cuda_lib, ashape, bshape, gemm_mode):
     np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5 * np.sqrt(k))
 
 
-@pytest.mark.parametrize("gemm_mode", [0, 1])
+@pytest.mark.parametrize("gemm_mode", [0, 1, 3])
 def test_gemm(cuda_lib, gemm_mode):
     a = RNG.standard_normal((7, 9)).astype(np.float32)
     for ta, ash in ((False, (7, 9)), (True, (9, 7))):
@@ -233,7 +233,7 @@ CONV_CASES = [(1, 1, 28, 8, 5, 1, 2, 1, True), (2, 4, 15, 6, 3, 2, 1, 1, True), 
 
 
 @pytest.mark.parametrize("n,c,h,oc,k,s,p,g,with_bias", CONV_CASES)
-@pytest.mark.parametrize("gemm_mode", [0, 1])
+@pytest.mark.parametrize("gemm_mode", [0, 1, 3])
 def test_conv2d(cuda_lib, n, c, h, oc, k, s, p, g, with_bias, gemm_mode):
     x = RNG.standard_normal((n, c, h, h)).astype(np.float32)
     w = RNG.standard_normal((oc, c // g, k, k)).astype(np.float32)
@@ -260,7 +260,7 @@ TC_SHAPES = [((2, 197, 768), (768, 2304)), ((394, 3072), (3072, 768)), ((1000, 7
 
 
 @pytest.mark.parametrize("ashape,bshape", TC_SHAPES)
-@pytest.mark.parametrize("gemm_mode", [0, 1])
+@pytest.mark.parametrize("gemm_mode", [0, 1, 3])
 def test_matmul_constant_weight(cuda_lib, ashape, bshape, gemm_mode):
     a = RNG.standard_normal(ashape).astype(np.float32)
     w = RNG.standard_normal(bshape).astype(np.float32)
@@ -322,7 +322,7 @@ def test_linear_gelu_residual_epilogue(cuda_lib):
         return [g.op("Add", ri, h)]
     m = _chain_model(build)
     bound = 5e-6 * (np.abs(x).reshape(-1, 768) @ np.abs(w) + np.abs(b)).reshape(4, 197, 384)
-    for opts in (dict(gemm_mode=0), dict(gemm_mode=1), dict(gemm_mode=0, fuse=False)):
+    for opts in (dict(gemm_mode=0), dict(gemm_mode=1), dict(gemm_mode=3), dict(gemm_mode=0, fuse=False)):
         got, want = both(m, [x, r], **opts)
         assert (np.abs(got[0] - want[0]) <= 1e-5 * np.abs(want[0]) + bound).all()
 
@@ -332,7 +332,7 @@ def test_gemm_transb_constant_weight(cuda_lib):
     w = (0.02 * RNG.standard_normal((1000, 1280))).astype(np.float32)
     c = RNG.standard_normal(1000).astype(np.float32)
     m = single_op_model("Gemm", [a], [w, c], alpha=1.0, beta=1.0, trans_a=False, trans_b=True)
-    for mode in (0, 1):
+    for mode in (0, 1, 3):
         got, want = both(m, [a], gemm_mode=mode)
         bound = 1e-5 * np.abs(want[0]) + 5e-6 * (np.abs(a) @ np.abs(w.T) + np.abs(c))
         assert (np.abs(got[0] - want[0]) <= bound).all()
@@ -364,10 +364,25 @@ def test_fused_attention_core(cuda_lib, B, T, H):
     m = _chain_model(build)
     from altius_b200.session import CudaSessionBuilder
     sess = CudaSessionBuilder(m).build()
-    assert [e["kind"] for e in sess.schedule()] == ["attention_fused"]
+    tc = T > 64   # the tcgen05 kernel takes 64 < T <= 256; shorter sequences stay on the CUDA cores
+    assert [e["kind"] for e in sess.schedule()] == ["attention_tcgen05" if tc else "attention_fused"]
     sess.close()
     want = run_oracle(m, [qkv])[0]
     got = run_cuda(m, [qkv])[0]
+    if tc:
+        # 3xTF32 products with the tensor memory accumulator: a score is off by at most
+        # 5e-6 * sum|q||k| * scale, which moves every softmax weight by that relative amount
+        # (numerator and denominator), and the second product adds 5e-6 * sum p|v|.
+        x = qkv.astype(np.float64).reshape(B, T, 3, H, hd).transpose(2, 0, 3, 1, 4)
+        q64, k64, v64 = x[0], x[1], x[2]
+        s64 = np.einsum("bhid,bhjd->bhij", q64, k64) * 0.125
+        err_s = 5e-6 * 0.125 * np.einsum("bhid,bhjd->bhij", np.abs(q64), np.abs(k64)).max(axis=-1, keepdims=True)
+        p64 = np.exp(s64 - s64.max(axis=-1, keepdims=True))
+        p64 /= p64.sum(axis=-1, keepdims=True)
+        pv = np.einsum("bhij,bhjd->bhid", p64, np.abs(v64))
+        bound = ((2 * err_s + 5e-6) * pv).transpose(0, 2, 1, 3).reshape(B, T, D) + 1e-5 * np.abs(want) + 1e-6
+        assert (np.abs(got.astype(np.float64) - want) <= bound).all(), float(np.abs(got - want).max())
+        got = run_cuda(m, [qkv], gemm_mode=1)[0]   # exact fp32 chains: the CUDA-core fused kernel
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
     unfused = run_cuda(m, [qkv], fuse=False, gemm_mode=1)[0]
     np.testing.assert_allclose(unfused, want, rtol=1e-5, atol=1e-6)

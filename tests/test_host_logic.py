@@ -66,7 +66,7 @@ def test_fusion_folds_the_expected_chains():
     kinds = collections.Counter(e["kind"] for e in plan(model).schedule())
     gemms = sum(v for k, v in kinds.items() if k.startswith("gemm"))
     assert gemms == 2 * 4 + 2          # per layer: qkv, proj, mlp1, mlp2; patch embed; head
-    assert kinds["attention_fused"] == 2   # Split/Reshape/Transpose/QK^T/scale/Softmax/PV/merge in one kernel
+    assert kinds["attention_tcgen05"] == 2   # Split/Reshape/Transpose/QK^T/scale/Softmax/PV/merge in one kernel
     assert not any(k in kinds for k in ("split_copy", "transpose_copy", "softmax", "softmax_scaled"))
     unfused = collections.Counter(e["kind"] for e in plan(model, fuse=False).schedule())
     assert unfused["split_copy"] == 6 and unfused["softmax"] == 2
