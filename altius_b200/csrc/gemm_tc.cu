@@ -738,6 +738,11 @@ int sm_count() {
     int dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    // Debug toggle: ALTIUS_CUDA_TC_SMS caps the persistent grid (scaling experiments).
+    if (const char* e = std::getenv("ALTIUS_CUDA_TC_SMS")) {
+      const int v = std::atoi(e);
+      if (v > 0 && v < n) n = v;
+    }
   }
   return n;
 }

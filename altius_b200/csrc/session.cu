@@ -186,9 +186,89 @@ int set_err(AcSession* s, int status, const std::string& msg) {
   return status;
 }
 
+std::unique_ptr<GraphCopy> copy_graph(const AcGraphDesc& g) {
+  std::unique_ptr<GraphCopy> c(new GraphCopy());
+  c->opset = g.opset_version;
+  c->values.assign(g.values, g.values + g.n_values);
+  c->nodes.resize(g.n_nodes);
+  for (int i = 0; i < g.n_nodes; ++i) {
+    const AcNodeDesc& d = g.nodes[i];
+    GraphCopy::NodeCopy& n = c->nodes[i];
+    n.op = d.op;
+    if (d.n_inputs > 0) n.inputs.assign(d.inputs, d.inputs + d.n_inputs);
+    if (d.n_outputs > 0) n.outputs.assign(d.outputs, d.outputs + d.n_outputs);
+    if (d.n_ints > 0) n.ints.assign(d.ints, d.ints + d.n_ints);
+    if (d.n_floats > 0) n.floats.assign(d.floats, d.floats + d.n_floats);
+    n.has_name = d.name != nullptr;
+    if (d.name) n.name = d.name;
+  }
+  if (g.n_inits > 0) c->inits.assign(g.inits, g.inits + g.n_inits);
+  for (AcInitDesc& d : c->inits) d.data = nullptr;
+  if (g.n_inputs > 0) c->inputs.assign(g.inputs, g.inputs + g.n_inputs);
+  if (g.n_outputs > 0) c->outputs.assign(g.outputs, g.outputs + g.n_outputs);
+  return c;
+}
+
+int create_session(const AcGraphDesc* graph, const AcOptions* options, AcSession** out);
+
+// Second session on the 3xTF32 path, built from the kept description; its initializers
+// are read from this session's weight blob (or the host copies of the small ones).
+int create_fallback(AcSession* s) {
+  if (s->fallback) return AC_OK;
+  if (!s->desc) return set_err(s, AC_ERR_CUDA, "an operand exceeds the fp16 range and no fallback description was kept");
+  GraphCopy& c = *s->desc;
+  std::vector<AcNodeDesc> nodes(c.nodes.size());
+  for (size_t i = 0; i < c.nodes.size(); ++i) {
+    GraphCopy::NodeCopy& n = c.nodes[i];
+    nodes[i] = AcNodeDesc{n.op, (int32_t)n.inputs.size(), n.inputs.data(), (int32_t)n.outputs.size(), n.outputs.data(),
+                          (int32_t)n.ints.size(), n.ints.data(), (int32_t)n.floats.size(), n.floats.data(),
+                          n.has_name ? n.name.c_str() : nullptr};
+  }
+  std::vector<AcInitDesc> inits = c.inits;
+  for (AcInitDesc& d : inits) {
+    const Value& v = s->values[d.value];
+    if (!v.host_owned.empty()) { d.location = 0; d.data = v.host_owned.data(); }
+    else { d.location = 1; d.data = s->ptr(d.value); }
+  }
+  AcGraphDesc g{};
+  g.opset_version = c.opset;
+  g.n_values = (int32_t)c.values.size(); g.values = c.values.data();
+  g.n_nodes = (int32_t)nodes.size(); g.nodes = nodes.data();
+  g.n_inits = (int32_t)inits.size(); g.inits = inits.data();
+  g.n_inputs = (int32_t)c.inputs.size(); g.inputs = c.inputs.data();
+  g.n_outputs = (int32_t)c.outputs.size(); g.outputs = c.outputs.data();
+  AcOptions o = s->opt;
+  o.gemm_mode = 3;
+  const int rc = create_session(&g, &o, &s->fallback);
+  if (rc != AC_OK) return set_err(s, rc, "building the 3xTF32 fallback failed: " + g_create_error);
+  return AC_OK;
+}
+
+// The error word after a run: 0 fine; the range code switches to the fallback session
+// (returns 1: the caller re-runs there); anything else is a kernel that gave up a wait.
+int check_err_word(AcSession* s) {
+  const int code = *s->err_host;
+  if (code == 0) return AC_OK;
+  cudaMemsetAsync(s->err_word, 0, sizeof(int), s->stream);
+  cudaStreamSynchronize(s->stream);
+  *s->err_host = 0;
+  if (code == kGemmRangeCode && s->opt.gemm_mode == 0) {
+    const int rc = create_fallback(s);
+    if (rc != AC_OK) return rc;
+    s->use_fallback = true;
+    return 1;
+  }
+  return set_err(s, AC_ERR_CUDA, "a kernel gave up a bounded wait (code " + std::to_string(code) + ")");
+}
+
 int run_common(AcSession* s, const void* const* ins, void* const* outs, bool device_io) {
   if (!s || (!ins && !s->inputs.empty()) || !outs) return set_err(s, AC_ERR_INVALID, "null argument");
   if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
+  if (s->use_fallback) {
+    const int rc = run_common(s->fallback, ins, outs, device_io);
+    if (rc != AC_OK) s->err = s->fallback->err;
+    return rc;
+  }
   cudaError_t e = cudaSetDevice(s->device);
   if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, cudaGetErrorString(e));
   const cudaMemcpyKind in_kind = device_io ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
@@ -224,8 +304,7 @@ int run_common(AcSession* s, const void* const* ins, void* const* outs, bool dev
   cudaMemcpyAsync(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost, s->stream);
   e = cudaStreamSynchronize(s->stream);
   if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("run: ") + cudaGetErrorString(e));
-  if (*s->err_host != 0)
-    return set_err(s, AC_ERR_CUDA, "a kernel gave up a bounded wait (code " + std::to_string(*s->err_host) + ")");
+  if (const int rc = check_err_word(s)) return rc == 1 ? run_common(s, ins, outs, device_io) : rc;
   if (s->opt.enable_profiling) {
     for (size_t i = 0; i < s->steps.size(); ++i) {
       float ms = 0.f;
@@ -250,7 +329,10 @@ int altius_cuda_device_count(void) {
   return n;
 }
 
-int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSession** out) {
+}  // extern "C"
+
+namespace {
+int create_session(const AcGraphDesc* graph, const AcOptions* options, AcSession** out) {
   if (!graph || !out) return set_err(nullptr, AC_ERR_INVALID, "null argument");
   *out = nullptr;
   AcSession* s = new AcSession();
@@ -288,7 +370,9 @@ int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSes
     for (Step& st : s->init_steps) AC_CUDA(st.fn(s->stream));
     AC_CUDA(cudaStreamSynchronize(s->stream));
     AC_CUDA(cudaMemcpy(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*s->err_host == kGemmRangeCode) fail(-kGemmRangeCode, "a constant operand exceeds the fp16 range");
     if (*s->err_host != 0) fail(AC_ERR_CUDA, "a kernel gave up a bounded wait while preparing constants");
+    if (s->opt.gemm_mode == 0) s->desc = copy_graph(*graph);
     if (s->opt.enable_profiling) {
       s->events.resize(s->steps.size() + 1);
       for (cudaEvent_t& ev : s->events) AC_CUDA(cudaEventCreate(&ev));
@@ -312,6 +396,21 @@ int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSes
   *out = s;
   return AC_OK;
 }
+}  // namespace
+
+extern "C" {
+
+int altius_cuda_create(const AcGraphDesc* graph, const AcOptions* options, AcSession** out) {
+  int rc = create_session(graph, options, out);
+  if (rc == -kGemmRangeCode) {
+    // A weight does not fit the fp16 split: lower everything on the 3xTF32 path instead.
+    AcOptions o{};
+    if (options) o = *options;
+    o.gemm_mode = 3;
+    rc = create_session(graph, &o, out);
+  }
+  return rc;
+}
 
 int altius_cuda_run(AcSession* s, const void* const* ins, void* const* outs) {
   return run_common(s, ins, outs, false);
@@ -327,6 +426,11 @@ int altius_cuda_time_device_runs(AcSession* s, const void* const* d_ins, void* c
     return set_err(s, AC_ERR_INVALID, "bad argument");
   if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
   if (s->opt.enable_profiling) return set_err(s, AC_ERR_INVALID, "not available on a profiling session");
+  if (s->use_fallback) {
+    const int rc = altius_cuda_time_device_runs(s->fallback, d_ins, d_outs, iters, elapsed_ms);
+    if (rc != AC_OK) s->err = s->fallback->err;
+    return rc;
+  }
   cudaError_t e = cudaSetDevice(s->device);
   cudaEvent_t t0 = nullptr, t1 = nullptr;
   if (e == cudaSuccess) e = cudaEventCreate(&t0);
@@ -347,7 +451,8 @@ int altius_cuda_time_device_runs(AcSession* s, const void* const* d_ins, void* c
   if (e == cudaSuccess && *s->err_host != 0) {
     if (t0) cudaEventDestroy(t0);
     if (t1) cudaEventDestroy(t1);
-    return set_err(s, AC_ERR_CUDA, "a kernel gave up a bounded wait (code " + std::to_string(*s->err_host) + ")");
+    const int rc = check_err_word(s);
+    return rc == 1 ? altius_cuda_time_device_runs(s, d_ins, d_outs, iters, elapsed_ms) : rc;
   }
   if (e == cudaSuccess) e = cudaEventElapsedTime(elapsed_ms, t0, t1);
   if (t0) cudaEventDestroy(t0);
@@ -374,10 +479,17 @@ int altius_cuda_value_info(const AcSession* s, int32_t value, AcValueDesc* out) 
   return AC_OK;
 }
 
-int64_t altius_cuda_launches_per_run(const AcSession* s) { return s ? s->launches_per_run : -1; }
-uint64_t altius_cuda_arena_bytes(const AcSession* s) { return s ? s->arena_bytes : 0; }
+int64_t altius_cuda_launches_per_run(const AcSession* s) {
+  if (s && s->use_fallback) s = s->fallback;
+  return s ? s->launches_per_run : -1;
+}
+uint64_t altius_cuda_arena_bytes(const AcSession* s) {
+  if (s && s->use_fallback) s = s->fallback;
+  return s ? s->arena_bytes : 0;
+}
 
 int altius_cuda_profile(AcSession* s, AcProfileEntry* entries, size_t* n) {
+  if (s && s->use_fallback) s = s->fallback;
   if (!s || !n) return AC_ERR_INVALID;
   const size_t cap = *n;
   size_t i = 0;
@@ -398,6 +510,7 @@ int altius_cuda_profile(AcSession* s, AcProfileEntry* entries, size_t* n) {
 }
 
 int altius_cuda_schedule(const AcSession* s, AcProfileEntry* entries, size_t* n) {
+  if (s && s->use_fallback) s = s->fallback;
   if (!s || !n) return AC_ERR_INVALID;
   const size_t cap = *n;
   for (size_t i = 0; i < s->steps.size() && entries && i < cap; ++i) {
@@ -413,6 +526,7 @@ int altius_cuda_schedule(const AcSession* s, AcProfileEntry* entries, size_t* n)
 }
 
 int altius_cuda_profile_reset(AcSession* s) {
+  if (s && s->use_fallback) s = s->fallback;
   if (!s) return AC_ERR_INVALID;
   s->profile.clear();
   return AC_OK;
@@ -424,6 +538,7 @@ const char* altius_cuda_last_error(const AcSession* s) {
 
 void altius_cuda_destroy(AcSession* s) {
   if (!s) return;
+  if (s->fallback) altius_cuda_destroy(s->fallback);
   if (s->stream) cudaSetDevice(s->device);
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
   if (s->graph) cudaGraphDestroy(s->graph);

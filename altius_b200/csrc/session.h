@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <functional>
 #include <map>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -67,6 +68,26 @@ struct ProfileAcc {
 
 }  // namespace ac
 
+namespace ac {
+// What create() keeps of the caller's graph description (everything but the initializer
+// payloads) so that the session can be lowered a second time with other options.
+struct GraphCopy {
+  struct NodeCopy {
+    int32_t op;
+    std::vector<int32_t> inputs, outputs;
+    std::vector<int64_t> ints;
+    std::vector<float> floats;
+    std::string name;
+    bool has_name;
+  };
+  int64_t opset;
+  std::vector<AcValueDesc> values;
+  std::vector<NodeCopy> nodes;
+  std::vector<AcInitDesc> inits;      // data pointers are filled in when the copy is used
+  std::vector<int32_t> inputs, outputs;
+};
+}  // namespace ac
+
 struct AcSession {
   int device = 0;
   AcOptions opt{};
@@ -91,6 +112,11 @@ struct AcSession {
   std::map<std::string, ac::ProfileAcc> profile;
   int64_t launches_per_run = 0;
   std::string err;
+  // gemm_mode 0 only: when an operand of an fp16-split GEMM turns out not to fit fp16,
+  // a second session lowered with gemm_mode 3 (3xTF32) takes over for good.
+  std::unique_ptr<ac::GraphCopy> desc;
+  AcSession* fallback = nullptr;
+  bool use_fallback = false;
 
   void* ptr(int value) const {
     const ac::Storage& st = storages[values[value].storage];

@@ -273,6 +273,46 @@ def test_matmul_constant_weight(cuda_lib, ashape, bshape, gemm_mode):
     assert (np.abs(got[0] - want[0]) <= bound).all()
 
 
+def test_fp16_split_falls_back_to_tf32_when_an_activation_is_out_of_range(cuda_lib):
+    """gemm_mode 0 multiplies constant weights with fp16-split operands; an activation
+    beyond 65504 is detected on the device and the session switches, for good, to a
+    second plan on the 3xTF32 path and repeats the run there."""
+    from altius_b200.session import CudaSessionBuilder
+    a = RNG.standard_normal((128, 256)).astype(np.float32)
+    w = RNG.standard_normal((256, 256)).astype(np.float32)
+    m = single_op_model("MatMul", [a], [w])
+    sess = CudaSessionBuilder(m).build()
+    try:
+        kinds = lambda: [e["kind"] for e in sess.schedule()]
+        assert kinds() == ["gemm_f16x3_tcgen05"]
+        big = np.where(np.arange(a.size).reshape(a.shape) == 901, 1e6, a).astype(np.float32)
+        # in range, out of range (switches), in range again (the switch is permanent)
+        for x, kind_after in ((a, "gemm_f16x3_tcgen05"), (big, "gemm_tf32x3_tcgen05"), (a, "gemm_tf32x3_tcgen05")):
+            want = run_oracle(m, [x])[0]
+            got = sess.run([x])[0]
+            bound = 1e-5 * np.abs(want) + 5e-6 * (np.abs(x) @ np.abs(w))
+            assert (np.abs(got - want) <= bound).all()
+            assert kinds() == [kind_after]
+    finally:
+        sess.close()
+
+
+def test_fp16_split_is_not_used_for_weights_out_of_range(cuda_lib):
+    from altius_b200.session import CudaSessionBuilder
+    a = RNG.standard_normal((128, 256)).astype(np.float32)
+    w = RNG.standard_normal((256, 256)).astype(np.float32)
+    w[5, 17] = 1e5
+    m = single_op_model("MatMul", [a], [w])
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["gemm_tf32x3_tcgen05"]
+        want = run_oracle(m, [a])[0]
+        got = sess.run([a])[0]
+        assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 5e-6 * (np.abs(a) @ np.abs(w))).all()
+    finally:
+        sess.close()
+
+
 def test_matmul_tf32x1_is_looser_but_close(cuda_lib):
     a = RNG.standard_normal((512, 768)).astype(np.float32)
     w = RNG.standard_normal((768, 512)).astype(np.float32)
