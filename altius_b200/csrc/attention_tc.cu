@@ -20,17 +20,23 @@
 //               four P chunks [128 x 16].
 // Tensor memory: S in columns [0, NS), O in columns [256, 320).
 //
-//   all 8 warps  stage Q and K (global -> registers -> split -> swizzled stores),
-//                prefetch V into registers, and after S transpose-store V;
-//   warp 4       one thread issues the MMAs and commits to mbarriers;
-//   warps 0-3    one query row per thread (= tensor-memory lane): pass 1 row maximum
-//                of the scaled scores, pass 2 e = exp(s - max) with the reference's
-//                polynomial, running sum, e split into hi/lo and stored as the A
-//                operand of the second product; finally O * (1 / sum) to global.
+//   warps 0-7    stage Q and K (global -> registers -> split -> swizzled stores),
+//                prefetch V into registers, and after S transpose-store V; then softmax,
+//                two threads per query row (= tensor-memory lane), one per half of the
+//                key columns: pass 1 row maximum of the scaled scores, pass 2
+//                e = exp(s - max) with the reference's polynomial, running sum, e split
+//                into hi/lo and stored as the A operand of the second product; maxima and
+//                sums of the two halves meet in shared memory; finally O * (1 / sum) goes
+//                to global through a shared-memory transpose (full 128-byte lines);
+//   warp 8       allocates tensor memory; one thread issues the MMAs and commits to
+//                mbarriers (the P chunks of the two halves alternate).
 // P is fed unnormalised and O scaled by 1 / sum at the end (the reference
 // normalises P first); the difference is a few ulp.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the
 // error word and runs to its end without touching the barrier again.
+#include <cstdio>
+#include <cstdlib>
+
 #include "kernels.h"
 #include "ref_math.cuh"
 #include "tc_common.cuh"
@@ -42,7 +48,8 @@ using namespace tc;
 
 constexpr int HD = 64;                        // head dimension
 constexpr int QM = 128;                       // query rows per CTA = tensor-memory lanes
-constexpr int kAtThreads = 256;
+constexpr int kAtThreads = 256;              // warps 0-7: staging and softmax
+constexpr int kAtLaunch = kAtThreads + 32;    // + warp 8: MMA issue, tensor-memory allocation
 constexpr int kSlots = 4;                     // P ring depth
 constexpr int kSlotBytes = 2 * QM * 64;       // hi + lo of a [128 x 16] chunk
 constexpr int kQBytes = 2 * 4 * QM * 64;      // hi + lo of Q as 4 blocks = the P ring
@@ -56,7 +63,10 @@ struct AttnTcDev {
   int heads, tokens;
   const float* scale; int scale_mode;   // 0 none, 1 multiply, 2 divide
   int* err;
+  long long* dbg;   // phase time stamps of CTA (0, 0) when not null (debug toggle)
 };
+__device__ long long g_attn_stamps[16];
+#define AT_STAMP(i) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.dbg[i] = clock64(); } while (0)
 
 // Byte offset of 16-byte chunk `chunk` (0..3) of row `row` in a K-major block with
 // 64-byte rows and the 64-byte swizzle: address bits 4-5 are XORed with bits 7-8.
@@ -86,9 +96,16 @@ __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ float apply_scale(float s, float sc, int mode) {
-  if (mode == 1) return __fmul_rn(s, sc);
-  if (mode == 2) return __fdiv_rn(s, sc);
+// Barrier of the two softmax warps that share tensor-memory lane quarter q (named barriers 1-4).
+__device__ __forceinline__ void pair_sync(int q) {
+  asm volatile("bar.sync %0, 64;" ::"r"(q + 1) : "memory");
+}
+
+// MODE 0: none, 1: multiply, 2: divide (the graph's Mul / Div node, one rounded operation).
+template <int MODE>
+__device__ __forceinline__ float apply_scale(float s, float sc) {
+  if (MODE == 1) return __fmul_rn(s, sc);
+  if (MODE == 2) return __fdiv_rn(s, sc);
   return s;
 }
 
@@ -100,8 +117,8 @@ __device__ __forceinline__ void store_split(uint8_t* hi_base, uint8_t* lo_base, 
 }
 
 // NB = 16-column blocks of keys: NS = 16 * NB >= tokens.
-template <int NB>
-__global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p) {
+template <int NB, int SMODE>
+__global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p) {
   constexpr int NS = NB * 16;
   constexpr int kKBlock = NS * 64;            // bytes of one [NS x 16] block of K
   constexpr int kVBlock = HD * 64;            // bytes of one [64 x 16] block of V^T
@@ -116,6 +133,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
   uint64_t* ready = bars + 2;                  // [kSlots] P chunk written by the 128 softmax threads
   uint64_t* freeb = ready + kSlots;            // [kSlots] P chunk consumed by its MMAs
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(freeb + kSlots);
+  float* xch = reinterpret_cast<float*>(bars + 16);   // [2][128] row maxima, then row sums, of the two halves
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int T = p.tokens;
@@ -127,6 +145,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
   const float* kg = p.k + base;
   const float* vg = p.v + base;
   bool ok = true;
+  AT_STAMP(0);
 
   if (tid == 0) {
     mbar_init(s_full, 1);
@@ -137,62 +156,66 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == 8) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
 
   // ---- stage Q [128 x 64] and K [NS x 64]: 16 threads per row, one float4 each ----
-  {
+  if (warp < 8) {
+    // Rows past the end are read from the last row (unconditional loads, all in flight
+    // at once) and zeroed when stored.
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 qv[8], kvv[NB];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
-      qv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (q0 + row < T) qv[i] = __ldg(reinterpret_cast<const float4*>(qg + (long long)(q0 + row) * p.row_stride + c4 * 4));
+      qv[i] = __ldg(reinterpret_cast<const float4*>(qg + (long long)min(q0 + row, T - 1) * p.row_stride + c4 * 4));
     }
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
       const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
-      kvv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row < T) kvv[i] = __ldg(reinterpret_cast<const float4*>(kg + (long long)row * p.row_stride + c4 * 4));
+      kvv[i] = __ldg(reinterpret_cast<const float4*>(kg + (long long)min(row, T - 1) * p.row_stride + c4 * 4));
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
       uint8_t* blk = qp + (c4 >> 2) * (QM * 64);
-      store_split(blk, blk + 4 * QM * 64, sw64_off(row, c4 & 3), qv[i]);
+      store_split(blk, blk + 4 * QM * 64, sw64_off(row, c4 & 3), q0 + row < T ? qv[i] : zero4);
     }
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
       const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
       uint8_t* blk = kv + (c4 >> 2) * kKBlock;
-      store_split(blk, blk + 4 * kKBlock, sw64_off(row, c4 & 3), kvv[i]);
+      store_split(blk, blk + 4 * kKBlock, sw64_off(row, c4 & 3), row < T ? kvv[i] : zero4);
     }
   }
   // ---- V into registers: thread (d, tg) takes tokens 16 i + 4 tg + {0..3} of column d,
   // the 16-byte chunk tg of row d in block i of V^T ----
-  const int vd = tid & 63, vtg = tid >> 6;
+  const int vd = tid & 63, vtg = (tid >> 6) & 3;
   float vv[NB][4];
+  if (warp < 8)
 #pragma unroll
   for (int i = 0; i < NB; ++i)
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int t = 16 * i + 4 * vtg + u;
-      vv[i][u] = (t < T) ? __ldg(vg + (long long)t * p.row_stride + vd) : 0.f;
+      vv[i][u] = __ldg(vg + (long long)min(t, T - 1) * p.row_stride + vd);   // masked when stored
     }
 
+  AT_STAMP(1);
   fence_proxy_async();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  AT_STAMP(2);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NS >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
   const uint32_t idesc_o = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
 
   // ---- S = Q K^T: 4 blocks x 2 K-steps x 3 MMAs ----
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
 #pragma unroll
     for (int blk = 0; blk < 4; ++blk)
 #pragma unroll
@@ -210,47 +233,65 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
   __syncwarp();
   if (!mbar_wait(s_full, 0)) { atomicExch(p.err, 11); ok = false; }
   tc_fence_after();
+  AT_STAMP(3);
 
   // ---- K is consumed: store V^T (hi / lo) over it ----
+  if (warp < 8)
 #pragma unroll
   for (int i = 0; i < NB; ++i) {
     uint8_t* blk = kv + i * kVBlock;
-    store_split(blk, blk + NB * kVBlock, sw64_off(vd, vtg), make_float4(vv[i][0], vv[i][1], vv[i][2], vv[i][3]));
+    const int t0 = 16 * i + 4 * vtg;
+    store_split(blk, blk + NB * kVBlock, sw64_off(vd, vtg),
+                make_float4(t0 < T ? vv[i][0] : 0.f, t0 + 1 < T ? vv[i][1] : 0.f, t0 + 2 < T ? vv[i][2] : 0.f,
+                            t0 + 3 < T ? vv[i][3] : 0.f));
   }
   fence_proxy_async();
   __syncthreads();
+  AT_STAMP(4);
 
-  if (warp < 4) {
-    // ---------------- softmax: one row per thread ----------------
-    const int row = warp * 32 + lane;
-    const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const float sc = p.scale_mode ? __ldg(p.scale) : 1.f;
-    const int mode = p.scale_mode;
+  constexpr int NB0 = (NB + 1) / 2;            // chunks of the first column half
+  if (warp < 8) {
+    // ---------------- softmax: two threads per row, one per column half ----------------
+    const int q = warp & 3, hf = warp >> 2;    // tensor-memory lane quarter, column half
+    const int row = q * 32 + lane;
+    const int c_begin = hf ? NB0 : 0, c_count = hf ? NB - NB0 : NB0;
+    const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
+    const float sc = SMODE ? __ldg(p.scale) : 1.f;
     float m = CUDART_NAN_F;
 #pragma unroll 1
-    for (int c = 0; c < NB; ++c) {
+    for (int i = 0; i < c_count; ++i) {
+      const int c = c_begin + i;
       uint32_t v[16];
       tc_ld_32x16(trow + (uint32_t)(c * 16), v);
+      // Columns past T hold exact zeros (zero rows of K); they are kept out of the maximum
+      // by a select, not a branch, so that the 16 chains stay interleaved.
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
-        if (c * 16 + u < T) m = fmaxf(apply_scale(__uint_as_float(v[u]), sc, mode), m);
+      for (int u = 0; u < 16; ++u) {
+        const float sv = apply_scale<SMODE>(__uint_as_float(v[u]), sc);
+        m = fmaxf(c * 16 + u < T ? sv : CUDART_NAN_F, m);
+      }
     }
+    xch[hf * QM + row] = m;
+    pair_sync(q);
+    m = fmaxf(xch[QM + row], xch[row]);
+    pair_sync(q);                              // both have read before the sums overwrite
+    AT_STAMP(5);
     float sum = 0.f;
 #pragma unroll 1
-    for (int c = 0; c < NB; ++c) {
-      const int slot = c % kSlots;
-      if (ok && c >= kSlots && !mbar_wait(&freeb[slot], ((c / kSlots) - 1) & 1)) { atomicExch(p.err, 12); ok = false; }
+    for (int i = 0; i < c_count; ++i) {
+      const int c = c_begin + i;
+      const int slot = 2 * hf + (i & 1);
+      if (ok && i >= 2 && !mbar_wait(&freeb[slot], ((i >> 1) - 1) & 1)) { atomicExch(p.err, 12); ok = false; }
       uint32_t v[16];
       tc_ld_32x16(trow + (uint32_t)(c * 16), v);
       float e[16];
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
-        e[u] = 0.f;
-        if (c * 16 + u < T) {
-          e[u] = exp_poly_softmax(__fsub_rn(apply_scale(__uint_as_float(v[u]), sc, mode), m));
-          sum = __fadd_rn(sum, e[u]);
-        }
+        const float ev = exp_poly_softmax(__fsub_rn(apply_scale<SMODE>(__uint_as_float(v[u]), sc), m));
+        e[u] = c * 16 + u < T ? ev : 0.f;
       }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);   // + 0 for masked columns: exact
       uint8_t* sl = qp + slot * kSlotBytes;
 #pragma unroll
       for (int j = 0; j < 4; ++j)
@@ -258,29 +299,41 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
       fence_proxy_async();
       if (ok) mbar_arrive(&ready[slot]);
     }
-    // ---- O * (1 / sum) -> out[b, q0 + row, h * 64 ...] ----
+    xch[hf * QM + row] = sum;
+    pair_sync(q);
+    sum = __fadd_rn(xch[row], xch[QM + row]);
+    // ---- O * (1 / sum): this warp takes 32 of the 64 columns; through a 4 KB tile of the
+    // (now idle) P ring so that every 8 lanes write one full 128-byte line ----
+    AT_STAMP(6);
     if (ok && !mbar_wait(o_full, 0)) { atomicExch(p.err, 13); ok = false; }
     tc_fence_after();
+    AT_STAMP(7);
     const float recip = __fdiv_rn(1.f, sum);
-    float* og = p.out + (long long)b * p.out_batch_stride + (long long)h * HD + (long long)(q0 + row) * p.out_row_stride;
+    uint32_t o[32];
+    tc_ld_32x32(trow + kOCol + (uint32_t)(hf * 32), o);
+    float4* stage = reinterpret_cast<float4*>(qp + warp * 4096);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t o[32];
-      tc_ld_32x32(trow + kOCol + (uint32_t)(half * 32), o);
-      if (ok && q0 + row < T) {
+    for (int j = 0; j < 8; ++j)
+      stage[lane * 8 + (j ^ (lane & 7))] =
+          make_float4(__fmul_rn(__uint_as_float(o[4 * j]), recip), __fmul_rn(__uint_as_float(o[4 * j + 1]), recip),
+                      __fmul_rn(__uint_as_float(o[4 * j + 2]), recip), __fmul_rn(__uint_as_float(o[4 * j + 3]), recip));
+    __syncwarp();
+    const int c4 = lane & 7, rsub = lane >> 3;
+    float* og = p.out + (long long)b * p.out_batch_stride + (long long)h * HD + hf * 32 + 4 * c4;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4*>(og + half * 32 + 4 * j) =
-              make_float4(__fmul_rn(__uint_as_float(o[4 * j]), recip), __fmul_rn(__uint_as_float(o[4 * j + 1]), recip),
-                          __fmul_rn(__uint_as_float(o[4 * j + 2]), recip), __fmul_rn(__uint_as_float(o[4 * j + 3]), recip));
-      }
+    for (int i = 0; i < 8; ++i) {
+      const int rl = 4 * i + rsub, r = q0 + q * 32 + rl;
+      if (ok && r < T) *reinterpret_cast<float4*>(og + (long long)r * p.out_row_stride) = stage[rl * 8 + (c4 ^ (rl & 7))];
     }
-  } else if (warp == 4 && lane == 0) {
-    // ---------------- O = P V: per chunk 2 K-steps x 3 MMAs ----------------
+  } else if (lane == 0) {
+    // ---------------- O = P V: per chunk 2 K-steps x 3 MMAs; the halves alternate ----------------
 #pragma unroll 1
-    for (int c = 0; ok && c < NB; ++c) {
-      const int slot = c % kSlots;
-      if (!mbar_wait(&ready[slot], (c / kSlots) & 1)) { atomicExch(p.err, 14); ok = false; break; }
+    for (int n = 0; ok && n < 2 * NB0; ++n) {
+      const int hf = n & 1, i = n >> 1;
+      const int c = hf ? NB0 + i : i;
+      if (c >= NB) continue;
+      const int slot = 2 * hf + (i & 1);
+      if (!mbar_wait(&ready[slot], (i >> 1) & 1)) { atomicExch(p.err, 14); ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
@@ -288,7 +341,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
         const uint32_t va = smem_u32(kv + c * kVBlock) + kk * 32;
         const uint64_t a_hi = desc_sw64(pa), a_lo = desc_sw64(pa + QM * 64);
         const uint64_t b_hi = desc_sw64(va), b_lo = desc_sw64(va + NB * kVBlock);
-        tc_mma_tf32(tmem_base + kOCol, a_lo, b_hi, idesc_o, (c | kk) ? 1u : 0u);
+        tc_mma_tf32(tmem_base + kOCol, a_lo, b_hi, idesc_o, (n | kk) ? 1u : 0u);
         tc_mma_tf32(tmem_base + kOCol, a_hi, b_lo, idesc_o, 1u);
         tc_mma_tf32(tmem_base + kOCol, a_hi, b_hi, idesc_o, 1u);
       }
@@ -296,27 +349,35 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(AttnTcDev p
     }
     if (ok) tc_commit(o_full);
   }
+  AT_STAMP(8);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
   }
 }
 
-template <int NB>
-cudaError_t launch_nb(const AttnTcDev& d, int bh, cudaStream_t st) {
-  constexpr int kDyn = NB * 8192 + kQBytes + 128 /*barriers*/ + 1024 /*alignment*/;
+template <int NB, int SMODE>
+cudaError_t launch_nb_mode(const AttnTcDev& d, int bh, cudaStream_t st) {
+  constexpr int kDyn = NB * 8192 + kQBytes + 128 /*barriers*/ + 1024 /*row exchange*/ + 1024 /*alignment*/;
   static_assert(kDyn <= 227 * 1024, "shared memory per CTA");
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn);
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<NB, SMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
   dim3 grid((d.tokens + QM - 1) / QM, bh);
-  attention_tc_kernel<NB><<<grid, kAtThreads, kDyn, st>>>(d);
+  attention_tc_kernel<NB, SMODE><<<grid, kAtLaunch, kDyn, st>>>(d);
   return cudaGetLastError();
+}
+
+template <int NB>
+cudaError_t launch_nb(const AttnTcDev& d, int bh, cudaStream_t st) {
+  if (d.scale_mode == 1) return launch_nb_mode<NB, 1>(d, bh, st);
+  if (d.scale_mode == 2) return launch_nb_mode<NB, 2>(d, bh, st);
+  return launch_nb_mode<NB, 0>(d, bh, st);
 }
 
 }  // namespace
@@ -338,10 +399,21 @@ cudaError_t launch_attention_tc(const AttentionParams& p, cudaStream_t st) {
   d.heads = p.heads; d.tokens = p.tokens;
   d.scale = p.scale; d.scale_mode = p.scale ? p.scale_mode : 0;
   d.err = p.err_word;
+  d.dbg = nullptr;
+  // Debug toggle: ALTIUS_CUDA_ATTN_STAMPS=1 prints the phase clocks of CTA (0, 0) after every launch.
+  static const bool stamps = std::getenv("ALTIUS_CUDA_ATTN_STAMPS") != nullptr;
+  if (stamps) cudaGetSymbolAddress(reinterpret_cast<void**>(&d.dbg), g_attn_stamps);
   const int bh = p.batch * p.heads;
-  if (p.tokens <= 128) return launch_nb<8>(d, bh, st);
-  if (p.tokens <= 208) return launch_nb<13>(d, bh, st);
-  return launch_nb<16>(d, bh, st);
+  cudaError_t e = p.tokens <= 128 ? launch_nb<8>(d, bh, st) : p.tokens <= 208 ? launch_nb<13>(d, bh, st) : launch_nb<16>(d, bh, st);
+  if (stamps && e == cudaSuccess) {
+    long long h[16];
+    cudaStreamSynchronize(st);
+    cudaMemcpyFromSymbol(h, g_attn_stamps, sizeof(h));
+    std::fprintf(stderr, "attention_tc stamps:");
+    for (int i = 1; i <= 8; ++i) std::fprintf(stderr, " %lld", h[i] - h[0]);
+    std::fprintf(stderr, "\n");
+  }
+  return e;
 }
 
 }  // namespace ac

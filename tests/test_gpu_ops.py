@@ -378,8 +378,9 @@ def test_gemm_transb_constant_weight(cuda_lib):
         assert (np.abs(got[0] - want[0]) <= bound).all()
 
 
-@pytest.mark.parametrize("B,T,H", [(2, 197, 12), (3, 198, 6), (1, 33, 2), (2, 256, 1), (1, 7, 3)])
-def test_fused_attention_core(cuda_lib, B, T, H):
+@pytest.mark.parametrize("scale_op", ["Mul", "Div"])
+@pytest.mark.parametrize("B,T,H", [(2, 197, 12), (3, 198, 6), (1, 33, 2), (2, 256, 1), (1, 7, 3), (2, 100, 2), (1, 65, 1)])
+def test_fused_attention_core(cuda_lib, B, T, H, scale_op):
     """Split -> head reshapes/transposes -> Q K^T -> scale -> Softmax -> P V -> merge heads,
     lowered to one kernel when fusion is on; compared with the oracle running the chain."""
     hd, D = 64, 64 * H
@@ -395,7 +396,7 @@ def test_fused_attention_core(cuda_lib, B, T, H):
             return g.op("Reshape", t, g.new_init(np.array([B * H, T, hd], np.int64)))
         q, k, v = heads(q), heads(k), heads(v)
         s = g.op("MatMul", q, g.op("Transpose", k, perm=[0, 2, 1]))
-        s = g.op("Mul", s, g.new_init(np.array([0.125], np.float32)))
+        s = g.op(scale_op, s, g.new_init(np.array([0.125 if scale_op == "Mul" else 8.0], np.float32)))
         p = g.op("Softmax", s, axis=-1)
         o = g.op("MatMul", p, v)
         o = g.op("Reshape", o, g.new_init(np.array([B, H, T, hd], np.int64)))
