@@ -7,6 +7,8 @@
 // are warp-shuffle trees. The per-element arithmetic restates the reference
 // (crates/session_interpreter/src/session.rs and fast_math.rs); only the
 // summation order differs (tree instead of 8-lane partial sums).
+#include <cstdlib>
+
 #include "kernels.h"
 #include "ref_math.cuh"
 
@@ -167,8 +169,12 @@ __device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lan
   }
 }
 
-template <int NV, bool FUSED>
-__global__ void __launch_bounds__(kThreads) layer_norm_vec(LnDev p) {
+// The fused variants are bound by arithmetic (the Gelu above all), not by memory: they keep
+// only the current row in registers (no prefetch of the next one), which lets two or three
+// blocks share an SM.
+template <int NV, bool FUSED, bool GELU>
+__global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev p) {
+  constexpr bool PREFETCH = !FUSED;
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -177,27 +183,35 @@ __global__ void __launch_bounds__(kThreads) layer_norm_vec(LnDev p) {
   int64_t row = warp;
   if (row >= p.rows) return;
   float4 v[NV], r[FUSED ? NV : 1];
-  float4 nv[NV], nr[FUSED ? NV : 1];
+  float4 nv[PREFETCH ? NV : 1];
   if (FUSED) ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
   else ln_load_row<NV, false>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(v));
   while (true) {
     const int64_t next = row + nwarps;
     const bool has_next = next < p.rows;
-    if (has_next) {
-      if (FUSED) ln_load_row<NV, true>(p, next, lane, nvec, nv, reinterpret_cast<float4(&)[NV]>(nr));
-      else ln_load_row<NV, false>(p, next, lane, nvec, nv, reinterpret_cast<float4(&)[NV]>(nv));
-    }
+    if (PREFETCH && has_next)
+      ln_load_row<NV, false>(p, next, lane, nvec, reinterpret_cast<float4(&)[NV]>(nv), reinterpret_cast<float4(&)[NV]>(nv));
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
       if (c < nvec) {
         if (FUSED) {
-          const float4 rv = p.residual ? r[i] : make_float4(0, 0, 0, 0);
-          v[i].x = ln_prologue(p, v[i].x, 4 * c + 0, rv.x);
-          v[i].y = ln_prologue(p, v[i].y, 4 * c + 1, rv.y);
-          v[i].z = ln_prologue(p, v[i].z, 4 * c + 2, rv.z);
-          v[i].w = ln_prologue(p, v[i].w, 4 * c + 3, rv.w);
+          // Same operations as ln_prologue, with the options tested per float4 (or at
+          // compile time for the Gelu) instead of per element.
+          if (p.pre_bias) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(p.pre_bias) + c);
+            v[i].x = __fadd_rn(v[i].x, bv.x); v[i].y = __fadd_rn(v[i].y, bv.y);
+            v[i].z = __fadd_rn(v[i].z, bv.z); v[i].w = __fadd_rn(v[i].w, bv.w);
+          }
+          if (GELU) {
+            v[i].x = gelu_ref(v[i].x); v[i].y = gelu_ref(v[i].y);
+            v[i].z = gelu_ref(v[i].z); v[i].w = gelu_ref(v[i].w);
+          }
+          if (p.residual) {
+            v[i].x = __fadd_rn(v[i].x, r[i].x); v[i].y = __fadd_rn(v[i].y, r[i].y);
+            v[i].z = __fadd_rn(v[i].z, r[i].z); v[i].w = __fadd_rn(v[i].w, r[i].w);
+          }
           if (p.sum_out) reinterpret_cast<float4*>(p.sum_out + row * p.len)[c] = v[i];
         }
         sum = __fadd_rn(sum, __fadd_rn(__fadd_rn(v[i].x, v[i].y), __fadd_rn(v[i].z, v[i].w)));
@@ -236,10 +250,11 @@ __global__ void __launch_bounds__(kThreads) layer_norm_vec(LnDev p) {
     }
     if (!has_next) break;
     row = next;
+    if (PREFETCH) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      v[i] = nv[i];
-      if (FUSED) r[i] = nr[i];
+      for (int i = 0; i < NV; ++i) v[i] = nv[PREFETCH ? i : 0];
+    } else {
+      ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
     }
   }
 }
@@ -312,11 +327,74 @@ __global__ void __launch_bounds__(kThreads) reduce_last(const float* __restrict_
   }
 }
 
+// Rows of NV * 128 floats, 16-byte aligned: a warp takes two rows per step and issues all
+// of their 2 * NV float4 loads before the first use. Same order of additions as reduce_last.
+template <int MODE, int NV>
+__global__ void __launch_bounds__(kThreads) reduce_last_vec(const float* __restrict__ x,
+                                                            float* __restrict__ out, int64_t rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  constexpr int len = NV * 128;
+  const float inv_len = __fdiv_rn(1.0f, (float)len);
+  for (int64_t row = 2 * warp; row < rows; row += 2 * nwarps) {
+    const bool two = row + 1 < rows;
+    const float4* x0 = reinterpret_cast<const float4*>(x + row * len);
+    const float4* x1 = reinterpret_cast<const float4*>(x + (two ? row + 1 : row) * len);
+    float4 a[NV], b[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) a[j] = __ldg(x0 + lane + 32 * j);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) b[j] = __ldg(x1 + lane + 32 * j);
+    float acc0 = MODE == 1 ? -CUDART_INF_F : 0.f, acc1 = acc0;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (MODE == 1) {
+        acc0 = fmaxf(fmaxf(fmaxf(a[j].x, a[j].y), fmaxf(a[j].z, a[j].w)), acc0);
+        acc1 = fmaxf(fmaxf(fmaxf(b[j].x, b[j].y), fmaxf(b[j].z, b[j].w)), acc1);
+      } else {
+        acc0 = __fadd_rn(acc0, __fadd_rn(__fadd_rn(a[j].x, a[j].y), __fadd_rn(a[j].z, a[j].w)));
+        acc1 = __fadd_rn(acc1, __fadd_rn(__fadd_rn(b[j].x, b[j].y), __fadd_rn(b[j].z, b[j].w)));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {      // the two rows' trees interleaved
+      const float t0 = __shfl_xor_sync(0xffffffffu, acc0, o), t1 = __shfl_xor_sync(0xffffffffu, acc1, o);
+      acc0 = MODE == 1 ? fmaxf(acc0, t0) : __fadd_rn(acc0, t0);
+      acc1 = MODE == 1 ? fmaxf(acc1, t1) : __fadd_rn(acc1, t1);
+    }
+    if (lane < 2 && (lane == 0 || two)) {
+      const float acc = lane == 0 ? acc0 : acc1;
+      float r;
+      if (MODE == 0) r = __fmul_rn(acc, inv_len);
+      else if (MODE == 1) r = acc;
+      else r = __fdiv_rn(acc, (float)len);
+      out[row + lane] = r;
+    }
+  }
+}
+
 template <int MODE>
 cudaError_t reduce_last_dispatch(const float* x, float* out, int64_t rows, int64_t len,
                                  cudaStream_t st) {
   if (rows == 0) return cudaSuccess;
   const int64_t blocks64 = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  if ((len % 128) == 0 && len <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // Enough warps to fill the chip four blocks deep, each walking pairs of rows.
+    const int64_t want = (rows + 2 * kWarpsPerBlock - 1) / (2 * kWarpsPerBlock);
+    const unsigned vb = (unsigned)(want > 148 * 4 ? 148 * 4 : want);
+    switch (len / 128) {
+      case 1: reduce_last_vec<MODE, 1><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      case 2: reduce_last_vec<MODE, 2><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      case 3: reduce_last_vec<MODE, 3><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      case 4: reduce_last_vec<MODE, 4><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      case 5: reduce_last_vec<MODE, 5><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      case 6: reduce_last_vec<MODE, 6><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      case 7: reduce_last_vec<MODE, 7><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+      default: reduce_last_vec<MODE, 8><<<vb, kThreads, 0, st>>>(x, out, rows); break;
+    }
+    return cudaGetLastError();
+  }
   const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
   reduce_last<MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, len);
   return cudaGetLastError();
@@ -359,18 +437,25 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
   const int64_t blocks64 = (q.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
   auto al = [](const void* ptr) { return ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
-  const bool vec = (q.len % 4) == 0 && q.len <= 32 * 4 * 8 && al(q.x) && al(q.residual) &&
+  const bool vec = (q.len % 4) == 0 && q.len <= 32 * 4 * 8 && al(q.x) && al(q.residual) && al(q.pre_bias) &&
                    al(q.gamma) && al(q.beta) && al(q.sum_out) && al(q.out);
   if (vec) {
     const int nv = (int)((q.len / 4 + 31) / 32);
     const bool fused = q.pre_bias || q.residual || q.gelu || q.sum_out;
     // Two blocks of 8 warps per SM: several rows per warp, so the prefetch of the next
     // row overlaps the stores of the current one.
-    const unsigned vblocks = blocks64 > 148 * 2 ? 148 * 2 : (unsigned)blocks64;
+    // (Debug toggle ALTIUS_CUDA_LN_BLOCKS_PER_SM overrides the depth.)
+    static const int env_depth = [] {
+      const char* e = std::getenv("ALTIUS_CUDA_LN_BLOCKS_PER_SM");
+      return e ? std::atoi(e) : 0;
+    }();
+    const int depth = env_depth > 0 ? env_depth : (fused ? 3 : 2);    // the fused variants are bound by arithmetic
+    const unsigned vblocks = blocks64 > 148 * depth ? 148 * depth : (unsigned)blocks64;
 #define AC_LN(NVV)                                                                         \
   do {                                                                                     \
-    if (fused) layer_norm_vec<NVV, true><<<vblocks, kThreads, 0, st>>>(p);                 \
-    else layer_norm_vec<NVV, false><<<vblocks, kThreads, 0, st>>>(p);                      \
+    if (fused && q.gelu) layer_norm_vec<NVV, true, true><<<vblocks, kThreads, 0, st>>>(p);  \
+    else if (fused) layer_norm_vec<NVV, true, false><<<vblocks, kThreads, 0, st>>>(p);      \
+    else layer_norm_vec<NVV, false, false><<<vblocks, kThreads, 0, st>>>(p);                \
   } while (0)
     if (nv <= 1) AC_LN(1);
     else if (nv <= 2) AC_LN(2);

@@ -108,7 +108,8 @@ struct AcSession {
   cudaStream_t stream = nullptr;
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
-  std::vector<cudaEvent_t> events;     // profiling: steps.size() + 1 events
+  std::vector<cudaEvent_t> events;     // profiling: a start and a stop event per step
+  char* sweep_buf = nullptr;           // enable_profiling 2: buffer read before each step to clear L2
   std::map<std::string, ac::ProfileAcc> profile;
   int64_t launches_per_run = 0;
   std::string err;

@@ -19,10 +19,10 @@ from . import configs, ir
 from .session import CudaSessionBuilder
 
 
-def _run(model, feeds, mode, fuse, iters):
+def _run(model, feeds, mode, fuse, iters, cold=False):
     import torch
     sess = (CudaSessionBuilder(model).with_gemm_mode(mode).with_fusion(fuse)
-            .with_profiling_enabled(True).build())
+            .with_profiling_enabled(True, cold_l2=cold).build())
     ins = [torch.from_numpy(np.ascontiguousarray(v)).cuda() for v in feeds]
     outs = [torch.empty(tuple(shape), dtype=torch.float32, device="cuda") for shape, _ in sess.output_info]
     for it in range(iters + 2):
@@ -52,6 +52,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--no-fuse", action="store_true")
+    ap.add_argument("--cold-l2", action="store_true", help="sweep L2 before every kernel (micrograph)")
     a = ap.parse_args(argv)
     rng = np.random.default_rng(0)
     if a.what == "gemm":
@@ -86,7 +87,7 @@ def main(argv=None):
         rows = _run(ir.Model(g, 13), [qkv], a.mode, not a.no_fuse, a.iters)
     else:
         model, feeds = configs.micrograph(batch=a.batch)
-        rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters)
+        rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters, cold=a.cold_l2)
     for kind, row in rows.items():
         print(json.dumps({kind: row}))
 

@@ -381,8 +381,10 @@ class CudaSessionBuilder:
     def with_intra_op_num_threads(self, _n: int):
         return self
 
-    def with_profiling_enabled(self, b: bool):
-        self.enable_profiling = b
+    def with_profiling_enabled(self, b: bool, cold_l2: bool = False):
+        """`cold_l2`: additionally sweep L2 before every kernel, so that each one is timed
+        from a cold cache without dirty lines (kernel-level HBM measurements)."""
+        self.enable_profiling = 2 if (b and cold_l2) else b
         return self
 
     def with_cuda_graph(self, b: bool):

@@ -173,7 +173,9 @@ def reference_arm(args, rank):
 
 
 def micrograph_hbm(device, peaks):
-    """Per-kernel achieved HBM GB/s on the tensor-op micrograph at B=64."""
+    """Per-kernel achieved HBM GB/s on the tensor-op micrograph at B=64. L2 is swept before
+    every kernel (a 256 MB read), so each is timed cold and without another kernel's dirty
+    lines to write back."""
     from altius_b200 import configs
     from altius_b200.session import CudaSessionBuilder
     import torch
@@ -181,7 +183,7 @@ def micrograph_hbm(device, peaks):
     out = {}
     for fuse in (True, False):
         sess = (CudaSessionBuilder(model).with_device(device).with_fusion(fuse)
-                .with_profiling_enabled(True).build())
+                .with_profiling_enabled(True, cold_l2=True).build())
         ins = [torch.from_numpy(v).to(f"cuda:{device}") for v in feeds.values()]
         outs = [torch.empty(tuple(shape), dtype=torch.float32, device=f"cuda:{device}")
                 for shape, _ in sess.output_info]

@@ -140,7 +140,8 @@ typedef struct AcGraphDesc {
  * meaning on a GPU and is not carried). Zero-initialise for defaults. */
 typedef struct AcOptions {
   int32_t device;            /* CUDA device ordinal                               */
-  int32_t enable_profiling;  /* time every kernel with CUDA events                */
+  int32_t enable_profiling;  /* 1: time every kernel with CUDA events; 2: same, and
+                                sweep L2 before each kernel (cold, clean cache)    */
   int32_t disable_cuda_graph;/* 1: launch kernels one by one instead of a graph   */
   int32_t disable_fusion;    /* 1: one kernel per node, no producer/consumer folds*/
   int32_t gemm_mode;         /* 0 auto (tcgen05: fp16-split products for constant
