@@ -3,22 +3,27 @@
 //
 //   S = (Q K^T) (* | /) scale ;  P = Softmax(S) ;  O = P V
 //
-// with both products issued as tcgen05.mma (kind::tf32, 3xTF32 split, fp32
-// accumulators in tensor memory). It replaces the same operator chain as the
-// CUDA-core kernel in attention.cu (Split / Reshape / Transpose / MatMul / Mul /
-// Softmax / MatMul / Transpose / Reshape of crates/session_interpreter/src/
-// session.rs:621-682, 990-1026, 1179-1278, 1488-1512) and reads Q, K, V in place
-// from the [B, T, 3D] projection buffer.
+// with both products issued as tcgen05.mma with fp32 accumulators in tensor memory:
+// Q K^T as 3xTF32 (kind::tf32), P V with fp16-split operands (kind::f16, two
+// accumulators, see gemm_tc.cu) after a power-of-two scaling that makes the split
+// safe: P = e * 2^13 with e <= 1, V times 2^s with s from the head's largest |v|.
+// It replaces the same operator chain as the CUDA-core kernel in attention.cu
+// (Split / Reshape / Transpose / MatMul / Mul / Softmax / MatMul / Transpose /
+// Reshape of crates/session_interpreter/src/session.rs:621-682, 990-1026,
+// 1179-1278, 1488-1512) and reads Q, K, V in place from the [B, T, 3D] projection
+// buffer.
 //
-// Shared memory holds every operand as K-major blocks of 16 floats per row with
-// the 64-byte swizzle (the layout the GEMM kernel's TMA boxes have), each as a
-// TF32-rounded `hi` copy and a `lo` copy of the remainder:
-//   region KV : K [NS x 64] as 4 blocks; after S is complete it is overwritten by
-//               V^T [64 x NS] as NS/16 blocks (V is transposed on the way in, so
-//               that the second product also takes a K-major B operand);
-//   region QP : Q [128 x 64] as 4 blocks; after S is complete it becomes a ring of
-//               four P chunks [128 x 16].
-// Tensor memory: S in columns [0, NS), O in columns [256, 320).
+// Shared memory holds every operand as K-major tiles with 64-byte rows and the
+// 64-byte swizzle (the layout the GEMM kernel's TMA boxes have), as a `hi` and a
+// `lo` copy:
+//   region KV : K [NS x 64] TF32 as 4 blocks of 16 floats; after S is complete it is
+//               overwritten by V^T [64 x NS] fp16 as blocks of 32 keys (V is
+//               transposed on the way in, so that the second product also takes a
+//               K-major B operand);
+//   region QP : Q [128 x 64] TF32 as 4 blocks; after S is complete it becomes a ring
+//               of four P blocks [128 x 32 keys] fp16.
+// Tensor memory: S in columns [0, NS), O in columns [256, 320) (hi * hi) and
+// [320, 384) (cross terms, scaled by 2^11).
 //
 //   warps 0-7    stage Q and K (global -> registers -> split -> swizzled stores),
 //                prefetch V into registers, and after S transpose-store V; then softmax,
@@ -51,7 +56,7 @@ constexpr int QM = 128;                       // query rows per CTA = tensor-mem
 constexpr int kAtThreads = 256;              // warps 0-7: staging and softmax
 constexpr int kAtLaunch = kAtThreads + 32;    // + warp 8: MMA issue, tensor-memory allocation
 constexpr int kSlots = 4;                     // P ring depth
-constexpr int kSlotBytes = 2 * QM * 64;       // hi + lo of a [128 x 16] chunk
+constexpr int kSlotBytes = 2 * QM * 64;       // hi + lo of a [128 x 32 keys] fp16 block of P
 constexpr int kQBytes = 2 * 4 * QM * 64;      // hi + lo of Q as 4 blocks = the P ring
 constexpr uint32_t kOCol = 256;               // first tensor-memory column of O
 constexpr uint32_t kTmemCols = 512;
@@ -121,8 +126,7 @@ template <int NB, int SMODE>
 __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p) {
   constexpr int NS = NB * 16;
   constexpr int kKBlock = NS * 64;            // bytes of one [NS x 16] block of K
-  constexpr int kVBlock = HD * 64;            // bytes of one [64 x 16] block of V^T
-  static_assert(8 * kKBlock == 2 * NB * kVBlock, "K and V^T share one region");
+  constexpr int kVBlock = HD * 64;            // bytes of one [64 x 32] fp16 block of V^T
   extern __shared__ uint8_t at_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* kv = smem;                          // 8 * kKBlock bytes
@@ -203,6 +207,17 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       const int t = 16 * i + 4 * vtg + u;
       vv[i][u] = __ldg(vg + (long long)min(t, T - 1) * p.row_stride + vd);   // masked when stored
     }
+  // Largest |v| of this head, for the power-of-two scale that puts V into the fp16 range.
+  if (warp < 8) {
+    float vmax = 0.f;
+#pragma unroll
+    for (int i = 0; i < NB; ++i)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) vmax = fmaxf(vmax, fabsf(vv[i][u]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    if (lane == 0) xch[warp] = vmax;
+  }
 
   AT_STAMP(1);
   fence_proxy_async();
@@ -212,7 +227,22 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
   AT_STAMP(2);
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NS >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
-  const uint32_t idesc_o = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
+  // Second product: fp16 operands (format 0), N = 64.
+  const uint32_t idesc_o = (1u << 4) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
+  // sv = 2^(13 - floor(log2 max|v|)): |v * sv| < 2^14. A zero, infinite or NaN maximum leaves V
+  // unscaled (the result is then zero, or not finite as in fp32).
+  float sv = 1.f, inv_sv = 1.f;
+  {
+    float vm = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) vm = fmaxf(vm, xch[w]);
+    const int eb = (int)((__float_as_uint(vm) >> 23) & 0xFFu);
+    if (eb > 0 && eb < 255) {
+      const int f = min(max(267 - eb, 1), 253);
+      sv = __uint_as_float((uint32_t)f << 23);
+      inv_sv = __uint_as_float((uint32_t)(254 - f) << 23);
+    }
+  }
 
   // ---- S = Q K^T: 4 blocks x 2 K-steps x 3 MMAs ----
   if (warp == 8 && lane == 0) {
@@ -235,40 +265,47 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
   tc_fence_after();
   AT_STAMP(3);
 
-  // ---- K is consumed: store V^T (hi / lo) over it ----
+  // ---- K is consumed: store V^T over it as fp16 hi / lo of v * sv, blocks of 32 tokens
+  // (64-byte rows); an odd last block gets zeros in its second half ----
+  constexpr int NBLK = (NB + 1) / 2;           // 32-token blocks
   if (warp < 8)
 #pragma unroll
-  for (int i = 0; i < NB; ++i) {
-    uint8_t* blk = kv + i * kVBlock;
+  for (int i = 0; i < 2 * NBLK; ++i) {
     const int t0 = 16 * i + 4 * vtg;
-    store_split(blk, blk + NB * kVBlock, sw64_off(vd, vtg),
-                make_float4(t0 < T ? vv[i][0] : 0.f, t0 + 1 < T ? vv[i][1] : 0.f, t0 + 2 < T ? vv[i][2] : 0.f,
-                            t0 + 3 < T ? vv[i][3] : 0.f));
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < NB)
+      x = make_float4(t0 < T ? __fmul_rn(vv[i < NB ? i : 0][0], sv) : 0.f, t0 + 1 < T ? __fmul_rn(vv[i < NB ? i : 0][1], sv) : 0.f,
+                      t0 + 2 < T ? __fmul_rn(vv[i < NB ? i : 0][2], sv) : 0.f, t0 + 3 < T ? __fmul_rn(vv[i < NB ? i : 0][3], sv) : 0.f);
+    uint2 hi, lo;
+    f16_split(x, hi, lo);
+    const uint32_t off = (uint32_t)((i >> 1) * kVBlock) + sw64_off8(vd, 4 * (i & 1) + vtg);
+    *reinterpret_cast<uint2*>(kv + off) = hi;
+    *reinterpret_cast<uint2*>(kv + NBLK * kVBlock + off) = lo;
   }
   fence_proxy_async();
   __syncthreads();
   AT_STAMP(4);
 
-  constexpr int NB0 = (NB + 1) / 2;            // chunks of the first column half
+  constexpr int NBLK0 = (NBLK + 1) / 2;        // blocks of the first column half
   if (warp < 8) {
     // ---------------- softmax: two threads per row, one per column half ----------------
     const int q = warp & 3, hf = warp >> 2;    // tensor-memory lane quarter, column half
     const int row = q * 32 + lane;
-    const int c_begin = hf ? NB0 : 0, c_count = hf ? NB - NB0 : NB0;
+    const int b_begin = hf ? NBLK0 : 0, b_count = hf ? NBLK - NBLK0 : NBLK0;
     const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
     const float sc = SMODE ? __ldg(p.scale) : 1.f;
     float m = CUDART_NAN_F;
 #pragma unroll 1
-    for (int i = 0; i < c_count; ++i) {
-      const int c = c_begin + i;
+    for (int i = 0; i < 2 * b_count; ++i) {
+      const int c = 2 * b_begin + i;           // 16-column chunk; chunks past NS read junk that is masked
       uint32_t v[16];
       tc_ld_32x16(trow + (uint32_t)(c * 16), v);
-      // Columns past T hold exact zeros (zero rows of K); they are kept out of the maximum
+      // Columns past T (exact zeros up to NS, junk beyond) are kept out of the maximum
       // by a select, not a branch, so that the 16 chains stay interleaved.
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
-        const float sv = apply_scale<SMODE>(__uint_as_float(v[u]), sc);
-        m = fmaxf(c * 16 + u < T ? sv : CUDART_NAN_F, m);
+        const float sv_ = apply_scale<SMODE>(__uint_as_float(v[u]), sc);
+        m = fmaxf(c * 16 + u < T ? sv_ : CUDART_NAN_F, m);
       }
     }
     xch[hf * QM + row] = m;
@@ -278,45 +315,60 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
     AT_STAMP(5);
     float sum = 0.f;
 #pragma unroll 1
-    for (int i = 0; i < c_count; ++i) {
-      const int c = c_begin + i;
+    for (int i = 0; i < b_count; ++i) {
+      const int blk = b_begin + i;
       const int slot = 2 * hf + (i & 1);
       if (ok && i >= 2 && !mbar_wait(&freeb[slot], ((i >> 1) - 1) & 1)) { atomicExch(p.err, 12); ok = false; }
-      uint32_t v[16];
-      tc_ld_32x16(trow + (uint32_t)(c * 16), v);
-      float e[16];
-#pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const float ev = exp_poly_softmax(__fsub_rn(apply_scale<SMODE>(__uint_as_float(v[u]), sc), m));
-        e[u] = c * 16 + u < T ? ev : 0.f;
-      }
-#pragma unroll
-      for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);   // + 0 for masked columns: exact
       uint8_t* sl = qp + slot * kSlotBytes;
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        store_split(sl, sl + QM * 64, sw64_off(row, j), make_float4(e[4 * j], e[4 * j + 1], e[4 * j + 2], e[4 * j + 3]));
+      for (int h16 = 0; h16 < 2; ++h16) {
+        const int c0 = blk * 32 + h16 * 16;
+        uint32_t v[16];
+        tc_ld_32x16(trow + (uint32_t)c0, v);
+        float e[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float ev = exp_poly_softmax(__fsub_rn(apply_scale<SMODE>(__uint_as_float(v[u]), sc), m));
+          e[u] = c0 + u < T ? ev : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);   // + 0 for masked columns: exact
+        // P as fp16 hi / lo of e * 2^13 (e <= 1: in range, and far from the subnormals)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint2 h0, l0, h1, l1;
+          f16_split(make_float4(e[8 * j] * 8192.f, e[8 * j + 1] * 8192.f, e[8 * j + 2] * 8192.f, e[8 * j + 3] * 8192.f), h0, l0);
+          f16_split(make_float4(e[8 * j + 4] * 8192.f, e[8 * j + 5] * 8192.f, e[8 * j + 6] * 8192.f, e[8 * j + 7] * 8192.f), h1, l1);
+          const uint32_t off = sw64_off(row, 2 * h16 + j);
+          *reinterpret_cast<uint4*>(sl + off) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+          *reinterpret_cast<uint4*>(sl + QM * 64 + off) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+        }
+      }
       fence_proxy_async();
       if (ok) mbar_arrive(&ready[slot]);
     }
     xch[hf * QM + row] = sum;
     pair_sync(q);
     sum = __fadd_rn(xch[row], xch[QM + row]);
-    // ---- O * (1 / sum): this warp takes 32 of the 64 columns; through a 4 KB tile of the
-    // (now idle) P ring so that every 8 lanes write one full 128-byte line ----
+    // ---- O = (D1 + D2 * 2^-11) * (1 / sum) * 2^-13 / sv: this warp takes 32 of the 64
+    // columns; through a 4 KB tile of the (now idle) P ring so that every 8 lanes write one
+    // full 128-byte line ----
     AT_STAMP(6);
     if (ok && !mbar_wait(o_full, 0)) { atomicExch(p.err, 13); ok = false; }
     tc_fence_after();
     AT_STAMP(7);
     const float recip = __fdiv_rn(1.f, sum);
-    uint32_t o[32];
+    uint32_t o[32], o2[32];
     tc_ld_32x32(trow + kOCol + (uint32_t)(hf * 32), o);
+    tc_ld_32x32(trow + kOCol + (uint32_t)(HD + hf * 32), o2);
     float4* stage = reinterpret_cast<float4*>(qp + warp * 4096);
+    auto fin = [&](int j) {
+      const float y = fmaf(__uint_as_float(o2[j]), kLoUnscale, __uint_as_float(o[j]));
+      return __fmul_rn(__fmul_rn(__fmul_rn(y, recip), 1.f / 8192.f), inv_sv);
+    };
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      stage[lane * 8 + (j ^ (lane & 7))] =
-          make_float4(__fmul_rn(__uint_as_float(o[4 * j]), recip), __fmul_rn(__uint_as_float(o[4 * j + 1]), recip),
-                      __fmul_rn(__uint_as_float(o[4 * j + 2]), recip), __fmul_rn(__uint_as_float(o[4 * j + 3]), recip));
+      stage[lane * 8 + (j ^ (lane & 7))] = make_float4(fin(4 * j), fin(4 * j + 1), fin(4 * j + 2), fin(4 * j + 3));
     __syncwarp();
     const int c4 = lane & 7, rsub = lane >> 3;
     float* og = p.out + (long long)b * p.out_batch_stride + (long long)h * HD + hf * 32 + 4 * c4;
@@ -326,24 +378,25 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       if (ok && r < T) *reinterpret_cast<float4*>(og + (long long)r * p.out_row_stride) = stage[rl * 8 + (c4 ^ (rl & 7))];
     }
   } else if (lane == 0) {
-    // ---------------- O = P V: per chunk 2 K-steps x 3 MMAs; the halves alternate ----------------
+    // ---------------- O = P V: per 32-key block 2 K-steps x 3 fp16 MMAs; the halves alternate ----------------
 #pragma unroll 1
-    for (int n = 0; ok && n < 2 * NB0; ++n) {
+    for (int n = 0; ok && n < 2 * NBLK0; ++n) {
       const int hf = n & 1, i = n >> 1;
-      const int c = hf ? NB0 + i : i;
-      if (c >= NB) continue;
+      const int blk = hf ? NBLK0 + i : i;
+      if (blk >= NBLK) continue;
       const int slot = 2 * hf + (i & 1);
       if (!mbar_wait(&ready[slot], (i >> 1) & 1)) { atomicExch(p.err, 14); ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < 2; ++kk) {
         const uint32_t pa = smem_u32(qp + slot * kSlotBytes) + kk * 32;
-        const uint32_t va = smem_u32(kv + c * kVBlock) + kk * 32;
+        const uint32_t va = smem_u32(kv + blk * kVBlock) + kk * 32;
         const uint64_t a_hi = desc_sw64(pa), a_lo = desc_sw64(pa + QM * 64);
-        const uint64_t b_hi = desc_sw64(va), b_lo = desc_sw64(va + NB * kVBlock);
-        tc_mma_tf32(tmem_base + kOCol, a_lo, b_hi, idesc_o, (n | kk) ? 1u : 0u);
-        tc_mma_tf32(tmem_base + kOCol, a_hi, b_lo, idesc_o, 1u);
-        tc_mma_tf32(tmem_base + kOCol, a_hi, b_hi, idesc_o, 1u);
+        const uint64_t b_hi = desc_sw64(va), b_lo = desc_sw64(va + NBLK * kVBlock);
+        const uint32_t first = (n | kk) ? 1u : 0u;
+        tc_mma_f16(tmem_base + kOCol, a_hi, b_hi, idesc_o, first);            // hi * hi      -> D1
+        tc_mma_f16(tmem_base + kOCol + HD, a_lo, b_hi, idesc_o, first);       // lo' * hi     -> D2
+        tc_mma_f16(tmem_base + kOCol + HD, a_hi, b_lo, idesc_o, 1u);          // hi * lo'     -> D2
       }
       tc_commit(&freeb[slot]);
     }

@@ -27,7 +27,6 @@
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the
 // error word, drains, frees its tensor memory and returns.
 #include <cuda.h>
-#include <cuda_fp16.h>
 
 #include <algorithm>
 #include <cstdlib>
@@ -53,7 +52,6 @@ constexpr int kThreads = (kSplitWarps + 6) * 32;   // + 4 epilogue warps, TMA wa
 // TC_F16X3: operands split into fp16 hi + fp16 (remainder * 2^11); hi*hi goes to one
 // accumulator, the two cross terms (scaled by 2^11) to a second one.
 enum TcMode { TC_3X_BLO_TMA = 0, TC_3X_SPLIT_B = 1, TC_1X = 2, TC_F16X3 = 3 };
-constexpr float kLoScale = 2048.f, kLoUnscale = 1.f / 2048.f;
 
 struct TcEpilogue {
   int m, n;
@@ -86,18 +84,6 @@ __device__ __forceinline__ unsigned beyond_half(float x) {
   const unsigned ab = __float_as_uint(x) & 0x7FFFFFFFu;
   return (ab - 0x477FE001u) <= (0x7F800000u - 0x477FE001u) ? 1u : 0u;
 }
-// hi = rn_fp16(x); lo = rn_fp16((x - hi) * 2^11); x - hi is exact in fp32.
-__device__ __forceinline__ void f16_split(float4 x, uint2& hi, uint2& lo) {
-  const __half2 h01 = __floats2half2_rn(x.x, x.y), h23 = __floats2half2_rn(x.z, x.w);
-  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-  const __half2 l01 = __floats2half2_rn(__fmul_rn(__fsub_rn(x.x, f01.x), kLoScale),
-                                        __fmul_rn(__fsub_rn(x.y, f01.y), kLoScale));
-  const __half2 l23 = __floats2half2_rn(__fmul_rn(__fsub_rn(x.z, f23.x), kLoScale),
-                                        __fmul_rn(__fsub_rn(x.w, f23.y), kLoScale));
-  hi.x = *reinterpret_cast<const uint32_t*>(&h01); hi.y = *reinterpret_cast<const uint32_t*>(&h23);
-  lo.x = *reinterpret_cast<const uint32_t*>(&l01); lo.y = *reinterpret_cast<const uint32_t*>(&l23);
-}
-
 // 32 accumulator columns of this warp's rows. D2OFF != 0: the fp16 mode's second
 // accumulator (cross terms, scaled by 2^11) sits D2OFF columns further on.
 template <int D2OFF>
@@ -110,12 +96,6 @@ __device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32]) {
     for (int j = 0; j < 32; ++j)
       v[j] = __float_as_uint(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])));
   }
-}
-
-// Byte offset of 8-byte chunk `c8` (4 halves) of row `row` in a K-major fp16 tile with
-// 64-byte rows and the 64-byte swizzle (16-byte chunks XORed with bits 1-2 of the row).
-__device__ __forceinline__ uint32_t sw64_off8(int row, int c8) {
-  return (uint32_t)((row >> 3) * 512 + (row & 7) * 64 + (((c8 >> 1) ^ ((row & 7) >> 1)) << 4) + (c8 & 1) * 8);
 }
 
 // Epilogue of one warp's 32 rows. The accumulator chunk arrives with one thread

@@ -3,6 +3,7 @@
 // tensor-memory loads, and the TF32 hi/lo split. sm_100a only.
 #pragma once
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -10,6 +11,8 @@ namespace ac {
 namespace tc {
 
 constexpr uint32_t kWaitLimit = 1u << 24;    // polls before a wait gives up
+// fp16 split: x = hi + lo * 2^-11 with lo kept scaled by 2^11 (out of the fp16 subnormals).
+constexpr float kLoScale = 2048.f, kLoUnscale = 1.f / 2048.f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -107,6 +110,25 @@ __device__ __forceinline__ void tf32_split(float4 v, float4& hi, float4& lo) {
   hi.y = round_tf32(v.y); lo.y = round_tf32(__fsub_rn(v.y, hi.y));
   hi.z = round_tf32(v.z); lo.z = round_tf32(__fsub_rn(v.z, hi.z));
   hi.w = round_tf32(v.w); lo.w = round_tf32(__fsub_rn(v.w, hi.w));
+}
+
+
+// hi = rn_fp16(x); lo = rn_fp16((x - hi) * 2^11); x - hi is exact in fp32.
+__device__ __forceinline__ void f16_split(float4 x, uint2& hi, uint2& lo) {
+  const __half2 h01 = __floats2half2_rn(x.x, x.y), h23 = __floats2half2_rn(x.z, x.w);
+  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+  const __half2 l01 = __floats2half2_rn(__fmul_rn(__fsub_rn(x.x, f01.x), kLoScale),
+                                        __fmul_rn(__fsub_rn(x.y, f01.y), kLoScale));
+  const __half2 l23 = __floats2half2_rn(__fmul_rn(__fsub_rn(x.z, f23.x), kLoScale),
+                                        __fmul_rn(__fsub_rn(x.w, f23.y), kLoScale));
+  hi.x = *reinterpret_cast<const uint32_t*>(&h01); hi.y = *reinterpret_cast<const uint32_t*>(&h23);
+  lo.x = *reinterpret_cast<const uint32_t*>(&l01); lo.y = *reinterpret_cast<const uint32_t*>(&l23);
+}
+
+// Byte offset of 8-byte chunk `c8` (4 halves) of row `row` in a K-major fp16 tile with
+// 64-byte rows and the 64-byte swizzle (16-byte chunks XORed with bits 1-2 of the row).
+__device__ __forceinline__ uint32_t sw64_off8(int row, int c8) {
+  return (uint32_t)((row >> 3) * 512 + (row & 7) * 64 + (((c8 >> 1) ^ ((row & 7) >> 1)) << 4) + (c8 & 1) * 8);
 }
 
 }  // namespace tc
