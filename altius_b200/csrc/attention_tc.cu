@@ -41,6 +41,7 @@
 // error word and runs to its end without touching the barrier again.
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 #include "kernels.h"
 #include "ref_math.cuh"
@@ -70,8 +71,8 @@ struct AttnTcDev {
   int* err;
   long long* dbg;   // phase time stamps of CTA (0, 0) when not null (debug toggle)
 };
-__device__ long long g_attn_stamps[16];
-#define AT_STAMP(i) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.dbg[i] = clock64(); } while (0)
+__device__ long long g_attn_stamps[32];   // [0]: kernel entry; [1..8] first query tile, [11..18] second
+#define AT_STAMP(i) do { if (p.dbg && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) p.dbg[(i) + stamp_base] = clock64(); } while (0)
 
 // Byte offset of 16-byte chunk `chunk` (0..3) of row `row` in a K-major block with
 // 64-byte rows and the 64-byte swizzle: address bits 4-5 are XORed with bits 7-8.
@@ -121,21 +122,70 @@ __device__ __forceinline__ void store_split(uint8_t* hi_base, uint8_t* lo_base, 
   *reinterpret_cast<float4*>(lo_base + off) = lo;
 }
 
-// NB = 16-column blocks of keys: NS = 16 * NB >= tokens.
-template <int NB, int SMODE>
+// V^T as fp16 hi / lo of v * sv, blocks of 32 keys (64-byte rows); an odd last block gets
+// zeros in its second half. Thread (vd, vtg) holds keys 16 i + 4 vtg + {0..3} of column vd.
+template <int NB>
+__device__ __forceinline__ void store_vt(uint8_t* vt, const float (&vv)[NB][4], float sv, int vd, int vtg, int T) {
+  constexpr int NBLK = (NB + 1) / 2;
+  constexpr int kVBlock = HD * 64;
+#pragma unroll
+  for (int i = 0; i < 2 * NBLK; ++i) {
+    const int t0 = 16 * i + 4 * vtg;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < NB) {
+      constexpr int kLast = NB - 1;
+      const int ii = i < NB ? i : kLast;
+      x = make_float4(t0 < T ? __fmul_rn(vv[ii][0], sv) : 0.f, t0 + 1 < T ? __fmul_rn(vv[ii][1], sv) : 0.f,
+                      t0 + 2 < T ? __fmul_rn(vv[ii][2], sv) : 0.f, t0 + 3 < T ? __fmul_rn(vv[ii][3], sv) : 0.f);
+    }
+    uint2 hi, lo;
+    f16_split(x, hi, lo);
+    const uint32_t off = (uint32_t)((i >> 1) * kVBlock) + sw64_off8(vd, 4 * (i & 1) + vtg);
+    *reinterpret_cast<uint2*>(vt + off) = hi;
+    *reinterpret_cast<uint2*>(vt + NBLK * kVBlock + off) = lo;
+  }
+}
+
+// sv = 2^(13 - floor(log2 max|v|)) from the eight warp maxima in xch: |v * sv| < 2^14. A zero,
+// infinite or NaN maximum leaves V unscaled (the result is then zero, or not finite as in fp32).
+__device__ __forceinline__ void scale_from_maxima(const float* xch, float& sv, float& inv_sv) {
+  float vm = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) vm = fmaxf(vm, xch[w]);
+  const int eb = (int)((__float_as_uint(vm) >> 23) & 0xFFu);
+  if (eb > 0 && eb < 255) {
+    const int f = min(max(267 - eb, 1), 253);
+    sv = __uint_as_float((uint32_t)f << 23);
+    inv_sv = __uint_as_float((uint32_t)(254 - f) << 23);
+  }
+}
+
+// Barrier of the eight staging / softmax warps (named barrier 5).
+__device__ __forceinline__ void group_sync() {
+  asm volatile("bar.sync 5, 256;" ::: "memory");
+}
+
+// NB = 16-column blocks of keys: NS = 16 * NB >= tokens. RESIDENT: K and V^T have shared
+// memory of their own, and one CTA walks all query tiles of its (image, head) with K and V
+// staged once (grid.x = 1); otherwise V^T overwrites K and each query tile is a CTA of
+// its own (grid.x = tiles).
+template <int NB, int SMODE, bool RESIDENT>
 __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p) {
   constexpr int NS = NB * 16;
   constexpr int kKBlock = NS * 64;            // bytes of one [NS x 16] block of K
   constexpr int kVBlock = HD * 64;            // bytes of one [64 x 32] fp16 block of V^T
+  constexpr int NBLK = (NB + 1) / 2;          // 32-key blocks of V^T and P
+  constexpr int NBLK0 = (NBLK + 1) / 2;       // blocks of the first column half
   extern __shared__ uint8_t at_smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(at_smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* kv = smem;                          // 8 * kKBlock bytes
-  uint8_t* qp = smem + 8 * kKBlock;            // kQBytes
+  uint8_t* kv = smem;                                              // K: 8 * kKBlock bytes
+  uint8_t* vt = RESIDENT ? smem + 8 * kKBlock : smem;              // V^T: 2 * NBLK * kVBlock bytes
+  uint8_t* qp = vt + (RESIDENT ? 2 * NBLK * kVBlock : 8 * kKBlock);   // Q, then the P ring: kQBytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(qp + kQBytes);
   uint64_t* s_full = bars;                     // S complete in tensor memory
   uint64_t* o_full = bars + 1;                 // O complete
-  uint64_t* ready = bars + 2;                  // [kSlots] P chunk written by the 128 softmax threads
-  uint64_t* freeb = ready + kSlots;            // [kSlots] P chunk consumed by its MMAs
+  uint64_t* ready = bars + 2;                  // [kSlots] P block written by the 128 threads of a half
+  uint64_t* freeb = ready + kSlots;            // [kSlots] P block consumed by its MMAs
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(freeb + kSlots);
   float* xch = reinterpret_cast<float*>(bars + 16);   // [2][128] row maxima, then row sums, of the two halves
 
@@ -143,12 +193,13 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
   const int T = p.tokens;
   const int bh = blockIdx.y;
   const int b = bh / p.heads, h = bh % p.heads;
-  const int q0 = blockIdx.x * QM;
+  const int n_tiles = RESIDENT ? (T + QM - 1) / QM : 1;
   const long long base = (long long)b * p.batch_stride + (long long)h * HD;
   const float* qg = p.q + base;
   const float* kg = p.k + base;
   const float* vg = p.v + base;
   bool ok = true;
+  int stamp_base = 0;
   AT_STAMP(0);
 
   if (tid == 0) {
@@ -166,243 +217,256 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
 
-  // ---- stage Q [128 x 64] and K [NS x 64]: 16 threads per row, one float4 each ----
-  if (warp < 8) {
-    // Rows past the end are read from the last row (unconditional loads, all in flight
-    // at once) and zeroed when stored.
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    float4 qv[8], kvv[NB];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
-      qv[i] = __ldg(reinterpret_cast<const float4*>(qg + (long long)min(q0 + row, T - 1) * p.row_stride + c4 * 4));
-    }
-#pragma unroll
-    for (int i = 0; i < NB; ++i) {
-      const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
-      kvv[i] = __ldg(reinterpret_cast<const float4*>(kg + (long long)min(row, T - 1) * p.row_stride + c4 * 4));
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
-      uint8_t* blk = qp + (c4 >> 2) * (QM * 64);
-      store_split(blk, blk + 4 * QM * 64, sw64_off(row, c4 & 3), q0 + row < T ? qv[i] : zero4);
-    }
-#pragma unroll
-    for (int i = 0; i < NB; ++i) {
-      const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
-      uint8_t* blk = kv + (c4 >> 2) * kKBlock;
-      store_split(blk, blk + 4 * kKBlock, sw64_off(row, c4 & 3), row < T ? kvv[i] : zero4);
-    }
-  }
-  // ---- V into registers: thread (d, tg) takes tokens 16 i + 4 tg + {0..3} of column d,
-  // the 16-byte chunk tg of row d in block i of V^T ----
-  const int vd = tid & 63, vtg = (tid >> 6) & 3;
-  float vv[NB][4];
-  if (warp < 8)
-#pragma unroll
-  for (int i = 0; i < NB; ++i)
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int t = 16 * i + 4 * vtg + u;
-      vv[i][u] = __ldg(vg + (long long)min(t, T - 1) * p.row_stride + vd);   // masked when stored
-    }
-  // Largest |v| of this head, for the power-of-two scale that puts V into the fp16 range.
-  if (warp < 8) {
-    float vmax = 0.f;
-#pragma unroll
-    for (int i = 0; i < NB; ++i)
-#pragma unroll
-      for (int u = 0; u < 4; ++u) vmax = fmaxf(vmax, fabsf(vv[i][u]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-    if (lane == 0) xch[warp] = vmax;
-  }
-
-  AT_STAMP(1);
-  fence_proxy_async();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  AT_STAMP(2);
-  const uint32_t tmem_base = *tmem_slot;
   const uint32_t idesc_s = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NS >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
   // Second product: fp16 operands (format 0), N = 64.
   const uint32_t idesc_o = (1u << 4) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QM >> 4) << 24);
-  // sv = 2^(13 - floor(log2 max|v|)): |v * sv| < 2^14. A zero, infinite or NaN maximum leaves V
-  // unscaled (the result is then zero, or not finite as in fp32).
-  float sv = 1.f, inv_sv = 1.f;
-  {
-    float vm = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) vm = fmaxf(vm, xch[w]);
-    const int eb = (int)((__float_as_uint(vm) >> 23) & 0xFFu);
-    if (eb > 0 && eb < 255) {
-      const int f = min(max(267 - eb, 1), 253);
-      sv = __uint_as_float((uint32_t)f << 23);
-      inv_sv = __uint_as_float((uint32_t)(254 - f) << 23);
-    }
-  }
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int vd = tid & 63, vtg = (tid >> 6) & 3;   // V: thread (d, tg) takes keys 16 i + 4 tg + {0..3} of column d
+  float sv = 1.f, inv_sv = 1.f;                // power-of-two scale of V and its inverse
+  uint32_t tmem_base = 0;
+  int uses0 = 0, uses1 = 0;                    // softmax: uses so far of this half's two ring slots
+  uint32_t mma_par = 0;                        // MMA thread: bit s = parity of the next use of ring slot s
+  float4 qnext[8];                             // the next query tile, fetched while this one finishes
 
-  // ---- S = Q K^T: 4 blocks x 2 K-steps x 3 MMAs ----
-  if (warp == 8 && lane == 0) {
+  // One query tile. The first one also stages K and V (FIRST: compiled as its own copy, so
+  // that V's registers are not carried through the later tiles).
+  auto do_tile = [&](auto first_tag, const int tile) {
+    constexpr bool FIRST = decltype(first_tag)::value;
+    stamp_base = FIRST ? 0 : 10;
+    float vv[FIRST ? NB : 1][4];
+    const int q0 = (RESIDENT ? tile : (int)blockIdx.x) * QM;
+    const uint32_t par = (uint32_t)(tile & 1);
+    // ---- stage Q [128 x 64] (and, once, K [NS x 64] and V): 16 threads per row, one float4
+    // each. Rows past the end are read from the last row (unconditional loads, all in
+    // flight at once) and zeroed when stored. ----
+    if (warp < 8) {
+      if (!FIRST) group_sync();                // every warp is done with the P ring / output tiles in qp
+      float4 qv[8];
 #pragma unroll
-    for (int blk = 0; blk < 4; ++blk)
-#pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        const uint32_t qa = smem_u32(qp + blk * (QM * 64)) + kk * 32;
-        const uint32_t ka = smem_u32(kv + blk * kKBlock) + kk * 32;
-        const uint64_t a_hi = desc_sw64(qa), a_lo = desc_sw64(qa + 4 * QM * 64);
-        const uint64_t b_hi = desc_sw64(ka), b_lo = desc_sw64(ka + 4 * kKBlock);
-        tc_mma_tf32(tmem_base, a_lo, b_hi, idesc_s, (blk | kk) ? 1u : 0u);
-        tc_mma_tf32(tmem_base, a_hi, b_lo, idesc_s, 1u);
-        tc_mma_tf32(tmem_base, a_hi, b_hi, idesc_s, 1u);
+      for (int i = 0; i < 8; ++i) {
+        const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
+        if (FIRST) qv[i] = __ldg(reinterpret_cast<const float4*>(qg + (long long)min(q0 + row, T - 1) * p.row_stride + c4 * 4));
+        else qv[i] = qnext[i];
       }
-    tc_commit(s_full);
-  }
-  __syncwarp();
-  if (!mbar_wait(s_full, 0)) { atomicExch(p.err, 11); ok = false; }
-  tc_fence_after();
-  AT_STAMP(3);
-
-  // ---- K is consumed: store V^T over it as fp16 hi / lo of v * sv, blocks of 32 tokens
-  // (64-byte rows); an odd last block gets zeros in its second half ----
-  constexpr int NBLK = (NB + 1) / 2;           // 32-token blocks
-  if (warp < 8)
+      if constexpr (FIRST) {
+        float4 kvv[NB];
 #pragma unroll
-  for (int i = 0; i < 2 * NBLK; ++i) {
-    const int t0 = 16 * i + 4 * vtg;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (i < NB)
-      x = make_float4(t0 < T ? __fmul_rn(vv[i < NB ? i : 0][0], sv) : 0.f, t0 + 1 < T ? __fmul_rn(vv[i < NB ? i : 0][1], sv) : 0.f,
-                      t0 + 2 < T ? __fmul_rn(vv[i < NB ? i : 0][2], sv) : 0.f, t0 + 3 < T ? __fmul_rn(vv[i < NB ? i : 0][3], sv) : 0.f);
-    uint2 hi, lo;
-    f16_split(x, hi, lo);
-    const uint32_t off = (uint32_t)((i >> 1) * kVBlock) + sw64_off8(vd, 4 * (i & 1) + vtg);
-    *reinterpret_cast<uint2*>(kv + off) = hi;
-    *reinterpret_cast<uint2*>(kv + NBLK * kVBlock + off) = lo;
-  }
-  fence_proxy_async();
-  __syncthreads();
-  AT_STAMP(4);
-
-  constexpr int NBLK0 = (NBLK + 1) / 2;        // blocks of the first column half
-  if (warp < 8) {
-    // ---------------- softmax: two threads per row, one per column half ----------------
-    const int q = warp & 3, hf = warp >> 2;    // tensor-memory lane quarter, column half
-    const int row = q * 32 + lane;
-    const int b_begin = hf ? NBLK0 : 0, b_count = hf ? NBLK - NBLK0 : NBLK0;
-    const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
-    const float sc = SMODE ? __ldg(p.scale) : 1.f;
-    float m = CUDART_NAN_F;
-#pragma unroll 1
-    for (int i = 0; i < 2 * b_count; ++i) {
-      const int c = 2 * b_begin + i;           // 16-column chunk; chunks past NS read junk that is masked
-      uint32_t v[16];
-      tc_ld_32x16(trow + (uint32_t)(c * 16), v);
-      // Columns past T (exact zeros up to NS, junk beyond) are kept out of the maximum
-      // by a select, not a branch, so that the 16 chains stay interleaved.
+        for (int i = 0; i < NB; ++i) {
+          const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
+          kvv[i] = __ldg(reinterpret_cast<const float4*>(kg + (long long)min(row, T - 1) * p.row_stride + c4 * 4));
+        }
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const float sv_ = apply_scale<SMODE>(__uint_as_float(v[u]), sc);
-        m = fmaxf(c * 16 + u < T ? sv_ : CUDART_NAN_F, m);
+        for (int i = 0; i < NB; ++i) {
+          const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
+          uint8_t* blk = kv + (c4 >> 2) * kKBlock;
+          store_split(blk, blk + 4 * kKBlock, sw64_off(row, c4 & 3), row < T ? kvv[i] : zero4);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = tid + kAtThreads * i, row = idx >> 4, c4 = idx & 15;
+        uint8_t* blk = qp + (c4 >> 2) * (QM * 64);
+        store_split(blk, blk + 4 * QM * 64, sw64_off(row, c4 & 3), q0 + row < T ? qv[i] : zero4);
+      }
+      if constexpr (FIRST) {
+        // V into registers; it is used after the barrier below, under the first product.
+#pragma unroll
+        for (int i = 0; i < NB; ++i)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int t = 16 * i + 4 * vtg + u;
+            vv[i][u] = __ldg(vg + (long long)min(t, T - 1) * p.row_stride + vd);   // masked when stored
+          }
       }
     }
-    xch[hf * QM + row] = m;
-    pair_sync(q);
-    m = fmaxf(xch[QM + row], xch[row]);
-    pair_sync(q);                              // both have read before the sums overwrite
-    AT_STAMP(5);
-    float sum = 0.f;
-#pragma unroll 1
-    for (int i = 0; i < b_count; ++i) {
-      const int blk = b_begin + i;
-      const int slot = 2 * hf + (i & 1);
-      if (ok && i >= 2 && !mbar_wait(&freeb[slot], ((i >> 1) - 1) & 1)) { atomicExch(p.err, 12); ok = false; }
-      uint8_t* sl = qp + slot * kSlotBytes;
+    AT_STAMP(1);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    AT_STAMP(2);
+    if (FIRST) tmem_base = *tmem_slot;
+
+    // ---- S = Q K^T: 4 blocks x 2 K-steps x 3 TF32 MMAs ----
+    if (warp == 8 && lane == 0) {
 #pragma unroll
-      for (int h16 = 0; h16 < 2; ++h16) {
-        const int c0 = blk * 32 + h16 * 16;
+      for (int blk = 0; blk < 4; ++blk)
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint32_t qa = smem_u32(qp + blk * (QM * 64)) + kk * 32;
+          const uint32_t ka = smem_u32(kv + blk * kKBlock) + kk * 32;
+          const uint64_t a_hi = desc_sw64(qa), a_lo = desc_sw64(qa + 4 * QM * 64);
+          const uint64_t b_hi = desc_sw64(ka), b_lo = desc_sw64(ka + 4 * kKBlock);
+          tc_mma_tf32(tmem_base, a_lo, b_hi, idesc_s, (blk | kk) ? 1u : 0u);
+          tc_mma_tf32(tmem_base, a_hi, b_lo, idesc_s, 1u);
+          tc_mma_tf32(tmem_base, a_hi, b_hi, idesc_s, 1u);
+        }
+      tc_commit(s_full);
+    }
+    __syncwarp();
+    if constexpr (FIRST) {
+    if (warp < 8) {
+      // Largest |v| of this head, for the power-of-two scale that puts V into the fp16 range.
+      float vmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < NB; ++i)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) vmax = fmaxf(vmax, fabsf(vv[i][u]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+      if (lane == 0) xch[warp] = vmax;
+      group_sync();
+      scale_from_maxima(xch, sv, inv_sv);
+      // V^T with memory of its own is stored under the first product; otherwise it
+      // overwrites K and has to wait for S.
+      if (RESIDENT) store_vt<NB>(vt, vv, sv, vd, vtg, T);
+    }
+    if (RESIDENT) {
+      fence_proxy_async();
+      __syncthreads();
+    }
+    }
+    if (ok && !warp_mbar_wait(s_full, par, lane)) { atomicExch(p.err, 11); ok = false; }
+    tc_fence_after();
+    AT_STAMP(3);
+    if constexpr (FIRST && !RESIDENT) {
+      if (warp < 8) store_vt<NB>(vt, vv, sv, vd, vtg, T);
+      fence_proxy_async();
+      __syncthreads();
+    }
+    AT_STAMP(4);
+
+    if (warp < 8) {
+      // ---------------- softmax: two threads per row, one per column half ----------------
+      const int q = warp & 3, hf = warp >> 2;    // tensor-memory lane quarter, column half
+      const int row = q * 32 + lane;
+      const int b_begin = hf ? NBLK0 : 0, b_count = hf ? NBLK - NBLK0 : NBLK0;
+      const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
+      const float sc = SMODE ? __ldg(p.scale) : 1.f;
+      float m = CUDART_NAN_F;
+#pragma unroll 1
+      for (int i = 0; i < 2 * b_count; ++i) {
+        const int c = 2 * b_begin + i;           // 16-column chunk; chunks past NS read junk that is masked
         uint32_t v[16];
-        tc_ld_32x16(trow + (uint32_t)c0, v);
-        float e[16];
+        tc_ld_32x16(trow + (uint32_t)(c * 16), v);
+        // Columns past T (exact zeros up to NS, junk beyond) are kept out of the maximum
+        // by a select, not a branch, so that the 16 chains stay interleaved.
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          const float ev = exp_poly_softmax(__fsub_rn(apply_scale<SMODE>(__uint_as_float(v[u]), sc), m));
-          e[u] = c0 + u < T ? ev : 0.f;
-        }
-#pragma unroll
-        for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);   // + 0 for masked columns: exact
-        // P as fp16 hi / lo of e * 2^13 (e <= 1: in range, and far from the subnormals)
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          uint2 h0, l0, h1, l1;
-          f16_split(make_float4(e[8 * j] * 8192.f, e[8 * j + 1] * 8192.f, e[8 * j + 2] * 8192.f, e[8 * j + 3] * 8192.f), h0, l0);
-          f16_split(make_float4(e[8 * j + 4] * 8192.f, e[8 * j + 5] * 8192.f, e[8 * j + 6] * 8192.f, e[8 * j + 7] * 8192.f), h1, l1);
-          const uint32_t off = sw64_off(row, 2 * h16 + j);
-          *reinterpret_cast<uint4*>(sl + off) = make_uint4(h0.x, h0.y, h1.x, h1.y);
-          *reinterpret_cast<uint4*>(sl + QM * 64 + off) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+          const float sv_ = apply_scale<SMODE>(__uint_as_float(v[u]), sc);
+          m = fmaxf(c * 16 + u < T ? sv_ : CUDART_NAN_F, m);
         }
       }
-      fence_proxy_async();
-      if (ok) mbar_arrive(&ready[slot]);
-    }
-    xch[hf * QM + row] = sum;
-    pair_sync(q);
-    sum = __fadd_rn(xch[row], xch[QM + row]);
-    // ---- O = (D1 + D2 * 2^-11) * (1 / sum) * 2^-13 / sv: this warp takes 32 of the 64
-    // columns; through a 4 KB tile of the (now idle) P ring so that every 8 lanes write one
-    // full 128-byte line ----
-    AT_STAMP(6);
-    if (ok && !mbar_wait(o_full, 0)) { atomicExch(p.err, 13); ok = false; }
-    tc_fence_after();
-    AT_STAMP(7);
-    const float recip = __fdiv_rn(1.f, sum);
-    uint32_t o[32], o2[32];
-    tc_ld_32x32(trow + kOCol + (uint32_t)(hf * 32), o);
-    tc_ld_32x32(trow + kOCol + (uint32_t)(HD + hf * 32), o2);
-    float4* stage = reinterpret_cast<float4*>(qp + warp * 4096);
-    auto fin = [&](int j) {
-      const float y = fmaf(__uint_as_float(o2[j]), kLoUnscale, __uint_as_float(o[j]));
-      return __fmul_rn(__fmul_rn(__fmul_rn(y, recip), 1.f / 8192.f), inv_sv);
-    };
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      stage[lane * 8 + (j ^ (lane & 7))] = make_float4(fin(4 * j), fin(4 * j + 1), fin(4 * j + 2), fin(4 * j + 3));
-    __syncwarp();
-    const int c4 = lane & 7, rsub = lane >> 3;
-    float* og = p.out + (long long)b * p.out_batch_stride + (long long)h * HD + hf * 32 + 4 * c4;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int rl = 4 * i + rsub, r = q0 + q * 32 + rl;
-      if (ok && r < T) *reinterpret_cast<float4*>(og + (long long)r * p.out_row_stride) = stage[rl * 8 + (c4 ^ (rl & 7))];
-    }
-  } else if (lane == 0) {
-    // ---------------- O = P V: per 32-key block 2 K-steps x 3 fp16 MMAs; the halves alternate ----------------
+      xch[hf * QM + row] = m;
+      pair_sync(q);
+      m = fmaxf(xch[QM + row], xch[row]);
+      pair_sync(q);                              // both have read before the sums overwrite
+      AT_STAMP(5);
+      float sum = 0.f;
 #pragma unroll 1
-    for (int n = 0; ok && n < 2 * NBLK0; ++n) {
-      const int hf = n & 1, i = n >> 1;
-      const int blk = hf ? NBLK0 + i : i;
-      if (blk >= NBLK) continue;
-      const int slot = 2 * hf + (i & 1);
-      if (!mbar_wait(&ready[slot], (i >> 1) & 1)) { atomicExch(p.err, 14); ok = false; break; }
-      tc_fence_after();
+      for (int i = 0; i < b_count; ++i) {
+        const int blk = b_begin + i;
+        const int slot = 2 * hf + (i & 1);
+        const int n = (i & 1) ? uses1 : uses0;   // this is use n of the slot over the whole kernel
+        if (ok && n >= 1 && !warp_mbar_wait(&freeb[slot], (uint32_t)((n - 1) & 1), lane)) { atomicExch(p.err, 12); ok = false; }
+        if (i & 1) ++uses1; else ++uses0;
+        uint8_t* sl = qp + slot * kSlotBytes;
 #pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        const uint32_t pa = smem_u32(qp + slot * kSlotBytes) + kk * 32;
-        const uint32_t va = smem_u32(kv + blk * kVBlock) + kk * 32;
-        const uint64_t a_hi = desc_sw64(pa), a_lo = desc_sw64(pa + QM * 64);
-        const uint64_t b_hi = desc_sw64(va), b_lo = desc_sw64(va + NBLK * kVBlock);
-        const uint32_t first = (n | kk) ? 1u : 0u;
-        tc_mma_f16(tmem_base + kOCol, a_hi, b_hi, idesc_o, first);            // hi * hi      -> D1
-        tc_mma_f16(tmem_base + kOCol + HD, a_lo, b_hi, idesc_o, first);       // lo' * hi     -> D2
-        tc_mma_f16(tmem_base + kOCol + HD, a_hi, b_lo, idesc_o, 1u);          // hi * lo'     -> D2
+        for (int h16 = 0; h16 < 2; ++h16) {
+          const int c0 = blk * 32 + h16 * 16;
+          uint32_t v[16];
+          tc_ld_32x16(trow + (uint32_t)c0, v);
+          float e[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const float ev = exp_poly_softmax(__fsub_rn(apply_scale<SMODE>(__uint_as_float(v[u]), sc), m));
+            e[u] = c0 + u < T ? ev : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);   // + 0 for masked columns: exact
+          // P as fp16 hi / lo of e * 2^13 (e <= 1: in range, and far from the subnormals)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            uint2 h0, l0, h1, l1;
+            f16_split(make_float4(e[8 * j] * 8192.f, e[8 * j + 1] * 8192.f, e[8 * j + 2] * 8192.f, e[8 * j + 3] * 8192.f), h0, l0);
+            f16_split(make_float4(e[8 * j + 4] * 8192.f, e[8 * j + 5] * 8192.f, e[8 * j + 6] * 8192.f, e[8 * j + 7] * 8192.f), h1, l1);
+            const uint32_t off = sw64_off(row, 2 * h16 + j);
+            *reinterpret_cast<uint4*>(sl + off) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+            *reinterpret_cast<uint4*>(sl + QM * 64 + off) = make_uint4(l0.x, l0.y, l1.x, l1.y);
+          }
+        }
+        fence_proxy_async();
+        if (ok) mbar_arrive(&ready[slot]);
       }
-      tc_commit(&freeb[slot]);
+      if (tile + 1 < n_tiles) {                  // next query tile into registers, under the tail of this one
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int idx = tid + kAtThreads * i, r2 = idx >> 4, c4 = idx & 15;
+          qnext[i] = __ldg(reinterpret_cast<const float4*>(qg + (long long)min(q0 + QM + r2, T - 1) * p.row_stride + c4 * 4));
+        }
+      }
+      xch[hf * QM + row] = sum;
+      pair_sync(q);
+      sum = __fadd_rn(xch[row], xch[QM + row]);
+      // ---- O = (D1 + D2 * 2^-11) * (1 / sum) * 2^-13 / sv: this warp takes 32 of the 64
+      // columns; through a 4 KB tile of the (now idle) P ring so that every 8 lanes write one
+      // full 128-byte line ----
+      AT_STAMP(6);
+      if (ok && !warp_mbar_wait(o_full, par, lane)) { atomicExch(p.err, 13); ok = false; }
+      tc_fence_after();
+      AT_STAMP(7);
+      const float recip = __fdiv_rn(1.f, sum);
+      uint32_t o[32], o2[32];
+      tc_ld_32x32(trow + kOCol + (uint32_t)(hf * 32), o);
+      tc_ld_32x32(trow + kOCol + (uint32_t)(HD + hf * 32), o2);
+      float4* stage = reinterpret_cast<float4*>(qp + warp * 4096);
+      auto fin = [&](int j) {
+        const float y = fmaf(__uint_as_float(o2[j]), kLoUnscale, __uint_as_float(o[j]));
+        return __fmul_rn(__fmul_rn(__fmul_rn(y, recip), 1.f / 8192.f), inv_sv);
+      };
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        stage[lane * 8 + (j ^ (lane & 7))] = make_float4(fin(4 * j), fin(4 * j + 1), fin(4 * j + 2), fin(4 * j + 3));
+      __syncwarp();
+      const int c4 = lane & 7, rsub = lane >> 3;
+      float* og = p.out + (long long)b * p.out_batch_stride + (long long)h * HD + hf * 32 + 4 * c4;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rl = 4 * i + rsub, r = q0 + q * 32 + rl;
+        if (ok && r < T) *reinterpret_cast<float4*>(og + (long long)r * p.out_row_stride) = stage[rl * 8 + (c4 ^ (rl & 7))];
+      }
+      tc_fence_before();                         // the tensor-memory loads above precede the next tile's MMAs
+    } else if (lane == 0) {
+      // ---------------- O = P V: per 32-key block 2 K-steps x 3 fp16 MMAs; the halves alternate ----------------
+#pragma unroll 1
+      for (int n = 0; ok && n < 2 * NBLK0; ++n) {
+        const int hf = n & 1, i = n >> 1;
+        const int blk = hf ? NBLK0 + i : i;
+        if (blk >= NBLK) continue;
+        const int slot = 2 * hf + (i & 1);
+        if (!mbar_wait(&ready[slot], (mma_par >> slot) & 1u)) { atomicExch(p.err, 14); ok = false; break; }
+        mma_par ^= 1u << slot;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint32_t pa = smem_u32(qp + slot * kSlotBytes) + kk * 32;
+          const uint32_t va = smem_u32(vt + blk * kVBlock) + kk * 32;
+          const uint64_t a_hi = desc_sw64(pa), a_lo = desc_sw64(pa + QM * 64);
+          const uint64_t b_hi = desc_sw64(va), b_lo = desc_sw64(va + NBLK * kVBlock);
+          const uint32_t first = (n | kk) ? 1u : 0u;
+          tc_mma_f16(tmem_base + kOCol, a_hi, b_hi, idesc_o, first);            // hi * hi      -> D1
+          tc_mma_f16(tmem_base + kOCol + HD, a_lo, b_hi, idesc_o, first);       // lo' * hi     -> D2
+          tc_mma_f16(tmem_base + kOCol + HD, a_hi, b_lo, idesc_o, 1u);          // hi * lo'     -> D2
+        }
+        tc_commit(&freeb[slot]);
+      }
+      if (ok) tc_commit(o_full);
     }
-    if (ok) tc_commit(o_full);
-  }
-  AT_STAMP(8);
+    AT_STAMP(8);
+  };
+  do_tile(std::true_type{}, 0);
+#pragma unroll 1
+  for (int tile = 1; tile < n_tiles; ++tile) do_tile(std::false_type{}, tile);
   tc_fence_before();
   __syncthreads();
   if (warp == 8) {
@@ -413,16 +477,21 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
 
 template <int NB, int SMODE>
 cudaError_t launch_nb_mode(const AttnTcDev& d, int bh, cudaStream_t st) {
-  constexpr int kDyn = NB * 8192 + kQBytes + 128 /*barriers*/ + 1024 /*row exchange*/ + 1024 /*alignment*/;
+  constexpr int kExtra = 128 /*barriers*/ + 1024 /*row exchange*/ + 1024 /*alignment*/;
+  constexpr int kDynResident = NB * 8192 + ((NB + 1) / 2) * 8192 + kQBytes + kExtra;
+  constexpr int kDynOverlay = NB * 8192 + kQBytes + kExtra;
+  constexpr bool kResident = kDynResident <= 227 * 1024;
+  constexpr int kDyn = kResident ? kDynResident : kDynOverlay;
   static_assert(kDyn <= 227 * 1024, "shared memory per CTA");
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<NB, SMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn);
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<NB, SMODE, kResident>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  dim3 grid((d.tokens + QM - 1) / QM, bh);
-  attention_tc_kernel<NB, SMODE><<<grid, kAtLaunch, kDyn, st>>>(d);
+  dim3 grid(kResident ? 1 : (d.tokens + QM - 1) / QM, bh);
+  attention_tc_kernel<NB, SMODE, kResident><<<grid, kAtLaunch, kDyn, st>>>(d);
   return cudaGetLastError();
 }
 
@@ -459,11 +528,13 @@ cudaError_t launch_attention_tc(const AttentionParams& p, cudaStream_t st) {
   const int bh = p.batch * p.heads;
   cudaError_t e = p.tokens <= 128 ? launch_nb<8>(d, bh, st) : p.tokens <= 208 ? launch_nb<13>(d, bh, st) : launch_nb<16>(d, bh, st);
   if (stamps && e == cudaSuccess) {
-    long long h[16];
+    long long h[32];
     cudaStreamSynchronize(st);
     cudaMemcpyFromSymbol(h, g_attn_stamps, sizeof(h));
     std::fprintf(stderr, "attention_tc stamps:");
     for (int i = 1; i <= 8; ++i) std::fprintf(stderr, " %lld", h[i] - h[0]);
+    std::fprintf(stderr, " |");
+    for (int i = 11; i <= 18; ++i) std::fprintf(stderr, " %lld", h[i] - h[0]);
     std::fprintf(stderr, "\n");
   }
   return e;

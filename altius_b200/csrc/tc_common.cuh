@@ -43,6 +43,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+// A whole warp waits on an mbarrier phase: one lane polls (fewer probes of shared memory
+// while the tensor core fetches its operands from it), the others get the result by shuffle.
+__device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, int lane) {
+  int done = 1;
+  if (lane == 0) done = mbar_wait(bar, parity) ? 1 : 0;
+  done = __shfl_sync(0xffffffffu, done, 0);
+  return done != 0;
+}
+
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x,
                                             int y, int z) {
   asm volatile(
