@@ -340,10 +340,11 @@ struct TcSmem {
   static constexpr int kABytes = kF16 ? MT * BM * kKb * 2 : MT * BM * kKb * 4;   // one of A hi / lo
   static constexpr int kBBytes = kF16 ? BN * kKb * 2 : BN * kKb * 4;             // one of B hi / lo
   static constexpr int kOffAHi = kARaw;
+  static constexpr bool k1X = MODE == TC_1X;                      // one copy of each operand, no lo tiles
   static constexpr int kOffALo = kARaw + kABytes;
-  static constexpr int kOffBHi = kARaw + 2 * kABytes;
+  static constexpr int kOffBHi = kARaw + (k1X ? 1 : 2) * kABytes;
   static constexpr int kOffBLo = kOffBHi + kBBytes;
-  static constexpr int kStageBytes = kARaw + 2 * kABytes + 2 * kBBytes;
+  static constexpr int kStageBytes = k1X ? kABytes + kBBytes : kARaw + 2 * kABytes + 2 * kBBytes;
   static constexpr int kTxBytes = (kF16 ? kARaw : kABytes) + kBBytes + ((kF16 || MODE == TC_3X_BLO_TMA) ? kBBytes : 0);
   static constexpr int kStages = (200 * 1024) / kStageBytes;      // TF32: 4 / 6 / 8; fp16: 3 / 4 / 5 (BN 256 / 128 / 64)
   static constexpr int kEpiBytes = 4 * 4096;                      // one 4 KB transpose tile per epilogue warp

@@ -439,6 +439,61 @@ int altius_cuda_run_device(AcSession* s, const void* const* d_ins, void* const* 
   return run_common(s, d_ins, d_outs, true);
 }
 
+int altius_cuda_run_batches(AcSession* s, int32_t n_batches, const void* const* ins, void* const* outs) {
+  if (!s || n_batches < 0 || (!ins && !s->inputs.empty() && n_batches) || (!outs && n_batches))
+    return set_err(s, AC_ERR_INVALID, "bad argument");
+  if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
+  const size_t ni = s->inputs.size(), no = s->outputs.size();
+  // Sessions that profile, or that have switched to their fallback plan, take the plain path.
+  if (s->opt.enable_profiling || s->use_fallback || n_batches < 2) {
+    for (int b = 0; b < n_batches; ++b) {
+      const int rc = run_common(s, ins + (size_t)b * ni, outs + (size_t)b * no, false);
+      if (rc != AC_OK) return rc;
+    }
+    return AC_OK;
+  }
+  cudaError_t e = cudaSetDevice(s->device);
+  if (e == cudaSuccess && !s->copy_stream) {
+    e = cudaStreamCreateWithFlags(&s->copy_stream, cudaStreamNonBlocking);
+    for (int k = 0; k < 2 && e == cudaSuccess; ++k) {
+      s->staging[k].assign(ni, nullptr);
+      for (size_t i = 0; i < ni && e == cudaSuccess; ++i)
+        e = cudaMalloc(&s->staging[k][i], std::max<size_t>(s->values[s->inputs[i]].bytes(), 16));
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->staged[k], cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->consumed[k], cudaEventDisableTiming);
+    }
+  }
+  for (int b = 0; b < n_batches && e == cudaSuccess; ++b) {
+    const int k = b & 1;
+    // copy stream: inputs of batch b into staging set k (free again once batch b-2 has left it)
+    if (b >= 2) e = cudaStreamWaitEvent(s->copy_stream, s->consumed[k], 0);
+    for (size_t i = 0; i < ni && e == cudaSuccess; ++i) {
+      const void* src = ins[(size_t)b * ni + i];
+      if (!src) return set_err(s, AC_ERR_INVALID, "null input buffer");
+      e = cudaMemcpyAsync(s->staging[k][i], src, s->values[s->inputs[i]].bytes(), cudaMemcpyHostToDevice, s->copy_stream);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(s->staged[k], s->copy_stream);
+    // compute stream: staging -> arena (device copy), schedule, outputs to the host
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s->stream, s->staged[k], 0);
+    for (size_t i = 0; i < ni && e == cudaSuccess; ++i)
+      e = cudaMemcpyAsync(s->ptr(s->inputs[i]), s->staging[k][i], s->values[s->inputs[i]].bytes(),
+                          cudaMemcpyDeviceToDevice, s->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(s->consumed[k], s->stream);
+    if (e == cudaSuccess) e = s->graph_exec ? cudaGraphLaunch(s->graph_exec, s->stream) : replay(s, s->stream);
+    for (size_t i = 0; i < no && e == cudaSuccess; ++i) {
+      void* dst = outs[(size_t)b * no + i];
+      if (!dst) return set_err(s, AC_ERR_INVALID, "null output buffer");
+      e = cudaMemcpyAsync(dst, s->ptr(s->outputs[i]), s->values[s->outputs[i]].bytes(), cudaMemcpyDeviceToHost, s->stream);
+    }
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost, s->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
+  if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("run_batches: ") + cudaGetErrorString(e));
+  if (const int rc = check_err_word(s))   // out of fp16 range somewhere: all batches again on the fallback plan
+    return rc == 1 ? altius_cuda_run_batches(s, n_batches, ins, outs) : rc;
+  return AC_OK;
+}
+
 int altius_cuda_time_device_runs(AcSession* s, const void* const* d_ins, void* const* d_outs,
                                  int32_t iters, float* elapsed_ms) {
   if (!s || !elapsed_ms || iters <= 0 || !d_outs || (!d_ins && !s->inputs.empty()))
@@ -565,6 +620,13 @@ void altius_cuda_destroy(AcSession* s) {
     if (ev) cudaEventDestroy(ev);
   if (s->err_word) cudaFree(s->err_word);
   if (s->sweep_buf) cudaFree(s->sweep_buf);
+  for (int k = 0; k < 2; ++k) {
+    for (void* p : s->staging[k])
+      if (p) cudaFree(p);
+    if (s->staged[k]) cudaEventDestroy(s->staged[k]);
+    if (s->consumed[k]) cudaEventDestroy(s->consumed[k]);
+  }
+  if (s->copy_stream) cudaStreamDestroy(s->copy_stream);
   if (s->err_host) cudaFreeHost(s->err_host);
   if (s->arena) cudaFree(s->arena);
   if (s->weights) cudaFree(s->weights);

@@ -115,6 +115,11 @@ struct AcSession {
   std::string err;
   // gemm_mode 0 only: when an operand of an fp16-split GEMM turns out not to fit fp16,
   // a second session lowered with gemm_mode 3 (3xTF32) takes over for good.
+  // run_batches: second stream, two sets of device staging buffers for the inputs, events
+  cudaStream_t copy_stream = nullptr;
+  std::vector<void*> staging[2];
+  cudaEvent_t staged[2] = {nullptr, nullptr};    // H2D of a staging set has landed
+  cudaEvent_t consumed[2] = {nullptr, nullptr};  // the set has been copied into the arena
   std::unique_ptr<ac::GraphCopy> desc;
   AcSession* fallback = nullptr;
   bool use_fallback = false;

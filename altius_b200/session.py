@@ -83,7 +83,7 @@ class AcProfileEntry(ctypes.Structure):
 
 # Every symbol include/altius_session_cuda.h declares.
 ABI_SYMBOLS = (
-    "altius_cuda_create", "altius_cuda_run", "altius_cuda_run_device",
+    "altius_cuda_create", "altius_cuda_run", "altius_cuda_run_device", "altius_cuda_run_batches",
     "altius_cuda_time_device_runs", "altius_cuda_num_inputs",
     "altius_cuda_num_outputs", "altius_cuda_input_value", "altius_cuda_output_value",
     "altius_cuda_value_info", "altius_cuda_launches_per_run", "altius_cuda_arena_bytes",
@@ -109,6 +109,7 @@ def load_library() -> ctypes.CDLL:
                                        ctypes.POINTER(P)]
     lib.altius_cuda_run.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(P)]
     lib.altius_cuda_run_device.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(P)]
+    lib.altius_cuda_run_batches.argtypes = [P, ctypes.c_int32, ctypes.POINTER(P), ctypes.POINTER(P)]
     lib.altius_cuda_time_device_runs.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(P),
                                                  ctypes.c_int32, ctypes.POINTER(ctypes.c_float)]
     for name in ("altius_cuda_num_inputs", "altius_cuda_num_outputs"):
@@ -302,6 +303,32 @@ class CudaSession:
         ins = (ctypes.c_void_p * max(1, len(arrs)))(*[a.ctypes.data for a in arrs])
         outs = (ctypes.c_void_p * max(1, len(outputs)))(*[o.ctypes.data for o in outputs])
         self._check(self._lib.altius_cuda_run(self._handle, ins, outs))
+        return outputs
+
+    def run_batches(self, batches: Sequence[Sequence[np.ndarray]],
+                    outputs: Optional[List[List[np.ndarray]]] = None) -> List[List[np.ndarray]]:
+        """`run` for a queue of batches, pipelined: the inputs of batch b+1 are copied to the
+        device while batch b computes. Pass page-locked arrays (`alloc_pinned`) for the copies
+        to overlap. Returns one output list per batch."""
+        checked = []
+        for inputs in batches:
+            if len(inputs) != len(self.input_ids):
+                raise SessionError(1, f"expected {len(self.input_ids)} inputs, got {len(inputs)}")
+            row = []
+            for a, (shape, dt) in zip(inputs, self.input_info):
+                a = np.ascontiguousarray(a, dtype=dt)
+                if tuple(a.shape) != tuple(shape):
+                    raise SessionError(2, f"input shape {a.shape} does not match {shape}")
+                row.append(a)
+            checked.append(row)
+        if outputs is None:
+            outputs = [[np.empty(shape, dt) for shape, dt in self.output_info] for _ in checked]
+        n = len(checked)
+        flat_in = [a.ctypes.data for row in checked for a in row]
+        flat_out = [o.ctypes.data for row in outputs for o in row]
+        ins = (ctypes.c_void_p * max(1, len(flat_in)))(*flat_in)
+        outs = (ctypes.c_void_p * max(1, len(flat_out)))(*flat_out)
+        self._check(self._lib.altius_cuda_run_batches(self._handle, n, ins, outs))
         return outputs
 
     def run_device(self, in_ptrs: Sequence[int], out_ptrs: Sequence[int]) -> None:

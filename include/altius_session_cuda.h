@@ -184,6 +184,16 @@ int altius_cuda_run(AcSession *s, const void *const *ins, void *const *outs);
  * in HBM); returns after the work is complete. */
 int altius_cuda_run_device(AcSession *s, const void *const *d_ins, void *const *d_outs);
 
+/* `n_batches` independent runs from HOST buffers, pipelined: `ins` holds n_batches *
+ * num_inputs pointers (batch-major), `outs` n_batches * num_outputs. The inputs of batch
+ * b+1 travel to the device (second stream, double-buffered staging) while batch b
+ * computes; outputs are complete on return. The buffers should be page-locked
+ * (altius_cuda_host_alloc), otherwise the copies do not overlap. Results are those of
+ * n_batches calls of altius_cuda_run. The reference has no counterpart (its run() is
+ * synchronous CPU code, session.rs:66-134); a caller with a queue of batches uses this
+ * to keep the copy engines and the SMs busy at the same time. */
+int altius_cuda_run_batches(AcSession *s, int32_t n_batches, const void *const *ins, void *const *outs);
+
 /* `iters` back-to-back runs with device buffers, timed on the device: CUDA
  * events recorded on the session's stream before the first and after the last
  * run; *elapsed_ms receives the time between them. For measurement harnesses

@@ -81,3 +81,32 @@ def test_profile_reports_every_kernel_kind(cuda_lib):
     assert sum(p["launches"] for p in prof.values()) == sess.launches_per_run
     assert all(p["total_ms"] > 0 for p in prof.values())
     sess.close()
+
+
+def test_run_batches_equals_run_per_batch(cuda_lib):
+    """The pipelined queue call returns, batch by batch, exactly what `run` returns; with
+    pageable and with page-locked buffers, and for a single batch."""
+    from altius_b200.session import alloc_pinned
+    model, feeds = configs.vit_base_16(batch=2, depth=2)
+    x0 = next(iter(feeds.values()))
+    rng = np.random.default_rng(5)
+    xs = [x0] + [rng.standard_normal(x0.shape).astype(np.float32) for _ in range(4)]
+    sess = CudaSessionBuilder(model).build()
+    try:
+        want = [sess.run([x])[0].copy() for x in xs]
+        got = sess.run_batches([[x] for x in xs])
+        for g, w in zip(got, want):
+            assert_bit_exact(g[0], w)
+        pinned_in = []
+        for x in xs:
+            p = alloc_pinned(x.shape)
+            p[...] = x
+            pinned_in.append([p])
+        pinned_out = [[alloc_pinned(want[0].shape)] for _ in xs]
+        sess.run_batches(pinned_in, outputs=pinned_out)
+        for g, w in zip(pinned_out, want):
+            assert_bit_exact(np.array(g[0]), w)
+        assert_bit_exact(sess.run_batches([[xs[3]]])[0][0], want[3])
+        assert sess.run_batches([]) == []
+    finally:
+        sess.close()
