@@ -102,6 +102,13 @@ cudaError_t launch_strided_copy(const CopyParams& p, const void* in, void* out, 
 cudaError_t launch_transpose2d(const float* in, float* out, int64_t batch, int r, int c,
                                cudaStream_t st);
 
+// Resize of [planes, ih, iw] -> [planes, oh, ow] as the interpreter does it
+// (crates/session_interpreter/src/session.rs:1057-1132): one scale oh / ih for both
+// axes; mode 0 nearest (source index = trunc(dst / scale)), else bilinear around
+// max(dst / scale - 0.5, 0). Source indices are clamped to the input.
+cudaError_t launch_resize(const float* x, float* out, int64_t planes, int ih, int iw, int oh, int ow, int mode,
+                          cudaStream_t st);
+
 // ---- convolution ------------------------------------------------------------
 enum Act { ACT_NONE = 0, ACT_RELU, ACT_HARDSIGMOID, ACT_HARDSWISH, ACT_GELU };
 struct ConvParams {

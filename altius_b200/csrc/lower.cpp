@@ -923,6 +923,46 @@ void lower_node(Emit& em, Plan& plan, int nid) {
       });
       return;
     }
+    case AC_OP_EXPAND: {
+      // compute_expand, session.rs:299-323, tiles an i64 [1,1,1,k] row; here any tensor
+      // is broadcast to the requested shape (stride 0 along the expanded dims).
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      const Value& ov = V(o);
+      if (xv.rank > ov.rank) fail(AC_ERR_SHAPE, "Expand: input rank above the requested shape's");
+      CopyParams p{};
+      p.rank = ov.rank;
+      int64_t in_str[AC_MAX_RANK];
+      contiguous_strides(xv.dims, xv.rank, in_str);
+      for (int i = 0; i < ov.rank; ++i) {
+        const int xi = i - (ov.rank - xv.rank);
+        p.dims[i] = ov.dims[i];
+        if (xi < 0 || xv.dims[xi] == 1) p.in_str[i] = 0;
+        else if (xv.dims[xi] == ov.dims[i]) p.in_str[i] = in_str[xi];
+        else fail(AC_ERR_SHAPE, "Expand: shapes cannot be broadcast");
+      }
+      contiguous_strides(p.dims, p.rank, p.out_str);
+      p.n = ov.numel();
+      p.elem_bytes = (int)xv.elem_bytes();
+      lower_copy(em, "expand_copy", n.op, x, o, p);
+      return;
+    }
+    case AC_OP_RESIZE: {
+      const int x = n.inputs[0], o = n.outputs[0];
+      const Value& xv = V(x);
+      const Value& ov = V(o);
+      require_f32(xv, "Resize");
+      if (ov.dims[0] != xv.dims[0] || ov.dims[1] != xv.dims[1])
+        fail(AC_ERR_UNSUPPORTED, "Resize: batch and channel extents must not change");
+      const int64_t planes = xv.dims[0] * xv.dims[1];
+      const int ih = (int)xv.dims[2], iw = (int)xv.dims[3], oh = (int)ov.dims[2], ow = (int)ov.dims[3];
+      const int mode = (int)n.ints[0];
+      em.add(mode == 0 ? "resize_nearest" : "resize_bilinear", n.op, {x}, {o}, (double)xv.bytes() + ov.bytes(), 0,
+             [=](cudaStream_t st) {
+               return launch_resize(s->fptr(x), s->fptr_mut(o), planes, ih, iw, oh, ow, mode, st);
+             });
+      return;
+    }
     case AC_OP_CAST: {
       const int x = n.inputs[0], o = n.outputs[0];
       const int from = V(x).elem_ty, to = (int)n.ints[0];

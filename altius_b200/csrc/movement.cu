@@ -116,7 +116,45 @@ __global__ void __launch_bounds__(256) patchify_kernel(const float* __restrict__
   reinterpret_cast<float4*>(rows)[i] = __ldg(reinterpret_cast<const float4*>(src));
 }
 
+// compute_resize, crates/session_interpreter/src/session.rs:1057-1132. Every operation is
+// rounded separately, as the Rust expressions are.
+__global__ void __launch_bounds__(256) resize_kernel(const float* __restrict__ x, float* __restrict__ out,
+                                                     int64_t total, int ih, int iw, int oh, int ow, int mode) {
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  const int w = (int)(i % ow);
+  const int h = (int)((i / ow) % oh);
+  const int64_t plane = i / ((int64_t)ow * oh);
+  const float* in = x + plane * (int64_t)ih * iw;
+  const float scale = __fdiv_rn((float)oh, (float)ih);
+  if (mode == 0) {
+    const int sy = min((int)__fdiv_rn((float)h, scale), ih - 1);
+    const int sx = min((int)__fdiv_rn((float)w, scale), iw - 1);
+    out[i] = __ldg(in + (int64_t)sy * iw + sx);
+    return;
+  }
+  const float yf = fmaxf(__fsub_rn(__fdiv_rn((float)h, scale), 0.5f), 0.f);
+  const float xf = fmaxf(__fsub_rn(__fdiv_rn((float)w, scale), 0.5f), 0.f);
+  const int y = (int)yf, xx = (int)xf;
+  const int y0 = min(y, ih - 1), y1 = min(y + 1, ih - 1);
+  const int x0 = min(xx, iw - 1), x1 = min(xx + 1, iw - 1);
+  const float v00 = __ldg(in + (int64_t)y0 * iw + x0), v01 = __ldg(in + (int64_t)y0 * iw + x1);
+  const float v10 = __ldg(in + (int64_t)y1 * iw + x0), v11 = __ldg(in + (int64_t)y1 * iw + x1);
+  const float fy = __fsub_rn(yf, (float)y), fx = __fsub_rn(xf, (float)xx);
+  const float hd = __fadd_rn(v00, __fmul_rn(__fsub_rn(v10, v00), fy));
+  const float hw = __fadd_rn(v01, __fmul_rn(__fsub_rn(v11, v01), fy));
+  out[i] = __fadd_rn(hd, __fmul_rn(__fsub_rn(hw, hd), fx));
+}
+
 }  // namespace
+
+cudaError_t launch_resize(const float* x, float* out, int64_t planes, int ih, int iw, int oh, int ow, int mode,
+                          cudaStream_t st) {
+  const int64_t total = planes * oh * ow;
+  if (total == 0) return cudaSuccess;
+  resize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(x, out, total, ih, iw, oh, ow, mode);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_patchify(const ConvParams& p, const float* x, float* rows, cudaStream_t st) {
   const int64_t total4 = (int64_t)p.n * p.oh * p.ow * p.c * p.kh * (p.kw / 4);

@@ -173,6 +173,43 @@ void infer_shapes(AcSession& s) {
       case AC_OP_WHERE:
         set_shape(out(0), in(1).elem_ty, broadcast(in(1), in(2), "Where"));
         break;
+      case AC_OP_EXPAND: {
+        // shape.rs:148-160: the output shape is the `shape` input, taken as it is.
+        const Value& sh = in(1);
+        if (!sh.host || sh.elem_ty != AC_I64) fail(AC_ERR_UNSUPPORTED, "Expand: shape must be a constant i64 tensor");
+        const int64_t* d = static_cast<const int64_t*>(sh.host);
+        const int64_t r = sh.numel();
+        if (r > AC_MAX_RANK) fail(AC_ERR_SHAPE, "rank above 8 is not supported");
+        set_shape(out(0), in(0).elem_ty, std::vector<int64_t>(d, d + r));
+        break;
+      }
+      case AC_OP_RESIZE: {
+        // shape.rs:209-254: sizes (4 inputs) or floor(dims * scales) (3 inputs; asymmetric,
+        // nearest, floor only).
+        need_ints(3);
+        const Value& x = in(0);
+        if (x.rank != 4) fail(AC_ERR_SHAPE, "Resize: 4-D input expected");
+        if (n.inputs.size() == 4) {
+          const Value& sz = in(3);
+          if (!sz.host || sz.elem_ty != AC_I64 || sz.rank != 1 || sz.dims[0] != 4)
+            fail(AC_ERR_UNSUPPORTED, "Resize: sizes must be a constant i64[4]");
+          const int64_t* d = static_cast<const int64_t*>(sz.host);
+          set_shape(out(0), x.elem_ty, {d[0], d[1], d[2], d[3]});
+        } else if (n.inputs.size() == 3) {
+          if (n.ints[0] != 0 || n.ints[1] != 0 || n.ints[2] != 0)
+            fail(AC_ERR_UNSUPPORTED, "Resize: Unsupported pattern");
+          const Value& sc = in(2);
+          if (!sc.host || sc.elem_ty != AC_F32 || sc.numel() != 4)
+            fail(AC_ERR_UNSUPPORTED, "Resize: scales must be a constant f32[4]");
+          const float* f = static_cast<const float*>(sc.host);
+          std::vector<int64_t> d(4);
+          for (int k = 0; k < 4; ++k) d[k] = (int64_t)std::floor((float)x.dims[k] * f[k]);
+          set_shape(out(0), x.elem_ty, d);
+        } else {
+          fail(AC_ERR_UNSUPPORTED, "Resize: Unsupported pattern");
+        }
+        break;
+      }
       case AC_OP_CONV2D: {
         need_ints(10);
         const Value& x = in(0);

@@ -164,6 +164,10 @@ def _attr_arrays(node: ir.Node):
         floats = [a.get("alpha", 0.2), a.get("beta", 0.5)]
     elif op == "LeakyReLU":
         floats = [a.get("alpha", 0.01)]
+    elif op == "Resize":
+        ints = [0 if a.get("mode", "nearest") == "nearest" else 1,
+                0 if a.get("coordinate_transformation_mode", "half_pixel") == "asymmetric" else 1,
+                0 if a.get("nearest_mode", "round_prefer_floor") == "floor" else 1]
     elif op in ("Softmax",):
         ints = [a.get("axis", -1)]
     elif op == "Flatten":

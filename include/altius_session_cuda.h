@@ -81,6 +81,9 @@ typedef struct AcValueDesc {
  *            floats = activation alpha, activation beta
  *   MAXPOOL  ints  = kh, kw, sh, sw, auto_pad, npads, pads[npads]
  *   HARDSIGMOID floats = alpha, beta      LEAKYRELU floats = alpha
+ *   RESIZE   ints = mode (0 nearest, 1 anything else: bilinear, as the interpreter),
+ *                   coordinate_transformation_mode (0 asymmetric, 1 other),
+ *                   nearest_mode (0 floor, 1 other)
  *   SOFTMAX  ints = axis                  FLATTEN ints = axis
  *   CAST     ints = to (AcElemType)       CONCAT  ints = axis
  *   TRANSPOSE ints = perm[rank]           GATHER  ints = axis

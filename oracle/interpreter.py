@@ -61,6 +61,7 @@ def lib():
             "or_reduce_max_all": [P, P, L64],
             "or_gavg_pool": [P, P, L64, L64],
             "or_max_pool": [P, P] + [L64] * 11,
+            "or_resize": [P, P] + [L64] * 5 + [ctypes.c_int],
             "or_batch_norm": [P, P, P, P, P, P, L64, L64, L64, F],
             "or_sgemm": [I, I, L64, L64, L64, F, P, L64, P, L64, F, P, L64, I],
             "or_sgemm_batched": [L64, L64, L64, L64, P, P, P, I],
@@ -362,6 +363,29 @@ class InterpreterSession:
             L.or_max_pool(_fp(x), _fp(out), x.shape[0] * x.shape[1], x.shape[2], x.shape[3], oh, ow,
                           k[0], k[1], s[0], s[1], pad[0], pad[1])
             return [out]
+        if op == "Resize":
+            # shape.rs:209-254 (sizes, or floor(dims * scales) for asymmetric / nearest / floor),
+            # session.rs:1057-1132
+            x = _f32(ins[0])
+            if len(ins) == 4:
+                oshape = tuple(int(v) for v in np.asarray(ins[3]).reshape(-1))
+            elif len(ins) == 3:
+                assert at.get("coordinate_transformation_mode", "half_pixel") == "asymmetric"
+                assert at.get("mode", "nearest") == "nearest" and at.get("nearest_mode") == "floor"
+                sc = np.asarray(ins[2], np.float32).reshape(-1)
+                oshape = tuple(int(np.floor(np.float32(d) * s)) for d, s in zip(x.shape, sc))
+            else:
+                raise NotImplementedError("Resize: Unsupported pattern")
+            assert len(oshape) == 4 and oshape[:2] == x.shape[:2]
+            out = np.empty(oshape, np.float32)
+            L.or_resize(_fp(x), _fp(out), x.shape[0] * x.shape[1], x.shape[2], x.shape[3], oshape[2], oshape[3],
+                        0 if at.get("mode", "nearest") == "nearest" else 1)
+            return [out]
+        if op == "Expand":
+            # shape.rs:148-160 takes the shape input as the output shape; session.rs:299-323
+            # tiles an i64 row. Restated as a broadcast of any tensor to that shape.
+            shape = tuple(int(v) for v in np.asarray(ins[1]).reshape(-1))
+            return [np.ascontiguousarray(np.broadcast_to(ins[0], shape))]
         if op == "BatchNormalization":
             x = _f32(ins[0])
             out = np.empty_like(x)

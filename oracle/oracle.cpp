@@ -497,6 +497,40 @@ OR_API void or_gavg_pool(const float* x, float* out, int64_t nc, int64_t hw) {
   }
 }
 
+// compute_resize, crates/session_interpreter/src/session.rs:1057-1132: one scale
+// (output_h / input_h) for both axes; "nearest" truncates dst / scale, anything else is the
+// bilinear blend around max(dst / scale - 0.5, 0). The reference indexes without clamping in
+// the nearest branch (it panics when the aspect ratio changes); indices are clamped here.
+OR_API void or_resize(const float* x, float* out, int64_t outer, int64_t ih, int64_t iw, int64_t oh, int64_t ow,
+                      int mode) {
+  const float scale = (float)oh / (float)ih;
+#pragma omp parallel for
+  for (int64_t p = 0; p < outer; ++p) {
+    const float* in = x + p * ih * iw;
+    float* o = out + p * oh * ow;
+    for (int64_t h = 0; h < oh; ++h) {
+      for (int64_t w = 0; w < ow; ++w) {
+        if (mode == 0) {
+          const int64_t sy = std::min<int64_t>((int64_t)((float)h / scale), ih - 1);
+          const int64_t sx = std::min<int64_t>((int64_t)((float)w / scale), iw - 1);
+          o[h * ow + w] = in[sy * iw + sx];
+        } else {
+          const float yf = std::max((float)h / scale - 0.5f, 0.f);
+          const float xf = std::max((float)w / scale - 0.5f, 0.f);
+          const int64_t y = (int64_t)yf, xx = (int64_t)xf;
+          const int64_t y0 = std::min(y, ih - 1), y1 = std::min(y + 1, ih - 1);
+          const int64_t x0 = std::min(xx, iw - 1), x1 = std::min(xx + 1, iw - 1);
+          const float v00 = in[y0 * iw + x0], v01 = in[y0 * iw + x1];
+          const float v10 = in[y1 * iw + x0], v11 = in[y1 * iw + x1];
+          const float hd = v00 + (v10 - v00) * (yf - (float)y);
+          const float hw = v01 + (v11 - v01) * (yf - (float)y);
+          o[h * ow + w] = hd + (hw - hd) * (xf - (float)xx);
+        }
+      }
+    }
+  }
+}
+
 // crates/session_interpreter/src/session.rs:325-382 `compute_max_pool`
 OR_API void or_max_pool(const float* x, float* out, int64_t outer, int64_t ih, int64_t iw,
                         int64_t oh, int64_t ow, int64_t kh, int64_t kw, int64_t sh, int64_t sw,

@@ -427,3 +427,39 @@ def test_fused_attention_core(cuda_lib, B, T, H, scale_op):
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
     unfused = run_cuda(m, [qkv], fuse=False, gemm_mode=1)[0]
     np.testing.assert_allclose(unfused, want, rtol=1e-5, atol=1e-6)
+
+
+# ---- Resize / Expand (the interpreter's restricted patterns, session.rs:299-323, 1057-1132) ----
+@pytest.mark.parametrize("mode", ["nearest", "linear"])
+@pytest.mark.parametrize("ishape,oshape", [((2, 3, 7, 7), (2, 3, 14, 14)), ((1, 5, 16, 16), (1, 5, 8, 8)),
+                                            ((2, 2, 9, 9), (2, 2, 21, 21)), ((1, 1, 4, 6), (1, 1, 8, 12))])
+def test_resize_with_sizes(cuda_lib, mode, ishape, oshape):
+    x = RNG.standard_normal(ishape).astype(np.float32)
+    roi = np.zeros(0, np.float32)
+    scales = np.zeros(0, np.float32)
+    m = single_op_model("Resize", [x], [roi, scales, np.array(oshape, np.int64)], mode=mode,
+                        coordinate_transformation_mode="half_pixel", nearest_mode="round_prefer_floor")
+    got, want = both(m, [x])
+    assert want[0].shape == oshape
+    assert_bit_exact(got[0], want[0])
+
+
+def test_resize_with_scales_nearest_floor(cuda_lib):
+    x = RNG.standard_normal((2, 4, 10, 10)).astype(np.float32)
+    m = single_op_model("Resize", [x], [np.zeros(0, np.float32), np.array([1, 1, 2, 2], np.float32)], mode="nearest",
+                        coordinate_transformation_mode="asymmetric", nearest_mode="floor")
+    got, want = both(m, [x])
+    assert want[0].shape == (2, 4, 20, 20)
+    assert_bit_exact(got[0], want[0])
+    assert_bit_exact(got[0], x.repeat(2, axis=2).repeat(2, axis=3))
+
+
+@pytest.mark.parametrize("ishape,oshape,dtype", [((1, 1, 1, 9), (1, 1, 5, 9), np.int64), ((1, 1, 1, 4), (2, 3, 5, 4), np.int64),
+                                                  ((3, 1, 8), (2, 3, 6, 8), np.float32), ((1,), (4, 7), np.float32)])
+def test_expand(cuda_lib, ishape, oshape, dtype):
+    x = (RNG.standard_normal(ishape) * 100).astype(dtype)
+    m = single_op_model("Expand", [x], [np.array(oshape, np.int64)])
+    got, want = both(m, [x])
+    assert want[0].shape == oshape and want[0].dtype == dtype
+    assert_bit_exact(got[0], want[0])
+    assert_bit_exact(got[0], np.broadcast_to(x, oshape))

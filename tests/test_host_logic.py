@@ -130,6 +130,29 @@ def test_errors_are_reported_at_create():
         session.InferenceSession(configs.mnist_cnn()[0], backend="interpreter")
 
 
+def test_resize_and_expand_shapes():
+    """shape.rs:148-160 (Expand) and :209-254 (Resize: sizes, or floor(dims * scales) for the
+    asymmetric / nearest / floor pattern only)."""
+    x = np.zeros((2, 3, 10, 10), np.float32)
+    none = np.zeros(0, np.float32)
+    s = plan(single_op_model("Resize", [x], [none, none, np.array([2, 3, 25, 15], np.int64)], mode="linear"))
+    assert s.output_info[0][0] == (2, 3, 25, 15)
+    assert [e["kind"] for e in s.schedule()] == ["resize_bilinear"]
+    s = plan(single_op_model("Resize", [x], [none, np.array([1, 1, 2.5, 2.5], np.float32)], mode="nearest",
+                             coordinate_transformation_mode="asymmetric", nearest_mode="floor"))
+    assert s.output_info[0][0] == (2, 3, 25, 25)
+    with pytest.raises(SessionError) as e:               # 3-input form outside the one supported pattern
+        plan(single_op_model("Resize", [x], [none, np.array([1, 1, 2, 2], np.float32)], mode="linear",
+                             coordinate_transformation_mode="asymmetric", nearest_mode="floor"))
+    assert e.value.status == 3 and "Unsupported pattern" in str(e.value)
+    i = np.zeros((1, 1, 1, 7), np.int64)
+    s = plan(single_op_model("Expand", [i], [np.array([1, 1, 4, 7], np.int64)]))
+    assert s.output_info[0][0] == (1, 1, 4, 7) and [e["kind"] for e in s.schedule()] == ["expand_copy"]
+    with pytest.raises(SessionError) as e:
+        plan(single_op_model("Expand", [np.zeros((3,), np.float32)], [np.array([2, 4], np.int64)]))
+    assert e.value.status == 2
+
+
 def test_create_without_a_gpu_fails_loudly():
     lib = session.load_library()
     if lib.altius_cuda_device_count() > 0:

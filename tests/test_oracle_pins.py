@@ -223,3 +223,30 @@ def test_models_own_vs_openblas_sgemm_agree():
         b = run_oracle(model, feeds.values(), threads=8, sgemm="openblas")[0]
         assert np.abs(a - b).max() < 1e-4
         assert (a.argmax(-1) == b.argmax(-1)).all()
+
+
+def test_resize_known_answers():
+    """compute_resize (session.rs:1057-1132): nearest with an integer scale replicates pixels;
+    the bilinear branch reproduces a constant image and blends rows / columns half a pixel
+    off (its source coordinate is max(dst / scale - 0.5, 0))."""
+    from helpers import run_oracle, single_op_model
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((1, 2, 5, 5)).astype(np.float32)
+    none = np.zeros(0, np.float32)
+    m = single_op_model("Resize", [x], [none, none, np.array([1, 2, 15, 15], np.int64)], mode="nearest")
+    np.testing.assert_array_equal(run_oracle(m, [x])[0], x.repeat(3, axis=2).repeat(3, axis=3))
+    c = np.full((1, 1, 4, 4), 2.5, np.float32)
+    m = single_op_model("Resize", [c], [none, none, np.array([1, 1, 9, 9], np.int64)], mode="linear")
+    np.testing.assert_array_equal(run_oracle(m, [c])[0], np.full((1, 1, 9, 9), 2.5, np.float32))
+    r = np.arange(16, dtype=np.float32).reshape(1, 1, 4, 4)
+    m = single_op_model("Resize", [r], [none, none, np.array([1, 1, 4, 4], np.int64)], mode="linear")
+    out = run_oracle(m, [r])[0][0, 0]
+    assert out[0, 0] == 0.0 and out[1, 0] == 2.0 and out[0, 1] == 0.5 and out[3, 3] == 12.5   # half a pixel off
+
+
+def test_expand_is_a_broadcast_to_the_shape_input():
+    from helpers import run_oracle, single_op_model
+    x = np.arange(6, dtype=np.int64).reshape(1, 1, 1, 6)
+    m = single_op_model("Expand", [x], [np.array([1, 1, 4, 6], np.int64)])
+    out = run_oracle(m, [x])[0]
+    assert out.dtype == np.int64 and out.shape == (1, 1, 4, 6) and (out == x).all()
