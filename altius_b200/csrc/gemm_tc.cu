@@ -330,8 +330,9 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
 
 // Shared-memory stage of the main loop. MT = 128-row sub-tiles per CTA tile.
 // TF32 modes: A arrives by TMA where its hi copy lives (split in place), lo beside it.
-// fp16 mode: A arrives as fp32 rows of 32 floats (no swizzle) in a raw area and the
-// splitters write the fp16 hi / lo tiles; B arrives as fp16 hi / lo by TMA.
+// fp16 mode: A arrives as fp32 rows of 32 floats (no swizzle); the splitters read it into
+// registers and write the fp16 hi / lo tiles over it (same size); B arrives as fp16 hi / lo
+// by TMA.
 template <int BN, int MT, int MODE>
 struct TcSmem {
   static constexpr bool kF16 = MODE == TC_F16X3;
@@ -339,14 +340,15 @@ struct TcSmem {
   static constexpr int kARaw = kF16 ? MT * BM * kKb * 4 : 0;
   static constexpr int kABytes = kF16 ? MT * BM * kKb * 2 : MT * BM * kKb * 4;   // one of A hi / lo
   static constexpr int kBBytes = kF16 ? BN * kKb * 2 : BN * kKb * 4;             // one of B hi / lo
-  static constexpr int kOffAHi = kARaw;
+  static constexpr int kOffAHi = 0;
   static constexpr bool k1X = MODE == TC_1X;                      // one copy of each operand, no lo tiles
-  static constexpr int kOffALo = kARaw + kABytes;
-  static constexpr int kOffBHi = kARaw + (k1X ? 1 : 2) * kABytes;
+  static constexpr int kOffALo = kABytes;
+  static constexpr int kOffBHi = (k1X ? 1 : 2) * kABytes;         // fp16: kARaw == 2 * kABytes
   static constexpr int kOffBLo = kOffBHi + kBBytes;
-  static constexpr int kStageBytes = k1X ? kABytes + kBBytes : kARaw + 2 * kABytes + 2 * kBBytes;
+  static constexpr int kStageBytes = k1X ? kABytes + kBBytes : 2 * kABytes + 2 * kBBytes;
+  static_assert(!kF16 || kARaw == 2 * kABytes, "the fp16 tiles replace the fp32 rows in place");
   static constexpr int kTxBytes = (kF16 ? kARaw : kABytes) + kBBytes + ((kF16 || MODE == TC_3X_BLO_TMA) ? kBBytes : 0);
-  static constexpr int kStages = (200 * 1024) / kStageBytes;      // TF32: 4 / 6 / 8; fp16: 3 / 4 / 5 (BN 256 / 128 / 64)
+  static constexpr int kStages = (200 * 1024) / kStageBytes;      // TF32 and fp16: 4 / 6 / 8 (BN 256 / 128 / 64)
   static constexpr int kEpiBytes = 4 * 4096;                      // one 4 KB transpose tile per epilogue warp
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   static constexpr int kAccCols = (kF16 ? 2 : 1) * MT * BN;       // tensor-memory columns of one accumulator set
@@ -543,16 +545,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
           if (MODE == TC_F16X3) {
             // fp32 rows of 32 floats -> fp16 hi / lo tiles; one float4 (4 consecutive k) per item.
+            // The tiles take the place of the rows: everything is read first, the group's
+            // 128 threads meet at a named barrier, then everything is written.
             const float4* raw = reinterpret_cast<const float4*>(a_raw(s));
             uint8_t* hi_t = a_hi(s);
             uint8_t* lo_t = a_lo(s);
+            constexpr int kItems = L::kARaw / 16 / kSplitThreads;
+            float4 x[kItems > 0 ? kItems : 1];
 #pragma unroll
-            for (int i = 0; i < L::kARaw / 16 / kSplitThreads; ++i) {
+            for (int i = 0; i < kItems; ++i) x[i] = raw[i * kSplitThreads + t0];
+            asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kSplitThreads) : "memory");
+#pragma unroll
+            for (int i = 0; i < kItems; ++i) {
               const int item = i * kSplitThreads + t0;
-              const float4 x = raw[item];
-              range_bad |= beyond_half(x.x) | beyond_half(x.y) | beyond_half(x.z) | beyond_half(x.w);
+              range_bad |= beyond_half(x[i].x) | beyond_half(x[i].y) | beyond_half(x[i].z) | beyond_half(x[i].w);
               uint2 hi, lo;
-              f16_split(x, hi, lo);
+              f16_split(x[i], hi, lo);
               const uint32_t off = sw64_off8(item >> 3, item & 7);
               *reinterpret_cast<uint2*>(hi_t + off) = hi;
               *reinterpret_cast<uint2*>(lo_t + off) = lo;
