@@ -295,12 +295,22 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
   const int row = tm * bm + rl, col0 = tn * bn + cl;
   if (row >= ep.m || col0 >= ep.n) return;
   const float* src = ws + (size_t)tt * parts * bm * bn + (size_t)rl * bn + cl;
+  // Slices are added in slice order; their loads are issued eight at a time so that the
+  // chain of additions does not also serialise the L2 round trips.
   float4 acc = __ldg(reinterpret_cast<const float4*>(src));
-  for (int p = 1; p < parts; ++p) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(src + (size_t)p * bm * bn));
+  auto add = [&](const float4& v) {
     acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
     acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+  };
+  int p = 1;
+  for (; p + 8 <= parts; p += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(src + (size_t)(p + j) * bm * bn));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add(v[j]);
   }
+  for (; p < parts; ++p) add(__ldg(reinterpret_cast<const float4*>(src + (size_t)p * bm * bn)));
   float* c = ep.c + (long long)bz * ep.sc;
   const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
   const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
@@ -759,7 +769,7 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn, int mt,
   const int tail = (int)(tiles % sms);
   static const bool no_tail = std::getenv("ALTIUS_CUDA_TC_NO_TAIL_SPLIT") != nullptr;   // debug toggle
   if (tail > 0 && !no_tail) {
-    const int parts = std::min(sms / tail, num_kb / 2);   // at least two K-blocks per slice
+    const int parts = std::min(std::min(sms / tail, num_kb / 2), 32);   // at least two K-blocks per slice
     if (parts >= 2) {
       pl.sc.dp_tiles = (int)(tiles - tail);
       pl.sc.tail_parts = parts;
