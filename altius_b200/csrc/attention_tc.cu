@@ -29,14 +29,15 @@
 //                prefetch V into registers, and after S transpose-store V; then softmax,
 //                two threads per query row (= tensor-memory lane), one per half of the
 //                key columns: pass 1 row maximum of the scaled scores, pass 2
-//                e = exp(s - max) with the reference's polynomial, running sum, e split
+//                e = 2^((s - max) log2 e) by ex2.approx (2 ulp), running sum, e split
 //                into hi/lo and stored as the A operand of the second product; maxima and
 //                sums of the two halves meet in shared memory; finally O * (1 / sum) goes
 //                to global through a shared-memory transpose (full 128-byte lines);
 //   warp 8       allocates tensor memory; one thread issues the MMAs and commits to
 //                mbarriers (the P chunks of the two halves alternate).
 // P is fed unnormalised and O scaled by 1 / sum at the end (the reference
-// normalises P first); the difference is a few ulp.
+// normalises P first), and the exponential is the hardware's instead of the reference's
+// degree-6 polynomial: differences of a few ulp, far below those of the split products.
 // Every mbarrier wait is bounded; on expiry the kernel records a code in the
 // error word and runs to its end without touching the barrier again.
 #include <cstdio>
@@ -102,17 +103,15 @@ __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Barrier of the two softmax warps that share tensor-memory lane quarter q (named barriers 1-4).
 __device__ __forceinline__ void pair_sync(int q) {
   asm volatile("bar.sync %0, 64;" ::"r"(q + 1) : "memory");
-}
-
-// MODE 0: none, 1: multiply, 2: divide (the graph's Mul / Div node, one rounded operation).
-template <int MODE>
-__device__ __forceinline__ float apply_scale(float s, float sc) {
-  if (MODE == 1) return __fmul_rn(s, sc);
-  if (MODE == 2) return __fdiv_rn(s, sc);
-  return s;
 }
 
 __device__ __forceinline__ void store_split(uint8_t* hi_base, uint8_t* lo_base, uint32_t off, float4 v) {
@@ -342,7 +341,12 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       const int row = q * 32 + lane;
       const int b_begin = hf ? NBLK0 : 0, b_count = hf ? NBLK - NBLK0 : NBLK0;
       const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
+      // Scores enter the exponential as t = acc * c1 with c1 = log2(e) (* | /) scale, so that
+      // e = 2^(t - max t) is one FFMA and one ex2.approx per score (2 ulp; the CUDA-core kernel
+      // keeps the reference's polynomial).
+      const float kLog2e = 1.44269504088896341f;
       const float sc = SMODE ? __ldg(p.scale) : 1.f;
+      const float c1 = SMODE == 1 ? __fmul_rn(sc, kLog2e) : (SMODE == 2 ? __fdiv_rn(kLog2e, sc) : kLog2e);
       float m = CUDART_NAN_F;
 #pragma unroll 1
       for (int i = 0; i < 2 * b_count; ++i) {
@@ -353,8 +357,8 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
         // by a select, not a branch, so that the 16 chains stay interleaved.
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          const float sv_ = apply_scale<SMODE>(__uint_as_float(v[u]), sc);
-          m = fmaxf(c * 16 + u < T ? sv_ : CUDART_NAN_F, m);
+          const float t = __fmul_rn(__uint_as_float(v[u]), c1);
+          m = fmaxf(c * 16 + u < T ? t : CUDART_NAN_F, m);
         }
       }
       xch[hf * QM + row] = m;
@@ -362,7 +366,8 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       m = fmaxf(xch[QM + row], xch[row]);
       pair_sync(q);                              // both have read before the sums overwrite
       AT_STAMP(5);
-      float sum = 0.f;
+      const float m13 = __fsub_rn(m, 13.f);      // P = e * 2^13 comes out of the exponential directly
+      float sum = 0.f;                           // of e * 2^13; the factor cancels in O / sum
 #pragma unroll 1
       for (int i = 0; i < b_count; ++i) {
         const int blk = b_begin + i;
@@ -379,17 +384,17 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
           float e[16];
 #pragma unroll
           for (int u = 0; u < 16; ++u) {
-            const float ev = exp_poly_softmax(__fsub_rn(apply_scale<SMODE>(__uint_as_float(v[u]), sc), m));
+            const float ev = ex2_approx(fmaf(__uint_as_float(v[u]), c1, -m13));
             e[u] = c0 + u < T ? ev : 0.f;
           }
 #pragma unroll
           for (int u = 0; u < 16; ++u) sum = __fadd_rn(sum, e[u]);   // + 0 for masked columns: exact
-          // P as fp16 hi / lo of e * 2^13 (e <= 1: in range, and far from the subnormals)
+          // P as fp16 hi / lo (at most 2^13: in range, and far from the subnormals)
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             uint2 h0, l0, h1, l1;
-            f16_split(make_float4(e[8 * j] * 8192.f, e[8 * j + 1] * 8192.f, e[8 * j + 2] * 8192.f, e[8 * j + 3] * 8192.f), h0, l0);
-            f16_split(make_float4(e[8 * j + 4] * 8192.f, e[8 * j + 5] * 8192.f, e[8 * j + 6] * 8192.f, e[8 * j + 7] * 8192.f), h1, l1);
+            f16_split(make_float4(e[8 * j], e[8 * j + 1], e[8 * j + 2], e[8 * j + 3]), h0, l0);
+            f16_split(make_float4(e[8 * j + 4], e[8 * j + 5], e[8 * j + 6], e[8 * j + 7]), h1, l1);
             const uint32_t off = sw64_off(row, 2 * h16 + j);
             *reinterpret_cast<uint4*>(sl + off) = make_uint4(h0.x, h0.y, h1.x, h1.y);
             *reinterpret_cast<uint4*>(sl + QM * 64 + off) = make_uint4(l0.x, l0.y, l1.x, l1.y);
@@ -408,7 +413,7 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       xch[hf * QM + row] = sum;
       pair_sync(q);
       sum = __fadd_rn(xch[row], xch[QM + row]);
-      // ---- O = (D1 + D2 * 2^-11) * (1 / sum) * 2^-13 / sv: this warp takes 32 of the 64
+      // ---- O = (D1 + D2 * 2^-11) * (1 / sum) / sv: this warp takes 32 of the 64
       // columns; through a 4 KB tile of the (now idle) P ring so that every 8 lanes write one
       // full 128-byte line ----
       AT_STAMP(6);
@@ -422,7 +427,7 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       float4* stage = reinterpret_cast<float4*>(qp + warp * 4096);
       auto fin = [&](int j) {
         const float y = fmaf(__uint_as_float(o2[j]), kLoUnscale, __uint_as_float(o[j]));
-        return __fmul_rn(__fmul_rn(__fmul_rn(y, recip), 1.f / 8192.f), inv_sv);
+        return __fmul_rn(__fmul_rn(y, recip), inv_sv);
       };
 #pragma unroll
       for (int j = 0; j < 8; ++j)
