@@ -91,6 +91,19 @@ __device__ __forceinline__ uint64_t desc_sw64(uint32_t saddr) {
   return d;
 }
 
+// The load alone: several may be in flight before one tc_ld_wait().
+__device__ __forceinline__ void tc_ld_32x16_issue(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -349,17 +362,22 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
       const float c1 = SMODE == 1 ? __fmul_rn(sc, kLog2e) : (SMODE == 2 ? __fdiv_rn(kLog2e, sc) : kLog2e);
       float m = CUDART_NAN_F;
 #pragma unroll 1
-      for (int i = 0; i < 2 * b_count; ++i) {
-        const int c = 2 * b_begin + i;           // 16-column chunk; chunks past NS read junk that is masked
-        uint32_t v[16];
-        tc_ld_32x16(trow + (uint32_t)(c * 16), v);
+      for (int i = 0; i < b_count; ++i) {
+        const int c0 = (b_begin + i) * 32;       // 32 columns per step; columns past NS read junk that is masked
+        uint32_t v[2][16];
+        tc_ld_32x16_issue(trow + (uint32_t)c0, v[0]);
+        tc_ld_32x16_issue(trow + (uint32_t)(c0 + 16), v[1]);
+        tc_ld_wait();
         // Columns past T (exact zeros up to NS, junk beyond) are kept out of the maximum
-        // by a select, not a branch, so that the 16 chains stay interleaved.
+        // by a select, not a branch, so that the chains stay interleaved.
+        float m0 = CUDART_NAN_F, m1 = CUDART_NAN_F;
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          const float t = __fmul_rn(__uint_as_float(v[u]), c1);
-          m = fmaxf(c * 16 + u < T ? t : CUDART_NAN_F, m);
+          const float t0 = __fmul_rn(__uint_as_float(v[0][u]), c1), t1 = __fmul_rn(__uint_as_float(v[1][u]), c1);
+          m0 = fmaxf(c0 + u < T ? t0 : CUDART_NAN_F, m0);
+          m1 = fmaxf(c0 + 16 + u < T ? t1 : CUDART_NAN_F, m1);
         }
+        m = fmaxf(fmaxf(m0, m1), m);
       }
       xch[hf * QM + row] = m;
       pair_sync(q);
