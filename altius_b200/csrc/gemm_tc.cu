@@ -1,29 +1,39 @@
-// Tensor-core GEMM for sm_100a: tcgen05.mma (kind::tf32) with the accumulator
-// in tensor memory, operands staged in shared memory by TMA, 3xTF32 split for
-// fp32 fidelity.
+// Tensor-core GEMM for sm_100a: tcgen05.mma with the accumulators in tensor memory,
+// operands staged in shared memory by TMA, split operands for fp32 fidelity.
 //
 //   C[b] = epilogue( A[b] (M x K, K contiguous) * B[b]^T (B stored N x K, K contiguous) )
 //
 // It replaces the cblas_sgemm the reference calls for MatMul / Gemm / Conv2d
 // (crates/session_interpreter/src/gemm.rs:36-51, session.rs:621-794,
-// conv2d.rs:145-209). Every fp32 operand x is split into x_hi = x rounded to
-// TF32 (round to nearest) and x_lo = (x - x_hi) rounded to TF32; x - x_hi is
-// exact in fp32. Each product is evaluated as a_lo*b_hi + a_hi*b_lo + a_hi*b_hi
-// with fp32 accumulation in TMEM; the dropped a_lo*b_lo term and the rounding
-// of x_lo are each below 2^-22 relative.
+// conv2d.rs:145-209). Two ways of getting fp32-level products out of narrow MMAs:
+//   3xTF32   x_hi = x rounded to TF32, x_lo = (x - x_hi) rounded to TF32 (x - x_hi is exact
+//            in fp32); a_lo*b_hi + a_hi*b_lo + a_hi*b_hi as three kind::tf32 MMAs into one
+//            accumulator. The dropped a_lo*b_lo term and the rounding of x_lo are each below
+//            2^-22 relative.
+//   fp16 split (constant B)  x_hi = x rounded to fp16, x_lo = ((x - x_hi) * 2^11) rounded to
+//            fp16 (the scaling keeps x_lo out of the fp16 subnormals); a_hi*b_hi into one
+//            accumulator, a_lo*b_hi + a_hi*b_lo into a second one that the epilogue adds
+//            scaled by 2^-11. Same 22 bits per operand, half the operand bytes and twice the
+//            MMA rate. |x| must not exceed 65504: B is checked when it is split at load time,
+//            A by the splitters, which leave kRangeCode in the error word (the host then
+//            repeats the run on the 3xTF32 path).
 //
 // Persistent CTAs (one per SM) walk the 128 x BN output tiles:
-//   warp 12     TMA producer: one elected thread issues cp.async.bulk.tensor
-//               loads (64B-swizzled boxes of 16 floats along K) into a ring of
-//               stages, completion on an mbarrier per stage;
-//   warps 0-7   splitters (two groups on alternate stages): rewrite the A tile as x_hi in place and write x_lo
-//               beside it (the same for the B tile unless B is a constant whose
-//               split was prepared at load time and arrives by TMA);
-//   warp 13     one thread issues the tcgen05.mma stream and tcgen05.commit into
-//               one of two accumulators in tensor memory;
-//   warps 8-11  epilogue of the other accumulator: tcgen05.ld, a shared-memory
-//               transpose to row-contiguous float4s, bias / activation /
-//               residual, full-line global stores.
+//   warp 12     TMA producer: one elected thread issues cp.async.bulk.tensor loads (boxes of
+//               64-byte rows, 64-byte swizzle; the fp32 rows of A in the fp16 mode: 128-byte
+//               rows, no swizzle) into a ring of stages, completion on an mbarrier per stage;
+//   warps 0-7   splitters (two groups on alternate stages). TF32: rewrite the A tile as x_hi
+//               in place and write x_lo beside it (the same for the B tile unless B is a
+//               constant whose split was prepared at load time and arrives by TMA). fp16: read
+//               the fp32 rows of A into registers, meet at a named barrier, write the fp16
+//               hi / lo tiles over them;
+//   warp 13     one thread issues the tcgen05.mma stream and tcgen05.commit into an
+//               accumulator set in tensor memory (two sets when they fit 512 columns);
+//   warps 8-11  epilogue of the other set: tcgen05.ld, a shared-memory transpose to
+//               row-contiguous float4s, bias / activation / residual, full-line global stores.
+// Tiles beyond the last whole round of the grid are cut along K into slices (one per
+// otherwise idle SM) whose unreduced accumulators go to a workspace; a small second kernel
+// adds them in slice order and applies the epilogue.
 // Every mbarrier wait is bounded: on expiry the kernel records a code in the
 // error word, drains, frees its tensor memory and returns.
 #include <cuda.h>
