@@ -379,7 +379,8 @@ def test_gemm_transb_constant_weight(cuda_lib):
 
 
 @pytest.mark.parametrize("scale_op", ["Mul", "Div"])
-@pytest.mark.parametrize("B,T,H", [(2, 197, 12), (3, 198, 6), (1, 33, 2), (2, 256, 1), (1, 7, 3), (2, 100, 2), (1, 65, 1)])
+@pytest.mark.parametrize("B,T,H", [(2, 197, 12), (3, 198, 6), (1, 33, 2), (2, 256, 1), (1, 7, 3), (2, 100, 2), (1, 65, 1),
+                                   (1, 208, 2), (1, 209, 1), (1, 129, 2), (2, 128, 1)])
 def test_fused_attention_core(cuda_lib, B, T, H, scale_op):
     """Split -> head reshapes/transposes -> Q K^T -> scale -> Softmax -> P V -> merge heads,
     lowered to one kernel when fusion is on; compared with the oracle running the chain."""
