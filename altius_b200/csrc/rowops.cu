@@ -380,9 +380,10 @@ cudaError_t reduce_last_dispatch(const float* x, float* out, int64_t rows, int64
   if (rows == 0) return cudaSuccess;
   const int64_t blocks64 = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   if ((len % 128) == 0 && len <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-    // Enough warps to fill the chip four blocks deep, each walking pairs of rows.
+    // One pair of rows per warp up to six blocks per SM (measured: a second pass of a
+    // partly idle grid costs more than the extra blocks), a grid-stride walk beyond that.
     const int64_t want = (rows + 2 * kWarpsPerBlock - 1) / (2 * kWarpsPerBlock);
-    const unsigned vb = (unsigned)(want > 148 * 4 ? 148 * 4 : want);
+    const unsigned vb = (unsigned)(want > 148 * 6 ? 148 * 6 : want);
     switch (len / 128) {
       case 1: reduce_last_vec<MODE, 1><<<vb, kThreads, 0, st>>>(x, out, rows); break;
       case 2: reduce_last_vec<MODE, 2><<<vb, kThreads, 0, st>>>(x, out, rows); break;

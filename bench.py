@@ -344,7 +344,11 @@ def main():
         peak = peaks["bf16_tflops_sustained"] / (1.0 if f16 else 2.0)
         roofline = {"kernel": top_kind, "bound": "tensor", "achieved": round(achieved, 2),
                     "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
-                    "traffic": None,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at the
+                    # QKV shape (M 6304, K 768, N 2304; algorithmic operand + result bytes 84.6 MB, of
+                    # which A, B and most of C stay in L2), from the ncu capture summarised in
+                    # profiles/gemm_f16x3_6304x768x2304.md
+                    "traffic": 46552320 if f16 else None,
                     "tensor_pipe_frac": round(3.0 * achieved / peak, 4),
                     "peak_note": f"{peaks['source']} sustained bf16 cuBLAS TFLOP/s"
                                  + ("" if f16 else " / 2 (no TF32 peak is measured)")
