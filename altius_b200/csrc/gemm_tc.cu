@@ -39,6 +39,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -562,7 +563,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           ok = mbar_wait(&full[s], ph);
-          if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
+          if (MODE != TC_F16X3 && !ok) { atomicExch(err, 3); *abort_flag = 1; break; }
           if (MODE == TC_F16X3) {
             // fp32 rows of 32 floats -> fp16 hi / lo tiles; one float4 (4 consecutive k) per item.
             // The tiles take the place of the rows: everything is read first, the group's
@@ -574,7 +575,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             float4 x[kItems > 0 ? kItems : 1];
 #pragma unroll
             for (int i = 0; i < kItems; ++i) x[i] = raw[i * kSplitThreads + t0];
-            asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(kSplitThreads) : "memory");
+            // The barrier also ORs the threads' wait results, so that the whole group leaves
+            // together if the wait above expired for any of them.
+            ok = !group_barrier_or(group + 1, kSplitThreads, !ok);
+            if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
 #pragma unroll
             for (int i = 0; i < kItems; ++i) {
               const int item = i * kSplitThreads + t0;
@@ -678,6 +682,269 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   }
 }
 
+// ---- CTA pairs ---------------------------------------------------------------------------
+// fp16-split GEMM on clusters of two CTAs (tcgen05 .cta_group::2): a pair owns a 256 x BN
+// tile. Each CTA stages its own 128 rows of A and HALF of the B tile (BN / 2 rows): the
+// tensor cores of the two SMs exchange the B halves, so every SM pulls 32 KB per stage
+// instead of 48 KB -- the main loop is bound by exactly that feed. Per CTA: TMA producer and
+// splitters as in the one-CTA kernel (local `full` barriers); the splitters of both CTAs
+// arrive on the LEADER's (rank 0) `ready` barrier; one thread of the leader issues the MMAs
+// for both SMs and commits to the `empty` / `acc_full` barriers of both CTAs; each CTA's
+// epilogue warps drain its own 128 accumulator rows and arrive on the leader's `acc_empty`.
+// Work is distributed over pairs exactly as over CTAs in the one-CTA kernel.
+__device__ __forceinline__ bool pair_get_work(const TcSched& sc, int w, TcWork* out) {
+  const int c = blockIdx.x >> 1, g = gridDim.x >> 1;
+  const int n_dp = sc.dp_tiles > c ? (sc.dp_tiles - c + g - 1) / g : 0;
+  if (w < n_dp) {
+    out->tile = c + w * g; out->k0 = 0; out->k1 = sc.num_kb; out->raw = -1;
+    return true;
+  }
+  if (w == n_dp && sc.tail_parts >= 2 && c < (sc.num_tiles - sc.dp_tiles) * sc.tail_parts) {
+    const int part = c % sc.tail_parts;
+    out->tile = sc.dp_tiles + c / sc.tail_parts;
+    out->k0 = (int)((long long)part * sc.num_kb / sc.tail_parts);
+    out->k1 = (int)((long long)(part + 1) * sc.num_kb / sc.tail_parts);
+    out->raw = c;
+    return true;
+  }
+  return false;
+}
+
+template <int BN>
+struct PairSmem {
+  static constexpr int kKb = BK16;                      // floats of K per stage
+  static constexpr int kABytes = BM * kKb * 2;          // fp16 hi tile of A; the lo tile follows
+  static constexpr int kBBytes = (BN / 2) * kKb * 2;    // this CTA's half of B: one of hi / lo
+  static constexpr int kOffALo = kABytes;
+  static constexpr int kOffBHi = 2 * kABytes;
+  static constexpr int kOffBLo = kOffBHi + kBBytes;
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+  static constexpr int kTxBytes = 2 * kBBytes;          // TMA brings B only; A goes global -> registers -> tiles
+  static constexpr int kStages = (200 * 1024) / kStageBytes;   // 6 at BN 256
+  static constexpr int kEpiBytes = 4 * 4096;
+  static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
+  static constexpr int kTmemCols = 2 * BN;              // D1 and D2, one accumulator set
+  static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tensor memory");
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
+                    const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_blo,
+                    TcEpilogue ep, TcSched sc, int tiles_m, int tiles_n, float* workspace, int* err) {
+  using L = PairSmem<BN>;
+  constexpr int S = L::kStages;
+  constexpr int KB = L::kKb;
+  constexpr int D2 = BN;                 // column offset of the cross-term accumulator
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* epi_smem = smem + S * L::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + L::kEpiBytes);
+  uint64_t* full = bars;                 // this CTA's TMA bytes landed
+  uint64_t* ready = bars + S;            // leader's: both CTAs' fp16 tiles written (2 x 4 warps arrive)
+  uint64_t* empty = bars + 2 * S;        // this CTA's: the pair's MMAs that read the stage have completed
+  uint64_t* acc_full = bars + 3 * S;     // this CTA's: accumulators complete
+  uint64_t* acc_empty = bars + 3 * S + 1;   // leader's: drained by the 8 epilogue warps of the pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+
+  auto a_raw = [&](int s) { return smem + s * L::kStageBytes; };    // fp16 hi tile of A
+  auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kOffALo; };
+  auto b_hi = [&](int s) { return smem + s * L::kStageBytes + L::kOffBHi; };
+  auto b_lo = [&](int s) { return smem + s * L::kStageBytes + L::kOffBLo; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&ready[s], 2 * (kSplitThreads / 32));   // one arrival per splitter warp of the pair
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 8);             // one arrival per epilogue warp of the pair
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kSplitWarps + 5) {         // the same warp in both CTAs, the same shared-memory slot
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)L::kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  cluster_sync_all();                    // barriers of both CTAs initialised before any remote arrival
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == kSplitWarps + 4) {
+    // ---------------- TMA producer (each CTA for itself) ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      TcWork wk;
+      for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
+        const int t = wk.tile;
+        const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
+          mbar_arrive_expect_tx(&full[s], L::kTxBytes);
+          tma_load_3d(b_hi(s), &tm_b, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
+          tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
+        }
+      }
+    }
+  } else if (warp == kSplitWarps + 5) {
+    // ---------------- MMA issuer (leader only) ----------------
+    if (leader && lane == 0) {
+      // fp32 accumulators, fp16 A and B (format 0), both K-major, N = BN, M = 256 over the pair.
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      const uint32_t acc_full_peer = map_to_cta(acc_full, 1);
+      int it = 0, ti = 0;
+      bool ok = true;
+      TcWork wk;
+      for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w, ++ti) {
+        // The eight epilogue warps must have drained the accumulators of the previous tile.
+        if (!mbar_wait(acc_empty, (ti & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
+        tc_fence_after();
+        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          ok = mbar_wait(&ready[s], ph);
+          if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_u32(a_raw(s))), dal = make_smem_desc(smem_u32(a_lo(s)));
+          const uint64_t db = make_smem_desc(smem_u32(b_hi(s))), dbl = make_smem_desc(smem_u32(b_lo(s)));
+#pragma unroll
+          for (int kk = 0; kk < 2; ++kk) {                  // two K-steps of 16 halves per 64-byte row
+            const uint64_t off = (uint64_t)(kk * 32 >> 4);
+            const uint32_t acc = (kb > wk.k0 || kk > 0) ? 1u : 0u;
+            tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);          // a_hi * b_hi
+            tc_mma_f16_pair(tmem_base + D2, dal + off, db + off, idesc, acc);    // a_lo' * b_hi
+            tc_mma_f16_pair(tmem_base + D2, da + off, dbl + off, idesc, 1u);     // a_hi * b_lo'
+          }
+          tc_commit_pair(smem_u32(&empty[s]));      // the stage is free again in this CTA ...
+          tc_commit_pair(map_to_cta(&empty[s], 1)); // ... and in the peer
+        }
+        if (ok) {
+          tc_commit_pair(smem_u32(acc_full));
+          tc_commit_pair(acc_full_peer);
+        }
+      }
+    }
+  } else if (warp < kSplitWarps) {
+    // ---------------- splitters (each CTA its own A rows) ----------------
+    // A does not pass through shared memory as fp32: each thread loads its eight float4
+    // (row, four consecutive k) of the stage from global memory, splits them in registers and
+    // writes the fp16 hi / lo tiles. The loads of a group's next stage are in flight while
+    // it waits for that stage to be free.
+    const int t0 = threadIdx.x & (kSplitThreads - 1);
+    const int group = threadIdx.x / kSplitThreads;   // takes the K-blocks with it % kSplitGroups == group
+    constexpr int kItems = BM * KB / 4 / kSplitThreads;   // 8
+    int it = 0;
+    bool ok = true;
+    unsigned range_bad = 0;
+    TcWork wk;
+    for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
+      const int t = wk.tile;
+      const int tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+      const int m0 = tm * (2 * BM) + (int)rank * BM;
+      const float* a_tile = a_ptr + (long long)bz * 0 + (long long)m0 * lda;   // one GEMM (batch 1)
+      for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
+        if (it % kSplitGroups != group) continue;
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
+        float4 x[kItems];
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+          const int item = i * kSplitThreads + t0;
+          const int r = item >> 3, kcol = kb * KB + (item & 7) * 4;
+          x[i] = (m0 + r < ep.m && kcol < k_total)
+                     ? __ldg(reinterpret_cast<const float4*>(a_tile + (long long)r * lda + kcol))
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        ok = mbar_wait(&empty[s], ph ^ 1);          // the pair's MMAs on the previous use of the stage are done
+        if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
+        uint8_t* hi_t = a_raw(s);
+        uint8_t* lo_t = a_lo(s);
+#pragma unroll
+        for (int i = 0; i < kItems; ++i) {
+          const int item = i * kSplitThreads + t0;
+          range_bad |= beyond_half(x[i].x) | beyond_half(x[i].y) | beyond_half(x[i].z) | beyond_half(x[i].w);
+          uint2 hi, lo;
+          f16_split(x[i], hi, lo);
+          const uint32_t off = sw64_off8(item >> 3, item & 7);
+          *reinterpret_cast<uint2*>(hi_t + off) = hi;
+          *reinterpret_cast<uint2*>(lo_t + off) = lo;
+        }
+        fence_proxy_async();
+        ok = mbar_wait(&full[s], ph);               // this CTA's half of B has landed too
+        if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
+        __syncwarp();                               // one remote arrival per warp, not per thread
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(&ready[s], 0));
+      }
+    }
+    if (range_bad) atomicCAS(err, 0, kRangeCode);
+  } else {
+    // ---------------- epilogue (each CTA its own 128 rows) ----------------
+    const int q = warp - kSplitWarps;
+    float4* stage = reinterpret_cast<float4*>(epi_smem + q * 4096);
+    const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
+    const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
+                        ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
+                        (!ep.res || ((ep.ldres % 4) == 0 && (ep.sres % 4) == 0 &&
+                                     (reinterpret_cast<uintptr_t>(ep.res) & 15) == 0)) &&
+                        (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
+    const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
+    int ti = 0;
+    TcWork wk;
+    for (int w = 0; pair_get_work(sc, w, &wk); ++w, ++ti) {
+      const int t = wk.tile;
+      const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+      if (!mbar_wait(acc_full, ti & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
+      tc_fence_after();
+      const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+      if (m0 < ep.m) {
+        if (wk.raw >= 0) {
+          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane);
+        } else
+        switch (key) {
+          case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          default: epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0 && warp == kSplitWarps + 4 && lane == 0) {
+    for (int s = 0; s < S; ++s) {        // copies that may still be in flight: a bounded time to land
+      (void)mbar_wait(&full[s], 0);
+      (void)mbar_wait(&full[s], 1);
+    }
+  }
+  cluster_sync_all();                    // no CTA leaves while its peer may still signal it or read its B half
+  if (warp == kSplitWarps + 5) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)L::kTmemCols));
+  }
+}
+
 // hi / lo split of a whole tensor (constant operands, once at load).
 __global__ void tf32_split_kernel(const float* __restrict__ x, float* __restrict__ hi,
                                   float* __restrict__ lo, int64_t n) {
@@ -764,9 +1031,10 @@ struct TcPlan {
   TcSched sc;
   size_t workspace_bytes;
 };
-TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn, int mt, int kb_floats) {
+// `workers`: CTAs (or CTA pairs) that walk the tiles; 0 = one per SM.
+TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn, int mt, int kb_floats, int workers = 0) {
   TcPlan pl{};
-  const int sms = sm_count();
+  const int sms = workers > 0 ? workers : sm_count();
   pl.tiles_n = (int)((n + bn - 1) / bn);
   pl.tiles_m = (int)((m + mt * BM - 1) / (mt * BM));
   const long long tiles = (long long)pl.tiles_n * pl.tiles_m * batch;
@@ -814,6 +1082,29 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
   return cudaGetLastError();
 }
 
+template <int BN>
+cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap& mb, const CUtensorMap& mbl,
+                        const TcEpilogue& ep, const TcPlan& pl, float* workspace, int* err, cudaStream_t st) {
+  using L = PairSmem<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         L::kDynBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  // pl.grid counts pairs; the cluster shape (2, 1, 1) is a compile-time attribute of the kernel.
+  gemm_tc_pair_kernel<BN><<<2 * pl.grid, kThreads, L::kDynBytes, st>>>(a, lda, k, mb, mbl, ep, pl.sc, pl.tiles_m,
+                                                                     pl.tiles_n, workspace, err);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || pl.sc.tail_parts < 2) return e;
+  const int tail = pl.sc.num_tiles - pl.sc.dp_tiles;
+  dim3 grid((2 * BM * BN / 4 + 255) / 256, tail);
+  gemm_tc_fixup_kernel<<<grid, 256, 0, st>>>(workspace, ep, 2 * BM, BN, pl.sc.dp_tiles, pl.sc.tail_parts, pl.tiles_m,
+                                             pl.tiles_n);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 bool gemm_tc_supported(const GemmParams& q) {
@@ -828,7 +1119,35 @@ bool gemm_tc_supported(const GemmParams& q) {
 }
 
 namespace {
-struct TcShape { int bn, mt; };
+struct TcShape { int bn, mt; bool pair; };
+
+// CTA pairs that can be resident at once for the pair kernel (0: clusters unavailable).
+int pair_count() {
+  static int n = -1;
+  if (n < 0) {
+    n = 0;
+    {
+      using L = PairSmem<256>;
+      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               L::kDynBytes) == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sm_count() & ~1);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = L::kDynBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<256>, &cfg) == cudaSuccess && clusters > 0)
+          n = std::min(clusters, sm_count() / 2);
+      }
+      (void)cudaGetLastError();
+    }
+  }
+  return n;
+}
 
 // Tile shape by a cost model in SM clocks, fitted to measurements: TMA fills shared
 // memory at about 28 bytes per clock per SM (8 TB/s over the chip, the L2 -> SM
@@ -838,15 +1157,15 @@ struct TcShape { int bn, mt; };
 // (a K-sliced tail costs 1 / parts of a round); a shape that fills tensor memory with
 // one accumulator set cannot hide its epilogue. variant: 0 TF32 with B arriving split,
 // 1 TF32 with one B copy, 2 fp16 split.
-TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant) {
-  static const TcShape cands[3] = {{256, 1}, {128, 1}, {64, 1}};
+TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, bool allow_pairs) {
+  static const TcShape cands[3] = {{256, 1, false}, {128, 1, false}, {64, 1, false}};
   // Debug toggle: ALTIUS_CUDA_TC_BN=64|128|256 forces the tile width.
   const char* ebn = std::getenv("ALTIUS_CUDA_TC_BN");
   const int fbn = ebn ? std::atoi(ebn) : 0;
   const int sms = sm_count();
   const bool f16 = variant == 2;
   const int kbf = f16 ? BK16 : BK;
-  TcShape best = {256, 1};
+  TcShape best = {256, 1, false};
   double best_cost = 1e300;
   for (int i = 0; i < 3; ++i) {
     const TcShape c = cands[i];
@@ -864,13 +1183,23 @@ TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant) 
     if (pl.sc.num_tiles < sms) cost += 1.0;   // ties: prefer the shape with more tiles in flight
     if (cost < best_cost - 1e-9) { best_cost = cost; best = c; }
   }
+  // CTA pairs (fp16 split, one GEMM, BN 256): 256 x 256 tiles, each SM pulls its A rows and
+  // half of B (32 KB per stage), the pair's MMAs cost 128 clocks per SM; single accumulator set.
+  const int pairs = allow_pairs ? pair_count() : 0;
+  if (f16 && batch == 1 && (k % 4) == 0 && pairs > 0 && (!fbn || fbn == 256)) {
+    const TcPlan pl = make_plan(m, n, k, batch, 256, 2, kbf, pairs);
+    double rounds = (double)(pl.sc.dp_tiles / pairs) + (pl.sc.dp_tiles % pairs ? 1.0 : 0.0);
+    if (pl.sc.tail_parts >= 2) rounds += 1.0 / pl.sc.tail_parts + 0.05;
+    const double cost = rounds * (pl.sc.num_kb * std::max(6.0 * 128.0, 32768.0 / 28.0) + 256 * 24.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = {256, 2, true}; }
+  }
   return best;
 }
 }  // namespace
 
-size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant) {
-  const TcShape sh = pick_shape(m, n, k, batch, variant);
-  return make_plan(m, n, k, batch, sh.bn, sh.mt, variant == 2 ? BK16 : BK).workspace_bytes;
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, bool allow_pairs) {
+  const TcShape sh = pick_shape(m, n, k, batch, variant, allow_pairs);
+  return make_plan(m, n, k, batch, sh.bn, sh.mt, variant == 2 ? BK16 : BK, sh.pair ? pair_count() : 0).workspace_bytes;
 }
 
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
@@ -880,15 +1209,17 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
                     : (mode == 0 && q.b16_hi && q.b16_lo) ? TC_F16X3
                     : (q.b_lo ? TC_3X_BLO_TMA : TC_3X_SPLIT_B);
   const int variant = kmode == TC_F16X3 ? 2 : (kmode == TC_3X_BLO_TMA ? 0 : 1);
-  const TcShape sh = pick_shape(q.m, q.n, q.k, q.batch, variant);
+  const TcShape sh = pick_shape(q.m, q.n, q.k, q.batch, variant, q.allow_pairs != 0);
   const int bn = sh.bn;
   CUtensorMap ma, mb, mbl;
   const int b_batched = (q.batch > 1 && q.stride_b > 0) ? 1 : 0;
   if (kmode == TC_F16X3) {
     if (b_batched || (q.ldb16 % 8) != 0) return cudaErrorInvalidValue;
-    if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK16, sh.mt * BM, false)) return cudaErrorInvalidValue;
-    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, bn, true)) return cudaErrorInvalidValue;
-    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, bn, true)) return cudaErrorInvalidValue;
+    // A pair's CTAs each load their own 128 rows of A and half of the B tile.
+    const int a_rows = sh.pair ? BM : sh.mt * BM, b_rows = sh.pair ? bn / 2 : bn;
+    if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK16, a_rows, false)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, true)) return cudaErrorInvalidValue;
+    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, true)) return cudaErrorInvalidValue;
   } else {
     if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK, sh.mt * BM, true)) return cudaErrorInvalidValue;
     if (!make_map(&mb, q.b, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, true))
@@ -908,13 +1239,14 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.bias_n = q.bias_n; ep.bias_m = q.bias_m; ep.bias_scale = q.bias_scale;
   ep.act = q.act; ep.act_alpha = q.act_alpha; ep.act_beta = q.act_beta;
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
-  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, kmode == TC_F16X3 ? BK16 : BK);
+  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, kmode == TC_F16X3 ? BK16 : BK, sh.pair ? pair_count() : 0);
   if (pl.sc.tail_parts >= 2 && (!q.workspace || q.workspace_bytes < pl.workspace_bytes)) {
     // No (or too small a) workspace: fall back to whole tiles only.
     pl.sc.dp_tiles = pl.sc.num_tiles;
     pl.sc.tail_parts = 0;
   }
   float* ws = q.workspace;
+  if (sh.pair) return launch_pair<256>(q.a, q.lda, (int)q.k, mb, mbl, ep, pl, ws, err_word, st);
 #define AC_TC(BNV)                                                                              \
   (kmode == TC_1X ? launch_tc<BNV, 1, TC_1X>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)     \
    : kmode == TC_F16X3                                                                          \

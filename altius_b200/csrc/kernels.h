@@ -150,6 +150,7 @@ struct GemmParams {
   int residual_first;       // residual + v instead of v + residual (same value, kept for clarity)
   float* workspace;         // tensor-core path: scratch for K-sliced tail tiles, or null
   size_t workspace_bytes;
+  int allow_pairs;          // fp16 split: may run on clusters of two CTAs (tcgen05 .cta_group::2)
 };
 cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
 
@@ -163,7 +164,7 @@ bool gemm_tc_supported(const GemmParams& p);
 cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStream_t st);
 // Scratch the tensor-core path wants for this problem (0 when its tiles fill whole rounds).
 // variant: 0 TF32 with B arriving split, 1 TF32 with one copy of B, 2 fp16 split.
-size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant);
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, bool allow_pairs);
 constexpr int kGemmRangeCode = 21;
 // fp16 split of a constant [rows, k] operand (row stride ld) into [rows, k8] halves
 // (k8 >= k, a multiple of 8, padding zero); leaves kGemmRangeCode in *err_word when an

@@ -565,6 +565,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
 
   // ---- tensor-core eligibility (static part; alignment is re-checked at launch) ----
   const int mode = s->opt.gemm_mode;
+  const bool pairs = s->opt.gemm_pairs != 0;
   bool tc = mode != 1 && !g.ta && (g.lda % 4) == 0 && (a_off % 4) == 0 && (g.sa % 4) == 0 &&
             flops >= double(1 << 23) && g.k >= 8;
   int b_use = b, b_lo = -1;
@@ -622,7 +623,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
   int ws = -1;
   size_t ws_bytes = 0;
   if (tc) {
-    ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b16_hi >= 0 ? 2 : (b_lo >= 0 ? 0 : 1));
+    ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b16_hi >= 0 ? 2 : (b_lo >= 0 ? 0 : 1), pairs);
     if (ws_bytes) ws = new_value(em.c, (int64_t)(ws_bytes / 4), false);
   }
   std::vector<int> reads = {a, bsrc, b_lo, b16_hi, b16_lo, c_in, bias_n, bias_m, res};
@@ -634,6 +635,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     GemmParams p{};
     p.workspace = ws >= 0 ? s->fptr_mut(ws) : nullptr;
     p.workspace_bytes = ws_bytes;
+    p.allow_pairs = pairs ? 1 : 0;
     p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
     p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
     p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;

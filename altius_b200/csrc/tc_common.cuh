@@ -140,5 +140,63 @@ __device__ __forceinline__ uint32_t sw64_off8(int row, int c8) {
   return (uint32_t)((row >> 3) * 512 + (row & 7) * 64 + (((c8 >> 1) ^ ((row & 7) >> 1)) << 4) + (c8 & 1) * 8);
 }
 
+
+// Named barrier `id` over `nthreads` threads that also returns the OR of their predicates.
+__device__ __forceinline__ bool group_barrier_or(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %3, 0;\n\t"
+      "barrier.cta.red.or.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+// ---- CTA pairs (clusters of two; tcgen05 .cta_group::2) ----------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of both CTAs.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(const void* local, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(local)), "r"(rank));
+  return a;
+}
+// Arrive on an mbarrier given by its shared::cluster address (own or peer CTA). Default
+// (CTA-scope release) semantics: what the arrival publishes is shared memory of the arriving
+// CTA, written behind a fence.proxy.async and read by that CTA's own tensor core; a
+// cluster-scope release here cost a memory-barrier stall per stage.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// MMA of a CTA pair: M = 256 (128 rows per CTA), B rows split between the two CTAs; issued by
+// one thread of the leader CTA (rank 0). The eight zero words disable no output lane.
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+// Completion of the pair's MMAs issued so far -> one arrival on the mbarrier at a
+// shared::cluster address (own or peer CTA).
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
 }  // namespace tc
 }  // namespace ac

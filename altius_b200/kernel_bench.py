@@ -19,9 +19,9 @@ from . import configs, ir
 from .session import CudaSessionBuilder
 
 
-def _run(model, feeds, mode, fuse, iters, cold=False):
+def _run(model, feeds, mode, fuse, iters, cold=False, pairs=False):
     import torch
-    sess = (CudaSessionBuilder(model).with_gemm_mode(mode).with_fusion(fuse)
+    sess = (CudaSessionBuilder(model).with_gemm_mode(mode).with_fusion(fuse).with_gemm_pairs(pairs)
             .with_profiling_enabled(True, cold_l2=cold).build())
     ins = [torch.from_numpy(np.ascontiguousarray(v)).cuda() for v in feeds]
     outs = [torch.empty(tuple(shape), dtype=torch.float32, device="cuda") for shape, _ in sess.output_info]
@@ -52,6 +52,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--no-fuse", action="store_true")
+    ap.add_argument("--pairs", action="store_true", help="fp16-split GEMM on clusters of two CTAs")
     ap.add_argument("--cold-l2", action="store_true", help="sweep L2 before every kernel (micrograph)")
     a = ap.parse_args(argv)
     rng = np.random.default_rng(0)
@@ -63,7 +64,7 @@ def main(argv=None):
         xi = g.add_input("x", x.shape)
         out = g.op("MatMul", xi, g.new_init(w))
         g.outputs.append(out)
-        rows = _run(ir.Model(g, 13), [x], a.mode, True, a.iters)
+        rows = _run(ir.Model(g, 13), [x], a.mode, True, a.iters, pairs=a.pairs)
     elif a.what == "attention":
         B, T, H = a.dims
         hd, D = 64, 64 * H

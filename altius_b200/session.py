@@ -72,7 +72,7 @@ class AcOptions(ctypes.Structure):
     _fields_ = [("device", ctypes.c_int32), ("enable_profiling", ctypes.c_int32),
                 ("disable_cuda_graph", ctypes.c_int32), ("disable_fusion", ctypes.c_int32),
                 ("gemm_mode", ctypes.c_int32), ("plan_only", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 2)]
+                ("gemm_pairs", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 class AcProfileEntry(ctypes.Structure):
@@ -200,7 +200,7 @@ class CudaSession:
 
     def __init__(self, model: ir.Model, device: int, enable_profiling: bool, use_cuda_graph: bool,
                  fuse: bool, gemm_mode: int, device_inits: Optional[Dict[int, int]] = None,
-                 plan_only: bool = False):
+                 plan_only: bool = False, gemm_pairs: bool = False):
         self._model = model
         self._lib = load_library()
         self._handle = ctypes.c_void_p()
@@ -254,6 +254,7 @@ class CudaSession:
         opt.disable_fusion = int(not fuse)
         opt.gemm_mode = gemm_mode
         opt.plan_only = int(plan_only)
+        opt.gemm_pairs = int(gemm_pairs)
         rc = self._lib.altius_cuda_create(ctypes.byref(desc), ctypes.byref(opt),
                                           ctypes.byref(self._handle))
         if rc != 0:
@@ -399,6 +400,7 @@ class CudaSessionBuilder:
         self.gemm_mode = 0
         self.device_inits: Optional[Dict[int, int]] = None
         self.plan_only = False
+        self.gemm_pairs = False
 
     def with_plan_only(self, b: bool):
         """Shapes, schedule and arena plan only; no GPU is touched and `run` fails."""
@@ -430,6 +432,11 @@ class CudaSessionBuilder:
         self.gemm_mode = mode
         return self
 
+    def with_gemm_pairs(self, b: bool):
+        """fp16-split GEMMs on clusters of two CTAs (see AcOptions.gemm_pairs)."""
+        self.gemm_pairs = b
+        return self
+
     def with_device_initializers(self, ptrs: Dict[int, int]):
         """value id -> device address of an initializer already resident on the
         session's device (the landing buffer of a weight broadcast)."""
@@ -438,7 +445,7 @@ class CudaSessionBuilder:
 
     def build(self) -> CudaSession:
         return CudaSession(self.model, self.device, self.enable_profiling, self.use_cuda_graph,
-                           self.fuse, self.gemm_mode, self.device_inits, self.plan_only)
+                           self.fuse, self.gemm_mode, self.device_inits, self.plan_only, self.gemm_pairs)
 
 
 class InferenceSession:

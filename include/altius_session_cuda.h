@@ -154,7 +154,10 @@ typedef struct AcOptions {
   int32_t plan_only;         /* 1: infer shapes, lower and plan the arena without
                                 touching a GPU; run() then fails. For inspecting
                                 the schedule on a machine without a device.      */
-  int32_t reserved[2];
+  int32_t gemm_pairs;        /* 1: fp16-split GEMMs of 256-row tiles on clusters of two
+                                CTAs (tcgen05 .cta_group::2, each SM stages half of the
+                                weight tile); same results, not faster yet: off by default */
+  int32_t reserved;
 } AcOptions;
 
 typedef struct AcSession AcSession;

@@ -36,6 +36,8 @@ def run_cuda(model, inputs, **opts):
         b = b.with_cuda_graph(opts["graph"])
     if "gemm_mode" in opts:
         b = b.with_gemm_mode(opts["gemm_mode"])
+    if "pairs" in opts:
+        b = b.with_gemm_pairs(opts["pairs"])
     sess = b.build()
     try:
         return sess.run(list(inputs))

@@ -313,6 +313,42 @@ def test_fp16_split_is_not_used_for_weights_out_of_range(cuda_lib):
         sess.close()
 
 
+@pytest.mark.parametrize("ashape,bshape", [((2, 197, 768), (768, 2304)), ((394, 3072), (3072, 768)), ((1000, 768), (768, 768)),
+                                            ((300, 100), (100, 72)), ((257, 36), (36, 513)), ((5000, 64), (64, 256))])
+def test_matmul_on_cta_pairs(cuda_lib, ashape, bshape):
+    """The fp16-split GEMM on clusters of two CTAs (tcgen05 .cta_group::2; each CTA stages its
+    rows of A and half of the weight tile) computes the same products as the one-CTA kernel;
+    only the K-slicing of tail tiles (and with it the order of a few additions) can differ."""
+    a = RNG.standard_normal(ashape).astype(np.float32)
+    w = RNG.standard_normal(bshape).astype(np.float32)
+    m = single_op_model("MatMul", [a], [w])
+    want = run_oracle(m, [a])[0]
+    got = run_cuda(m, [a], pairs=True)[0]
+    bound = 1e-5 * np.abs(want) + 5e-6 * (np.abs(a).reshape(-1, ashape[-1]) @ np.abs(w)).reshape(want.shape)
+    assert (np.abs(got - want) <= bound).all()
+    single = run_cuda(m, [a])[0]
+    assert (np.abs(got - single) <= 2e-6 * (np.abs(a).reshape(-1, ashape[-1]) @ np.abs(w)).reshape(want.shape)).all()
+
+
+def test_cta_pairs_in_a_model_with_epilogues_and_range_fallback(cuda_lib):
+    from altius_b200 import configs
+    from altius_b200.session import CudaSessionBuilder
+    model, feeds = configs.vit_base_16(batch=2, depth=2)
+    x = next(iter(feeds.values()))
+    want = run_cuda(model, [x])[0]
+    sess = CudaSessionBuilder(model).with_gemm_pairs(True).build()
+    try:
+        got = sess.run([x])[0]
+        assert np.abs(got - want).max() <= 1e-4 and (got.argmax(-1) == want.argmax(-1)).all()
+        big = x.copy()
+        big[0, 0, 0, 0] = 1e9            # beyond fp16 after the patch embedding: detected, 3xTF32 plan takes over
+        out = sess.run([big])[0]
+        assert np.isfinite(out).all()
+        assert any(e["kind"] == "gemm_tf32x3_tcgen05" for e in sess.schedule())
+    finally:
+        sess.close()
+
+
 def test_matmul_tf32x1_is_looser_but_close(cuda_lib):
     a = RNG.standard_normal((512, 768)).astype(np.float32)
     w = RNG.standard_normal((768, 512)).astype(np.float32)
