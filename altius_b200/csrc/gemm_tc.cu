@@ -786,8 +786,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       bool ok = true;
       TcWork wk;
       for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
-        const int t = wk.tile;
-        const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+        const int tn = wk.tile % tiles_n;
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -851,9 +850,9 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     TcWork wk;
     for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
       const int t = wk.tile;
-      const int tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+      const int tm = (t / tiles_n) % tiles_m;
       const int m0 = tm * (2 * BM) + (int)rank * BM;
-      const float* a_tile = a_ptr + (long long)bz * 0 + (long long)m0 * lda;   // one GEMM (batch 1)
+      const float* a_tile = a_ptr + (long long)m0 * lda;   // one GEMM (batch 1)
       for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
         if (it % kSplitGroups != group) continue;
         const int s = it % S;
@@ -1045,8 +1044,7 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn, int mt,
   pl.sc.tail_parts = 0;
   pl.grid = (int)std::min<long long>(tiles, sms);
   const int tail = (int)(tiles % sms);
-  static const bool no_tail = std::getenv("ALTIUS_CUDA_TC_NO_TAIL_SPLIT") != nullptr;   // debug toggle
-  if (tail > 0 && !no_tail) {
+  if (tail > 0) {
     const int parts = std::min(std::min(sms / tail, num_kb / 2), 32);   // at least two K-blocks per slice
     if (parts >= 2) {
       pl.sc.dp_tiles = (int)(tiles - tail);

@@ -587,12 +587,6 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       tc = false;
     }
   }
-  // Debug toggle: ALTIUS_CUDA_SPLIT_B_IN_KERNEL=1 splits constant weights inside the
-  // GEMM kernel too (less L2 traffic, more shared-memory traffic) instead of at load.
-  static const bool split_b_in_kernel = [] {
-    const char* e = std::getenv("ALTIUS_CUDA_SPLIT_B_IN_KERNEL");
-    return e && e[0] == '1';
-  }();
   // mode 0 with a constant rhs: the fp16 split (hi, remainder * 2^11) prepared once, [N, K8] halves.
   int b16_hi = -1, b16_lo = -1;
   int64_t ldb16 = 0;
@@ -607,7 +601,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word, st);
     });
   }
-  if (tc && b16_hi < 0 && mode != 2 && em.c.val(b_use).is_const && !split_b_in_kernel) {
+  if (tc && b16_hi < 0 && mode != 2 && em.c.val(b_use).is_const) {
     // TF32 hi / lo split of a constant rhs, prepared once.
     const int64_t cnt = em.c.val(b_use).numel();
     const int hi = new_value(em.c, cnt, true);
@@ -998,8 +992,7 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         const double bytes = 4.0 * B * T * hd * H * 4;
         const double flops = 4.0 * B * H * T * T * hd;
         // gemm_mode 1 asks for exact fp32 FMA chains: it keeps the CUDA-core kernel.
-        static const bool no_tc_attn = std::getenv("ALTIUS_CUDA_NO_TC_ATTENTION") != nullptr;   // debug toggle
-        const bool tc_attn = s->opt.gemm_mode != 1 && !no_tc_attn && hd == 64 && T > 64 && T <= 256;
+        const bool tc_attn = s->opt.gemm_mode != 1 && hd == 64 && T > 64 && T <= 256;
         em.add(tc_attn ? "attention_tcgen05" : "attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, {f.out}, bytes, flops,
                [=](cudaStream_t st) {
                  AttentionParams p{};

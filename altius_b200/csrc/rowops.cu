@@ -445,12 +445,7 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
     const bool fused = q.pre_bias || q.residual || q.gelu || q.sum_out;
     // Two blocks of 8 warps per SM: several rows per warp, so the prefetch of the next
     // row overlaps the stores of the current one.
-    // (Debug toggle ALTIUS_CUDA_LN_BLOCKS_PER_SM overrides the depth.)
-    static const int env_depth = [] {
-      const char* e = std::getenv("ALTIUS_CUDA_LN_BLOCKS_PER_SM");
-      return e ? std::atoi(e) : 0;
-    }();
-    const int depth = env_depth > 0 ? env_depth : (fused ? 3 : 2);    // the fused variants are bound by arithmetic
+    const int depth = fused ? 3 : 2;    // the fused variants are bound by arithmetic (measured: 1, 3, 4 are slower for the plain one)
     const unsigned vblocks = blocks64 > 148 * depth ? 148 * depth : (unsigned)blocks64;
 #define AC_LN(NVV)                                                                         \
   do {                                                                                     \
