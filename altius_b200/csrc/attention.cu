@@ -245,13 +245,9 @@ int pick_rows(int T) {
 
 template <int NJ, int R>
 cudaError_t launch_nj(const AttnDev& d, int bh, cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_kernel<NJ, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)attn_smem_bytes(NJ * 32, R));
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static unsigned long long attr_done = 0;
+  cudaError_t e = ensure_dynamic_smem(attention_kernel<NJ, R>, (int)attn_smem_bytes(NJ * 32, R), &attr_done);
+  if (e != cudaSuccess) return e;
   dim3 grid((d.tokens + WARPS * R - 1) / (WARPS * R), bh);
   attention_kernel<NJ, R><<<grid, THREADS, attn_smem_bytes(d.tokens, R), st>>>(d);
   return cudaGetLastError();

@@ -506,13 +506,9 @@ cudaError_t launch_nb_mode(const AttnTcDev& d, int bh, cudaStream_t st) {
   constexpr bool kResident = kDynResident <= 227 * 1024;
   constexpr int kDyn = kResident ? kDynResident : kDynOverlay;
   static_assert(kDyn <= 227 * 1024, "shared memory per CTA");
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<NB, SMODE, kResident>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kDyn);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static unsigned long long attr_done = 0;
+  cudaError_t e = ensure_dynamic_smem(attention_tc_kernel<NB, SMODE, kResident>, kDyn, &attr_done);
+  if (e != cudaSuccess) return e;
   dim3 grid(kResident ? 1 : (d.tokens + QM - 1) / QM, bh);
   attention_tc_kernel<NB, SMODE, kResident><<<grid, kAtLaunch, kDyn, st>>>(d);
   return cudaGetLastError();

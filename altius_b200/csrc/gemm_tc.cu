@@ -1062,13 +1062,8 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
                       const TcEpilogue& ep, const TcPlan& pl, int b_batched, float* workspace, int* err,
                       cudaStream_t st) {
   using L = TcSmem<BN, MT, MODE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         L::kDynBytes);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static unsigned long long attr_done = 0;
+  if (cudaError_t e0 = ensure_dynamic_smem(gemm_tc_kernel<BN, MT, MODE>, L::kDynBytes, &attr_done)) return e0;
   gemm_tc_kernel<BN, MT, MODE><<<pl.grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, pl.sc, b_batched, pl.tiles_m,
                                                                     pl.tiles_n, workspace, err);
   cudaError_t e = cudaGetLastError();
@@ -1084,13 +1079,8 @@ template <int BN>
 cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap& mb, const CUtensorMap& mbl,
                         const TcEpilogue& ep, const TcPlan& pl, float* workspace, int* err, cudaStream_t st) {
   using L = PairSmem<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         L::kDynBytes);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
+  static unsigned long long attr_done = 0;
+  if (cudaError_t e0 = ensure_dynamic_smem(gemm_tc_pair_kernel<BN>, L::kDynBytes, &attr_done)) return e0;
   // pl.grid counts pairs; the cluster shape (2, 1, 1) is a compile-time attribute of the kernel.
   gemm_tc_pair_kernel<BN><<<2 * pl.grid, kThreads, L::kDynBytes, st>>>(a, lda, k, mb, mbl, ep, pl.sc, pl.tiles_m,
                                                                      pl.tiles_n, workspace, err);

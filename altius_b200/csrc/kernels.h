@@ -9,6 +9,21 @@ namespace ac {
 
 constexpr int kMaxRank = 8;
 
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs to
+// the device the call is made on; sessions on several devices may share one process).
+// `done` is the caller's per-kernel record, one bit per device ordinal.
+template <typename Kernel>
+cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, unsigned long long* done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (*done & bit) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) *done |= bit;
+  return e;
+}
+
 // ---- elementwise -----------------------------------------------------------
 enum BinOp { BIN_ADD = 0, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW };
 

@@ -110,3 +110,21 @@ def test_run_batches_equals_run_per_batch(cuda_lib):
         assert sess.run_batches([]) == []
     finally:
         sess.close()
+
+
+def test_sessions_on_two_devices_in_one_process(cuda_lib):
+    """Kernel attributes (dynamic shared memory limits) belong to a device: a second session
+    on another GPU of the same process must set them again."""
+    from altius_b200 import session
+    if session.load_library().altius_cuda_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    model, feeds = configs.vit_base_16(batch=2, depth=2)
+    x = next(iter(feeds.values()))
+    outs = []
+    for dev in (0, 1):
+        sess = CudaSessionBuilder(model).with_device(dev).build()
+        try:
+            outs.append(sess.run([x])[0].copy())
+        finally:
+            sess.close()
+    assert_bit_exact(outs[0], outs[1])
