@@ -58,7 +58,9 @@ constexpr int BK16 = 32;                     // floats of K per stage in the fp1
 constexpr int kSplitGroups = 2;                 // groups of 4 warps taking alternate stages
 constexpr int kSplitWarps = 4 * kSplitGroups;
 constexpr int kSplitThreads = 128;             // threads working on one stage
-constexpr int kThreads = (kSplitWarps + 6) * 32;   // + 4 epilogue warps, TMA warp, MMA warp
+constexpr int kEpiWarps = 8;                   // two per tensor-memory lane quarter, half of the columns each
+constexpr int kTmaWarp = kSplitWarps + kEpiWarps, kMmaWarp = kTmaWarp + 1;
+constexpr int kThreads = (kSplitWarps + kEpiWarps + 2) * 32;
 
 // TC_F16X3: operands split into fp16 hi + fp16 (remainder * 2^11); hi*hi goes to one
 // accumulator, the two cross terms (scaled by 2^11) to a second one.
@@ -116,7 +118,7 @@ __device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32]) {
 // keeps both the row-wise writes and the transposed reads free of bank conflicts.
 template <int BN, int D2OFF>
 __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
-                                              int warp, int lane, int m0, int n0, int bz) {
+                                              int warp, int lane, int m0, int n0, int bz, int cc0, int cc1) {
       float* c = ep.c + (long long)bz * ep.sc;
       const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
       const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
@@ -127,7 +129,7 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
       const int c4 = lane & 7;             // float4 column within the 32-column chunk
       const int rsub = lane >> 3;          // row within a group of 4
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
+      for (int cc = cc0; cc < cc1; ++cc) {
         const int col0 = n0 + cc * 32;
         if (col0 >= ep.n) break;           // uniform across the warp
         uint32_t v[32];
@@ -212,13 +214,13 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
 // compile time and the eight rows of a chunk processed as independent streams.
 template <int BN, int D2OFF, int ACT, bool HAS_BIAS, bool HAS_RES>
 __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
-                                              int warp, int lane, int m0, int n0, int bz) {
+                                              int warp, int lane, int m0, int n0, int bz, int cc0, int cc1) {
   float* c = ep.c + (long long)bz * ep.sc;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
   const int c4 = lane & 7, rsub = lane >> 3;
   const int row_base = m0 + warp * 32 + rsub;
 #pragma unroll 1
-  for (int cc = 0; cc < BN / 32; ++cc) {
+  for (int cc = cc0; cc < cc1; ++cc) {
     const int col0 = n0 + cc * 32;
     if (col0 >= ep.n) break;
     uint32_t v[32];
@@ -271,10 +273,10 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
 // as the real epilogues so that the stores are full lines.
 template <int BN, int D2OFF>
 __device__ __forceinline__ void epilogue_raw(float* ws_tile, float4* stage, uint32_t tmem_base, int warp,
-                                             int lane) {
+                                             int lane, int cc0, int cc1) {
   const int c4 = lane & 7, rsub = lane >> 3;
 #pragma unroll 1
-  for (int cc = 0; cc < BN / 32; ++cc) {
+  for (int cc = cc0; cc < cc1; ++cc) {
     uint32_t v[32];
     load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
     __syncwarp();
@@ -370,7 +372,7 @@ struct TcSmem {
   static_assert(!kF16 || kARaw == 2 * kABytes, "the fp16 tiles replace the fp32 rows in place");
   static constexpr int kTxBytes = (kF16 ? kARaw : kABytes) + kBBytes + ((kF16 || MODE == TC_3X_BLO_TMA) ? kBBytes : 0);
   static constexpr int kStages = (200 * 1024) / kStageBytes;      // TF32 and fp16: 4 / 6 / 8 (BN 256 / 128 / 64)
-  static constexpr int kEpiBytes = 4 * 4096;                      // one 4 KB transpose tile per epilogue warp
+  static constexpr int kEpiBytes = kEpiWarps * 4096;              // one 4 KB transpose tile per epilogue warp
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   static constexpr int kAccCols = (kF16 ? 2 : 1) * MT * BN;       // tensor-memory columns of one accumulator set
   static constexpr int kNumAcc = (2 * kAccCols <= 512) ? 2 : 1;   // sets: two when they fit (epilogue overlaps)
@@ -457,12 +459,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);     // one arrival per epilogue warp
+      mbar_init(&acc_empty[i], kEpiWarps);   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kSplitWarps + 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(kTmemCols));
@@ -473,7 +475,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == kSplitWarps + 4) {
+  if (warp == kTmaWarp) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const uint32_t bytes = L::kTxBytes;
@@ -496,7 +498,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
       }
     }
-  } else if (warp == kSplitWarps + 5) {
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       // Instruction descriptor: fp32 accumulator, A and B both TF32 (format 2) or both
@@ -620,9 +622,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       if (MODE == TC_F16X3 && range_bad) atomicCAS(err, 0, kRangeCode);
     }
   } else {
-    // ---------------- epilogue (warps 4-7) ----------------
-    const int q = warp - kSplitWarps;   // TMEM lane quarter (kSplitWarps is a multiple of 4)
-    float4* stage = reinterpret_cast<float4*>(epi_smem + q * 4096);
+    // ---------------- epilogue ----------------
+    const int e = warp - kSplitWarps, q = e & 3;   // TMEM lane quarter (kSplitWarps is a multiple of 4)
+    const int cc0 = (e >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // this warp's 32-column chunks
+    float4* stage = reinterpret_cast<float4*>(epi_smem + e * 4096);
     const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
                         ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
@@ -644,16 +647,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int m0 = (tm * MT + mt) * BM, n0 = tn * BN;
       if (m0 >= ep.m) break;                     // uniform: the second sub-tile may lie past M
       if (wk.raw >= 0) {
-        epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane);
+        epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane, cc0, cc1);
       } else
       switch (key) {
-        case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz); break;
-        default: epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz); break;
+        case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        default: epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
       }
       }
       // Every tcgen05.ld of this warp has completed (each is followed by
@@ -667,7 +670,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag != 0 && warp == kSplitWarps + 4 && lane == 0) {
+  if (*abort_flag != 0 && warp == kTmaWarp && lane == 0) {
     // Give copies that may still be in flight a bounded time to land before the
     // shared memory is released.
     for (int s = 0; s < S; ++s) {
@@ -676,7 +679,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
   }
   __syncthreads();
-  if (warp == kSplitWarps + 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
   }
@@ -721,7 +724,7 @@ struct PairSmem {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   static constexpr int kTxBytes = 2 * kBBytes;          // TMA brings B only; A goes global -> registers -> tiles
   static constexpr int kStages = (200 * 1024) / kStageBytes;   // 6 at BN 256
-  static constexpr int kEpiBytes = 4 * 4096;
+  static constexpr int kEpiBytes = kEpiWarps * 4096;
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;              // D1 and D2, one accumulator set
   static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
@@ -765,11 +768,11 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 8);             // one arrival per epilogue warp of the pair
+    mbar_init(acc_empty, 2 * kEpiWarps); // one arrival per epilogue warp of the pair
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kSplitWarps + 5) {         // the same warp in both CTAs, the same shared-memory slot
+  if (warp == kMmaWarp) {         // the same warp in both CTAs, the same shared-memory slot
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"((uint32_t)L::kTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
@@ -779,7 +782,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == kSplitWarps + 4) {
+  if (warp == kTmaWarp) {
     // ---------------- TMA producer (each CTA for itself) ----------------
     if (lane == 0) {
       int it = 0;
@@ -797,7 +800,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         }
       }
     }
-  } else if (warp == kSplitWarps + 5) {
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer (leader only) ----------------
     if (leader && lane == 0) {
       // fp32 accumulators, fp16 A and B (format 0), both K-major, N = BN, M = 256 over the pair.
@@ -890,8 +893,9 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     if (range_bad) atomicCAS(err, 0, kRangeCode);
   } else {
     // ---------------- epilogue (each CTA its own 128 rows) ----------------
-    const int q = warp - kSplitWarps;
-    float4* stage = reinterpret_cast<float4*>(epi_smem + q * 4096);
+    const int e = warp - kSplitWarps, q = e & 3;
+    const int cc0 = (e >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // this warp's 32-column chunks
+    float4* stage = reinterpret_cast<float4*>(epi_smem + e * 4096);
     const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
     const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
@@ -910,16 +914,16 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
       if (m0 < ep.m) {
         if (wk.raw >= 0) {
-          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane);
+          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane, cc0, cc1);
         } else
         switch (key) {
-          case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
-          case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
-          case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
-          case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
-          case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
-          case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
-          default: epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz); break;
+          case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          default: epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
         }
       }
       tc_fence_before();
@@ -931,14 +935,14 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag != 0 && warp == kSplitWarps + 4 && lane == 0) {
+  if (*abort_flag != 0 && warp == kTmaWarp && lane == 0) {
     for (int s = 0; s < S; ++s) {        // copies that may still be in flight: a bounded time to land
       (void)mbar_wait(&full[s], 0);
       (void)mbar_wait(&full[s], 1);
     }
   }
   cluster_sync_all();                    // no CTA leaves while its peer may still signal it or read its B half
-  if (warp == kSplitWarps + 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)L::kTmemCols));
   }

@@ -212,6 +212,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemm-mode", type=int, default=0)
+    ap.add_argument("--gemm-pairs", action="store_true", help="fp16-split GEMMs on clusters of two CTAs")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-micrograph", action="store_true")
     args = ap.parse_args()
@@ -241,7 +242,7 @@ def main():
 
     # Every rank builds the same graph; rank 0's weights are broadcast once.
     model, _ = configs.vit_base_16(batch=PER_GPU_BATCH, seed=0)
-    builder = CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode)
+    builder = CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode).with_gemm_pairs(args.gemm_pairs)
     blob = None
     if distributed:
         blob, ptrs = replicas.broadcast_weights(model, dev, src=0)
@@ -321,7 +322,7 @@ def main():
         return
 
     # ---- per-kernel profile of the same workload (rank 0) ---------------------------
-    prof_sess = (CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode)
+    prof_sess = (CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode).with_gemm_pairs(args.gemm_pairs)
                  .with_profiling_enabled(True).build())
     for it in range(6):
         if it == 2:
