@@ -255,7 +255,10 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
         x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
         x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
       }
-      if (ACT != ACT_NONE) {
+      if (ACT == ACT_GELU) {
+        const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
+        x = make_float4(lo.x, lo.y, hi.x, hi.y);
+      } else if (ACT != ACT_NONE) {
         x.x = apply_act(ACT, x.x, 0.f, 0.f); x.y = apply_act(ACT, x.y, 0.f, 0.f);
         x.z = apply_act(ACT, x.z, 0.f, 0.f); x.w = apply_act(ACT, x.w, 0.f, 0.f);
       }

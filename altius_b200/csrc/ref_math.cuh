@@ -42,6 +42,47 @@ __device__ __forceinline__ float gelu_ref(float x) {
   return __fmul_rn(__fadd_rn(t, 1.f), __fmul_rn(x, 0.5f));
 }
 
+// `gelu_ref` on two elements at a time with the packed fp32 instructions of
+// sm_100 (one issue slot per pair). Every packed operation rounds each half
+// exactly as its scalar counterpart. The quotient p / q uses the reciprocal
+// estimate and two FMA refinements: for q in [4.8e-3, 1.5] (the range of the
+// denominator polynomial) and |p| above 2^-40 that sequence returns the
+// correctly rounded quotient; a smaller |p| gives |t| < 2^-30, which the
+// following t + 1 rounds away, so the result equals `gelu_ref` bit for bit.
+__device__ __forceinline__ float2 gelu_ref2(float2 x) {
+  const float2 kB = make_float2(0.7978845608028654f, 0.7978845608028654f);
+  const float2 kC = make_float2(0.035677408136300125f, 0.035677408136300125f);
+  const float2 one = make_float2(1.f, 1.f), half = make_float2(0.5f, 0.5f);
+#define AC_F2(c) make_float2(c, c)
+  // The sum is written as fma(., 1, B): a packed multiply feeding a packed add was seen to be
+  // contracted into one fused operation, which rounds differently from the reference.
+  float2 v = __fmul2_rn(x, __ffma2_rn(__fmul2_rn(__fmul2_rn(kC, x), x), one, kB));
+  v.x = clampf_rust(v.x, -9.f, 9.f);
+  v.y = clampf_rust(v.y, -9.f, 9.f);
+  const float2 s = __fmul2_rn(v, v);
+  float2 p = __ffma2_rn(s, AC_F2(-2.76076847742355e-16f), AC_F2(2.00018790482477e-13f));
+  p = __ffma2_rn(p, s, AC_F2(-8.60467152213735e-11f));
+  p = __ffma2_rn(p, s, AC_F2(5.12229709037114e-08f));
+  p = __ffma2_rn(p, s, AC_F2(1.48572235717979e-05f));
+  p = __ffma2_rn(p, s, AC_F2(6.37261928875436e-04f));
+  p = __ffma2_rn(p, s, AC_F2(4.89352455891786e-03f));
+  p = __fmul2_rn(p, v);
+  float2 q = __ffma2_rn(s, AC_F2(1.19825839466702e-06f), AC_F2(1.18534705686654e-04f));
+  q = __ffma2_rn(q, s, AC_F2(2.26843463243900e-03f));
+  q = __ffma2_rn(q, s, AC_F2(4.89352518554385e-03f));
+#undef AC_F2
+  float2 r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(q.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(q.y));
+  const float2 nq = make_float2(-q.x, -q.y);
+  const float2 e = __ffma2_rn(nq, r, one);
+  r = __ffma2_rn(r, e, r);
+  float2 t = __fmul2_rn(p, r);
+  t = __ffma2_rn(__ffma2_rn(nq, t, p), r, t);
+  t = __ffma2_rn(__ffma2_rn(nq, t, p), r, t);
+  return __fmul2_rn(__fadd2_rn(t, one), __fmul2_rn(x, half));
+}
+
 // crates/session_interpreter/src/session.rs:840-903 `tanh`
 __device__ __forceinline__ float tanh_ref(float x) { return tanh_rational(clampf_rust(x, -9.f, 9.f)); }
 

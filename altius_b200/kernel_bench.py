@@ -1,6 +1,6 @@
 """Per-kernel microbenchmarks through the session's C ABI.
 
-    python -m altius_b200.kernel_bench gemm 6304 768 2304 [--mode 0|1|2] [--iters 10]
+    python -m altius_b200.kernel_bench gemm 6304 768 2304 [--mode 0|1|2] [--iters 10] [--bias] [--gelu] [--residual]
     python -m altius_b200.kernel_bench micrograph [--batch 64] [--no-fuse]
     python -m altius_b200.kernel_bench attention 32 197 12     # batch, tokens, heads (head dim 64)
 
@@ -53,6 +53,9 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--pairs", action="store_true", help="fp16-split GEMM on clusters of two CTAs")
+    ap.add_argument("--bias", action="store_true", help="gemm: + bias[n] in the epilogue")
+    ap.add_argument("--gelu", action="store_true", help="gemm: Gelu after the bias")
+    ap.add_argument("--residual", action="store_true", help="gemm: + residual[m, n] in the epilogue")
     ap.add_argument("--cold-l2", action="store_true", help="sweep L2 before every kernel (micrograph)")
     a = ap.parse_args(argv)
     rng = np.random.default_rng(0)
@@ -63,8 +66,17 @@ def main(argv=None):
         g = ir.Graph()
         xi = g.add_input("x", x.shape)
         out = g.op("MatMul", xi, g.new_init(w))
+        feeds = [x]
+        if a.bias or a.gelu:
+            out = g.op("Add", out, g.new_init((0.1 * rng.standard_normal(n)).astype(np.float32)))
+        if a.gelu:
+            out = g.op("Gelu", out)
+        if a.residual:
+            r = rng.standard_normal((m, n)).astype(np.float32)
+            out = g.op("Add", g.add_input("r", r.shape), out)
+            feeds.append(r)
         g.outputs.append(out)
-        rows = _run(ir.Model(g, 13), [x], a.mode, True, a.iters, pairs=a.pairs)
+        rows = _run(ir.Model(g, 13), feeds, a.mode, True, a.iters, pairs=a.pairs)
     elif a.what == "attention":
         B, T, H = a.dims
         hd, D = 64, 64 * H

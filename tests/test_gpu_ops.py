@@ -403,6 +403,25 @@ def test_linear_gelu_residual_epilogue(cuda_lib):
         assert (np.abs(got[0] - want[0]) <= 1e-5 * np.abs(want[0]) + bound).all()
 
 
+def test_gelu_in_the_gemm_epilogue_equals_the_gelu_kernel_bit_for_bit(cuda_lib):
+    # The epilogue evaluates Gelu on pairs with packed fp32 instructions and its own
+    # division sequence; the stand-alone kernel uses the scalar formulas. Same MatMul
+    # kernel in both sessions, so any difference comes from the activation.
+    x = RNG.standard_normal((1024, 64)).astype(np.float32)
+    x *= np.exp2(RNG.integers(-30, 4, size=(1024, 1))).astype(np.float32)   # pre-activations from 1e-9 to 100
+    w = (0.3 * RNG.standard_normal((64, 512))).astype(np.float32)
+    b = np.zeros(512, np.float32)
+
+    def build(g):
+        h = g.op("MatMul", g.add_input("x", x.shape), g.new_init(w))
+        return [g.op("Gelu", g.op("Add", h, g.new_init(b)))]
+    m = _chain_model(build)
+    fused = run_cuda(m, [x], gemm_mode=0)[0]
+    plain = run_cuda(m, [x], gemm_mode=0, fuse=False)[0]
+    assert np.abs(plain).max() > 50 and (np.abs(plain) < 1e-6).any()
+    assert_bit_exact(fused, plain)
+
+
 def test_gemm_transb_constant_weight(cuda_lib):
     a = RNG.standard_normal((300, 1280)).astype(np.float32)
     w = (0.02 * RNG.standard_normal((1000, 1280))).astype(np.float32)
