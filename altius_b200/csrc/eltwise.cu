@@ -174,9 +174,14 @@ __global__ void __launch_bounds__(kThreads) unary_vec4(const float4* __restrict_
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int64_t idx = base + (int64_t)i * kThreads;
-    if (idx < nvec)
+    if (idx >= nvec) continue;
+    if (OP == UN_GELU) {   // two elements per instruction; same bits as gelu_ref
+      const float2 lo = gelu_ref2(make_float2(v[i].x, v[i].y)), hi = gelu_ref2(make_float2(v[i].z, v[i].w));
+      o[idx] = make_float4(lo.x, lo.y, hi.x, hi.y);
+    } else {
       o[idx] = make_float4(un_apply<OP>(v[i].x, alpha, beta), un_apply<OP>(v[i].y, alpha, beta),
                            un_apply<OP>(v[i].z, alpha, beta), un_apply<OP>(v[i].w, alpha, beta));
+    }
   }
 }
 

@@ -205,8 +205,9 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
             v[i].z = __fadd_rn(v[i].z, bv.z); v[i].w = __fadd_rn(v[i].w, bv.w);
           }
           if (GELU) {
-            v[i].x = gelu_ref(v[i].x); v[i].y = gelu_ref(v[i].y);
-            v[i].z = gelu_ref(v[i].z); v[i].w = gelu_ref(v[i].w);
+            const float2 lo = gelu_ref2(make_float2(v[i].x, v[i].y));
+            const float2 hi = gelu_ref2(make_float2(v[i].z, v[i].w));
+            v[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
           }
           if (p.residual) {
             v[i].x = __fadd_rn(v[i].x, r[i].x); v[i].y = __fadd_rn(v[i].y, r[i].y);
