@@ -212,9 +212,16 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
 // Same data path for the common epilogues (alpha 1, no C input, no row bias,
 // everything 16-byte aligned, N a multiple of 4), with the options fixed at
 // compile time and the eight rows of a chunk processed as independent streams.
-template <int BN, int D2OFF, int ACT, bool HAS_BIAS, bool HAS_RES>
-__device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
-                                              int warp, int lane, int m0, int n0, int bz, int cc0, int cc1) {
+//
+// `release()` hands the accumulator back to the MMA warp. It is called as soon as the
+// warp's last chunk has left tensor memory, before that chunk's arithmetic and stores;
+// it returns whether it did so, and so does this function (no chunk in range, or a
+// sub-tile that is not the last: the caller releases).
+template <int BN, int D2OFF, int ACT, bool HAS_BIAS, bool HAS_RES, typename Release>
+__device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
+                                              int warp, int lane, int m0, int n0, int bz, int cc0, int cc1,
+                                              Release&& release) {
+  bool released = false;
   float* c = ep.c + (long long)bz * ep.sc;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
   const int c4 = lane & 7, rsub = lane >> 3;
@@ -225,6 +232,7 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
     if (col0 >= ep.n) break;
     uint32_t v[32];
     load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    if (cc + 1 == cc1 || col0 + 32 >= ep.n) released = release();   // uniform across the warp
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -270,6 +278,7 @@ __device__ __forceinline__ void epilogue_fast(const TcEpilogue& ep, float4* stag
       if (col_ok && row < ep.m) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
     }
   }
+  return released;
 }
 
 // Unreduced accumulator of a K-slice -> workspace tile [128][BN], same staging
@@ -644,8 +653,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int ab = ti % NACC;
       if (!mbar_wait(&acc_full[ab], (ti / NACC) & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
       tc_fence_after();
+      // Every tcgen05.ld of this warp has completed (each is followed by wait::ld) when the
+      // accumulator is handed back to the MMA warp.
+      int mt = 0;
+      bool released = false;
+      auto do_release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      };
+      auto release = [&]() -> bool {
+        if (mt != MT - 1) return false;
+        do_release();
+        return true;
+      };
 #pragma unroll 1
-      for (int mt = 0; mt < MT; ++mt) {
+      for (mt = 0; mt < MT; ++mt) {
       const uint32_t acc = tmem_base + (uint32_t)(ab * L::kAccCols + mt * BN);
       const int m0 = (tm * MT + mt) * BM, n0 = tn * BN;
       if (m0 >= ep.m) break;                     // uniform: the second sub-tile may lie past M
@@ -653,20 +676,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane, cc0, cc1);
       } else
       switch (key) {
-        case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
-        case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
-        case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
-        case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
-        case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
-        case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
+        case 0: released = epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 1: released = epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 2: released = epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 3: released = epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
         default: epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
       }
       }
-      // Every tcgen05.ld of this warp has completed (each is followed by
-      // wait::ld): hand the accumulator back to the MMA warp.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      if (!released) do_release();
     }
   }
 
@@ -915,23 +934,28 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       if (!mbar_wait(acc_full, ti & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
       tc_fence_after();
       const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+      bool released = false;
+      auto release = [&]() -> bool {     // all of this warp's tcgen05.ld have completed
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+        return true;
+      };
       if (m0 < ep.m) {
         if (wk.raw >= 0) {
           epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane, cc0, cc1);
         } else
         switch (key) {
-          case 0: epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
-          case 1: epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
-          case 2: epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
-          case 3: epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
-          case (ACT_GELU << 2) | 1: epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
-          case (ACT_RELU << 2) | 1: epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case 0: released = epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 1: released = epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 2: released = epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 3: released = epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
           default: epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      if (!released) release();
     }
   }
 
