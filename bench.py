@@ -349,7 +349,7 @@ def main():
                     # QKV shape (M 6304, K 768, N 2304; algorithmic operand + result bytes 84.6 MB, of
                     # which A, B and most of C stay in L2), from the ncu capture summarised in
                     # profiles/gemm_f16x3_6304x768x2304.md
-                    "traffic": 46552320 if f16 else None,
+                    "traffic": 50155264 if f16 else None,
                     "tensor_pipe_frac": round(3.0 * achieved / peak, 4),
                     "peak_note": f"{peaks['source']} sustained bf16 cuBLAS TFLOP/s"
                                  + ("" if f16 else " / 2 (no TF32 peak is measured)")
