@@ -3,6 +3,10 @@
 //
 //   C[b] = epilogue( A[b] (M x K, K contiguous) * B[b]^T (B stored N x K, K contiguous) )
 //
+// B may also be given K x N (N contiguous: a convolution's input planes or column buffer with
+// the filter matrix as A, the value operand of a batched product): its tiles are then MN-major
+// in shared memory (3xTF32 only). Either operand may be shared by the whole batch (stride 0).
+//
 // It replaces the cblas_sgemm the reference calls for MatMul / Gemm / Conv2d
 // (crates/session_interpreter/src/gemm.rs:36-51, session.rs:621-794,
 // conv2d.rs:145-209). Two ways of getting fp32-level products out of narrow MMAs:
@@ -19,7 +23,7 @@
 //            repeats the run on the 3xTF32 path).
 //
 // Persistent CTAs (one per SM) walk the 128 x BN output tiles:
-//   warp 12     TMA producer: one elected thread issues cp.async.bulk.tensor loads (boxes of
+//   warp 16     TMA producer: one elected thread issues cp.async.bulk.tensor loads (boxes of
 //               64-byte rows, 64-byte swizzle; the fp32 rows of A in the fp16 mode: 128-byte
 //               rows, no swizzle) into a ring of stages, completion on an mbarrier per stage;
 //   warps 0-7   splitters (two groups on alternate stages). TF32: rewrite the A tile as x_hi
@@ -27,9 +31,10 @@
 //               constant whose split was prepared at load time and arrives by TMA). fp16: read
 //               the fp32 rows of A into registers, meet at a named barrier, write the fp16
 //               hi / lo tiles over them;
-//   warp 13     one thread issues the tcgen05.mma stream and tcgen05.commit into an
+//   warp 17     one thread issues the tcgen05.mma stream and tcgen05.commit into an
 //               accumulator set in tensor memory (two sets when they fit 512 columns);
-//   warps 8-11  epilogue of the other set: tcgen05.ld, a shared-memory transpose to
+//   warps 8-15  epilogue of the other set (two warps per tensor-memory lane quarter, half of
+//               the tile's columns each): tcgen05.ld, a shared-memory transpose to
 //               row-contiguous float4s, bias / activation / residual, full-line global stores.
 // Tiles beyond the last whole round of the grid are cut along K into slices (one per
 // otherwise idle SM) whose unreduced accumulators go to a workspace; a small second kernel
@@ -64,7 +69,11 @@ constexpr int kThreads = (kSplitWarps + kEpiWarps + 2) * 32;
 
 // TC_F16X3: operands split into fp16 hi + fp16 (remainder * 2^11); hi*hi goes to one
 // accumulator, the two cross terms (scaled by 2^11) to a second one.
-enum TcMode { TC_3X_BLO_TMA = 0, TC_3X_SPLIT_B = 1, TC_1X = 2, TC_F16X3 = 3 };
+// TC_3X_SPLIT_B_MN: as TC_3X_SPLIT_B with B given [K, N] (N contiguous), the form of a
+// convolution's input and of the value operand of an attention product: its tiles are
+// MN-major in shared memory (32 columns x 16 k-rows per TMA box, 128-byte swizzle with
+// 32-byte atoms).
+enum TcMode { TC_3X_BLO_TMA = 0, TC_3X_SPLIT_B = 1, TC_1X = 2, TC_F16X3 = 3, TC_3X_SPLIT_B_MN = 4 };
 
 struct TcEpilogue {
   int m, n;
@@ -86,6 +95,22 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   d |= (uint64_t)((8 * 64) >> 4) << 32;          // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                        // descriptor version for this architecture
   d |= (uint64_t)4 << 61;                        // 64-byte swizzle
+  return d;
+}
+
+// Descriptor of an MN-major tile of 4-byte elements. The one layout the tensor core accepts
+// for them is the 128-byte swizzle with 32-byte atoms: 32 columns (128 bytes) x 4 k-rows form
+// a 512-byte atom in which the 32-byte quarter of a row is XORed with the row index; the
+// next 4 k-rows of the same columns follow at the stride byte offset (512 bytes), the next 32
+// columns `col_group_bytes` further on (the leading byte offset). TMA writes exactly this with
+// CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B and a box of 32 columns x any number of k-rows.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t saddr, uint32_t col_group_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((col_group_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;                        // 128-byte swizzle, 32-byte atoms
   return d;
 }
 
@@ -209,15 +234,16 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
       }
     }
 
-// Same data path for the common epilogues (alpha 1, no C input, no row bias,
+// Same data path for the common epilogues (alpha 1, no C input, one kind of bias,
 // everything 16-byte aligned, N a multiple of 4), with the options fixed at
 // compile time and the eight rows of a chunk processed as independent streams.
+// BIAS: 0 none, 1 per column (MatMul + Add), 2 per row (a convolution's channels).
 //
 // `release()` hands the accumulator back to the MMA warp. It is called as soon as the
 // warp's last chunk has left tensor memory, before that chunk's arithmetic and stores;
 // it returns whether it did so, and so does this function (no chunk in range, or a
 // sub-tile that is not the last: the caller releases).
-template <int BN, int D2OFF, int ACT, bool HAS_BIAS, bool HAS_RES, typename Release>
+template <int BN, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
 __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
                                               int warp, int lane, int m0, int n0, int bz, int cc0, int cc1,
                                               Release&& release) {
@@ -226,6 +252,11 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
   const int c4 = lane & 7, rsub = lane >> 3;
   const int row_base = m0 + warp * 32 + rsub;
+  float bm[8];
+  if (BIAS == 2) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bm[i] = row_base + 4 * i < ep.m ? __ldg(ep.bias_m + row_base + 4 * i) : 0.f;
+  }
 #pragma unroll 1
   for (int cc = cc0; cc < cc1; ++cc) {
     const int col0 = n0 + cc * 32;
@@ -243,7 +274,7 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
     const int col = col0 + 4 * c4;
     const bool col_ok = col < ep.n;   // n % 4 == 0: the whole float4 is in range
     float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (HAS_BIAS && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+    if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
     float4 a[8], r[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -259,16 +290,21 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       float4 x = a[i];
-      if (HAS_BIAS) {
+      if (BIAS == 1) {
         x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
         x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
+      }
+      if (BIAS == 2) {
+        x.x = __fadd_rn(x.x, bm[i]); x.y = __fadd_rn(x.y, bm[i]);
+        x.z = __fadd_rn(x.z, bm[i]); x.w = __fadd_rn(x.w, bm[i]);
       }
       if (ACT == ACT_GELU) {
         const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
         x = make_float4(lo.x, lo.y, hi.x, hi.y);
       } else if (ACT != ACT_NONE) {
-        x.x = apply_act(ACT, x.x, 0.f, 0.f); x.y = apply_act(ACT, x.y, 0.f, 0.f);
-        x.z = apply_act(ACT, x.z, 0.f, 0.f); x.w = apply_act(ACT, x.w, 0.f, 0.f);
+        const float al = ep.act_alpha, be = ep.act_beta;   // HardSigmoid / HardSwish coefficients
+        x.x = apply_act(ACT, x.x, al, be); x.y = apply_act(ACT, x.y, al, be);
+        x.z = apply_act(ACT, x.z, al, be); x.w = apply_act(ACT, x.w, al, be);
       }
       if (HAS_RES) {
         x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
@@ -429,15 +465,16 @@ __device__ __forceinline__ bool tc_get_work(const TcSched& sc, int w, TcWork* ou
 // epilogue of one tile overlaps the main loop of the next.
 //   warps 0-7   splitters, two groups of four taking alternate K-blocks (hi/lo of the
 //               A tile, and of B unless it arrives split)
-//   warps 8-11  epilogue (warp w owns TMEM lanes 32*(w-8) .. +31)
-//   warp  12    TMA producer (one thread)
-//   warp  13    MMA issuer (one thread); allocates and frees tensor memory
+//   warps 8-15  epilogue (warp w owns TMEM lanes 32*((w-8) % 4) .. +31 and half of the columns)
+//   warp  16    TMA producer (one thread)
+//   warp  17    MMA issuer (one thread); allocates and frees tensor memory
 template <int BN, int MT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-               const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, TcSched sc, int b_batched,
-               int tiles_m, int tiles_n, float* workspace, int* err) {
+               const __grid_constant__ CUtensorMap tm_blo, TcEpilogue ep, TcSched sc, int a_batched,
+               int b_batched, int tiles_m, int tiles_n, float* workspace, int* err) {
   using L = TcSmem<BN, MT, MODE>;
+  constexpr bool kBMN = MODE == TC_3X_SPLIT_B_MN;
   constexpr int S = L::kStages;
   constexpr int NACC = L::kNumAcc;      // accumulator sets in tensor memory
   constexpr int KB = L::kKb;            // floats of K per stage
@@ -497,13 +534,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w) {
         const int t = wk.tile;
         const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
-        const int bzb = b_batched ? bz : 0;
+        const int bzb = b_batched ? bz : 0, bza = a_batched ? bz : 0;
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
           mbar_arrive_expect_tx(&full[s], bytes);
-          tma_load_3d(a_raw(s), &tm_a, &full[s], kb * KB, tm * (MT * BM), bz);   // TF32 modes: a_raw == a_hi
+          tma_load_3d(a_raw(s), &tm_a, &full[s], kb * KB, tm * (MT * BM), bza);   // TF32 modes: a_raw == a_hi
+          if (kBMN) {
+            // [K, N] operand: one box per 32 columns (128 bytes) x KB k-rows.
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j)
+              tma_load_3d(b_hi(s) + j * (KB * 128), &tm_b, &full[s], tn * BN + 32 * j, kb * KB, bzb);
+          } else
           tma_load_3d(b_hi(s), &tm_b, &full[s], kb * KB, tn * BN, bzb);
           if (MODE == TC_3X_BLO_TMA || MODE == TC_F16X3)
             tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * KB, tn * BN, bzb);
@@ -516,8 +559,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       // Instruction descriptor: fp32 accumulator, A and B both TF32 (format 2) or both
       // fp16 (format 0), both K-major, N = BN, M = 128.
       constexpr uint32_t kFmt = MODE == TC_F16X3 ? 0u : 2u;
-      const uint32_t idesc = (1u << 4) | (kFmt << 7) | (kFmt << 10) | ((uint32_t)(BN >> 3) << 17) |
-                             ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (kFmt << 7) | (kFmt << 10) | (kBMN ? 1u << 16 : 0u) |   // bit 16: B MN-major
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       int it = 0, ti = 0;
       bool ok = true;
       TcWork wk;
@@ -533,11 +576,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           ok = mbar_wait(MODE == TC_1X ? &full[s] : &ready[s], ph);
           if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
           tc_fence_after();
-          const uint64_t db = make_smem_desc(smem_u32(b_hi(s)));
-          const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)));
+          const uint64_t db = kBMN ? make_smem_desc_mn(smem_u32(b_hi(s)), KB * 128) : make_smem_desc(smem_u32(b_hi(s)));
+          const uint64_t dbl = kBMN ? make_smem_desc_mn(smem_u32(b_lo(s)), KB * 128) : make_smem_desc(smem_u32(b_lo(s)));
 #pragma unroll
           for (int kk = 0; kk < 2; ++kk) {                  // two K-steps per 64-byte row
             const uint64_t off = (uint64_t)(kk * 32 >> 4);  // 8 floats or 16 halves = 32 bytes along K
+            // MN-major B: the second group of 8 k-rows (two atoms of 4) lies 1 KB further on.
+            const uint64_t boff = kBMN ? (uint64_t)(kk * 1024 >> 4) : off;
             const uint32_t acc = (kb > wk.k0 || kk > 0) ? 1u : 0u;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
@@ -545,15 +590,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
               const uint64_t dal = make_smem_desc(smem_u32(a_lo(s) + mt * (BM * 64)));
               const uint32_t d = d_tmem + (uint32_t)(mt * BN);
               if (MODE == TC_F16X3) {
-                tc_mma_f16(d, da + off, db + off, idesc, acc);            // a_hi * b_hi
-                tc_mma_f16(d + D2, dal + off, db + off, idesc, acc);      // a_lo' * b_hi  (scaled by 2^11)
-                tc_mma_f16(d + D2, da + off, dbl + off, idesc, 1u);       // a_hi * b_lo'
+                tc_mma_f16(d, da + off, db + boff, idesc, acc);            // a_hi * b_hi
+                tc_mma_f16(d + D2, dal + off, db + boff, idesc, acc);      // a_lo' * b_hi  (scaled by 2^11)
+                tc_mma_f16(d + D2, da + off, dbl + boff, idesc, 1u);       // a_hi * b_lo'
               } else if (MODE == TC_1X) {
-                tc_mma_tf32(d, da + off, db + off, idesc, acc);
+                tc_mma_tf32(d, da + off, db + boff, idesc, acc);
               } else {
-                tc_mma_tf32(d, dal + off, db + off, idesc, acc);   // a_lo * b_hi
-                tc_mma_tf32(d, da + off, dbl + off, idesc, 1u);    // a_hi * b_lo
-                tc_mma_tf32(d, da + off, db + off, idesc, 1u);     // a_hi * b_hi
+                tc_mma_tf32(d, dal + off, db + boff, idesc, acc);   // a_lo * b_hi
+                tc_mma_tf32(d, da + off, dbl + boff, idesc, 1u);    // a_hi * b_lo
+                tc_mma_tf32(d, da + off, db + boff, idesc, 1u);     // a_hi * b_hi
               }
             }
           }
@@ -614,7 +659,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             dst[i * kSplitThreads + t0] = lo;
           }
           }
-          if (MODE == TC_3X_SPLIT_B) {
+          if (MODE == TC_3X_SPLIT_B || MODE == TC_3X_SPLIT_B_MN) {   // elementwise: any tile layout
             float4* sb = reinterpret_cast<float4*>(b_hi(s));
             float4* dbp = reinterpret_cast<float4*>(b_lo(s));
 #pragma unroll
@@ -638,13 +683,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int e = warp - kSplitWarps, q = e & 3;   // TMEM lane quarter (kSplitWarps is a multiple of 4)
     const int cc0 = (e >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // this warp's 32-column chunks
     float4* stage = reinterpret_cast<float4*>(epi_smem + e * 4096);
-    const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
+    const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !(ep.bias_m && ep.bias_n) &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
                         ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
                         (!ep.res || ((ep.ldres % 4) == 0 && (ep.sres % 4) == 0 &&
                                      (reinterpret_cast<uintptr_t>(ep.res) & 15) == 0)) &&
                         (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
-    const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
+    const int key = !simple ? -1 : ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2) | (ep.bias_m ? 64 : 0));
     int ti = 0;
     TcWork wk;
     for (int w = 0; tc_get_work(sc, w, &wk); ++w, ++ti) {
@@ -676,12 +721,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane, cc0, cc1);
       } else
       switch (key) {
-        case 0: released = epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case 1: released = epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case 2: released = epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case 3: released = epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 0: released = epilogue_fast<BN, D2, ACT_NONE, 0, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 1: released = epilogue_fast<BN, D2, ACT_NONE, 1, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 2: released = epilogue_fast<BN, D2, ACT_NONE, 0, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 3: released = epilogue_fast<BN, D2, ACT_NONE, 1, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, 1, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, 1, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 64: released = epilogue_fast<BN, D2, ACT_NONE, 2, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 64 | 2: released = epilogue_fast<BN, D2, ACT_NONE, 2, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 64 | (ACT_RELU << 2): released = epilogue_fast<BN, D2, ACT_RELU, 2, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 64 | (ACT_HARDSWISH << 2): released = epilogue_fast<BN, D2, ACT_HARDSWISH, 2, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
         default: epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
       }
       }
@@ -919,13 +968,13 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     const int cc0 = (e >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // this warp's 32-column chunks
     float4* stage = reinterpret_cast<float4*>(epi_smem + e * 4096);
     const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
-    const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !ep.bias_m &&
+    const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !(ep.bias_m && ep.bias_n) &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
                         ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
                         (!ep.res || ((ep.ldres % 4) == 0 && (ep.sres % 4) == 0 &&
                                      (reinterpret_cast<uintptr_t>(ep.res) & 15) == 0)) &&
                         (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
-    const int key = simple ? ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2)) : -1;
+    const int key = !simple ? -1 : ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2) | (ep.bias_m ? 64 : 0));
     int ti = 0;
     TcWork wk;
     for (int w = 0; pair_get_work(sc, w, &wk); ++w, ++ti) {
@@ -946,12 +995,16 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane, cc0, cc1);
         } else
         switch (key) {
-          case 0: released = epilogue_fast<BN, D2, ACT_NONE, false, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 1: released = epilogue_fast<BN, D2, ACT_NONE, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 2: released = epilogue_fast<BN, D2, ACT_NONE, false, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 3: released = epilogue_fast<BN, D2, ACT_NONE, true, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, true, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 0: released = epilogue_fast<BN, D2, ACT_NONE, 0, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 1: released = epilogue_fast<BN, D2, ACT_NONE, 1, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 2: released = epilogue_fast<BN, D2, ACT_NONE, 0, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 3: released = epilogue_fast<BN, D2, ACT_NONE, 1, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, 1, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, 1, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 64: released = epilogue_fast<BN, D2, ACT_NONE, 2, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 64 | 2: released = epilogue_fast<BN, D2, ACT_NONE, 2, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 64 | (ACT_RELU << 2): released = epilogue_fast<BN, D2, ACT_RELU, 2, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
+        case 64 | (ACT_HARDSWISH << 2): released = epilogue_fast<BN, D2, ACT_HARDSWISH, 2, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
           default: epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
         }
       }
@@ -1021,20 +1074,24 @@ EncodeTiledFn encode_fn() {
 }
 
 // 3-D map over a row-major [batch, rows, k] tensor of f32 (elem_bytes 4) or fp16 (2):
-// box = box_k elements of K x box_rows rows. Swizzled boxes are 64 bytes wide.
+// box = box_k elements of K x box_rows rows. `swizzle`: 0, 64 or 128 (the latter with 32-byte
+// atoms, see make_smem_desc_mn); a swizzled box is exactly that many bytes wide. (For an operand given [K, N] the roles are swapped: "k" is N, the
+// contiguous dimension, and the rows are the k-rows.)
 bool make_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t k, int64_t rows, int64_t batch,
-              int64_t ld, int64_t batch_stride, int box_k, int box_rows, bool swizzle64) {
+              int64_t ld, int64_t batch_stride, int box_k, int box_rows, int swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(batch, 1)};
   cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes,
                            (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * elem_bytes};
   cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
-  if (swizzle64 && box_k * elem_bytes != 64) return false;
+  if (swizzle != 0 && box_k * elem_bytes != swizzle) return false;
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                           : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -1090,13 +1147,13 @@ TcPlan make_plan(int64_t m, int64_t n, int64_t k, int64_t batch, int bn, int mt,
 
 template <int BN, int MT, int MODE>
 cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mbl,
-                      const TcEpilogue& ep, const TcPlan& pl, int b_batched, float* workspace, int* err,
-                      cudaStream_t st) {
+                      const TcEpilogue& ep, const TcPlan& pl, int a_batched, int b_batched, float* workspace,
+                      int* err, cudaStream_t st) {
   using L = TcSmem<BN, MT, MODE>;
   static unsigned long long attr_done = 0;
   if (cudaError_t e0 = ensure_dynamic_smem(gemm_tc_kernel<BN, MT, MODE>, L::kDynBytes, &attr_done)) return e0;
-  gemm_tc_kernel<BN, MT, MODE><<<pl.grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, pl.sc, b_batched, pl.tiles_m,
-                                                                    pl.tiles_n, workspace, err);
+  gemm_tc_kernel<BN, MT, MODE><<<pl.grid, kThreads, L::kDynBytes, st>>>(ma, mb, mbl, ep, pl.sc, a_batched, b_batched,
+                                                                    pl.tiles_m, pl.tiles_n, workspace, err);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || pl.sc.tail_parts < 2) return e;
   const int tail = pl.sc.num_tiles - pl.sc.dp_tiles;
@@ -1127,12 +1184,13 @@ cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap&
 }  // namespace
 
 bool gemm_tc_supported(const GemmParams& q) {
-  if (q.trans_a || !q.trans_b) return false;
+  // A is [M, K]; B is [N, K] (trans_b) or [K, N] (the MN-major mode, 3xTF32 only).
+  if (q.trans_a) return false;
   if (q.m <= 0 || q.n <= 0 || q.k <= 0 || q.batch <= 0 || q.batch > 65535) return false;
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(q.a) || !al(q.b) || (q.lda % 4) || (q.ldb % 4)) return false;
   if (q.batch > 1 && ((q.stride_a % 4) || (q.stride_b % 4))) return false;
-  if (q.batch > 1 && q.stride_a <= 0) return false;
+  if (q.stride_a < 0 || q.stride_b < 0) return false;      // 0: the operand is shared by the batch
   if (q.b_lo && (!al(q.b_lo))) return false;
   return encode_fn() != nullptr;
 }
@@ -1224,7 +1282,9 @@ size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, i
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
   if (!gemm_tc_supported(q)) return cudaErrorInvalidValue;
   // mode 0: fp16 split when B comes with one, else 3xTF32; 2: 1xTF32; 3: 3xTF32.
-  const int kmode = mode == 2 ? TC_1X
+  if (!q.trans_b && mode == 2) return cudaErrorInvalidValue;   // the [K, N] form exists for 3xTF32 only
+  const int kmode = !q.trans_b ? TC_3X_SPLIT_B_MN
+                    : mode == 2 ? TC_1X
                     : (mode == 0 && q.b16_hi && q.b16_lo) ? TC_F16X3
                     : (q.b_lo ? TC_3X_BLO_TMA : TC_3X_SPLIT_B);
   const int variant = kmode == TC_F16X3 ? 2 : (kmode == TC_3X_BLO_TMA ? 0 : 1);
@@ -1232,19 +1292,27 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   const int bn = sh.bn;
   CUtensorMap ma, mb, mbl;
   const int b_batched = (q.batch > 1 && q.stride_b > 0) ? 1 : 0;
+  const int a_batched = (q.batch > 1 && q.stride_a > 0) ? 1 : 0;
+  const int64_t a_batch = a_batched ? q.batch : 1;
   if (kmode == TC_F16X3) {
     if (b_batched || (q.ldb16 % 8) != 0) return cudaErrorInvalidValue;
     // A pair's CTAs each load their own 128 rows of A and half of the B tile.
     const int a_rows = sh.pair ? BM : sh.mt * BM, b_rows = sh.pair ? bn / 2 : bn;
-    if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK16, a_rows, false)) return cudaErrorInvalidValue;
-    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, true)) return cudaErrorInvalidValue;
-    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, true)) return cudaErrorInvalidValue;
+    if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK16, a_rows, 0)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
+    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
+  } else if (kmode == TC_3X_SPLIT_B_MN) {
+    // B [K, N]: N is the contiguous dimension, boxes of 32 columns x BK k-rows.
+    if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK, sh.mt * BM, 64)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b, 4, q.n, q.k, b_batched ? q.batch : 1, q.ldb, q.stride_b, 32, BK, 128))
+      return cudaErrorInvalidValue;
+    mbl = mb;
   } else {
-    if (!make_map(&ma, q.a, 4, q.k, q.m, q.batch, q.lda, q.stride_a, BK, sh.mt * BM, true)) return cudaErrorInvalidValue;
-    if (!make_map(&mb, q.b, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, true))
+    if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK, sh.mt * BM, 64)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, 64))
       return cudaErrorInvalidValue;
     if (kmode == TC_3X_BLO_TMA) {
-      if (!make_map(&mbl, q.b_lo, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, true))
+      if (!make_map(&mbl, q.b_lo, 4, q.k, q.n, b_batched ? q.batch : 1, q.ldb, q.stride_b, BK, bn, 64))
         return cudaErrorInvalidValue;
     } else {
       mbl = mb;
@@ -1266,13 +1334,15 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   }
   float* ws = q.workspace;
   if (sh.pair) return launch_pair<256>(q.a, q.lda, (int)q.k, mb, mbl, ep, pl, ws, err_word, st);
-#define AC_TC(BNV)                                                                              \
-  (kmode == TC_1X ? launch_tc<BNV, 1, TC_1X>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)     \
-   : kmode == TC_F16X3                                                                          \
-       ? launch_tc<BNV, 1, TC_F16X3>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)           \
-   : kmode == TC_3X_BLO_TMA                                                                     \
-       ? launch_tc<BNV, 1, TC_3X_BLO_TMA>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st)      \
-       : launch_tc<BNV, 1, TC_3X_SPLIT_B>(ma, mb, mbl, ep, pl, b_batched, ws, err_word, st))
+#define AC_TC(BNV)                                                                                         \
+  (kmode == TC_1X ? launch_tc<BNV, 1, TC_1X>(ma, mb, mbl, ep, pl, a_batched, b_batched, ws, err_word, st)     \
+   : kmode == TC_F16X3                                                                                     \
+       ? launch_tc<BNV, 1, TC_F16X3>(ma, mb, mbl, ep, pl, a_batched, b_batched, ws, err_word, st)           \
+   : kmode == TC_3X_BLO_TMA                                                                                \
+       ? launch_tc<BNV, 1, TC_3X_BLO_TMA>(ma, mb, mbl, ep, pl, a_batched, b_batched, ws, err_word, st)      \
+   : kmode == TC_3X_SPLIT_B_MN                                                                             \
+       ? launch_tc<BNV, 1, TC_3X_SPLIT_B_MN>(ma, mb, mbl, ep, pl, a_batched, b_batched, ws, err_word, st)   \
+       : launch_tc<BNV, 1, TC_3X_SPLIT_B>(ma, mb, mbl, ep, pl, a_batched, b_batched, ws, err_word, st))
   if (bn == 256) return AC_TC(256);
   if (bn == 128) return AC_TC(128);
   return AC_TC(64);

@@ -566,8 +566,12 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
   // ---- tensor-core eligibility (static part; alignment is re-checked at launch) ----
   const int mode = s->opt.gemm_mode;
   const bool pairs = s->opt.gemm_pairs != 0;
+  // Below about 8 MFLOP the CUDA-core kernel wins, except for few rows against a long K (the
+  // squeeze-excite products, batch x channels): one or two of its blocks then walk K alone,
+  // while the persistent kernel cuts K into slices over the idle SMs.
+  const double tc_floor = (g.batch == 1 && g.m <= 128 && g.k >= 64) ? double(1 << 19) : double(1 << 23);
   bool tc = mode != 1 && !g.ta && (g.lda % 4) == 0 && (a_off % 4) == 0 && (g.sa % 4) == 0 &&
-            flops >= double(1 << 23) && g.k >= 8;
+            flops >= tc_floor && g.k >= 8;
   int b_use = b, b_lo = -1;
   const bool b_const = em.c.val(b).is_const;
   if (tc) {
@@ -584,7 +588,9 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       g.tb = 1;
       g.ldb = g.k;
     } else {
-      tc = false;
+      // Activation rhs stored [K, N] (a convolution's input or column buffer, the value
+      // operand of an unfused attention product): the 3xTF32 kernel reads it MN-major.
+      tc = mode != 2 && (g.ldb % 4) == 0 && (b_off % 4) == 0 && (g.sb % 4) == 0;
     }
   }
   // mode 0 with a constant rhs: the fp16 split (hi, remainder * 2^11) prepared once, [N, K8] halves.
@@ -601,7 +607,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word, st);
     });
   }
-  if (tc && b16_hi < 0 && mode != 2 && em.c.val(b_use).is_const) {
+  if (tc && b16_hi < 0 && mode != 2 && g.tb && em.c.val(b_use).is_const) {
     // TF32 hi / lo split of a constant rhs, prepared once.
     const int64_t cnt = em.c.val(b_use).numel();
     const int hi = new_value(em.c, cnt, true);
@@ -805,18 +811,65 @@ void lower_conv(Emit& em, int nid, const Epilogue* e) {
            [=](cudaStream_t st) { return launch_im2col(p, s->fptr(x), s->fptr_mut(col), st); });
     bsrc = col;
   }
+  // A pointwise convolution of 1 x 1 planes (squeeze-and-excite) is one product over the whole
+  // batch: out [n, oc] = x [n, c] * W^T, bias along the columns. As a batch of n matrix-vector
+  // products it would leave every tile of either GEMM kernel almost empty.
+  if (pointwise && p.group == 1 && ohw == 1 && ep.residual < 0) {
+    GemmShape g{};
+    g.m = p.n; g.k = p.c; g.n = p.oc; g.batch = 1;
+    g.lda = p.c; g.ldb = p.c; g.ldc = p.oc;
+    g.ta = 0; g.tb = 1;                       // W is [oc, c]: already K-major
+    Epilogue eg = ep;
+    emit_gemm(em, n.op, g, x, w, out, -1, bias, -1, 1.f, 0.f, 1.f, &eg);
+    return;
+  }
+  // The tensor-core kernel reads the input planes as they are ([K, N] operand, MN-major tiles)
+  // when the plane size is a multiple of four floats. Otherwise (7 x 7) the row stride is not a
+  // multiple of 16 bytes and TMA cannot address the planes: pointwise convolutions of some size
+  // then transpose them once to [n, hw, c], a K-contiguous rhs with row stride c.
+  bool rhs_transposed = false;
+  if (pointwise && p.group == 1 && (ohw % 4) != 0 && (p.c % 4) == 0 && flops >= double(1 << 23) &&
+      s->opt.gemm_mode != 1 && s->opt.gemm_mode != 2 && p.n <= 65535) {
+    const int xt = new_value(em.c, (int64_t)p.n * ohw * p.c, false);
+    const int64_t nb = p.n;
+    const int rows = p.c, cols = (int)ohw;
+    em.add("transpose_copy", n.op, {x}, {xt}, 2.0 * f32_bytes(xv), 0, [=](cudaStream_t st) {
+      return launch_transpose2d(s->fptr(x), s->fptr_mut(xt), nb, rows, cols, st);
+    });
+    bsrc = xt;
+    rhs_transposed = true;
+  }
+  // A filter matrix whose row length is not a multiple of four floats (3 x 3 x 3 = 27 in the
+  // first layer of the CNNs) gets a copy with padded rows, so that TMA can address it; K stays
+  // what it is, the tensor-core kernel zero-fills past it.
+  int a_src = w;
+  int64_t lda_use = kdim;
+  if (p.group == 1 && (kdim % 4) != 0 && !rhs_transposed && (ohw % 4) == 0 && flops >= double(1 << 23) &&
+      s->opt.gemm_mode != 1 && s->opt.gemm_mode != 2) {
+    const int64_t kpad = (kdim + 3) / 4 * 4, rows = p.oc, kd = kdim;
+    const int wp = new_value(em.c, rows * kpad, em.c.val(w).is_const);
+    em.add("weight_pad", n.op, {w}, {wp}, 4.0 * rows * (kd + kpad), 0, [=](cudaStream_t st) {
+      cudaError_t e = cudaMemsetAsync(s->fptr_mut(wp), 0, (size_t)(rows * kpad) * sizeof(float), st);
+      if (e != cudaSuccess) return e;
+      return cudaMemcpy2DAsync(s->fptr_mut(wp), (size_t)kpad * sizeof(float), s->fptr(w), (size_t)kd * sizeof(float),
+                               (size_t)kd * sizeof(float), (size_t)rows, cudaMemcpyDeviceToDevice, st);
+    }, 2);
+    a_src = wp;
+    lda_use = kpad;
+  }
   for (int gi = 0; gi < p.group; ++gi) {
     GemmShape g{};
     g.m = ocg; g.k = kdim; g.n = ohw; g.batch = p.n;
-    g.lda = kdim; g.ldb = ohw; g.ldc = ohw;
+    g.lda = lda_use; g.ldb = ohw; g.ldc = ohw;
     g.sa = 0; g.sb = (int64_t)p.c * p.kh * p.kw * ohw; g.sc = (int64_t)p.oc * ohw;
     g.ta = 0; g.tb = 0;
+    if (rhs_transposed) { g.tb = 1; g.ldb = kdim; }
     Epilogue eg = ep;
     // bias_m needs the group's slice of the bias: pass through an offset closure below.
     const int64_t a_off = (int64_t)gi * ocg * kdim, b_off = (int64_t)gi * kdim * ohw,
                   c_off = (int64_t)gi * ocg * ohw;
     if (p.group == 1) {
-      emit_gemm(em, n.op, g, w, bsrc, out, -1, -1, bias, 1.f, 0.f, 1.f, &eg, a_off, b_off, c_off);
+      emit_gemm(em, n.op, g, a_src, bsrc, out, -1, -1, bias, 1.f, 0.f, 1.f, &eg, a_off, b_off, c_off);
     } else {
       if (bias >= 0 || eg.residual >= 0)
         fail(AC_ERR_UNSUPPORTED, "Conv2d: grouped (non-depthwise) convolution with bias");

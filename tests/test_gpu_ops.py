@@ -229,7 +229,8 @@ def test_gemm(cuda_lib, gemm_mode):
 
 CONV_CASES = [(1, 1, 28, 8, 5, 1, 2, 1, True), (2, 4, 15, 6, 3, 2, 1, 1, True), (2, 16, 9, 16, 3, 1, 1, 16, True),
               (2, 16, 9, 16, 3, 1, 1, 16, False), (1, 3, 32, 8, 16, 16, 0, 1, True), (2, 24, 14, 40, 1, 1, 0, 1, True),
-              (2, 32, 14, 32, 5, 2, 2, 32, True), (2, 3, 64, 16, 3, 2, 1, 1, False)]
+              (2, 32, 14, 32, 5, 2, 2, 32, True), (2, 3, 64, 16, 3, 2, 1, 1, False),
+              (4, 24, 1, 8, 1, 1, 0, 1, True), (32, 960, 1, 240, 1, 1, 0, 1, True)]   # 1 x 1 planes (squeeze-excite)
 
 
 @pytest.mark.parametrize("n,c,h,oc,k,s,p,g,with_bias", CONV_CASES)
@@ -242,6 +243,57 @@ def test_conv2d(cuda_lib, n, c, h, oc, k, s, p, g, with_bias, gemm_mode):
                         padding=[p, p, p, p], dilations=[1, 1], group=g, auto_pad="")
     got, want = both(m, [x], gemm_mode=gemm_mode)
     np.testing.assert_allclose(got[0], want[0], rtol=1e-5, atol=1e-5 * np.sqrt(c // g * k * k) * 4)
+
+
+# Convolutions and batched products whose rhs is stored [K, N]: MN-major tiles in the
+# tensor-core kernel. Edges: HW not a multiple of the 32-column box or of the tile width, fewer
+# output channels than one 128-row tile, K not a multiple of the 16-float stage, batch-shared A.
+MN_CONV_CASES = [(4, 64, 56, 96, 1, 1, 0, "relu"), (3, 40, 28, 72, 1, 1, 0, None), (2, 16, 30, 24, 3, 1, 1, None),
+                 (2, 24, 16, 200, 3, 2, 1, "relu"), (16, 72, 14, 24, 1, 1, 0, None), (8, 160, 7, 320, 1, 1, 0, "relu"), (16, 3, 64, 16, 3, 2, 1, "relu")]
+
+
+@pytest.mark.parametrize("n,c,h,oc,k,s,p,act", MN_CONV_CASES)
+def test_conv2d_on_the_tensor_cores(cuda_lib, n, c, h, oc, k, s, p, act):
+    from altius_b200.session import CudaSessionBuilder
+    x = RNG.standard_normal((n, c, h, h)).astype(np.float32)
+    w = (RNG.standard_normal((oc, c, k, k)) / np.sqrt(c * k * k)).astype(np.float32)
+    bias = RNG.standard_normal(oc).astype(np.float32)
+
+    def build(g):
+        y = g.op("Conv2d", g.add_input("x", x.shape), g.new_init(w), g.new_init(bias), kernel_shape=[k, k],
+                 strides=[s, s], padding=[p, p, p, p], dilations=[1, 1], group=1, auto_pad="")
+        return [g.op("ReLU", y) if act == "relu" else y]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert "gemm_tf32x3_tcgen05" in [e["kind"] for e in sess.schedule()]
+        got = sess.run([x])[0]
+    finally:
+        sess.close()
+    want = run_oracle(m, [x])[0]
+    xa, wa = np.abs(x), np.abs(w)
+    import torch
+    bound = torch.nn.functional.conv2d(torch.from_numpy(xa), torch.from_numpy(wa), torch.from_numpy(np.abs(bias)),
+                                       stride=s, padding=p).numpy()
+    assert got.shape == want.shape
+    assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 5e-6 * bound).all()
+
+
+@pytest.mark.parametrize("ashape,bshape", [((8, 200, 72), (8, 72, 136)), ((24, 197, 200), (24, 200, 64)),
+                                           ((1, 3, 130, 48), (1, 3, 48, 260))])
+def test_batched_matmul_of_two_activations_on_the_tensor_cores(cuda_lib, ashape, bshape):
+    from altius_b200.session import CudaSessionBuilder
+    a = RNG.standard_normal(ashape).astype(np.float32)
+    b = RNG.standard_normal(bshape).astype(np.float32)
+    m = single_op_model("MatMul", [a, b])
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["gemm_tf32x3_tcgen05"]
+        got = sess.run([a, b])[0]
+    finally:
+        sess.close()
+    want = run_oracle(m, [a, b])[0]
+    assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 5e-6 * (np.abs(a) @ np.abs(b))).all()
 
 
 def test_conv2d_same_upper(cuda_lib):
@@ -407,9 +459,10 @@ def test_gelu_in_the_gemm_epilogue_equals_the_gelu_kernel_bit_for_bit(cuda_lib):
     # The epilogue evaluates Gelu on pairs with packed fp32 instructions and its own
     # division sequence; the stand-alone kernel uses the scalar formulas. Same MatMul
     # kernel in both sessions, so any difference comes from the activation.
-    x = RNG.standard_normal((1024, 64)).astype(np.float32)
-    x *= np.exp2(RNG.integers(-30, 4, size=(1024, 1))).astype(np.float32)   # pre-activations from 1e-9 to 100
-    w = (0.3 * RNG.standard_normal((64, 512))).astype(np.float32)
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((1024, 64)).astype(np.float32)
+    x *= np.exp2(np.arange(1024) % 34 - 30).astype(np.float32)[:, None]   # pre-activations from 1e-9 to 100
+    w = (0.3 * rng.standard_normal((64, 512))).astype(np.float32)
     b = np.zeros(512, np.float32)
 
     def build(g):
