@@ -241,6 +241,72 @@ __global__ void __launch_bounds__(256) depthwise_kernel(const float* __restrict_
   out[i] = apply_act(p.act, acc, p.act_alpha, p.act_beta);
 }
 
+// The same stencil for the shapes the CNNs have (square K x K filter, stride S, dilation 1),
+// four consecutive output pixels of one row per thread: the filter taps sit in registers, an
+// input row segment of 3 S + K values is loaded once per filter row and shared by the four
+// pixels. Per output the taps are visited in the same order as above and out-of-range taps are
+// skipped, so the results are bit-identical to the generic kernel.
+template <int K, int S, int ACT>
+__global__ void __launch_bounds__(256) depthwise_rows_kernel(const float* __restrict__ x,
+                                                             const float* __restrict__ w,
+                                                             const float* __restrict__ bias,
+                                                             float* __restrict__ out, ConvParams p,
+                                                             unsigned owg, unsigned items) {
+  const unsigned item = blockIdx.x * 256u + threadIdx.x;
+  if (item >= items) return;
+  const unsigned xg = item % owg, t = item / owg;
+  const unsigned oy = t % (unsigned)p.oh, plane = t / (unsigned)p.oh;   // plane = n * c + ch
+  const int ch = (int)(plane % (unsigned)p.c);
+  const float* in = x + (long long)plane * p.ih * p.iw;
+  float wk[K * K];
+#pragma unroll
+  for (int i = 0; i < K * K; ++i) wk[i] = __ldg(w + ch * (K * K) + i);
+  constexpr int SEG = 3 * S + K;
+  const int ox0 = (int)xg * 4;
+  const int y0 = (int)oy * S - p.pad_t, x0 = ox0 * S - p.pad_l;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int fy = 0; fy < K; ++fy) {
+    const int iy = y0 + fy;
+    if (iy < 0 || iy >= p.ih) continue;            // uniform per thread: all four pixels skip the row
+    const float* row = in + iy * p.iw;
+    float seg[SEG];
+#pragma unroll
+    for (int j = 0; j < SEG; ++j) {
+      const int ix = x0 + j;
+      seg[j] = (ix >= 0 && ix < p.iw) ? __ldg(row + ix) : 0.f;
+    }
+#pragma unroll
+    for (int fx = 0; fx < K; ++fx)
+#pragma unroll
+      for (int o = 0; o < 4; ++o) {
+        const int ix = x0 + o * S + fx;
+        if (ix >= 0 && ix < p.iw) acc[o] = fmaf(wk[fy * K + fx], seg[o * S + fx], acc[o]);
+      }
+  }
+  const float bv = bias ? __ldg(bias + ch) : 0.f;
+  float* dst = out + ((long long)plane * p.oh + oy) * p.ow + ox0;
+#pragma unroll
+  for (int o = 0; o < 4; ++o) {
+    if (ox0 + o >= p.ow) break;
+    float v = acc[o];
+    if (bias) v = __fadd_rn(bv, v);
+    dst[o] = apply_act(ACT, v, p.act_alpha, p.act_beta);
+  }
+}
+
+template <int K, int S>
+bool launch_depthwise_rows(const ConvParams& p, const float* x, const float* w, const float* bias, float* out,
+                           unsigned owg, unsigned items, cudaStream_t st) {
+  const unsigned blocks = (items + 255u) / 256u;
+  switch (p.act) {
+    case ACT_NONE: depthwise_rows_kernel<K, S, ACT_NONE><<<blocks, 256, 0, st>>>(x, w, bias, out, p, owg, items); return true;
+    case ACT_RELU: depthwise_rows_kernel<K, S, ACT_RELU><<<blocks, 256, 0, st>>>(x, w, bias, out, p, owg, items); return true;
+    case ACT_HARDSWISH: depthwise_rows_kernel<K, S, ACT_HARDSWISH><<<blocks, 256, 0, st>>>(x, w, bias, out, p, owg, items); return true;
+    default: return false;
+  }
+}
+
 inline bool al16(const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; }
 
 }  // namespace
@@ -270,6 +336,16 @@ cudaError_t launch_depthwise_conv(const ConvParams& p, const float* x, const flo
                                   const float* bias, float* out, cudaStream_t st) {
   const long long total = (long long)p.n * p.oc * p.oh * p.ow;
   if (total == 0) return cudaSuccess;
+  const long long owg = (p.ow + 3) / 4, items = (long long)p.n * p.oc * p.oh * owg;
+  if (p.kh == p.kw && p.sh == p.sw && p.dh == 1 && p.dw == 1 && items < (1ll << 31) &&
+      (long long)p.ih * p.iw < (1ll << 31)) {
+    bool done = false;
+    if (p.kh == 3 && p.sh == 1) done = launch_depthwise_rows<3, 1>(p, x, w, bias, out, (unsigned)owg, (unsigned)items, st);
+    else if (p.kh == 3 && p.sh == 2) done = launch_depthwise_rows<3, 2>(p, x, w, bias, out, (unsigned)owg, (unsigned)items, st);
+    else if (p.kh == 5 && p.sh == 1) done = launch_depthwise_rows<5, 1>(p, x, w, bias, out, (unsigned)owg, (unsigned)items, st);
+    else if (p.kh == 5 && p.sh == 2) done = launch_depthwise_rows<5, 2>(p, x, w, bias, out, (unsigned)owg, (unsigned)items, st);
+    if (done) return cudaGetLastError();
+  }
   depthwise_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(x, w, bias, out, p, total);
   return cudaGetLastError();
 }
