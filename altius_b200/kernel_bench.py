@@ -3,6 +3,7 @@
     python -m altius_b200.kernel_bench gemm 6304 768 2304 [--mode 0|1|2] [--iters 10] [--bias] [--gelu] [--residual]
     python -m altius_b200.kernel_bench micrograph [--batch 64] [--no-fuse]
     python -m altius_b200.kernel_bench attention 32 197 12     # batch, tokens, heads (head dim 64)
+    python -m altius_b200.kernel_bench conv 16 64 112 [--k 1] [--depthwise] [--batch 32]   # c_in, c_out, H = W
 
 Builds a one-node (or micrograph) session with per-kernel CUDA-event profiling
 and prints, per kernel kind, the mean device time and the achieved algorithmic
@@ -46,7 +47,7 @@ def _run(model, feeds, mode, fuse, iters, cold=False, pairs=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "micrograph", "attention"])
+    ap.add_argument("what", choices=["gemm", "micrograph", "attention", "conv"])
     ap.add_argument("dims", nargs="*", type=int)
     ap.add_argument("--mode", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -56,6 +57,8 @@ def main(argv=None):
     ap.add_argument("--bias", action="store_true", help="gemm: + bias[n] in the epilogue")
     ap.add_argument("--gelu", action="store_true", help="gemm: Gelu after the bias")
     ap.add_argument("--residual", action="store_true", help="gemm: + residual[m, n] in the epilogue")
+    ap.add_argument("--k", type=int, default=1, help="conv: square filter size (stride 1, same padding)")
+    ap.add_argument("--depthwise", action="store_true", help="conv: one filter per channel (c_out is ignored)")
     ap.add_argument("--cold-l2", action="store_true", help="sweep L2 before every kernel (micrograph)")
     a = ap.parse_args(argv)
     rng = np.random.default_rng(0)
@@ -77,6 +80,20 @@ def main(argv=None):
             feeds.append(r)
         g.outputs.append(out)
         rows = _run(ir.Model(g, 13), feeds, a.mode, True, a.iters, pairs=a.pairs)
+    elif a.what == "conv":
+        cin, cout, hw = a.dims
+        batch = a.batch if a.batch != 64 else 32
+        group = cin if a.depthwise else 1
+        cout = cin if a.depthwise else cout
+        x = rng.standard_normal((batch, cin, hw, hw)).astype(np.float32)
+        w = (rng.standard_normal((cout, cin // group, a.k, a.k)) / np.sqrt(cin // group * a.k * a.k)).astype(np.float32)
+        g = ir.Graph()
+        pad = a.k // 2
+        y = g.op("Conv2d", g.add_input("x", x.shape), g.new_init(w),
+                 g.new_init(rng.standard_normal(cout).astype(np.float32)), kernel_shape=[a.k, a.k], strides=[1, 1],
+                 padding=[pad, pad, pad, pad], dilations=[1, 1], group=group, auto_pad="")
+        g.outputs.append(g.op("ReLU", y))
+        rows = _run(ir.Model(g, 13), [x], a.mode, True, a.iters)
     elif a.what == "attention":
         B, T, H = a.dims
         hd, D = 64, 64 * H
