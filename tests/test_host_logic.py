@@ -80,6 +80,22 @@ def test_fusion_folds_the_expected_chains():
     assert kinds["binary_Mul"] == 8               # the squeeze-excite gates
     assert kinds["conv_depthwise"] == 15
 
+    # At the benchmark's batch the convolution GEMMs are large enough for the tensor cores:
+    # pointwise layers read the planes as a [K, N] rhs, the 7 x 7 layers through transposed planes,
+    # the first layer (3 x 3 x 3 = 27 taps) with zero-padded filter rows, the squeeze-excite
+    # layers (1 x 1 planes) as one product over the batch.
+    model, _ = configs.mobilenet_v3_large(batch=32)
+    steps = plan(model).schedule()
+    kinds = collections.Counter(e["kind"] for e in steps)
+    assert kinds["im2col"] == 1 and kinds["transpose_copy"] == 6
+    assert kinds["gemm_tf32x3_tcgen05"] == 31          # the first layer and the 30 pointwise layers on planes
+    assert kinds["gemm_f16x3_tcgen05"] == 12           # squeeze-excite, the 1 x 1 head convolution, the classifier
+    assert kinds["gemm_fp32_simt"] == 6                # the smallest squeeze-excite products
+    assert "weight_pad" not in kinds                   # prepared once at create, not per run
+    cuda_cores = CudaSessionBuilder(model).with_plan_only(True).with_gemm_mode(1).build().schedule()
+    assert sum(e["kind"] == "gemm_fp32_simt" for e in cuda_cores) == 49
+    assert not any(e["kind"].endswith("tcgen05") for e in cuda_cores)
+
 
 def test_flops_of_vit_match_the_published_count():
     model, _ = configs.vit_base_16(batch=1, depth=12)
