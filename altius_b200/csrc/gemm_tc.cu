@@ -83,6 +83,10 @@ struct TcEpilogue {
   const float* bias_n; const float* bias_m; float bias_scale;
   int act; float act_alpha, act_beta;
   const float* res; long long ldres, sres;
+  uint2* c16_hi; uint2* c16_lo; long long ldc16;   // result as fp16 hi / lo halves (4 per uint2; ldc16 in halves), or null
+  const float* acc_scale;   // device scalar the accumulators are multiplied by (B was scaled by its inverse), or null
+  int* err;                 // error word: range of the split output
+  int dbg;   // timing experiments only (0 in normal use)
 };
 
 // Shared-memory matrix descriptor for a K-major tile whose rows are 64 bytes
@@ -95,6 +99,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   d |= (uint64_t)((8 * 64) >> 4) << 32;          // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                        // descriptor version for this architecture
   d |= (uint64_t)4 << 61;                        // 64-byte swizzle
+  return d;
+}
+
+// K-major tile whose rows are 128 bytes (64 halves) with the 128-byte swizzle: 8-row groups
+// are 1024 bytes apart. A K-step of 16 halves advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                        // leading byte offset (ignored for swizzled K-major)
+  d |= (uint64_t)((8 * 128) >> 4) << 32;         // stride byte offset: 8 rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
   return d;
 }
 
@@ -114,27 +130,24 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t saddr, uint32_t c
   return d;
 }
 
-// Code left in the error word when an operand does not fit the fp16 split.
-constexpr int kRangeCode = 21;
-
-// |x| > 65504 (the largest fp16), infinities included, NaN excluded.
-__device__ __forceinline__ unsigned beyond_half(float x) {
-  const unsigned ab = __float_as_uint(x) & 0x7FFFFFFFu;
-  return (ab - 0x477FE001u) <= (0x7F800000u - 0x477FE001u) ? 1u : 0u;
-}
 // 32 accumulator columns of this warp's rows. D2OFF != 0: the fp16 mode's second
 // accumulator (cross terms, scaled by 2^11) sits D2OFF columns further on.
+// `sc`: power of two that undoes the scaling of a constant B (1 when there is none).
 template <int D2OFF>
-__device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32]) {
-  tc_ld_32x32(taddr, v);
+__device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32], float sc) {
+  tc_ld_32x32_nowait(taddr, v);
   if (D2OFF != 0) {
     uint32_t w[32];
-    tc_ld_32x32(taddr + (uint32_t)D2OFF, w);
+    tc_ld_32x32_nowait(taddr + (uint32_t)D2OFF, w);
+    tc_wait_ld();
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      v[j] = __float_as_uint(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])));
+      v[j] = __float_as_uint(__fmul_rn(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])), sc));
+  } else {
+    tc_wait_ld();
   }
 }
+__device__ __forceinline__ float acc_scale_of(const TcEpilogue& ep) { return ep.acc_scale ? __ldg(ep.acc_scale) : 1.f; }
 
 // Epilogue of one warp's 32 rows. The accumulator chunk arrives with one thread
 // per row (32 columns each); it goes through a 4 KB shared-memory tile so that
@@ -144,6 +157,7 @@ __device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32]) {
 template <int BN, int D2OFF>
 __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stage, uint32_t tmem_base,
                                               int warp, int lane, int m0, int n0, int bz, int cc0, int cc1) {
+      const float sc = acc_scale_of(ep);
       float* c = ep.c + (long long)bz * ep.sc;
       const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
       const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
@@ -158,7 +172,7 @@ __device__ __noinline__ void epilogue_generic(const TcEpilogue& ep, float4* stag
         const int col0 = n0 + cc * 32;
         if (col0 >= ep.n) break;           // uniform across the warp
         uint32_t v[32];
-        load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+        load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v, sc);
         __syncwarp();
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -248,6 +262,7 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
                                               int warp, int lane, int m0, int n0, int bz, int cc0, int cc1,
                                               Release&& release) {
   bool released = false;
+  const float sc = acc_scale_of(ep);
   float* c = ep.c + (long long)bz * ep.sc;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
   const int c4 = lane & 7, rsub = lane >> 3;
@@ -262,7 +277,7 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
     const int col0 = n0 + cc * 32;
     if (col0 >= ep.n) break;
     uint32_t v[32];
-    load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v, sc);
     if (cc + 1 == cc1 || col0 + 32 >= ep.n) released = release();   // uniform across the warp
     __syncwarp();
 #pragma unroll
@@ -317,16 +332,115 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
   return released;
 }
 
+// The same epilogue for a kernel with sixteen epilogue warps and 2 KB of staging per warp: a
+// warp owns 32 rows x (NCH * 32) columns. The two accumulators of a 32-column chunk are fetched
+// with one wait; tensor memory goes back to the MMA warp as soon as the warp's last chunk has
+// left it. A chunk passes through the staging tile in halves of 16 columns (four lanes then
+// own one row's 64 contiguous bytes, eight rows per instruction). 16-byte slots are
+// XOR-swizzled by bits 1-2 of the row: writes (a lane per row) and reads (four lanes per row)
+// are both free of bank conflicts. (Draining all chunks into registers first, to release
+// tensor memory earlier, needs more than the 96 registers a thread of this kernel can have.)
+template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
+__device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stage, uint32_t tmem_base, int q,
+                                              int lane, int m0, int n0, int bz, int cc0, Release&& release) {
+  bool released = false;
+  const float sc = acc_scale_of(ep);
+  float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
+  const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
+  const int c4 = lane & 3, rsub = lane >> 2;
+  const int row_base = m0 + q * 32 + rsub;
+  unsigned seen = 0;
+  float bm[4];
+  if (BIAS == 2) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) bm[i] = row_base + 8 * i < ep.m ? __ldg(ep.bias_m + row_base + 8 * i) : 0.f;
+  }
+#pragma unroll 1
+  for (int ci = 0; ci < NCH; ++ci) {
+    const int col0 = n0 + (cc0 + ci) * 32;
+    if (col0 >= ep.n) break;                       // uniform across the warp
+    uint32_t v[32];
+    {
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32);
+      tc_ld_32x32_nowait(taddr, v);
+      if (D2OFF != 0) {
+        uint32_t w[32];
+        tc_ld_32x32_nowait(taddr + (uint32_t)D2OFF, w);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          v[j] = __float_as_uint(__fmul_rn(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])), sc));
+      } else {
+        tc_wait_ld();
+      }
+    }
+    if (ci + 1 == NCH || col0 + 32 >= ep.n) released = release();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        stage[lane * 4 + (j ^ ((lane >> 1) & 3))] =
+            make_float4(__uint_as_float(v[16 * h + 4 * j]), __uint_as_float(v[16 * h + 4 * j + 1]),
+                        __uint_as_float(v[16 * h + 4 * j + 2]), __uint_as_float(v[16 * h + 4 * j + 3]));
+      __syncwarp();
+      const int col = col0 + 16 * h + 4 * c4;
+      const bool col_ok = col < ep.n;   // n % 4 == 0: the whole float4 is in range
+      float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+      float4 a[4], r[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rl = 8 * i + rsub;
+        a[i] = stage[rl * 4 + (c4 ^ ((rl >> 1) & 3))];
+        if (HAS_RES) {
+          const int row = row_base + 8 * i;
+          r[i] = (col_ok && row < ep.m)
+                     ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 x = a[i];
+        if (BIAS == 1) {
+          x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
+          x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
+        }
+        if (BIAS == 2) {
+          x.x = __fadd_rn(x.x, bm[i]); x.y = __fadd_rn(x.y, bm[i]);
+          x.z = __fadd_rn(x.z, bm[i]); x.w = __fadd_rn(x.w, bm[i]);
+        }
+        if (ACT == ACT_GELU) {
+          const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
+          x = make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else if (ACT != ACT_NONE) {
+          const float al = ep.act_alpha, be = ep.act_beta;
+          x.x = apply_act(ACT, x.x, al, be); x.y = apply_act(ACT, x.y, al, be);
+          x.z = apply_act(ACT, x.z, al, be); x.w = apply_act(ACT, x.w, al, be);
+        }
+        if (HAS_RES) {
+          x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
+          x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
+        }
+        const int row = row_base + 8 * i;
+        if (col_ok && row < ep.m) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
+      }
+    }
+  }
+  return released;
+}
+
 // Unreduced accumulator of a K-slice -> workspace tile [128][BN], same staging
 // as the real epilogues so that the stores are full lines.
 template <int BN, int D2OFF>
 __device__ __forceinline__ void epilogue_raw(float* ws_tile, float4* stage, uint32_t tmem_base, int warp,
-                                             int lane, int cc0, int cc1) {
+                                             int lane, int cc0, int cc1, float sc) {
   const int c4 = lane & 7, rsub = lane >> 3;
 #pragma unroll 1
   for (int cc = cc0; cc < cc1; ++cc) {
     uint32_t v[32];
-    load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v);
+    load_acc<D2OFF>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(cc * 32), v, sc);
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -718,7 +832,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int m0 = (tm * MT + mt) * BM, n0 = tn * BN;
       if (m0 >= ep.m) break;                     // uniform: the second sub-tile may lie past M
       if (wk.raw >= 0) {
-        epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane, cc0, cc1);
+        epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * MT + mt) * BM * BN, stage, acc, q, lane, cc0, cc1, acc_scale_of(ep));
       } else
       switch (key) {
         case 0: released = epilogue_fast<BN, D2, ACT_NONE, 0, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
@@ -784,16 +898,21 @@ __device__ __forceinline__ bool pair_get_work(const TcSched& sc, int w, TcWork* 
   return false;
 }
 
-template <int BN>
+// PRE: A arrives already split (fp16 hi / lo arrays written by the kernel that produced it), so
+// all four tiles of a stage come by TMA and no thread of the CTA touches them.
+template <int BN, bool PRE = false>
 struct PairSmem {
-  static constexpr int kKb = BK16;                      // floats of K per stage
+  // K per stage: 32 (64-byte rows, 64-byte swizzle), or with PRE 64 (128-byte rows, 128-byte
+  // swizzle: half as many stages to signal, and the layout the tensor core fetches fastest)
+  static constexpr int kKb = PRE ? 64 : BK16;
   static constexpr int kABytes = BM * kKb * 2;          // fp16 hi tile of A; the lo tile follows
   static constexpr int kBBytes = (BN / 2) * kKb * 2;    // this CTA's half of B: one of hi / lo
   static constexpr int kOffALo = kABytes;
   static constexpr int kOffBHi = 2 * kABytes;
   static constexpr int kOffBLo = kOffBHi + kBBytes;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
-  static constexpr int kTxBytes = 2 * kBBytes;          // TMA brings B only; A goes global -> registers -> tiles
+  // TMA brings B only (A goes global -> registers -> tiles), or everything (PRE)
+  static constexpr int kTxBytes = 2 * kBBytes + (PRE ? 2 * kABytes : 0);
   static constexpr int kStages = (200 * 1024) / kStageBytes;   // 6 at BN 256
   static constexpr int kEpiBytes = kEpiWarps * 4096;
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
@@ -802,31 +921,43 @@ struct PairSmem {
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tensor memory");
 };
 
-template <int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+// Debug aid (ALTIUS_CUDA_TC_DBG bit 0x1000): clock64 stamps of a few events per CTA.
+__device__ long long g_pair_stamps[160][16];
+__device__ __forceinline__ void pair_stamp(int dbg, int slot) {
+  if (dbg & 0x1000) g_pair_stamps[blockIdx.x][slot] = clock64();
+}
+
+// PRE runs 19 warps: sixteen epilogue warps (no thread has to touch the operand tiles), the TMA
+// producer, the MMA issuer and the relay.
+template <int BN, bool PRE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PRE ? kThreads + 32 : kThreads, 1)
 gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
+                    const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_alo,
                     const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_blo,
-                    TcEpilogue ep, TcSched sc, int tiles_m, int tiles_n, float* workspace, int* err) {
-  using L = PairSmem<BN>;
-  constexpr int S = L::kStages;
+                    TcEpilogue ep, TcSched sc, int tiles_m, int tiles_n, float* workspace, int* err, int dbg) {
+  using L = PairSmem<BN, PRE>;
+  const int S = (dbg >> 8) > 0 && (dbg >> 8) < L::kStages ? (dbg >> 8) : L::kStages;   // experiment: fewer stages
   constexpr int KB = L::kKb;
   constexpr int D2 = BN;                 // column offset of the cross-term accumulator
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi_smem = smem + S * L::kStageBytes;
+  constexpr int SM = L::kStages;
+  uint8_t* epi_smem = smem + SM * L::kStageBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + L::kEpiBytes);
   uint64_t* full = bars;                 // this CTA's TMA bytes landed
-  uint64_t* ready = bars + S;            // leader's: both CTAs' fp16 tiles written (2 x 4 warps arrive)
-  uint64_t* empty = bars + 2 * S;        // this CTA's: the pair's MMAs that read the stage have completed
-  uint64_t* acc_full = bars + 3 * S;     // this CTA's: accumulators complete
-  uint64_t* acc_empty = bars + 3 * S + 1;   // leader's: drained by the 8 epilogue warps of the pair
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * S + 2);
+  uint64_t* ready = bars + SM;            // leader's: both CTAs' fp16 tiles written (2 x 4 warps arrive)
+  uint64_t* empty = bars + 2 * SM;        // this CTA's: the pair's MMAs that read the stage have completed
+  uint64_t* acc_full = bars + 3 * SM;     // this CTA's: accumulators complete
+  uint64_t* acc_empty = bars + 3 * SM + 1;   // leader's: drained by the 8 epilogue warps of the pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * SM + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();
   const bool leader = rank == 0;
+  if (threadIdx.x == 0) pair_stamp(dbg, 0);
 
+  auto pwait = [&](uint64_t* bar, uint32_t parity) { return (dbg & 4) ? mbar_wait_spin(bar, parity) : mbar_wait(bar, parity); };
   auto a_raw = [&](int s) { return smem + s * L::kStageBytes; };    // fp16 hi tile of A
   auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kOffALo; };
   auto b_hi = [&](int s) { return smem + s * L::kStageBytes + L::kOffBHi; };
@@ -835,11 +966,12 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&ready[s], 2 * (kSplitThreads / 32));   // one arrival per splitter warp of the pair
+      // one arrival per splitter warp of the pair; PRE: one per CTA (its relay thread)
+      mbar_init(&ready[s], PRE ? 2 : 2 * (kSplitThreads / 32));
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 2 * kEpiWarps); // one arrival per epilogue warp of the pair
+    mbar_init(acc_empty, 2 * (PRE ? 16 : kEpiWarps)); // one arrival per epilogue warp of the pair
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -852,6 +984,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   cluster_sync_all();                    // barriers of both CTAs initialised before any remote arrival
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) pair_stamp(dbg, 1);
 
   if (warp == kTmaWarp) {
     // ---------------- TMA producer (each CTA for itself) ----------------
@@ -861,11 +994,17 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       TcWork wk;
       for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
         const int tn = wk.tile % tiles_n;
+        const int m0 = ((wk.tile / tiles_n) % tiles_m) * (2 * BM) + (int)rank * BM;
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
+          if (!pwait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
+          if (dbg & 2) { mbar_arrive(&full[s]); continue; }   // timing experiment: no loads
           mbar_arrive_expect_tx(&full[s], L::kTxBytes);
+          if (PRE) {   // this CTA's 128 rows of A, hi and lo (rows past M are zero-filled)
+            tma_load_3d(a_raw(s), &tm_a, &full[s], kb * KB, m0, 0);
+            tma_load_3d(a_lo(s), &tm_alo, &full[s], kb * KB, m0, 0);
+          }
           tma_load_3d(b_hi(s), &tm_b, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
           tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
         }
@@ -887,15 +1026,42 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
-          ok = mbar_wait(&ready[s], ph);
+          ok = pwait(&ready[s], ph);
           if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
+          if (it == 0) pair_stamp(dbg, 2);
           tc_fence_after();
-          const uint64_t da = make_smem_desc(smem_u32(a_raw(s))), dal = make_smem_desc(smem_u32(a_lo(s)));
-          const uint64_t db = make_smem_desc(smem_u32(b_hi(s))), dbl = make_smem_desc(smem_u32(b_lo(s)));
+          auto mk = [](uint32_t a) { return PRE ? make_smem_desc_sw128(a) : make_smem_desc(a); };
+          const uint64_t da = mk(smem_u32(a_raw(s))), dal = mk(smem_u32(a_lo(s)));
+          const uint64_t db = mk(smem_u32(b_hi(s))), dbl = mk(smem_u32(b_lo(s)));
+          if (!(dbg & 256)) {   // one accumulator after the other within a stage: alternating between them
+                                // with every MMA cost 30 % of the tensor pipe's rate (dbg bit 256: the old order)
 #pragma unroll
-          for (int kk = 0; kk < 2; ++kk) {                  // two K-steps of 16 halves per 64-byte row
+            for (int kk = 0; kk < KB / 16; ++kk)
+              tc_mma_f16_pair(tmem_base, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < KB / 16; ++kk) {
+              tc_mma_f16_pair(tmem_base + D2, dal + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16_pair(tmem_base + D2, da + (uint64_t)(kk * 2), dbl + (uint64_t)(kk * 2), idesc, 1u);
+            }
+          } else
+#pragma unroll
+          for (int kk = 0; kk < KB / 16; ++kk) {            // K-steps of 16 halves (32 bytes of a row)
             const uint64_t off = (uint64_t)(kk * 32 >> 4);
             const uint32_t acc = (kb > wk.k0 || kk > 0) ? 1u : 0u;
+            if (dbg & 1) continue;                                               // timing experiment: no MMAs
+            if (dbg & 32) { tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc); continue; }
+            if (dbg & 64) {
+              tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);
+              tc_mma_f16_pair(tmem_base, dal + off, db + off, idesc, 1u);
+              tc_mma_f16_pair(tmem_base, da + off, dbl + off, idesc, 1u);
+              continue;
+            }
+            if (dbg & 128) {
+              tc_mma_f16_pair(tmem_base + D2, dal + off, db + off, idesc, acc);
+              tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);
+              tc_mma_f16_pair(tmem_base + D2, da + off, dbl + off, idesc, 1u);
+              continue;
+            }
             tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);          // a_hi * b_hi
             tc_mma_f16_pair(tmem_base + D2, dal + off, db + off, idesc, acc);    // a_lo' * b_hi
             tc_mma_f16_pair(tmem_base + D2, da + off, dbl + off, idesc, 1u);     // a_hi * b_lo'
@@ -907,9 +1073,25 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           tc_commit_pair(smem_u32(acc_full));
           tc_commit_pair(acc_full_peer);
         }
+        if (ti < 5) pair_stamp(dbg, 3 + ti);   // all MMAs of tile ti issued
       }
     }
-  } else if (warp < kSplitWarps) {
+  } else if (PRE && warp == kMmaWarp + 1) {
+    // ---------------- relay (PRE): this CTA's tiles have landed -> tell the leader ----------------
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      TcWork wk;
+      for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
+        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
+          const int s = it % S;
+          ok = pwait(&full[s], (it / S) & 1);
+          if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
+          mbar_arrive_cluster(map_to_cta(&ready[s], 0));
+        }
+      }
+    }
+  } else if (!PRE && warp < kSplitWarps) {
     // ---------------- splitters (each CTA its own A rows) ----------------
     // A does not pass through shared memory as fp32: each thread loads its eight float4
     // (row, four consecutive k) of the stage from global memory, splits them in registers and
@@ -962,11 +1144,17 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       }
     }
     if (range_bad) atomicCAS(err, 0, kRangeCode);
-  } else {
+  } else if (!PRE || warp < 16) {
     // ---------------- epilogue (each CTA its own 128 rows) ----------------
-    const int e = warp - kSplitWarps, q = e & 3;
-    const int cc0 = (e >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // this warp's 32-column chunks
-    float4* stage = reinterpret_cast<float4*>(epi_smem + e * 4096);
+    // PRE: warps 0-15, a warp per lane quarter and quarter of the columns on the common
+    // epilogues (2 KB of staging each); the general and the K-slice epilogues are left to warps
+    // 8-15 with 4 KB each (the same 32 KB), the others only hand the accumulator back.
+    const int e = PRE ? warp : warp - kSplitWarps, q = e & 3;
+    const int eo = PRE ? e - 8 : e;                                // index among the eight "old" warps
+    const int cc0 = (eo >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // their 32-column chunks
+    const int hc0 = (e >> 2) * (BN / 128);                        // PRE, common epilogues: 64 columns from chunk hc0
+    float4* stage = reinterpret_cast<float4*>(epi_smem + (eo < 0 ? 0 : eo) * 4096);
+    float4* stage_h = reinterpret_cast<float4*>(epi_smem + e * 2048);
     const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
     const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !(ep.bias_m && ep.bias_n) &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
@@ -980,9 +1168,20 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     for (int w = 0; pair_get_work(sc, w, &wk); ++w, ++ti) {
       const int t = wk.tile;
       const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+      const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+      if (PRE && ep.res && key >= 0 && wk.raw < 0) {
+        // While the tile's MMAs run: pull this warp's 32 x 64 block of the residual into L2.
+        const float* rp = ep.res + (long long)bz * ep.sres;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int row = m0 + q * 32 + (lane >> 1) + 16 * i, col = n0 + hc0 * 32 + (lane & 1) * 32;
+          if (row < ep.m && col < ep.n)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + (long long)row * ep.ldres + col));
+        }
+      }
       if (!mbar_wait(acc_full, ti & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
       tc_fence_after();
-      const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+      if (e == 0 && lane == 0 && ti < 3) pair_stamp(dbg, 8 + 2 * ti);     // accumulator of tile ti complete
       bool released = false;
       auto release = [&]() -> bool {     // all of this warp's tcgen05.ld have completed
         tc_fence_before();
@@ -990,9 +1189,21 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         return true;
       };
-      if (m0 < ep.m) {
+      if (PRE && m0 < ep.m && wk.raw < 0) {
+        switch (key) {
+          case 0: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          case 1: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          case 2: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          case 3: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_GELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_RELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          default:
+            if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1);
+            break;
+        }
+      } else if (m0 < ep.m && eo >= 0) {
         if (wk.raw >= 0) {
-          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane, cc0, cc1);
+          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane, cc0, cc1, acc_scale_of(ep));
         } else
         switch (key) {
           case 0: released = epilogue_fast<BN, D2, ACT_NONE, 0, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
@@ -1009,10 +1220,12 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         }
       }
       if (!released) release();
+      if (e == 0 && lane == 0 && ti < 3) pair_stamp(dbg, 9 + 2 * ti);     // this warp's part of tile ti stored
     }
   }
 
   // ---------------- teardown ----------------
+  if (threadIdx.x == 0) pair_stamp(dbg, 14);
   tc_fence_before();
   __syncthreads();
   if (*abort_flag != 0 && warp == kTmaWarp && lane == 0) {
@@ -1026,6 +1239,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)L::kTmemCols));
   }
+  if (threadIdx.x == 0) pair_stamp(dbg, 15);
 }
 
 // hi / lo split of a whole tensor (constant operands, once at load).
@@ -1052,6 +1266,28 @@ __global__ void f16_split_kernel(const float* __restrict__ x, __half* __restrict
   hi[i] = h;
   lo[i] = __float2half_rn(__fmul_rn(__fsub_rn(v, __half2float(h)), kLoScale));
   if (beyond_half(v)) atomicCAS(err, 0, kRangeCode);
+}
+
+// The same split for an activation whose rows are a multiple of 8 floats, 16-byte aligned:
+// eight elements per thread (two 16-byte loads, one 16-byte store to each of hi and lo).
+__global__ void __launch_bounds__(256) f16_split_vec8_kernel(const float* __restrict__ x, uint4* __restrict__ hi,
+                                                             uint4* __restrict__ lo, int64_t rows, int64_t k8th,
+                                                             int64_t ld, int* err) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned bad = 0;
+  if (i < rows * k8th) {
+    const int64_t r = i / k8th, c = i % k8th;
+    const float4* src = reinterpret_cast<const float4*>(x + r * ld + c * 8);
+    const float4 v0 = __ldg(src), v1 = __ldg(src + 1);
+    uint2 h0, l0, h1, l1;
+    f16_split(v0, h0, l0);
+    f16_split(v1, h1, l1);
+    hi[i] = make_uint4(h0.x, h0.y, h1.x, h1.y);
+    lo[i] = make_uint4(l0.x, l0.y, l1.x, l1.y);
+    bad = beyond_half(v0.x) | beyond_half(v0.y) | beyond_half(v0.z) | beyond_half(v0.w) |
+          beyond_half(v1.x) | beyond_half(v1.y) | beyond_half(v1.z) | beyond_half(v1.w);
+  }
+  if (__any_sync(0xffffffffu, bad != 0) && (threadIdx.x & 31) == 0) atomicCAS(err, 0, kRangeCode);
 }
 
 // ---- host side ---------------------------------------------------------------------
@@ -1085,12 +1321,16 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t k, int
   cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes,
                            (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * elem_bytes};
   cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
+  // 1128: the plain 128-byte swizzle (K-major tiles of 128-byte rows); 128: the same span with 32-byte atoms
+  const bool sw128_plain = swizzle == 1128;
+  if (sw128_plain) swizzle = 128;
   if (swizzle != 0 && box_k * elem_bytes != swizzle) return false;
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                           : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+            sw128_plain ? CU_TENSOR_MAP_SWIZZLE_128B
+            : swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                             : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1163,15 +1403,28 @@ cudaError_t launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
   return cudaGetLastError();
 }
 
-template <int BN>
-cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap& mb, const CUtensorMap& mbl,
-                        const TcEpilogue& ep, const TcPlan& pl, float* workspace, int* err, cudaStream_t st) {
-  using L = PairSmem<BN>;
+template <int BN, bool PRE>
+cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap& ma, const CUtensorMap& mal,
+                        const CUtensorMap& mb, const CUtensorMap& mbl, const TcEpilogue& ep, const TcPlan& pl,
+                        float* workspace, int* err, cudaStream_t st) {
+  using L = PairSmem<BN, PRE>;
   static unsigned long long attr_done = 0;
-  if (cudaError_t e0 = ensure_dynamic_smem(gemm_tc_pair_kernel<BN>, L::kDynBytes, &attr_done)) return e0;
+  if (cudaError_t e0 = ensure_dynamic_smem(gemm_tc_pair_kernel<BN, PRE>, L::kDynBytes, &attr_done)) return e0;
   // pl.grid counts pairs; the cluster shape (2, 1, 1) is a compile-time attribute of the kernel.
-  gemm_tc_pair_kernel<BN><<<2 * pl.grid, kThreads, L::kDynBytes, st>>>(a, lda, k, mb, mbl, ep, pl.sc, pl.tiles_m,
-                                                                     pl.tiles_n, workspace, err);
+  static const int dbg = std::getenv("ALTIUS_CUDA_TC_DBG") ? std::atoi(std::getenv("ALTIUS_CUDA_TC_DBG")) : 0;
+  gemm_tc_pair_kernel<BN, PRE><<<2 * pl.grid, PRE ? kThreads + 32 : kThreads, L::kDynBytes, st>>>(a, lda, k, ma, mal, mb, mbl, ep, pl.sc,
+                                                                          pl.tiles_m, pl.tiles_n, workspace, err, dbg);
+  if (dbg & 0x1000) {
+    cudaStreamSynchronize(st);
+    static long long h[160][16];
+    cudaMemcpyFromSymbol(h, g_pair_stamps, sizeof(h));
+    for (int c : {0, 1, 64, 65, 146, 147}) {
+      if (c >= 2 * pl.grid) continue;
+      std::printf("pair cta %3d:", c);
+      for (int i = 1; i < 16; ++i) std::printf(" %lld", h[c][i] ? h[c][i] - h[c][0] : -1);
+      std::printf("\n");
+    }
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || pl.sc.tail_parts < 2) return e;
   const int tail = pl.sc.num_tiles - pl.sc.dp_tiles;
@@ -1203,9 +1456,15 @@ int pair_count() {
   static int n = -1;
   if (n < 0) {
     n = 0;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+      (void)cudaGetLastError();
+      n = sm_count() / 2;      // no device (a plan_only session): plan as for a B200
+      return n;
+    }
     {
-      using L = PairSmem<256>;
-      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      using L = PairSmem<256, false>;
+      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                L::kDynBytes) == cudaSuccess) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(sm_count() & ~1);
@@ -1217,7 +1476,7 @@ int pair_count() {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<256>, &cfg) == cudaSuccess && clusters > 0)
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<256, false>, &cfg) == cudaSuccess && clusters > 0)
           n = std::min(clusters, sm_count() / 2);
       }
       (void)cudaGetLastError();
@@ -1234,7 +1493,9 @@ int pair_count() {
 // (a K-sliced tail costs 1 / parts of a round); a shape that fills tensor memory with
 // one accumulator set cannot hide its epilogue. variant: 0 TF32 with B arriving split,
 // 1 TF32 with one B copy, 2 fp16 split.
-TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, bool allow_pairs) {
+// allow_pairs: 0 no CTA pairs, 1 pairs that stage A through registers, 2 pairs whose A arrives
+// already split by TMA (each SM then pulls 32 KB per stage and no thread touches a tile).
+TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, int allow_pairs) {
   static const TcShape cands[3] = {{256, 1, false}, {128, 1, false}, {64, 1, false}};
   // Debug toggle: ALTIUS_CUDA_TC_BN=64|128|256 forces the tile width.
   const char* ebn = std::getenv("ALTIUS_CUDA_TC_BN");
@@ -1263,20 +1524,26 @@ TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, 
   // CTA pairs (fp16 split, one GEMM, BN 256): 256 x 256 tiles, each SM pulls its A rows and
   // half of B (32 KB per stage), the pair's MMAs cost 128 clocks per SM; single accumulator set.
   const int pairs = allow_pairs ? pair_count() : 0;
-  if (f16 && batch == 1 && (k % 4) == 0 && pairs > 0 && (!fbn || fbn == 256)) {
-    const TcPlan pl = make_plan(m, n, k, batch, 256, 2, kbf, pairs);
+  if (f16 && batch == 1 && (k % (allow_pairs == 2 ? 8 : 4)) == 0 && pairs > 0 && (!fbn || fbn == 256)) {
+    const int pkb = allow_pairs == 2 ? 64 : kbf;       // pre-split A: 64 halves of K per stage
+    const TcPlan pl = make_plan(m, n, k, batch, 256, 2, pkb, pairs);
     double rounds = (double)(pl.sc.dp_tiles / pairs) + (pl.sc.dp_tiles % pairs ? 1.0 : 0.0);
     if (pl.sc.tail_parts >= 2) rounds += 1.0 / pl.sc.tail_parts + 0.05;
-    const double cost = rounds * (pl.sc.num_kb * std::max(6.0 * 128.0, 32768.0 / 28.0) + 256 * 24.0);
+    const double cost = rounds * (pl.sc.num_kb * (pkb / 32) * std::max(6.0 * 128.0, 32768.0 / 28.0) + 256 * 24.0);
     if (cost < best_cost - 1e-9) { best_cost = cost; best = {256, 2, true}; }
   }
   return best;
 }
 }  // namespace
 
-size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, bool allow_pairs) {
+bool gemm_tc_wants_presplit(int64_t m, int64_t n, int64_t k, int64_t batch) {
+  return pick_shape(m, n, k, batch, 2, 2).pair;
+}
+
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, int allow_pairs) {
   const TcShape sh = pick_shape(m, n, k, batch, variant, allow_pairs);
-  return make_plan(m, n, k, batch, sh.bn, sh.mt, variant == 2 ? BK16 : BK, sh.pair ? pair_count() : 0).workspace_bytes;
+  const int kbf = sh.pair && allow_pairs == 2 ? 64 : (variant == 2 ? BK16 : BK);
+  return make_plan(m, n, k, batch, sh.bn, sh.mt, kbf, sh.pair ? pair_count() : 0).workspace_bytes;
 }
 
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
@@ -1288,7 +1555,9 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
                     : (mode == 0 && q.b16_hi && q.b16_lo) ? TC_F16X3
                     : (q.b_lo ? TC_3X_BLO_TMA : TC_3X_SPLIT_B);
   const int variant = kmode == TC_F16X3 ? 2 : (kmode == TC_3X_BLO_TMA ? 0 : 1);
-  const TcShape sh = pick_shape(q.m, q.n, q.k, q.batch, variant, q.allow_pairs != 0);
+  const bool pre = q.allow_pairs == 2 && q.a16_hi && q.a16_lo;
+  const TcShape sh = pick_shape(q.m, q.n, q.k, q.batch, variant, pre ? 2 : (q.allow_pairs == 1 ? 1 : 0));
+  CUtensorMap mal;
   const int bn = sh.bn;
   CUtensorMap ma, mb, mbl;
   const int b_batched = (q.batch > 1 && q.stride_b > 0) ? 1 : 0;
@@ -1298,9 +1567,17 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
     if (b_batched || (q.ldb16 % 8) != 0) return cudaErrorInvalidValue;
     // A pair's CTAs each load their own 128 rows of A and half of the B tile.
     const int a_rows = sh.pair ? BM : sh.mt * BM, b_rows = sh.pair ? bn / 2 : bn;
-    if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK16, a_rows, 0)) return cudaErrorInvalidValue;
-    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
-    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
+    if (sh.pair && pre) {
+      if ((q.lda16 % 8) != 0) return cudaErrorInvalidValue;
+      if (!make_map(&ma, q.a16_hi, 2, q.k, q.m, 1, q.lda16, 0, 64, BM, 1128)) return cudaErrorInvalidValue;
+      if (!make_map(&mal, q.a16_lo, 2, q.k, q.m, 1, q.lda16, 0, 64, BM, 1128)) return cudaErrorInvalidValue;
+    } else {
+      if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK16, a_rows, 0)) return cudaErrorInvalidValue;
+      mal = ma;
+    }
+    const int bbox = (sh.pair && pre) ? 64 : BK16, bsw = (sh.pair && pre) ? 1128 : 64;
+    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, bbox, b_rows, bsw)) return cudaErrorInvalidValue;
+    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, bbox, b_rows, bsw)) return cudaErrorInvalidValue;
   } else if (kmode == TC_3X_SPLIT_B_MN) {
     // B [K, N]: N is the contiguous dimension, boxes of 32 columns x BK k-rows.
     if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK, sh.mt * BM, 64)) return cudaErrorInvalidValue;
@@ -1326,14 +1603,17 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.bias_n = q.bias_n; ep.bias_m = q.bias_m; ep.bias_scale = q.bias_scale;
   ep.act = q.act; ep.act_alpha = q.act_alpha; ep.act_beta = q.act_beta;
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
-  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, kmode == TC_F16X3 ? BK16 : BK, sh.pair ? pair_count() : 0);
+  ep.dbg = std::getenv("ALTIUS_CUDA_TC_DBG") ? std::atoi(std::getenv("ALTIUS_CUDA_TC_DBG")) : 0;
+  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, (sh.pair && pre) ? 64 : (kmode == TC_F16X3 ? BK16 : BK),
+                        sh.pair ? pair_count() : 0);
   if (pl.sc.tail_parts >= 2 && (!q.workspace || q.workspace_bytes < pl.workspace_bytes)) {
     // No (or too small a) workspace: fall back to whole tiles only.
     pl.sc.dp_tiles = pl.sc.num_tiles;
     pl.sc.tail_parts = 0;
   }
   float* ws = q.workspace;
-  if (sh.pair) return launch_pair<256>(q.a, q.lda, (int)q.k, mb, mbl, ep, pl, ws, err_word, st);
+  if (sh.pair && pre) return launch_pair<256, true>(q.a, q.lda, (int)q.k, ma, mal, mb, mbl, ep, pl, ws, err_word, st);
+  if (sh.pair) return launch_pair<256, false>(q.a, q.lda, (int)q.k, ma, ma, mb, mbl, ep, pl, ws, err_word, st);
 #define AC_TC(BNV)                                                                                         \
   (kmode == TC_1X ? launch_tc<BNV, 1, TC_1X>(ma, mb, mbl, ep, pl, a_batched, b_batched, ws, err_word, st)     \
    : kmode == TC_F16X3                                                                                     \
@@ -1353,6 +1633,13 @@ cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, i
                              int* err_word, cudaStream_t st) {
   const int64_t n = rows * k8;
   if (n == 0) return cudaSuccess;
+  if (k8 == k && (k % 8) == 0 && (ld % 4) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(hi) & 15) == 0 && (reinterpret_cast<uintptr_t>(lo) & 15) == 0) {
+    const int64_t n8 = n / 8;
+    f16_split_vec8_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(x, static_cast<uint4*>(hi), static_cast<uint4*>(lo),
+                                                                       rows, k / 8, ld, err_word);
+    return cudaGetLastError();
+  }
   f16_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, static_cast<__half*>(hi), static_cast<__half*>(lo),
                                                                rows, k, ld, k8, err_word);
   return cudaGetLastError();

@@ -24,6 +24,20 @@ cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, unsigned long long* do
   return e;
 }
 
+// Number of SMs of the current device (grids are sized in multiples of it); cached per
+// device ordinal. Falls back to 148 (B200) when the attribute cannot be read.
+inline int device_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return 148; }
+  int& n = cached[dev & 63];
+  if (n <= 0 && (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)) {
+    (void)cudaGetLastError();
+    n = 148;
+  }
+  return n;
+}
+
 // ---- elementwise -----------------------------------------------------------
 enum BinOp { BIN_ADD = 0, BIN_SUB, BIN_MUL, BIN_DIV, BIN_POW };
 
@@ -75,7 +89,10 @@ struct LayerNormParams {
   const float* gamma;
   const float* beta;
   float* sum_out;          // [rows, len] or null
-  float* out;
+  float* out;              // may be null when out16_hi / out16_lo are given
+  void* out16_hi;          // the result split for the fp16-split GEMM that consumes it: [rows, len]
+  void* out16_lo;          // halves each, hi = rn_fp16(y), lo = rn_fp16((y - hi) * 2^11); or null
+  int* err_word;           // receives kGemmRangeCode when the result does not fit that split
   int64_t rows;
   int64_t len;
   float eps;
@@ -153,7 +170,14 @@ struct GemmParams {
   const void* b16_hi;       // tensor-core path only: fp16 split of a constant B, [n, ldb16] halves each:
   const void* b16_lo;       // hi = rn_fp16(B), lo = rn_fp16((B - hi) * 2^11); or null
   int64_t ldb16;            // a multiple of 8
-  float* c; int64_t ldc; int64_t stride_c;
+  const void* a16_hi;       // tensor-core path only: fp16 split of A written by its producer, [m, lda16]
+  const void* a16_lo;       // halves each (same encoding as b16_hi / b16_lo); or null
+  int64_t lda16;            // a multiple of 8
+  float* c; int64_t ldc; int64_t stride_c;   // c may be null when c16_hi / c16_lo are given
+  void* c16_hi;             // tensor-core pair kernel only: the result also (or only) as fp16 hi / lo
+  void* c16_lo;             // halves [m, ldc16], for the GEMM that takes it as its pre-split A; or null
+  int64_t ldc16;
+  const float* b16_inv_scale;  // device scalar 2^-e when b16_hi / b16_lo hold B * 2^e; or null
   float alpha;
   float beta;               // applied to c_in (may alias c); 0: c_in not read
   const float* c_in; int64_t ldc_in; int64_t stride_c_in;
@@ -165,7 +189,8 @@ struct GemmParams {
   int residual_first;       // residual + v instead of v + residual (same value, kept for clarity)
   float* workspace;         // tensor-core path: scratch for K-sliced tail tiles, or null
   size_t workspace_bytes;
-  int allow_pairs;          // fp16 split: may run on clusters of two CTAs (tcgen05 .cta_group::2)
+  int allow_pairs;          // fp16 split on clusters of two CTAs (tcgen05 .cta_group::2): 0 no, 1 A staged
+                            // through registers, 2 A taken pre-split from a16_hi / a16_lo by TMA
 };
 cudaError_t launch_gemm_simt(const GemmParams& p, cudaStream_t st);
 
@@ -179,13 +204,22 @@ bool gemm_tc_supported(const GemmParams& p);
 cudaError_t launch_gemm_tc(const GemmParams& p, int mode, int* err_word, cudaStream_t st);
 // Scratch the tensor-core path wants for this problem (0 when its tiles fill whole rounds).
 // variant: 0 TF32 with B arriving split, 1 TF32 with one copy of B, 2 fp16 split.
-size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, bool allow_pairs);
+size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, int allow_pairs);
+// True when the fp16-split GEMM of this shape runs on CTA pairs that want A pre-split
+// (a16_hi / a16_lo): the producer of A, or a split kernel in front, then writes the halves.
+bool gemm_tc_wants_presplit(int64_t m, int64_t n, int64_t k, int64_t batch);
 constexpr int kGemmRangeCode = 21;
 // fp16 split of a constant [rows, k] operand (row stride ld) into [rows, k8] halves
 // (k8 >= k, a multiple of 8, padding zero); leaves kGemmRangeCode in *err_word when an
 // element exceeds the fp16 range.
+// `inv_scale` (constant operands): x is first multiplied by the power of two 2^e that brings its
+// largest magnitude into [2^13, 2^14), so that neither half meets the fp16 subnormals however
+// small the weights are; *inv_scale receives 2^-e for the GEMM's epilogue, `absmax_scratch` is
+// one device word of scratch. Null for activations (no scaling).
 cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, int64_t k, int64_t ld, int64_t k8,
-                             int* err_word, cudaStream_t st);
+                             int* err_word, float* inv_scale, unsigned* absmax_scratch, cudaStream_t st);
+// Whether the tensor-core pair kernel can write its result split (c16_hi / c16_lo) with this epilogue.
+bool gemm_tc_can_split_output(int act, bool bias_n, bool bias_m, bool c_in, float alpha, float bias_scale);
 // hi[i] = rn_tf32(x[i]); lo[i] = rn_tf32(x[i] - hi[i])
 cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st);
 
@@ -201,6 +235,8 @@ struct AttentionParams {
   int scale_mode;       // 1: multiply, 2: divide
   int use_tc;           // take the tcgen05 kernel when it supports the shape
   int* err_word;        // device word for the tcgen05 kernel's bounded waits (or null)
+  void* out16_hi;       // tcgen05 kernel only: the result also (or, with out == null, only) split into
+  void* out16_lo;       // fp16 hi / lo halves [B, T, H*hd] for the GEMM that consumes it; or null
 };
 bool attention_supported(const AttentionParams& p);
 // Dispatches to the tcgen05 kernel (use_tc and attention_tc_supported) or the CUDA-core kernel.

@@ -181,6 +181,8 @@ void detect_attention(Ctx& c, Plan& plan) {
     AttentionFusion f;
     int x = sm.inputs[0];
     if (c.val(x).rank != 3 || !c.single_use(x)) continue;
+    const int64_t sm_axis = sm.ints.empty() ? -1 : sm.ints[0];
+    if (!(sm_axis == -1 || sm_axis == c.val(x).rank - 1)) continue;   // the fused kernel is a last-axis softmax
     int px = c.producer[x];
     if (px < 0 || c.absorbed[px]) continue;
     if (c.node(px).op == AC_OP_MUL || c.node(px).op == AC_OP_DIV) {
@@ -354,6 +356,8 @@ void detect_softmax_scale(Ctx& c, Plan& plan) {
     const int x = n.inputs[0];
     const int p = c.producer[x];
     if (p < 0 || c.absorbed[p] || !c.single_use(x)) continue;
+    const int64_t axis = n.ints.empty() ? -1 : n.ints[0];
+    if (!(axis == -1 || axis == c.val(x).rank - 1)) continue;   // left to lower_node, which rejects it
     Node& m = c.node(p);
     if (m.op != AC_OP_MUL && m.op != AC_OP_DIV) continue;
     const Value& a = c.val(m.inputs[0]);
@@ -565,7 +569,9 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
 
   // ---- tensor-core eligibility (static part; alignment is re-checked at launch) ----
   const int mode = s->opt.gemm_mode;
-  const bool pairs = s->opt.gemm_pairs != 0;
+  // AcOptions.gemm_pairs: 0 (default) and 2 -> CTA pairs with A pre-split for TMA where the
+  // cost model prefers them, 1 -> pairs that stage A through registers, 3 -> no pairs.
+  const int pairs = s->opt.gemm_pairs == 0 ? 2 : (s->opt.gemm_pairs == 3 ? 0 : s->opt.gemm_pairs);
   // Below about 8 MFLOP the CUDA-core kernel wins, except for few rows against a long K (the
   // squeeze-excite products, batch x channels): one or two of its blocks then walk K alone,
   // while the persistent kernel cuts K into slices over the idle SMs.
@@ -607,6 +613,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word, st);
     });
   }
+  const int b_plain = b_use;   // the operand before any TF32 rounding
   if (tc && b16_hi < 0 && mode != 2 && g.tb && em.c.val(b_use).is_const) {
     // TF32 hi / lo split of a constant rhs, prepared once.
     const int64_t cnt = em.c.val(b_use).numel();
@@ -619,6 +626,22 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     b_use = hi;
   }
   const int bsrc = b_use;
+  // CTA pairs that take A by TMA want it already split into fp16 hi / lo halves: a split
+  // kernel in front of the GEMM writes them (rows of K8 halves, K8 a multiple of 8).
+  int a16_hi = -1, a16_lo = -1;
+  int64_t lda16 = 0;
+  if (tc && b16_hi >= 0 && pairs == 2 && g.batch == 1 && (g.k % 8) == 0 &&
+      gemm_tc_wants_presplit(g.m, g.n, g.k, g.batch)) {
+    lda16 = g.k;
+    const int64_t floats = g.m * lda16 / 2;
+    a16_hi = new_value(em.c, floats, false);
+    a16_lo = new_value(em.c, floats, false);
+    const int hi = a16_hi, lo = a16_lo;
+    const int64_t mm = g.m, kk = g.k, ld = g.lda, off = a_off;
+    em.add("act_f16_split", op, {a}, {hi, lo}, 8.0 * mm * kk, 0, [=](cudaStream_t st) {
+      return launch_f16_split(s->fptr(a) + off, s->fptr_mut(hi), s->fptr_mut(lo), mm, kk, ld, kk, s->err_word, st);
+    });
+  }
   // Scratch for the K-sliced tail tiles of the persistent kernel (lives for this step only).
   int ws = -1;
   size_t ws_bytes = 0;
@@ -626,7 +649,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b16_hi >= 0 ? 2 : (b_lo >= 0 ? 0 : 1), pairs);
     if (ws_bytes) ws = new_value(em.c, (int64_t)(ws_bytes / 4), false);
   }
-  std::vector<int> reads = {a, bsrc, b_lo, b16_hi, b16_lo, c_in, bias_n, bias_m, res};
+  std::vector<int> reads = {a, bsrc, b_plain, b_lo, b16_hi, b16_lo, a16_hi, a16_lo, c_in, bias_n, bias_m, res};
   const char* kind = !tc ? "gemm_fp32_simt"
                      : (mode == 2 ? "gemm_tf32x1_tcgen05" : (b16_hi >= 0 ? "gemm_f16x3_tcgen05" : "gemm_tf32x3_tcgen05"));
   std::vector<int> writes = {out};
@@ -635,7 +658,10 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     GemmParams p{};
     p.workspace = ws >= 0 ? s->fptr_mut(ws) : nullptr;
     p.workspace_bytes = ws_bytes;
-    p.allow_pairs = pairs ? 1 : 0;
+    p.allow_pairs = pairs;
+    p.a16_hi = a16_hi >= 0 ? s->ptr(a16_hi) : nullptr;
+    p.a16_lo = a16_lo >= 0 ? s->ptr(a16_lo) : nullptr;
+    p.lda16 = lda16;
     p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
     p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
     p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
@@ -652,6 +678,8 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.act = act; p.act_alpha = aa; p.act_beta = ab;
     p.residual = res >= 0 ? s->fptr(res) + c_off : nullptr; p.ld_res = g.ldc; p.stride_res = g.sc;
     if (tc && gemm_tc_supported(p)) return launch_gemm_tc(p, mode, s->err_word, st);
+    // The CUDA-core kernel multiplies the operand as given, not a TF32-rounded copy of it.
+    if (b_lo >= 0) { p.b = s->fptr(b_plain) + b_off; p.b_lo = nullptr; }
     return launch_gemm_simt(p, st);
   }, ws >= 0 ? 2 : 1);
 }
@@ -1368,8 +1396,6 @@ bool order_steps(AcSession& s) {
 void lower_graph(AcSession& s) {
   Ctx c(s);
   const int nv = (int)s.values.size();
-  // Scratch values are appended while lowering; references into `values` must stay valid.
-  s.values.reserve(s.values.size() + 4 * s.nodes.size() + 16);
   c.producer.assign(nv, -1);
   c.consumers.assign(nv, {});
   c.is_output.assign(nv, 0);
@@ -1418,11 +1444,18 @@ void lower_graph(AcSession& s) {
   }
   for (int o : s.outputs) s.storages[s.values[o].storage].pinned_live = true;
 
+  const size_t graph_values = s.values.size(), graph_storages = s.storages.size();
   for (int attempt = 0; attempt < 2; ++attempt) {
     const bool fuse = attempt == 0 && !s.opt.disable_fusion;
     Plan plan;
     std::fill(c.absorbed.begin(), c.absorbed.end(), 0);
     s.steps.clear();
+    // Scratch values and storages of a first attempt do not survive into the second.
+    s.values.resize(graph_values);
+    s.storages.resize(graph_storages);
+    c.producer.resize(graph_values);
+    c.consumers.resize(graph_values);
+    c.is_output.resize(graph_values);
     if (fuse) {
       detect_attention(c, plan);
       detect_epilogues(c, plan);

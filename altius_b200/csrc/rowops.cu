@@ -11,6 +11,7 @@
 
 #include "kernels.h"
 #include "ref_math.cuh"
+#include "tc_common.cuh"
 
 namespace ac {
 namespace {
@@ -114,7 +115,7 @@ template <int MODE>
 cudaError_t softmax_dispatch(const float* x, float* out, int64_t rows, int64_t len,
                              const float* scale, cudaStream_t st) {
   const int64_t blocks64 = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
+  const unsigned blocks = (unsigned)(blocks64 > device_sm_count() * 64 ? device_sm_count() * 64 : blocks64);
   const int vpt = (int)((len + 31) / 32);
 #define AC_SM(V)                                                                         \
   softmax_warp<V, MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, (int)len, scale)
@@ -141,6 +142,7 @@ cudaError_t softmax_dispatch(const float* x, float* out, int64_t rows, int64_t l
 struct LnDev {
   const float* x; const float* pre_bias; const float* residual; const float* gamma;
   const float* beta; float* sum_out; float* out; int64_t rows; int len; float eps; int gelu;
+  uint2* hi; uint2* lo; int* err;    // fp16 split of the result (4 halves per uint2), or null
 };
 
 __device__ __forceinline__ float ln_prologue(const LnDev& p, float v, int col, float res) {
@@ -172,16 +174,18 @@ __device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lan
 // The fused variants are bound by arithmetic (the Gelu above all), not by memory: they keep
 // only the current row in registers (no prefetch of the next one), which lets two or three
 // blocks share an SM.
-template <int NV, bool FUSED, bool GELU>
+// SPLIT: the result is (also) written as fp16 hi / lo halves for the GEMM that consumes it.
+template <int NV, bool FUSED, bool GELU, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev p) {
   constexpr bool PREFETCH = !FUSED;
+  unsigned seen = 0;
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
   const int nvec = p.len >> 2;
   const float inv_n = __fdiv_rn(1.f, (float)p.len);
   int64_t row = warp;
-  if (row >= p.rows) return;
+  if (row >= p.rows) return;      // whole warps only: `warp` is uniform across the lanes
   float4 v[NV], r[FUSED ? NV : 1];
   float4 nv[PREFETCH ? NV : 1];
   if (FUSED) ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
@@ -246,7 +250,14 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
         o.y = fmaf(__fmul_rn(v[i].y, inv), g.y, b.y);
         o.z = fmaf(__fmul_rn(v[i].z, inv), g.z, b.z);
         o.w = fmaf(__fmul_rn(v[i].w, inv), g.w, b.w);
-        orow[c] = o;
+        if (!SPLIT || p.out) orow[c] = o;
+        if (SPLIT) {
+          uint2 h, l;
+          tc::f16_split(o, h, l);
+          p.hi[row * nvec + c] = h;
+          p.lo[row * nvec + c] = l;
+          seen |= tc::split_seen(o);
+        }
       }
     }
     if (!has_next) break;
@@ -258,6 +269,7 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
       ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
     }
   }
+  if (SPLIT) tc::split_report_warp(seen, p.err);
 }
 
 // Any length / alignment: one warp per row, values recomputed from global
@@ -384,7 +396,8 @@ cudaError_t reduce_last_dispatch(const float* x, float* out, int64_t rows, int64
     // One pair of rows per warp up to six blocks per SM (measured: a second pass of a
     // partly idle grid costs more than the extra blocks), a grid-stride walk beyond that.
     const int64_t want = (rows + 2 * kWarpsPerBlock - 1) / (2 * kWarpsPerBlock);
-    const unsigned vb = (unsigned)(want > 148 * 6 ? 148 * 6 : want);
+    const int64_t cap = (int64_t)device_sm_count() * 6;
+    const unsigned vb = (unsigned)(want > cap ? cap : want);
     switch (len / 128) {
       case 1: reduce_last_vec<MODE, 1><<<vb, kThreads, 0, st>>>(x, out, rows); break;
       case 2: reduce_last_vec<MODE, 2><<<vb, kThreads, 0, st>>>(x, out, rows); break;
@@ -397,13 +410,13 @@ cudaError_t reduce_last_dispatch(const float* x, float* out, int64_t rows, int64
     }
     return cudaGetLastError();
   }
-  const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
+  const unsigned blocks = (unsigned)(blocks64 > device_sm_count() * 64 ? device_sm_count() * 64 : blocks64);
   reduce_last<MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, len);
   return cudaGetLastError();
 }
 
 // ---- whole-tensor max (compute_reduce_max, session.rs:1292-1305) ---------------------
-constexpr int kMaxAllBlocks = 148 * 8;
+constexpr int kMaxAllBlocks = 1184;   // fixed bound on the partial maxima (sizes the scratch), not a grid rule
 
 __global__ void __launch_bounds__(kThreads) max_all_stage(const float* __restrict__ x,
                                                           float* __restrict__ out, int64_t n) {
@@ -435,24 +448,34 @@ cudaError_t launch_softmax(const float* x, float* out, int64_t rows, int64_t len
 cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
   if (q.rows == 0 || q.len == 0) return cudaSuccess;
   LnDev p{q.x, q.pre_bias, q.residual, q.gamma, q.beta, q.sum_out, q.out, q.rows, (int)q.len,
-          q.eps, q.gelu};
+          q.eps, q.gelu, static_cast<uint2*>(q.out16_hi), static_cast<uint2*>(q.out16_lo), q.err_word};
+  const bool split = q.out16_hi != nullptr;
+  if (split && (!q.out16_lo || !q.err_word)) return cudaErrorInvalidValue;
+  if (!split && !q.out) return cudaErrorInvalidValue;
   const int64_t blocks64 = (q.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-  const unsigned blocks = (unsigned)(blocks64 > 148 * 64 ? 148 * 64 : blocks64);
+  const unsigned blocks = (unsigned)(blocks64 > device_sm_count() * 64 ? device_sm_count() * 64 : blocks64);
   auto al = [](const void* ptr) { return ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
   const bool vec = (q.len % 4) == 0 && q.len <= 32 * 4 * 8 && al(q.x) && al(q.residual) && al(q.pre_bias) &&
-                   al(q.gamma) && al(q.beta) && al(q.sum_out) && al(q.out);
+                   al(q.gamma) && al(q.beta) && al(q.sum_out) && al(q.out) && al(q.out16_hi) && al(q.out16_lo);
+  if (split && !vec) return cudaErrorInvalidValue;   // the split output exists on the vector path only
   if (vec) {
     const int nv = (int)((q.len / 4 + 31) / 32);
     const bool fused = q.pre_bias || q.residual || q.gelu || q.sum_out;
     // Two blocks of 8 warps per SM: several rows per warp, so the prefetch of the next
     // row overlaps the stores of the current one.
     const int depth = fused ? 3 : 2;    // the fused variants are bound by arithmetic (measured: 1, 3, 4 are slower for the plain one)
-    const unsigned vblocks = blocks64 > 148 * depth ? 148 * depth : (unsigned)blocks64;
+    const int64_t vcap = (int64_t)device_sm_count() * depth;
+    const unsigned vblocks = blocks64 > vcap ? (unsigned)vcap : (unsigned)blocks64;
+#define AC_LN2(NVV, SP)                                                                     \
+  do {                                                                                     \
+    if (fused && q.gelu) layer_norm_vec<NVV, true, true, SP><<<vblocks, kThreads, 0, st>>>(p);  \
+    else if (fused) layer_norm_vec<NVV, true, false, SP><<<vblocks, kThreads, 0, st>>>(p);      \
+    else layer_norm_vec<NVV, false, false, SP><<<vblocks, kThreads, 0, st>>>(p);                \
+  } while (0)
 #define AC_LN(NVV)                                                                         \
   do {                                                                                     \
-    if (fused && q.gelu) layer_norm_vec<NVV, true, true><<<vblocks, kThreads, 0, st>>>(p);  \
-    else if (fused) layer_norm_vec<NVV, true, false><<<vblocks, kThreads, 0, st>>>(p);      \
-    else layer_norm_vec<NVV, false, false><<<vblocks, kThreads, 0, st>>>(p);                \
+    if (split) AC_LN2(NVV, true);                                                          \
+    else AC_LN2(NVV, false);                                                               \
   } while (0)
     if (nv <= 1) AC_LN(1);
     else if (nv <= 2) AC_LN(2);
@@ -461,6 +484,7 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
     else if (nv <= 6) AC_LN(6);
     else AC_LN(8);
 #undef AC_LN
+#undef AC_LN2
   } else {
     layer_norm_generic<<<blocks, kThreads, 0, st>>>(p);
   }

@@ -274,8 +274,16 @@ int check_err_word(AcSession* s) {
 }
 
 int run_common(AcSession* s, const void* const* ins, void* const* outs, bool device_io) {
-  if (!s || (!ins && !s->inputs.empty()) || !outs) return set_err(s, AC_ERR_INVALID, "null argument");
+  if (!s) return set_err(s, AC_ERR_INVALID, "null argument");
+  std::lock_guard<std::recursive_mutex> lock(s->run_mutex);
+  if ((!ins && !s->inputs.empty()) || !outs) return set_err(s, AC_ERR_INVALID, "null argument");
   if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
+  // Every buffer is checked before anything is enqueued: an error return leaves no copy or
+  // kernel in flight that could still write into the caller's memory.
+  for (size_t i = 0; i < s->inputs.size(); ++i)
+    if (!ins[i]) return set_err(s, AC_ERR_INVALID, "null input buffer");
+  for (size_t i = 0; i < s->outputs.size(); ++i)
+    if (!outs[i]) return set_err(s, AC_ERR_INVALID, "null output buffer");
   if (s->use_fallback) {
     const int rc = run_common(s->fallback, ins, outs, device_io);
     if (rc != AC_OK) s->err = s->fallback->err;
@@ -285,36 +293,38 @@ int run_common(AcSession* s, const void* const* ins, void* const* outs, bool dev
   if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, cudaGetErrorString(e));
   const cudaMemcpyKind in_kind = device_io ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
   const cudaMemcpyKind out_kind = device_io ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost;
+  // An error after this point drains the stream before returning, for the same reason.
+  auto fail_cuda = [&](const std::string& what, cudaError_t err) {
+    cudaStreamSynchronize(s->stream);
+    return set_err(s, AC_ERR_CUDA, what + cudaGetErrorString(err));
+  };
   for (size_t i = 0; i < s->inputs.size(); ++i) {
-    if (!ins[i]) return set_err(s, AC_ERR_INVALID, "null input buffer");
     const Value& v = s->values[s->inputs[i]];
     e = cudaMemcpyAsync(s->ptr(s->inputs[i]), ins[i], v.bytes(), in_kind, s->stream);
-    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("input copy: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail_cuda("input copy: ", e);
   }
   if (s->opt.enable_profiling) {
     const size_t n = s->steps.size();
     for (size_t i = 0; i < n; ++i) {
       // enable_profiling 2: every step starts on a cold L2 that holds no dirty lines.
-      if (s->sweep_buf) l2_sweep_kernel<<<148 * 8, 256, 0, s->stream>>>(
+      if (s->sweep_buf) l2_sweep_kernel<<<device_sm_count() * 8, 256, 0, s->stream>>>(
           reinterpret_cast<const float4*>(s->sweep_buf), kSweepBytes / 16, reinterpret_cast<float*>(s->sweep_buf));
       cudaEventRecord(s->events[2 * i], s->stream);
       e = s->steps[i].fn(s->stream);
-      if (e != cudaSuccess)
-        return set_err(s, AC_ERR_CUDA, s->steps[i].kind + ": " + cudaGetErrorString(e));
+      if (e != cudaSuccess) return fail_cuda(s->steps[i].kind + ": ", e);
       cudaEventRecord(s->events[2 * i + 1], s->stream);
     }
   } else if (s->graph_exec) {
     e = cudaGraphLaunch(s->graph_exec, s->stream);
-    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("graph launch: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail_cuda("graph launch: ", e);
   } else {
     e = replay(s, s->stream);
-    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail_cuda("kernel launch: ", e);
   }
   for (size_t i = 0; i < s->outputs.size(); ++i) {
-    if (!outs[i]) return set_err(s, AC_ERR_INVALID, "null output buffer");
     const Value& v = s->values[s->outputs[i]];
     e = cudaMemcpyAsync(outs[i], s->ptr(s->outputs[i]), v.bytes(), out_kind, s->stream);
-    if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("output copy: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail_cuda("output copy: ", e);
   }
   cudaMemcpyAsync(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost, s->stream);
   e = cudaStreamSynchronize(s->stream);
@@ -440,10 +450,17 @@ int altius_cuda_run_device(AcSession* s, const void* const* d_ins, void* const* 
 }
 
 int altius_cuda_run_batches(AcSession* s, int32_t n_batches, const void* const* ins, void* const* outs) {
-  if (!s || n_batches < 0 || (!ins && !s->inputs.empty() && n_batches) || (!outs && n_batches))
+  if (!s) return set_err(s, AC_ERR_INVALID, "bad argument");
+  std::lock_guard<std::recursive_mutex> lock(s->run_mutex);
+  if (n_batches < 0 || (!ins && !s->inputs.empty() && n_batches) || (!outs && n_batches))
     return set_err(s, AC_ERR_INVALID, "bad argument");
   if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
   const size_t ni = s->inputs.size(), no = s->outputs.size();
+  // All buffers of all batches are checked before the first copy is enqueued.
+  for (size_t i = 0; i < (size_t)n_batches * ni; ++i)
+    if (!ins[i]) return set_err(s, AC_ERR_INVALID, "null input buffer");
+  for (size_t i = 0; i < (size_t)n_batches * no; ++i)
+    if (!outs[i]) return set_err(s, AC_ERR_INVALID, "null output buffer");
   // Sessions that profile, or that have switched to their fallback plan, take the plain path.
   if (s->opt.enable_profiling || s->use_fallback || n_batches < 2) {
     for (int b = 0; b < n_batches; ++b) {
@@ -469,7 +486,6 @@ int altius_cuda_run_batches(AcSession* s, int32_t n_batches, const void* const* 
     if (b >= 2) e = cudaStreamWaitEvent(s->copy_stream, s->consumed[k], 0);
     for (size_t i = 0; i < ni && e == cudaSuccess; ++i) {
       const void* src = ins[(size_t)b * ni + i];
-      if (!src) return set_err(s, AC_ERR_INVALID, "null input buffer");
       e = cudaMemcpyAsync(s->staging[k][i], src, s->values[s->inputs[i]].bytes(), cudaMemcpyHostToDevice, s->copy_stream);
     }
     if (e == cudaSuccess) e = cudaEventRecord(s->staged[k], s->copy_stream);
@@ -482,13 +498,17 @@ int altius_cuda_run_batches(AcSession* s, int32_t n_batches, const void* const* 
     if (e == cudaSuccess) e = s->graph_exec ? cudaGraphLaunch(s->graph_exec, s->stream) : replay(s, s->stream);
     for (size_t i = 0; i < no && e == cudaSuccess; ++i) {
       void* dst = outs[(size_t)b * no + i];
-      if (!dst) return set_err(s, AC_ERR_INVALID, "null output buffer");
       e = cudaMemcpyAsync(dst, s->ptr(s->outputs[i]), s->values[s->outputs[i]].bytes(), cudaMemcpyDeviceToHost, s->stream);
     }
   }
   if (e == cudaSuccess) e = cudaMemcpyAsync(s->err_host, s->err_word, sizeof(int), cudaMemcpyDeviceToHost, s->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s->stream);
-  if (e != cudaSuccess) return set_err(s, AC_ERR_CUDA, std::string("run_batches: ") + cudaGetErrorString(e));
+  if (e != cudaSuccess) {
+    // Whatever was enqueued before the failure finishes before the caller gets its buffers back.
+    if (s->copy_stream) cudaStreamSynchronize(s->copy_stream);
+    cudaStreamSynchronize(s->stream);
+    return set_err(s, AC_ERR_CUDA, std::string("run_batches: ") + cudaGetErrorString(e));
+  }
   if (const int rc = check_err_word(s))   // out of fp16 range somewhere: all batches again on the fallback plan
     return rc == 1 ? altius_cuda_run_batches(s, n_batches, ins, outs) : rc;
   return AC_OK;
@@ -496,10 +516,16 @@ int altius_cuda_run_batches(AcSession* s, int32_t n_batches, const void* const* 
 
 int altius_cuda_time_device_runs(AcSession* s, const void* const* d_ins, void* const* d_outs,
                                  int32_t iters, float* elapsed_ms) {
-  if (!s || !elapsed_ms || iters <= 0 || !d_outs || (!d_ins && !s->inputs.empty()))
+  if (!s) return set_err(s, AC_ERR_INVALID, "bad argument");
+  std::lock_guard<std::recursive_mutex> lock(s->run_mutex);
+  if (!elapsed_ms || iters <= 0 || !d_outs || (!d_ins && !s->inputs.empty()))
     return set_err(s, AC_ERR_INVALID, "bad argument");
   if (s->opt.plan_only) return set_err(s, AC_ERR_NO_DEVICE, "session was created with plan_only");
   if (s->opt.enable_profiling) return set_err(s, AC_ERR_INVALID, "not available on a profiling session");
+  for (size_t i = 0; i < s->inputs.size(); ++i)
+    if (!d_ins[i]) return set_err(s, AC_ERR_INVALID, "null input buffer");
+  for (size_t i = 0; i < s->outputs.size(); ++i)
+    if (!d_outs[i]) return set_err(s, AC_ERR_INVALID, "null output buffer");
   if (s->use_fallback) {
     const int rc = altius_cuda_time_device_runs(s->fallback, d_ins, d_outs, iters, elapsed_ms);
     if (rc != AC_OK) s->err = s->fallback->err;

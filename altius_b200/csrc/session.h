@@ -5,9 +5,11 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <deque>
 #include <functional>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -92,7 +94,7 @@ struct AcSession {
   int device = 0;
   AcOptions opt{};
   int64_t opset = 13;
-  std::vector<ac::Value> values;
+  std::deque<ac::Value> values;        // a deque: lowering appends scratch values while it holds references
   std::vector<ac::Node> nodes;
   std::vector<int> inputs, outputs;
   std::vector<int> order;              // topological order of node ids
@@ -123,6 +125,10 @@ struct AcSession {
   std::unique_ptr<ac::GraphCopy> desc;
   AcSession* fallback = nullptr;
   bool use_fallback = false;
+  // run / run_device / run_batches / time_device_runs share the arena, the staging buffers, the
+  // error word and the fallback switch: one caller at a time per session (recursive: a run
+  // re-enters itself once when it switches to the fallback plan).
+  std::recursive_mutex run_mutex;
 
   void* ptr(int value) const {
     const ac::Storage& st = storages[values[value].storage];

@@ -43,6 +43,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+// The same with the non-blocking test_wait: the thread keeps polling instead of being suspended
+// by the hardware, which notices arrivals from another CTA of the cluster sooner.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < (kWaitLimit << 4); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
 // A whole warp waits on an mbarrier phase: one lane polls (fewer probes of shared memory
 // while the tensor core fetches its operands from it), the others get the result by shuffle.
 __device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, int lane) {
@@ -107,6 +124,22 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same load without the wait: several loads can be in flight before one tc_wait_ld().
+__device__ __forceinline__ void tc_ld_32x32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+        "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+        "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Round to nearest (ties away from zero) to TF32's 10 mantissa bits, on the
 // integer ALU: cvt.rna.tf32.f32 gives the same bits but issues on the
 // quarter-rate conversion pipe.
@@ -132,6 +165,33 @@ __device__ __forceinline__ void f16_split(float4 x, uint2& hi, uint2& lo) {
                                         __fmul_rn(__fsub_rn(x.w, f23.y), kLoScale));
   hi.x = *reinterpret_cast<const uint32_t*>(&h01); hi.y = *reinterpret_cast<const uint32_t*>(&h23);
   lo.x = *reinterpret_cast<const uint32_t*>(&l01); lo.y = *reinterpret_cast<const uint32_t*>(&l23);
+}
+
+// ---- range of the fp16 split ------------------------------------------------------------
+// Code left in the session's error word when an operand does not fit the fp16 split; the host
+// then repeats the run on the 3xTF32 plan.
+constexpr int kRangeCode = 21;
+// |x| > 65504 (the largest fp16), infinities included, NaN excluded.
+__device__ __forceinline__ unsigned beyond_half(float x) {
+  const unsigned ab = __float_as_uint(x) & 0x7FFFFFFFu;
+  return (ab - 0x477FE001u) <= (0x7F800000u - 0x477FE001u) ? 1u : 0u;
+}
+// What a thread has seen of the values it split: bit 0 an element beyond fp16, bit 1 an
+// element of at least 2^-14 (the smallest normal fp16), bit 2 a non-zero element below it.
+// Below 2^-14 `hi` is a subnormal and the scaled remainder has an absolute floor of 2^-36:
+// harmless beside larger elements of the same rows, but a region whose non-zero elements are
+// ALL that small would lose its relative precision, so it is reported like an overflow.
+__device__ __forceinline__ unsigned split_seen(float x) {
+  const unsigned ab = __float_as_uint(x) & 0x7FFFFFFFu;
+  return beyond_half(x) | (ab >= 0x38800000u ? 2u : (ab != 0u ? 4u : 0u));
+}
+__device__ __forceinline__ unsigned split_seen(float4 v) {
+  return split_seen(v.x) | split_seen(v.y) | split_seen(v.z) | split_seen(v.w);
+}
+// Verdict of a warp over everything its lanes have seen: out of range, or only tiny values.
+__device__ __forceinline__ void split_report_warp(unsigned seen, int* err) {
+  const unsigned all = __reduce_or_sync(0xffffffffu, seen);
+  if (((all & 1u) || ((all & 4u) && !(all & 2u))) && (threadIdx.x & 31) == 0) atomicCAS(err, 0, kRangeCode);
 }
 
 // Byte offset of 8-byte chunk `c8` (4 halves) of row `row` in a K-major fp16 tile with

@@ -53,7 +53,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--no-fuse", action="store_true")
-    ap.add_argument("--pairs", action="store_true", help="fp16-split GEMM on clusters of two CTAs")
+    ap.add_argument("--pairs", type=int, default=0, help="fp16-split GEMM on clusters of two CTAs: 1 A staged through registers, 2 A pre-split")
     ap.add_argument("--bias", action="store_true", help="gemm: + bias[n] in the epilogue")
     ap.add_argument("--gelu", action="store_true", help="gemm: Gelu after the bias")
     ap.add_argument("--residual", action="store_true", help="gemm: + residual[m, n] in the epilogue")

@@ -432,8 +432,9 @@ class CudaSessionBuilder:
         self.gemm_mode = mode
         return self
 
-    def with_gemm_pairs(self, b: bool):
-        """fp16-split GEMMs on clusters of two CTAs (see AcOptions.gemm_pairs)."""
+    def with_gemm_pairs(self, b: int):
+        """fp16-split GEMMs on clusters of two CTAs (AcOptions.gemm_pairs: 0 / 2 the default
+        pre-split pairs, 1 register-staged pairs, 3 the one-CTA kernel only)."""
         self.gemm_pairs = b
         return self
 

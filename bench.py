@@ -212,7 +212,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemm-mode", type=int, default=0)
-    ap.add_argument("--gemm-pairs", action="store_true", help="fp16-split GEMMs on clusters of two CTAs")
+    ap.add_argument("--gemm-pairs", type=int, default=0, help="AcOptions.gemm_pairs (0 default, 3: the one-CTA GEMM kernel only)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-micrograph", action="store_true")
     args = ap.parse_args()

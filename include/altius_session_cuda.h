@@ -154,9 +154,13 @@ typedef struct AcOptions {
   int32_t plan_only;         /* 1: infer shapes, lower and plan the arena without
                                 touching a GPU; run() then fails. For inspecting
                                 the schedule on a machine without a device.      */
-  int32_t gemm_pairs;        /* 1: fp16-split GEMMs of 256-row tiles on clusters of two
-                                CTAs (tcgen05 .cta_group::2, each SM stages half of the
-                                weight tile); same results, not faster yet: off by default */
+  int32_t gemm_pairs;        /* fp16-split GEMMs of 256 x 256 tiles on clusters of two CTAs
+                                (tcgen05 .cta_group::2, each SM stages its rows of A and half
+                                of the weight tile). 0 (default) and 2: where the cost model
+                                prefers them, with A arriving already split into fp16 halves
+                                (written by the kernel that produced it, or by a split kernel
+                                in front) so that every tile comes by TMA; 1: pairs that split
+                                A in registers; 3: never (the one-CTA kernel). Same results. */
   int32_t reserved;
 } AcOptions;
 

@@ -366,29 +366,34 @@ def test_fp16_split_is_not_used_for_weights_out_of_range(cuda_lib):
 
 
 @pytest.mark.parametrize("ashape,bshape", [((2, 197, 768), (768, 2304)), ((394, 3072), (3072, 768)), ((1000, 768), (768, 768)),
-                                            ((300, 100), (100, 72)), ((257, 36), (36, 513)), ((5000, 64), (64, 256))])
-def test_matmul_on_cta_pairs(cuda_lib, ashape, bshape):
+                                            ((300, 100), (100, 72)), ((257, 36), (36, 513)), ((5000, 64), (64, 256)),
+                                            ((6304, 768), (768, 768))])
+@pytest.mark.parametrize("pairs", [1, 2])
+def test_matmul_on_cta_pairs(cuda_lib, ashape, bshape, pairs):
     """The fp16-split GEMM on clusters of two CTAs (tcgen05 .cta_group::2; each CTA stages its
     rows of A and half of the weight tile) computes the same products as the one-CTA kernel;
-    only the K-slicing of tail tiles (and with it the order of a few additions) can differ."""
+    only the K-slicing of tail tiles (and with it the order of a few additions) can differ.
+    pairs 1: each CTA splits its rows of A in registers; pairs 2: A arrives as fp16 hi / lo
+    halves written by a kernel in front, and every tile of a stage comes by TMA."""
     a = RNG.standard_normal(ashape).astype(np.float32)
     w = RNG.standard_normal(bshape).astype(np.float32)
     m = single_op_model("MatMul", [a], [w])
     want = run_oracle(m, [a])[0]
-    got = run_cuda(m, [a], pairs=True)[0]
+    got = run_cuda(m, [a], pairs=pairs)[0]
     bound = 1e-5 * np.abs(want) + 5e-6 * (np.abs(a).reshape(-1, ashape[-1]) @ np.abs(w)).reshape(want.shape)
     assert (np.abs(got - want) <= bound).all()
-    single = run_cuda(m, [a])[0]
+    single = run_cuda(m, [a], pairs=3)[0]
     assert (np.abs(got - single) <= 2e-6 * (np.abs(a).reshape(-1, ashape[-1]) @ np.abs(w)).reshape(want.shape)).all()
 
 
-def test_cta_pairs_in_a_model_with_epilogues_and_range_fallback(cuda_lib):
+@pytest.mark.parametrize("pairs", [1, 2])
+def test_cta_pairs_in_a_model_with_epilogues_and_range_fallback(cuda_lib, pairs):
     from altius_b200 import configs
     from altius_b200.session import CudaSessionBuilder
     model, feeds = configs.vit_base_16(batch=2, depth=2)
     x = next(iter(feeds.values()))
-    want = run_cuda(model, [x])[0]
-    sess = CudaSessionBuilder(model).with_gemm_pairs(True).build()
+    want = run_cuda(model, [x], pairs=3)[0]
+    sess = CudaSessionBuilder(model).with_gemm_pairs(pairs).build()
     try:
         got = sess.run([x])[0]
         assert np.abs(got - want).max() <= 1e-4 and (got.argmax(-1) == want.argmax(-1)).all()
