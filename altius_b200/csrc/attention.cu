@@ -271,6 +271,7 @@ bool attention_supported(const AttentionParams& p) {
 
 cudaError_t launch_attention(const AttentionParams& p, cudaStream_t st) {
   if (p.use_tc && attention_tc_supported(p)) return launch_attention_tc(p, st);
+  if (p.out16_hi || !p.out) return cudaErrorInvalidValue;   // the split result exists in the tcgen05 kernel only
   if (!attention_supported(p)) return cudaErrorInvalidValue;
   AttnDev d;
   d.q = p.q; d.k = p.k; d.v = p.v;

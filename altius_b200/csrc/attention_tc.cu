@@ -66,7 +66,8 @@ constexpr uint32_t kTmemCols = 512;
 struct AttnTcDev {
   const float* q; const float* k; const float* v;
   long long row_stride, batch_stride;
-  float* out; long long out_row_stride, out_batch_stride;
+  float* out; long long out_row_stride, out_batch_stride;   // out may be null when o16_hi / o16_lo are given
+  uint2* o16_hi; uint2* o16_lo;   // the result split into fp16 hi / lo halves (same strides, in elements), or null
   int heads, tokens;
   const float* scale; int scale_mode;   // 0 none, 1 multiply, 2 divide
   int* err;
@@ -211,6 +212,7 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
   const float* kg = p.k + base;
   const float* vg = p.v + base;
   bool ok = true;
+  unsigned seen_out = 0;   // range of what this thread wrote split (o16_hi)
   int stamp_base = 0;
   AT_STAMP(0);
 
@@ -452,11 +454,22 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
         stage[lane * 8 + (j ^ (lane & 7))] = make_float4(fin(4 * j), fin(4 * j + 1), fin(4 * j + 2), fin(4 * j + 3));
       __syncwarp();
       const int c4 = lane & 7, rsub = lane >> 3;
-      float* og = p.out + (long long)b * p.out_batch_stride + (long long)h * HD + hf * 32 + 4 * c4;
+      const long long obase = (long long)b * p.out_batch_stride + (long long)h * HD + hf * 32 + 4 * c4;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rl = 4 * i + rsub, r = q0 + q * 32 + rl;
-        if (ok && r < T) *reinterpret_cast<float4*>(og + (long long)r * p.out_row_stride) = stage[rl * 8 + (c4 ^ (rl & 7))];
+        if (ok && r < T) {
+          const float4 y = stage[rl * 8 + (c4 ^ (rl & 7))];
+          const long long o = obase + (long long)r * p.out_row_stride;
+          if (p.out) *reinterpret_cast<float4*>(p.out + o) = y;
+          if (p.o16_hi) {   // for the projection GEMM that takes this result as its pre-split A
+            uint2 hh, ll;
+            f16_split(y, hh, ll);
+            p.o16_hi[o >> 2] = hh;
+            p.o16_lo[o >> 2] = ll;
+            seen_out |= split_seen(y);
+          }
+        }
       }
       tc_fence_before();                         // the tensor-memory loads above precede the next tile's MMAs
     } else if (lane == 0) {
@@ -470,16 +483,22 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
         if (!mbar_wait(&ready[slot], (mma_par >> slot) & 1u)) { atomicExch(p.err, 14); ok = false; break; }
         mma_par ^= 1u << slot;
         tc_fence_after();
+        // One accumulator after the other: alternating between D1 and D2 with every MMA
+        // slows the tensor pipe down.
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint32_t pa = smem_u32(qp + slot * kSlotBytes) + kk * 32;
+          const uint32_t va = smem_u32(vt + blk * kVBlock) + kk * 32;
+          tc_mma_f16(tmem_base + kOCol, desc_sw64(pa), desc_sw64(va), idesc_o, (n | kk) ? 1u : 0u);     // hi * hi -> D1
+        }
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
           const uint32_t pa = smem_u32(qp + slot * kSlotBytes) + kk * 32;
           const uint32_t va = smem_u32(vt + blk * kVBlock) + kk * 32;
           const uint64_t a_hi = desc_sw64(pa), a_lo = desc_sw64(pa + QM * 64);
           const uint64_t b_hi = desc_sw64(va), b_lo = desc_sw64(va + NBLK * kVBlock);
-          const uint32_t first = (n | kk) ? 1u : 0u;
-          tc_mma_f16(tmem_base + kOCol, a_hi, b_hi, idesc_o, first);            // hi * hi      -> D1
-          tc_mma_f16(tmem_base + kOCol + HD, a_lo, b_hi, idesc_o, first);       // lo' * hi     -> D2
-          tc_mma_f16(tmem_base + kOCol + HD, a_hi, b_lo, idesc_o, 1u);          // hi * lo'     -> D2
+          tc_mma_f16(tmem_base + kOCol + HD, a_lo, b_hi, idesc_o, (n | kk) ? 1u : 0u);   // lo' * hi -> D2
+          tc_mma_f16(tmem_base + kOCol + HD, a_hi, b_lo, idesc_o, 1u);                   // hi * lo' -> D2
         }
         tc_commit(&freeb[slot]);
       }
@@ -490,6 +509,7 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
   do_tile(std::true_type{}, 0);
 #pragma unroll 1
   for (int tile = 1; tile < n_tiles; ++tile) do_tile(std::false_type{}, tile);
+  if (p.o16_hi && warp < 8) split_report_warp(seen_out, p.err);   // one head's rows: out of range, or all tiny
   tc_fence_before();
   __syncthreads();
   if (warp == 8) {
@@ -528,7 +548,8 @@ bool attention_tc_supported(const AttentionParams& p) {
   return p.head_dim == HD && p.tokens > 64 && p.tokens <= 256 && p.batch >= 1 && p.heads >= 1 &&
          (long long)p.batch * p.heads <= 65535 && (p.row_stride % 4) == 0 && (p.batch_stride % 4) == 0 &&
          (p.out_row_stride % 4) == 0 && (p.out_batch_stride % 4) == 0 && al(p.q) && al(p.k) && al(p.v) &&
-         al(p.out) && p.out != nullptr && p.err_word != nullptr;
+         al(p.out) && (p.out != nullptr || (p.out16_hi && p.out16_lo)) && al(p.out16_hi) && al(p.out16_lo) &&
+         p.err_word != nullptr;
 }
 
 cudaError_t launch_attention_tc(const AttentionParams& p, cudaStream_t st) {
@@ -537,6 +558,7 @@ cudaError_t launch_attention_tc(const AttentionParams& p, cudaStream_t st) {
   d.q = p.q; d.k = p.k; d.v = p.v;
   d.row_stride = p.row_stride; d.batch_stride = p.batch_stride;
   d.out = p.out; d.out_row_stride = p.out_row_stride; d.out_batch_stride = p.out_batch_stride;
+  d.o16_hi = static_cast<uint2*>(p.out16_hi); d.o16_lo = static_cast<uint2*>(p.out16_lo);
   d.heads = p.heads; d.tokens = p.tokens;
   d.scale = p.scale; d.scale_mode = p.scale ? p.scale_mode : 0;
   d.err = p.err_word;

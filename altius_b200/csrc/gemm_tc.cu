@@ -342,14 +342,14 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
 // tensor memory earlier, needs more than the 96 registers a thread of this kernel can have.)
 template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
 __device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stage, uint32_t tmem_base, int q,
-                                              int lane, int m0, int n0, int bz, int cc0, Release&& release) {
+                                              int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
+                                              Release&& release) {
   bool released = false;
   const float sc = acc_scale_of(ep);
   float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
   const int c4 = lane & 3, rsub = lane >> 2;
   const int row_base = m0 + q * 32 + rsub;
-  unsigned seen = 0;
   float bm[4];
   if (BIAS == 2) {
 #pragma unroll
@@ -424,7 +424,17 @@ __device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stag
           x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
         }
         const int row = row_base + 8 * i;
-        if (col_ok && row < ep.m) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
+        if (col_ok && row < ep.m) {
+          if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
+          if (ep.c16_hi) {   // the GEMM that consumes this result takes it split (batch 1)
+            uint2 h, l;
+            f16_split(x, h, l);
+            const long long o = ((long long)row * ep.ldc16 + col) >> 2;
+            ep.c16_hi[o] = h;
+            ep.c16_lo[o] = l;
+            seen |= split_seen(x);
+          }
+        }
       }
     }
   }
@@ -486,10 +496,11 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     for (int j = 0; j < 8; ++j) add(v[j]);
   }
   for (; p < parts; ++p) add(__ldg(reinterpret_cast<const float4*>(src + (size_t)p * bm * bn)));
-  float* c = ep.c + (long long)bz * ep.sc;
+  float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
   const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
   const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
   const float x[4] = {acc.x, acc.y, acc.z, acc.w};
+  float y4[4] = {0.f, 0.f, 0.f, 0.f};
   for (int e = 0; e < 4; ++e) {
     const int col = col0 + e;
     if (col >= ep.n) break;
@@ -509,7 +520,18 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     }
     y = apply_act(ep.act, y, ep.act_alpha, ep.act_beta);
     if (res) y = __fadd_rn(y, __ldg(res + (long long)row * ep.ldres + col));
-    c[(long long)row * ep.ldc + col] = y;
+    if (c) c[(long long)row * ep.ldc + col] = y;
+    y4[e] = y;
+  }
+  if (ep.c16_hi) {   // n is a multiple of 8 here: the whole float4 is in range
+    uint2 h, l;
+    const float4 yv = make_float4(y4[0], y4[1], y4[2], y4[3]);
+    f16_split(yv, h, l);
+    const long long o = ((long long)row * ep.ldc16 + col0) >> 2;
+    ep.c16_hi[o] = h;
+    ep.c16_lo[o] = l;
+    // A tile's few K-sliced elements say nothing about the tensor being tiny: overflow only.
+    if (split_seen(yv) & 1u) atomicCAS(ep.err, 0, kRangeCode);
   }
 }
 
@@ -704,15 +726,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
               const uint64_t dal = make_smem_desc(smem_u32(a_lo(s) + mt * (BM * 64)));
               const uint32_t d = d_tmem + (uint32_t)(mt * BN);
               if (MODE == TC_F16X3) {
-                tc_mma_f16(d, da + off, db + boff, idesc, acc);            // a_hi * b_hi
-                tc_mma_f16(d + D2, dal + off, db + boff, idesc, acc);      // a_lo' * b_hi  (scaled by 2^11)
-                tc_mma_f16(d + D2, da + off, dbl + boff, idesc, 1u);       // a_hi * b_lo'
+                // Issued further down, one accumulator after the other: alternating between the
+                // two with every MMA costs 30 % of the tensor pipe's rate.
               } else if (MODE == TC_1X) {
                 tc_mma_tf32(d, da + off, db + boff, idesc, acc);
               } else {
                 tc_mma_tf32(d, dal + off, db + boff, idesc, acc);   // a_lo * b_hi
                 tc_mma_tf32(d, da + off, dbl + boff, idesc, 1u);    // a_hi * b_lo
                 tc_mma_tf32(d, da + off, db + boff, idesc, 1u);     // a_hi * b_hi
+              }
+            }
+          }
+          if (MODE == TC_F16X3) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint64_t da = make_smem_desc(smem_u32(a_hi(s) + mt * (BM * 64)));
+              const uint64_t dal = make_smem_desc(smem_u32(a_lo(s) + mt * (BM * 64)));
+              const uint32_t d = d_tmem + (uint32_t)(mt * BN);
+#pragma unroll
+              for (int kk = 0; kk < 2; ++kk)                               // a_hi * b_hi -> D1
+                tc_mma_f16(d, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+              for (int kk = 0; kk < 2; ++kk) {                             // cross terms (scaled by 2^11) -> D2
+                tc_mma_f16(d + D2, dal + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
+                tc_mma_f16(d + D2, da + (uint64_t)(kk * 2), dbl + (uint64_t)(kk * 2), idesc, 1u);
               }
             }
           }
@@ -728,7 +765,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const int group = threadIdx.x / kSplitThreads;   // takes the K-blocks with it % kSplitGroups == group
       int it = 0;
       bool ok = true;
-      unsigned range_bad = 0;
+      unsigned seen = 0;
       TcWork wk;
       for (int w = 0; ok && tc_get_work(sc, w, &wk); ++w) {
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
@@ -755,7 +792,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < kItems; ++i) {
               const int item = i * kSplitThreads + t0;
-              range_bad |= beyond_half(x[i].x) | beyond_half(x[i].y) | beyond_half(x[i].z) | beyond_half(x[i].w);
+              seen |= split_seen(x[i]);
               uint2 hi, lo;
               f16_split(x[i], hi, lo);
               const uint32_t off = sw64_off8(item >> 3, item & 7);
@@ -788,9 +825,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           mbar_arrive(&ready[s]);
         }
       }
-      // An element of A too large for fp16: the result is not to be used (the host
-      // re-runs on the TF32 path); a code from a timed-out wait takes precedence.
-      if (MODE == TC_F16X3 && range_bad) atomicCAS(err, 0, kRangeCode);
+      // An element of A too large for fp16, or nothing but tiny ones: the result is not to be
+      // used (the host re-runs on the TF32 path); a code from a timed-out wait takes precedence.
+      if (MODE == TC_F16X3) split_report_warp(seen, err);
     }
   } else {
     // ---------------- epilogue ----------------
@@ -1102,7 +1139,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     constexpr int kItems = BM * KB / 4 / kSplitThreads;   // 8
     int it = 0;
     bool ok = true;
-    unsigned range_bad = 0;
+    unsigned seen = 0;
     TcWork wk;
     for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
       const int t = wk.tile;
@@ -1129,7 +1166,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
 #pragma unroll
         for (int i = 0; i < kItems; ++i) {
           const int item = i * kSplitThreads + t0;
-          range_bad |= beyond_half(x[i].x) | beyond_half(x[i].y) | beyond_half(x[i].z) | beyond_half(x[i].w);
+          seen |= split_seen(x[i]);
           uint2 hi, lo;
           f16_split(x[i], hi, lo);
           const uint32_t off = sw64_off8(item >> 3, item & 7);
@@ -1143,7 +1180,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         if (lane == 0) mbar_arrive_cluster(map_to_cta(&ready[s], 0));
       }
     }
-    if (range_bad) atomicCAS(err, 0, kRangeCode);
+    split_report_warp(seen, err);
   } else if (!PRE || warp < 16) {
     // ---------------- epilogue (each CTA its own 128 rows) ----------------
     // PRE: warps 0-15, a warp per lane quarter and quarter of the columns on the common
@@ -1164,6 +1201,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
                         (!ep.bias_n || (reinterpret_cast<uintptr_t>(ep.bias_n) & 15) == 0);
     const int key = !simple ? -1 : ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2) | (ep.bias_m ? 64 : 0));
     int ti = 0;
+    unsigned seen_out = 0;   // what this warp has seen of the results it wrote split (ep.c16_hi)
     TcWork wk;
     for (int w = 0; pair_get_work(sc, w, &wk); ++w, ++ti) {
       const int t = wk.tile;
@@ -1189,14 +1227,17 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         return true;
       };
+      // The K-slice and general epilogues use the staging memory in 4 KB pieces that overlap
+      // the 2 KB pieces of the common epilogue: nobody may still be in the previous tile's.
+      if (PRE && (wk.raw >= 0 || key < 0)) asm volatile("bar.sync 2, 512;" ::: "memory");
       if (PRE && m0 < ep.m && wk.raw < 0) {
         switch (key) {
-          case 0: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
-          case 1: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
-          case 2: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
-          case 3: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_GELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_RELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, release); break;
+          case 0: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 1: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 2: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 3: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_GELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_RELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
           default:
             if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1);
             break;
@@ -1222,6 +1263,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       if (!released) release();
       if (e == 0 && lane == 0 && ti < 3) pair_stamp(dbg, 9 + 2 * ti);     // this warp's part of tile ti stored
     }
+    if (PRE && ep.c16_hi) split_report_warp(seen_out, err);
   }
 
   // ---------------- teardown ----------------
@@ -1254,14 +1296,38 @@ __global__ void tf32_split_kernel(const float* __restrict__ x, float* __restrict
   }
 }
 
+// Largest magnitude of a [rows, k] operand as the bits of a non-negative float (finite values).
+__global__ void absmax_kernel(const float* __restrict__ x, int64_t rows, int64_t k, int64_t ld, unsigned* out) {
+  unsigned m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * k; i += (int64_t)gridDim.x * blockDim.x) {
+    const unsigned ab = __float_as_uint(__ldg(x + (i / k) * ld + (i % k))) & 0x7FFFFFFFu;
+    if (ab < 0x7F800000u) m = max(m, ab);
+  }
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+// Power of two 2^e that brings a largest magnitude `absmax_bits` into [2^13, 2^14); 1 for zero.
+__device__ __forceinline__ float weight_scale(unsigned absmax_bits) {
+  if (absmax_bits == 0) return 1.f;
+  const int ex = (int)(absmax_bits >> 23) - 127;           // floor(log2(max)); subnormals read as -127
+  int e = 13 - ex;
+  e = e > 100 ? 100 : (e < -100 ? -100 : e);
+  return __uint_as_float((unsigned)(e + 127) << 23);
+}
+
 // fp16 hi / lo split of a constant [rows, k] operand (row stride ld) into [rows, k8]
-// halves, columns k .. k8-1 zero. An element beyond fp16 leaves kRangeCode in *err.
+// halves, columns k .. k8-1 zero. With `absmax` the operand is first scaled by weight_scale
+// (and *inv_scale receives the inverse). An element beyond fp16 leaves kRangeCode in *err.
 __global__ void f16_split_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo,
-                                 int64_t rows, int64_t k, int64_t ld, int64_t k8, int* err) {
+                                 int64_t rows, int64_t k, int64_t ld, int64_t k8, int* err,
+                                 const unsigned* __restrict__ absmax, float* inv_scale) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const float sc = absmax ? weight_scale(*absmax) : 1.f;
+  if (i == 0 && inv_scale) *inv_scale = __fdiv_rn(1.f, sc);
   if (i >= rows * k8) return;
   const int64_t r = i / k8, c = i % k8;
-  const float v = c < k ? __ldg(x + r * ld + c) : 0.f;
+  const float v = c < k ? __fmul_rn(__ldg(x + r * ld + c), sc) : 0.f;
   const __half h = __float2half_rn(v);
   hi[i] = h;
   lo[i] = __float2half_rn(__fmul_rn(__fsub_rn(v, __half2float(h)), kLoScale));
@@ -1274,7 +1340,7 @@ __global__ void __launch_bounds__(256) f16_split_vec8_kernel(const float* __rest
                                                              uint4* __restrict__ lo, int64_t rows, int64_t k8th,
                                                              int64_t ld, int* err) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  unsigned bad = 0;
+  unsigned seen = 0;
   if (i < rows * k8th) {
     const int64_t r = i / k8th, c = i % k8th;
     const float4* src = reinterpret_cast<const float4*>(x + r * ld + c * 8);
@@ -1284,10 +1350,11 @@ __global__ void __launch_bounds__(256) f16_split_vec8_kernel(const float* __rest
     f16_split(v1, h1, l1);
     hi[i] = make_uint4(h0.x, h0.y, h1.x, h1.y);
     lo[i] = make_uint4(l0.x, l0.y, l1.x, l1.y);
-    bad = beyond_half(v0.x) | beyond_half(v0.y) | beyond_half(v0.z) | beyond_half(v0.w) |
-          beyond_half(v1.x) | beyond_half(v1.y) | beyond_half(v1.z) | beyond_half(v1.w);
+    seen = split_seen(v0) | split_seen(v1);
   }
-  if (__any_sync(0xffffffffu, bad != 0) && (threadIdx.x & 31) == 0) atomicCAS(err, 0, kRangeCode);
+  // The block's 2048 elements: out of range, or non-zero values that are all tiny.
+  const int over = __syncthreads_or(seen & 1u), big = __syncthreads_or(seen & 2u), tiny = __syncthreads_or(seen & 4u);
+  if (threadIdx.x == 0 && (over || (tiny && !big))) atomicCAS(err, 0, kRangeCode);
 }
 
 // ---- host side ---------------------------------------------------------------------
@@ -1603,6 +1670,20 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.bias_n = q.bias_n; ep.bias_m = q.bias_m; ep.bias_scale = q.bias_scale;
   ep.act = q.act; ep.act_alpha = q.act_alpha; ep.act_beta = q.act_beta;
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
+  ep.c16_hi = static_cast<uint2*>(q.c16_hi); ep.c16_lo = static_cast<uint2*>(q.c16_lo); ep.ldc16 = q.ldc16;
+  ep.acc_scale = kmode == TC_F16X3 ? q.b16_inv_scale : nullptr;
+  ep.err = err_word;
+  if (q.c16_hi) {
+    // Only the pair kernel's common epilogues (and the tail fix-up) write the split result.
+    if (!(sh.pair && pre) || !q.c16_lo || q.batch != 1 || (q.n % 8) != 0 || (q.ldc16 % 8) != 0 ||
+        !gemm_tc_can_split_output(q.act, q.bias_n != nullptr, q.bias_m != nullptr, q.c_in && q.beta != 0.f, q.alpha, q.bias_scale) ||
+        (q.c && ((q.ldc % 4) != 0 || (reinterpret_cast<uintptr_t>(q.c) & 15) != 0)) ||
+        (q.residual && ((q.ld_res % 4) != 0 || (reinterpret_cast<uintptr_t>(q.residual) & 15) != 0)) ||
+        (q.bias_n && (reinterpret_cast<uintptr_t>(q.bias_n) & 15) != 0))
+      return cudaErrorInvalidValue;
+  } else if (!q.c) {
+    return cudaErrorInvalidValue;
+  }
   ep.dbg = std::getenv("ALTIUS_CUDA_TC_DBG") ? std::atoi(std::getenv("ALTIUS_CUDA_TC_DBG")) : 0;
   TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, (sh.pair && pre) ? 64 : (kmode == TC_F16X3 ? BK16 : BK),
                         sh.pair ? pair_count() : 0);
@@ -1630,9 +1711,19 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
 }
 
 cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, int64_t k, int64_t ld, int64_t k8,
-                             int* err_word, cudaStream_t st) {
+                             int* err_word, float* inv_scale, unsigned* absmax_scratch, cudaStream_t st) {
   const int64_t n = rows * k8;
   if (n == 0) return cudaSuccess;
+  if (inv_scale) {   // a constant operand: scaled by a power of two first
+    if (!absmax_scratch) return cudaErrorInvalidValue;
+    cudaError_t e = cudaMemsetAsync(absmax_scratch, 0, sizeof(unsigned), st);
+    if (e != cudaSuccess) return e;
+    const int64_t blocks = std::min<int64_t>((rows * k + 255) / 256, 1184);
+    absmax_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, rows, k, ld, absmax_scratch);
+    f16_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, static_cast<__half*>(hi), static_cast<__half*>(lo),
+                                                                 rows, k, ld, k8, err_word, absmax_scratch, inv_scale);
+    return cudaGetLastError();
+  }
   if (k8 == k && (k % 8) == 0 && (ld % 4) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(hi) & 15) == 0 && (reinterpret_cast<uintptr_t>(lo) & 15) == 0) {
     const int64_t n8 = n / 8;
@@ -1641,8 +1732,13 @@ cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, i
     return cudaGetLastError();
   }
   f16_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, static_cast<__half*>(hi), static_cast<__half*>(lo),
-                                                               rows, k, ld, k8, err_word);
+                                                               rows, k, ld, k8, err_word, nullptr, nullptr);
   return cudaGetLastError();
+}
+
+bool gemm_tc_can_split_output(int act, bool bias_n, bool bias_m, bool c_in, float alpha, float bias_scale) {
+  // The epilogues the pair kernel has compiled in with the split store (epilogue_half's callers).
+  return !bias_m && !c_in && alpha == 1.f && bias_scale == 1.f && (act == ACT_NONE || (bias_n && (act == ACT_GELU || act == ACT_RELU)));
 }
 
 cudaError_t launch_tf32_split(const float* x, float* hi, float* lo, int64_t n, cudaStream_t st) {

@@ -30,6 +30,12 @@ struct Ctx {
   std::vector<std::vector<int>> consumers;   // value -> node ids (one entry per use)
   std::vector<char> is_output;
   std::vector<char> absorbed;                // node folded into another node's kernel
+  // Values that a CTA-pair GEMM takes as its A operand already split into fp16 hi / lo halves
+  // (scratch values `hi`, `lo`). `produced`: a step emitted so far writes the halves (the kernel
+  // that computes the value, or a split kernel); `fp32_needed`: someone still reads the value
+  // itself, so its producer writes it as well.
+  struct Split { int hi = -1, lo = -1; bool produced = false, fp32_needed = true; };
+  std::map<int, Split> split;
   explicit Ctx(AcSession& s_) : s(s_) {}
 
   Value& val(int v) { return s.values[v]; }
@@ -555,6 +561,78 @@ int new_value(Ctx& c, int64_t numel, bool is_const) {
   return (int)c.s.values.size() - 1;
 }
 
+int effective_pairs(const AcSession& s) {
+  // AcOptions.gemm_pairs: 0 (default) and 2 -> CTA pairs with A pre-split for TMA where the
+  // cost model prefers them, 1 -> pairs that stage A through registers, 3 -> no pairs.
+  return s.opt.gemm_pairs == 0 ? 2 : (s.opt.gemm_pairs == 3 ? 0 : s.opt.gemm_pairs);
+}
+
+// The static part of emit_gemm's decision to run a GEMM with a constant rhs on the CTA-pair
+// kernel that takes A pre-split (kept in one place: plan_presplit decides with it which
+// producers write split results before the GEMMs themselves are lowered).
+bool presplit_applies(const AcSession& s, const GemmShape& g, bool b_const, int64_t a_off, int64_t b_off) {
+  const int mode = s.opt.gemm_mode;
+  if (mode != 0 || effective_pairs(s) != 2 || !b_const || g.batch != 1 || g.ta || b_off != 0) return false;
+  const double flops = 2.0 * g.batch * g.m * g.n * g.k;
+  const double tc_floor = (g.batch == 1 && g.m <= 128 && g.k >= 64) ? double(1 << 19) : double(1 << 23);
+  if ((g.lda % 4) || (a_off % 4) || flops < tc_floor || g.k < 8 || (g.k % 8)) return false;
+  if (g.tb ? (g.ldb % 4) != 0 : (g.k % 4) != 0) return false;
+  return gemm_tc_wants_presplit(g.m, g.n, g.k, g.batch);
+}
+
+GemmShape matmul_shape(Ctx& c, const Node& n, bool trans_b_folded) {
+  const Value& av = c.val(n.inputs[0]);
+  const Value& ov = c.val(n.outputs[0]);
+  const Value& bv = c.val(n.inputs[1]);  // logical rhs [.., k, n]
+  GemmShape g{};
+  g.k = av.dims[av.rank - 1];
+  g.n = ov.dims[ov.rank - 1];
+  g.ta = 0;
+  g.tb = trans_b_folded ? 1 : 0;
+  g.lda = g.k;
+  g.ldb = g.tb ? g.k : g.n;
+  g.ldc = g.n;
+  if (bv.rank == 2) {  // 2Dx2D and 3Dx2D: one GEMM over the flattened rows (session.rs:653-660)
+    g.m = av.numel() / g.k;
+    g.batch = 1;
+  } else {             // 3Dx3D / 4Dx4D: a batch of GEMMs (session.rs:641-672)
+    g.m = av.dims[av.rank - 2];
+    g.batch = av.numel() / (g.m * g.k);
+    g.sa = g.m * g.k; g.sb = g.k * g.n; g.sc = g.m * g.n;
+  }
+  return g;
+}
+
+// Which values will be consumed pre-split: the A operands of the MatMul nodes that
+// presplit_applies to. Their scratch halves are created here.
+void plan_presplit(Ctx& c, Plan& plan) {
+  std::map<int, int> split_users;   // value -> MatMul nodes that take it pre-split
+  for (int nid : c.s.order) {
+    const Node& n = c.node(nid);
+    if (c.absorbed[nid] || n.op != AC_OP_MATMUL) continue;
+    const int a = n.inputs[0];
+    if (c.val(a).is_const || c.val(a).elem_ty != AC_F32 || c.val(a).rank < 2) continue;
+    auto it = plan.epi.find(nid);
+    const bool folded_t = it != plan.epi.end() && it->second.trans_b_src >= 0;
+    const int b = folded_t ? it->second.trans_b_src : n.inputs[1];
+    const GemmShape g = matmul_shape(c, n, folded_t);
+    if (!presplit_applies(c.s, g, c.val(b).is_const, 0, 0)) continue;
+    split_users[a]++;
+  }
+  for (auto& kv : split_users) {
+    const int a = kv.first;
+    const Value& av = c.val(a);
+    const int64_t k = av.dims[av.rank - 1];
+    const int64_t floats = av.numel() / 2;    // two halves per float of scratch; rows of k halves
+    (void)k;
+    Ctx::Split sp;
+    sp.hi = new_value(c, floats, false);
+    sp.lo = new_value(c, floats, false);
+    sp.fp32_needed = c.is_output[a] || (int)c.consumers[a].size() != kv.second;
+    c.split[a] = sp;
+  }
+}
+
 void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, int c_in, int bias_n,
                int bias_m, float alpha, float beta, float bias_scale, const Epilogue* e,
                int64_t a_off = 0, int64_t b_off = 0, int64_t c_off = 0) {
@@ -569,9 +647,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
 
   // ---- tensor-core eligibility (static part; alignment is re-checked at launch) ----
   const int mode = s->opt.gemm_mode;
-  // AcOptions.gemm_pairs: 0 (default) and 2 -> CTA pairs with A pre-split for TMA where the
-  // cost model prefers them, 1 -> pairs that stage A through registers, 3 -> no pairs.
-  const int pairs = s->opt.gemm_pairs == 0 ? 2 : (s->opt.gemm_pairs == 3 ? 0 : s->opt.gemm_pairs);
+  const int pairs = effective_pairs(*s);
   // Below about 8 MFLOP the CUDA-core kernel wins, except for few rows against a long K (the
   // squeeze-excite products, batch x channels): one or two of its blocks then walk K alone,
   // while the persistent kernel cuts K into slices over the idle SMs.
@@ -600,18 +676,23 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     }
   }
   // mode 0 with a constant rhs: the fp16 split (hi, remainder * 2^11) prepared once, [N, K8] halves.
-  int b16_hi = -1, b16_lo = -1;
+  int b16_hi = -1, b16_lo = -1, b16_scale = -1;
   int64_t ldb16 = 0;
   if (tc && mode == 0 && em.c.val(b_use).is_const && g.tb && g.batch == 1 && b_off == 0) {
     ldb16 = (g.k + 7) / 8 * 8;
     const int64_t floats = g.n * ldb16 / 2;     // two halves per float of scratch
     b16_hi = new_value(em.c, floats, true);
     b16_lo = new_value(em.c, floats, true);
-    const int src = b_use, hi = b16_hi, lo = b16_lo;
+    // The weight is split after scaling by a power of two that brings its largest magnitude to
+    // about 2^13 (weights of any magnitude then stay clear of the fp16 subnormals); the
+    // epilogue multiplies by the inverse, kept in word 0 of this scratch (word 1: the maximum).
+    b16_scale = new_value(em.c, 2, true);
+    const int src = b_use, hi = b16_hi, lo = b16_lo, scv = b16_scale;
     const int64_t nn = g.n, kk = g.k, ld = g.ldb, k8 = ldb16;
-    em.add("weight_f16_split", op, {src}, {hi, lo}, 4.0 * nn * kk + 4.0 * nn * k8, 0, [=](cudaStream_t st) {
-      return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word, st);
-    });
+    em.add("weight_f16_split", op, {src}, {hi, lo, scv}, 4.0 * nn * kk + 4.0 * nn * k8, 0, [=](cudaStream_t st) {
+      return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word,
+                              s->fptr_mut(scv), reinterpret_cast<unsigned*>(s->fptr_mut(scv)) + 1, st);
+    }, 3);
   }
   const int b_plain = b_use;   // the operand before any TF32 rounding
   if (tc && b16_hi < 0 && mode != 2 && g.tb && em.c.val(b_use).is_const) {
@@ -626,21 +707,51 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     b_use = hi;
   }
   const int bsrc = b_use;
-  // CTA pairs that take A by TMA want it already split into fp16 hi / lo halves: a split
-  // kernel in front of the GEMM writes them (rows of K8 halves, K8 a multiple of 8).
+  // CTA pairs that take A by TMA want it already split into fp16 hi / lo halves (rows of K
+  // halves): written by the kernel that produced A when plan_presplit arranged that, else by a
+  // split kernel in front of the GEMM.
   int a16_hi = -1, a16_lo = -1;
   int64_t lda16 = 0;
-  if (tc && b16_hi >= 0 && pairs == 2 && g.batch == 1 && (g.k % 8) == 0 &&
-      gemm_tc_wants_presplit(g.m, g.n, g.k, g.batch)) {
+  bool a_fp32_present = true;
+  if (tc && b16_hi >= 0 && presplit_applies(*s, g, true, a_off, b_off)) {
     lda16 = g.k;
-    const int64_t floats = g.m * lda16 / 2;
-    a16_hi = new_value(em.c, floats, false);
-    a16_lo = new_value(em.c, floats, false);
-    const int hi = a16_hi, lo = a16_lo;
-    const int64_t mm = g.m, kk = g.k, ld = g.lda, off = a_off;
-    em.add("act_f16_split", op, {a}, {hi, lo}, 8.0 * mm * kk, 0, [=](cudaStream_t st) {
-      return launch_f16_split(s->fptr(a) + off, s->fptr_mut(hi), s->fptr_mut(lo), mm, kk, ld, kk, s->err_word, st);
-    });
+    auto sp = em.c.split.find(a);
+    const bool planned = sp != em.c.split.end() && a_off == 0 && g.lda == g.k;
+    if (planned) {
+      a16_hi = sp->second.hi; a16_lo = sp->second.lo;
+      a_fp32_present = sp->second.fp32_needed || !sp->second.produced;
+    } else {
+      const int64_t floats = g.m * lda16 / 2;
+      a16_hi = new_value(em.c, floats, false);
+      a16_lo = new_value(em.c, floats, false);
+    }
+    if (!planned || !sp->second.produced) {
+      const int hi = a16_hi, lo = a16_lo;
+      const int64_t mm = g.m, kk = g.k, ld = g.lda, off = a_off;
+      em.add("act_f16_split", op, {a}, {hi, lo}, 8.0 * mm * kk, 0, [=](cudaStream_t st) {
+        return launch_f16_split(s->fptr(a) + off, s->fptr_mut(hi), s->fptr_mut(lo), mm, kk, ld, kk, s->err_word,
+                                nullptr, nullptr, st);
+      });
+      if (planned) sp->second.produced = true;
+    }
+  }
+  if (a16_hi < 0) {
+    auto sp = em.c.split.find(a);
+    if (sp != em.c.split.end() && sp->second.produced && !sp->second.fp32_needed)
+      fail(AC_ERR_INVALID, "internal: a GEMM operand was planned pre-split but its GEMM does not take it so");
+  }
+  // This GEMM's own result, when a later GEMM takes it pre-split and this one runs on the pair
+  // kernel with an epilogue that can write the halves.
+  int c16_hi = -1, c16_lo = -1;
+  bool c_fp32 = true;
+  {
+    auto so = em.c.split.find(out);
+    if (so != em.c.split.end() && !so->second.produced && a16_hi >= 0 && c_off == 0 && g.ldc == g.n && (g.n % 8) == 0 &&
+        gemm_tc_can_split_output(act, bias_n >= 0, bias_m >= 0, c_in >= 0, alpha, bias_scale)) {
+      c16_hi = so->second.hi; c16_lo = so->second.lo;
+      c_fp32 = so->second.fp32_needed;
+      so->second.produced = true;
+    }
   }
   // Scratch for the K-sliced tail tiles of the persistent kernel (lives for this step only).
   int ws = -1;
@@ -649,10 +760,15 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b16_hi >= 0 ? 2 : (b_lo >= 0 ? 0 : 1), pairs);
     if (ws_bytes) ws = new_value(em.c, (int64_t)(ws_bytes / 4), false);
   }
-  std::vector<int> reads = {a, bsrc, b_plain, b_lo, b16_hi, b16_lo, a16_hi, a16_lo, c_in, bias_n, bias_m, res};
+  std::vector<int> reads = {a_fp32_present ? a : -1, bsrc, b_plain, b_lo, b16_hi, b16_lo, b16_scale, a16_hi, a16_lo,
+                            c_in, bias_n, bias_m, res};
   const char* kind = !tc ? "gemm_fp32_simt"
-                     : (mode == 2 ? "gemm_tf32x1_tcgen05" : (b16_hi >= 0 ? "gemm_f16x3_tcgen05" : "gemm_tf32x3_tcgen05"));
-  std::vector<int> writes = {out};
+                     : (mode == 2 ? "gemm_tf32x1_tcgen05"
+                                  : (b16_hi >= 0 ? (a16_hi >= 0 ? "gemm_f16x3_pair_tcgen05" : "gemm_f16x3_tcgen05")
+                                                 : "gemm_tf32x3_tcgen05"));
+  std::vector<int> writes;
+  if (c_fp32) writes.push_back(out);
+  if (c16_hi >= 0) { writes.push_back(c16_hi); writes.push_back(c16_lo); }
   if (ws >= 0) writes.push_back(ws);
   em.add(kind, op, reads, writes, bytes, flops, [=](cudaStream_t st) {
     GemmParams p{};
@@ -663,13 +779,17 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.a16_lo = a16_lo >= 0 ? s->ptr(a16_lo) : nullptr;
     p.lda16 = lda16;
     p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
-    p.a = s->fptr(a) + a_off; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
+    p.a = a_fp32_present ? s->fptr(a) + a_off : nullptr; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
     p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
     p.b_lo = b_lo >= 0 ? s->fptr(b_lo) + b_off : nullptr;
     p.b16_hi = b16_hi >= 0 ? s->ptr(b16_hi) : nullptr;
     p.b16_lo = b16_lo >= 0 ? s->ptr(b16_lo) : nullptr;
     p.ldb16 = ldb16;
-    p.c = s->fptr_mut(out) + c_off; p.ldc = g.ldc; p.stride_c = g.sc;
+    p.c = c_fp32 ? s->fptr_mut(out) + c_off : nullptr; p.ldc = g.ldc; p.stride_c = g.sc;
+    p.c16_hi = c16_hi >= 0 ? s->ptr(c16_hi) : nullptr;
+    p.c16_lo = c16_lo >= 0 ? s->ptr(c16_lo) : nullptr;
+    p.ldc16 = g.n;
+    p.b16_inv_scale = b16_scale >= 0 ? s->fptr(b16_scale) : nullptr;
     p.alpha = alpha; p.beta = c_in >= 0 ? beta : 0.f;
     p.c_in = c_in >= 0 ? s->fptr(c_in) + c_off : nullptr; p.ldc_in = g.ldc; p.stride_c_in = g.sc;
     p.bias_n = bias_n >= 0 ? s->fptr(bias_n) : nullptr;
@@ -678,6 +798,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.act = act; p.act_alpha = aa; p.act_beta = ab;
     p.residual = res >= 0 ? s->fptr(res) + c_off : nullptr; p.ld_res = g.ldc; p.stride_res = g.sc;
     if (tc && gemm_tc_supported(p)) return launch_gemm_tc(p, mode, s->err_word, st);
+    if (!p.a || !p.c || p.c16_hi) return cudaErrorInvalidValue;   // operands exist for the tensor-core kernel only
     // The CUDA-core kernel multiplies the operand as given, not a TF32-rounded copy of it.
     if (b_lo >= 0) { p.b = s->fptr(b_plain) + b_off; p.b_lo = nullptr; }
     return launch_gemm_simt(p, st);
@@ -693,22 +814,8 @@ void lower_matmul(Emit& em, int nid, const Epilogue* e) {
   const Value& ov = em.c.val(n.outputs[0]);
   const Value& bv = em.c.val(n.inputs[1]);  // logical rhs [.., k, n]
   require_f32(av, "MatMul");
-  GemmShape g{};
-  g.k = av.dims[av.rank - 1];
-  g.n = ov.dims[ov.rank - 1];
-  g.ta = 0;
-  g.tb = (e && e->trans_b_src >= 0) ? 1 : 0;
-  g.lda = g.k;
-  g.ldb = g.tb ? g.k : g.n;
-  g.ldc = g.n;
-  if (bv.rank == 2) {  // 2Dx2D and 3Dx2D: one GEMM over the flattened rows (session.rs:653-660)
-    g.m = av.numel() / g.k;
-    g.batch = 1;
-  } else {             // 3Dx3D / 4Dx4D: a batch of GEMMs (session.rs:641-672)
-    g.m = av.dims[av.rank - 2];
-    g.batch = av.numel() / (g.m * g.k);
-    g.sa = g.m * g.k; g.sb = g.k * g.n; g.sc = g.m * g.n;
-  }
+  (void)ov; (void)bv;
+  const GemmShape g = matmul_shape(em.c, n, e && e->trans_b_src >= 0);
   emit_gemm(em, n.op, g, a, b, out, -1, e ? e->bias : -1, -1, 1.f, 0.f, 1.f, e);
 }
 
@@ -1074,14 +1181,29 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         const double flops = 4.0 * B * H * T * T * hd;
         // gemm_mode 1 asks for exact fp32 FMA chains: it keeps the CUDA-core kernel.
         const bool tc_attn = s->opt.gemm_mode != 1 && hd == 64 && T > 64 && T <= 256;
-        em.add(tc_attn ? "attention_tcgen05" : "attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, {f.out}, bytes, flops,
+        int o16_hi = -1, o16_lo = -1;
+        bool o_fp32 = true;
+        {
+          auto so = c.split.find(f.out);
+          if (so != c.split.end() && !so->second.produced && tc_attn) {
+            o16_hi = so->second.hi; o16_lo = so->second.lo;
+            o_fp32 = so->second.fp32_needed;
+            so->second.produced = true;
+          }
+        }
+        std::vector<int> awrites;
+        if (o_fp32) awrites.push_back(f.out);
+        if (o16_hi >= 0) { awrites.push_back(o16_hi); awrites.push_back(o16_lo); }
+        em.add(tc_attn ? "attention_tcgen05" : "attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, awrites, bytes, flops,
                [=](cudaStream_t st) {
                  AttentionParams p{};
                  p.q = s->fptr(f.q.src) + f.q.col;
                  p.k = s->fptr(f.k.src) + f.k.col;
                  p.v = s->fptr(f.v.src) + f.v.col;
                  p.row_stride = C; p.batch_stride = T * C;
-                 p.out = s->fptr_mut(f.out); p.out_row_stride = H * hd; p.out_batch_stride = T * H * hd;
+                 p.out = o_fp32 ? s->fptr_mut(f.out) : nullptr; p.out_row_stride = H * hd; p.out_batch_stride = T * H * hd;
+                 p.out16_hi = o16_hi >= 0 ? s->ptr(o16_hi) : nullptr;
+                 p.out16_lo = o16_lo >= 0 ? s->ptr(o16_lo) : nullptr;
                  p.batch = (int)B; p.heads = (int)H; p.tokens = (int)T; p.head_dim = (int)hd;
                  p.scale = f.scale >= 0 ? s->fptr(f.scale) : nullptr; p.scale_mode = f.scale_mode;
                  p.use_tc = tc_attn ? 1 : 0; p.err_word = s->err_word;
@@ -1131,7 +1253,20 @@ void lower_node(Emit& em, Plan& plan, int nid) {
       auto it = plan.ln.find(nid);
       if (it != plan.ln.end()) f = it->second;
       const int x = f.x, pb = f.pre_bias, res = f.residual, sum = f.sum_val, gelu = f.gelu;
-      std::vector<int> writes = {o};
+      // The GEMM(s) that consume the result may take it as fp16 hi / lo halves (vector path only).
+      int o16_hi = -1, o16_lo = -1;
+      bool o_fp32 = true;
+      {
+        auto so = c.split.find(o);
+        if (so != c.split.end() && !so->second.produced && (len % 8) == 0 && len <= 1024) {
+          o16_hi = so->second.hi; o16_lo = so->second.lo;
+          o_fp32 = so->second.fp32_needed;
+          so->second.produced = true;
+        }
+      }
+      std::vector<int> writes;
+      if (o_fp32) writes.push_back(o);
+      if (o16_hi >= 0) { writes.push_back(o16_hi); writes.push_back(o16_lo); }
       if (sum >= 0) writes.push_back(sum);
       double bytes = 8.0 * rows * len + 8.0 * len;
       if (res >= 0 && res != x) bytes += 4.0 * rows * len;
@@ -1145,7 +1280,10 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         p.residual = res >= 0 ? s->fptr(res) : nullptr;
         p.gamma = s->fptr(gamma); p.beta = s->fptr(beta);
         p.sum_out = sum >= 0 ? s->fptr_mut(sum) : nullptr;
-        p.out = s->fptr_mut(o);
+        p.out = o_fp32 ? s->fptr_mut(o) : nullptr;
+        p.out16_hi = o16_hi >= 0 ? s->ptr(o16_hi) : nullptr;
+        p.out16_lo = o16_lo >= 0 ? s->ptr(o16_lo) : nullptr;
+        p.err_word = s->err_word;
         p.rows = rows; p.len = len; p.eps = eps; p.gelu = gelu;
         return launch_layer_norm(p, st);
       });
@@ -1456,12 +1594,15 @@ void lower_graph(AcSession& s) {
     c.producer.resize(graph_values);
     c.consumers.resize(graph_values);
     c.is_output.resize(graph_values);
+    c.split.clear();
     if (fuse) {
       detect_attention(c, plan);
       detect_epilogues(c, plan);
       detect_softmax_scale(c, plan);
       detect_layer_norm(c, plan);
       detect_hardswish(c, plan);
+      // Debug toggle: ALTIUS_CUDA_NO_FUSED_SPLIT=1 keeps a split kernel in front of every pair GEMM.
+      if (!std::getenv("ALTIUS_CUDA_NO_FUSED_SPLIT")) plan_presplit(c, plan);
     }
     Emit em(c);
     for (int nid : s.order)

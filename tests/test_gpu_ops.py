@@ -349,18 +349,47 @@ def test_fp16_split_falls_back_to_tf32_when_an_activation_is_out_of_range(cuda_l
         sess.close()
 
 
-def test_fp16_split_is_not_used_for_weights_out_of_range(cuda_lib):
+@pytest.mark.parametrize("wscale", [1e5, 1.0, 1e-5, 1e-7, 1e-9, 1e-20])
+def test_fp16_split_scales_weights_of_any_magnitude(cuda_lib, wscale):
+    """Constant weights are split after scaling by a power of two that brings their largest
+    magnitude to about 2^13, and the epilogue undoes it: weights far outside the fp16 range
+    (either way) lose nothing. Infinite weights are the one case left for the 3xTF32 plan."""
     from altius_b200.session import CudaSessionBuilder
     a = RNG.standard_normal((128, 256)).astype(np.float32)
-    w = RNG.standard_normal((256, 256)).astype(np.float32)
-    w[5, 17] = 1e5
+    w = (wscale * RNG.standard_normal((256, 256))).astype(np.float32)
+    m = single_op_model("MatMul", [a], [w])
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["gemm_f16x3_tcgen05"]
+        want = run_oracle(m, [a])[0]
+        got = sess.run([a])[0]
+        assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 5e-6 * (np.abs(a) @ np.abs(w))).all()
+    finally:
+        sess.close()
+    w[5, 17] = np.inf
     m = single_op_model("MatMul", [a], [w])
     sess = CudaSessionBuilder(m).build()
     try:
         assert [e["kind"] for e in sess.schedule()] == ["gemm_tf32x3_tcgen05"]
+    finally:
+        sess.close()
+
+
+@pytest.mark.parametrize("ascale", [1e-5, 1e-7, 1e-9])
+def test_fp16_split_falls_back_when_the_activations_are_all_tiny(cuda_lib, ascale):
+    """Below 2^-14 the fp16 split of an activation loses relative precision (absolute floor
+    2^-36). A region of non-zero activations none of which reaches 2^-14 is reported like an
+    overflow, and the session repeats the run on its 3xTF32 plan."""
+    from altius_b200.session import CudaSessionBuilder
+    a = (ascale * RNG.standard_normal((512, 256))).astype(np.float32)
+    w = RNG.standard_normal((256, 256)).astype(np.float32)
+    m = single_op_model("MatMul", [a], [w])
+    sess = CudaSessionBuilder(m).build()
+    try:
         want = run_oracle(m, [a])[0]
         got = sess.run([a])[0]
         assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 5e-6 * (np.abs(a) @ np.abs(w))).all()
+        assert [e["kind"] for e in sess.schedule()] == ["gemm_tf32x3_tcgen05"]
     finally:
         sess.close()
 
@@ -577,3 +606,94 @@ def test_expand(cuda_lib, ishape, oshape, dtype):
     assert want[0].shape == oshape and want[0].dtype == dtype
     assert_bit_exact(got[0], want[0])
     assert_bit_exact(got[0], np.broadcast_to(x, oshape))
+
+
+# ---- results written split by their producers for the CTA-pair GEMM that consumes them ------
+def _split_chain_bound(want, scale=1.0):
+    return 2e-5 * np.abs(want) + 2e-4 * scale
+
+
+def test_layer_norm_writes_the_split_operand_of_the_next_gemm(cuda_lib):
+    """LayerNormalization -> MatMul at the benchmark's row count: the GEMM runs on CTA pairs and
+    takes its A operand as fp16 hi / lo halves that the LayerNormalization kernel writes itself
+    (no fp32 copy of the normalised rows exists)."""
+    from altius_b200.session import CudaSessionBuilder
+    x = RNG.standard_normal((32, 197, 768)).astype(np.float32)
+    gam = (1 + 0.02 * RNG.standard_normal(768)).astype(np.float32)
+    bet = (0.02 * RNG.standard_normal(768)).astype(np.float32)
+    w = (0.02 * RNG.standard_normal((768, 2304))).astype(np.float32)
+
+    def build(g):
+        xi = g.add_input("x", x.shape)
+        h = g.op("LayerNormalization", xi, g.new_init(gam), g.new_init(bet), axis=-1, epsilon=1e-6, stash_type=1)
+        return [g.op("MatMul", h, g.new_init(w))]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["layer_norm", "gemm_f16x3_pair_tcgen05"]
+        got = sess.run([x])[0]
+    finally:
+        sess.close()
+    want = run_oracle(m, [x], sgemm="openblas")[0]
+    assert (np.abs(got - want) <= _split_chain_bound(want)).all()
+
+
+def test_gemm_epilogue_writes_the_split_operand_of_the_next_gemm(cuda_lib):
+    """MatMul -> Add -> Gelu -> MatMul -> Add at the benchmark's row count: the first GEMM's
+    epilogue (and the fix-up kernel of its K-sliced tail tiles) writes the Gelu result only as
+    fp16 hi / lo halves, which the second GEMM takes by TMA."""
+    from altius_b200.session import CudaSessionBuilder
+    x = RNG.standard_normal((6304, 768)).astype(np.float32)
+    w1 = (0.02 * RNG.standard_normal((768, 3072))).astype(np.float32)
+    b1 = (0.02 * RNG.standard_normal(3072)).astype(np.float32)
+    w2 = (0.02 * RNG.standard_normal((3072, 768))).astype(np.float32)
+    b2 = (0.02 * RNG.standard_normal(768)).astype(np.float32)
+
+    def build(g):
+        xi = g.add_input("x", x.shape)
+        h = g.op("Gelu", g.op("Add", g.op("MatMul", xi, g.new_init(w1)), g.new_init(b1)))
+        return [g.op("Add", g.op("MatMul", h, g.new_init(w2)), g.new_init(b2))]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["act_f16_split", "gemm_f16x3_pair_tcgen05", "gemm_f16x3_pair_tcgen05"]
+        got = sess.run([x])[0]
+    finally:
+        sess.close()
+    want = run_oracle(m, [x], sgemm="openblas")[0]
+    assert (np.abs(got - want) <= _split_chain_bound(want)).all()
+
+
+def test_attention_writes_the_split_operand_of_the_projection(cuda_lib):
+    from altius_b200.session import CudaSessionBuilder
+    B, T, H, hd = 32, 197, 12, 64
+    D = H * hd
+    qkv = RNG.standard_normal((B, T, 3 * D)).astype(np.float32)
+    w = (0.02 * RNG.standard_normal((D, D))).astype(np.float32)
+
+    def build(g):
+        x = g.add_input("qkv", qkv.shape)
+        i64 = lambda v: g.new_init(np.asarray(v, np.int64))
+        q, k, v = g.add_node("Split", [x, i64([D, D, D])], 3, axis=2)
+
+        def heads(t):
+            t = g.op("Reshape", t, i64([B, T, H, hd]))
+            t = g.op("Transpose", t, perm=[0, 2, 1, 3])
+            return g.op("Reshape", t, i64([B * H, T, hd]))
+        q, k, v = heads(q), heads(k), heads(v)
+        s_ = g.op("MatMul", q, g.op("Transpose", k, perm=[0, 2, 1]))
+        s_ = g.op("Mul", s_, g.new_init(np.array([hd ** -0.5], np.float32)))
+        o = g.op("MatMul", g.op("Softmax", s_, axis=-1), v)
+        o = g.op("Reshape", o, i64([B, H, T, hd]))
+        o = g.op("Transpose", o, perm=[0, 2, 1, 3])
+        o = g.op("Reshape", o, i64([B, T, D]))
+        return [g.op("MatMul", o, g.new_init(w))]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["attention_tcgen05", "gemm_f16x3_pair_tcgen05"]
+        got = sess.run([qkv])[0]
+    finally:
+        sess.close()
+    want = run_oracle(m, [qkv], sgemm="openblas")[0]
+    assert (np.abs(got - want) <= _split_chain_bound(want, 0.3)).all()
