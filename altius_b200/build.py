@@ -6,6 +6,7 @@ GPU. Kernels are compiled with --fmad=false: every fused multiply-add in the
 kernels is an explicit fmaf, so no rounding is added or removed relative to the
 reference formulas.
 """
+import hashlib
 import os
 import subprocess
 import sys
@@ -23,14 +24,26 @@ COMMON = (["-DAC_TC_BK=" + os.environ["AC_TC_BK"]] if "AC_TC_BK" in os.environ e
           "-Xcudafe", "--diag_suppress=177"]
 
 SOURCES = ["session.cu", "shapes.cpp", "lower.cpp", "eltwise.cu", "rowops.cu", "movement.cu",
-           "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "noalloc.cu"]
+           "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "noalloc.cu",
+           "model.cpp", "onnx_load.cpp", "passes.cpp"]
 
 
-def _newer(target, deps):
-    if not os.path.exists(target):
+def _fingerprint(cmd, deps):
+    """Hash of the compile command and of the contents of everything it reads: an object is
+    rebuilt whenever its source, any header or a flag differs from what it was built from
+    (modification times are not trusted; prebuilt objects travel between machines)."""
+    h = hashlib.sha256(" ".join(cmd).encode())
+    for d in sorted(deps):
+        with open(d, "rb") as f:
+            h.update(hashlib.sha256(f.read()).digest())
+    return h.hexdigest()
+
+
+def _stale(obj, stamp, fingerprint):
+    if not os.path.exists(obj) or not os.path.exists(stamp):
         return True
-    t = os.path.getmtime(target)
-    return any(os.path.getmtime(d) > t for d in deps)
+    with open(stamp) as f:
+        return f.read().strip() != fingerprint
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -42,24 +55,37 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         path = os.path.join(CSRC, src)
         obj = os.path.join(OBJDIR, src.rsplit(".", 1)[0] + ".o")
+        stamp = obj + ".stamp"
         objs.append(obj)
-        if force or _newer(obj, [path] + headers):
-            cmd = [NVCC, *ARCH, *COMMON, "-x", "cu", "-c", path, "-o", obj]
+        cmd = [NVCC, *ARCH, *COMMON, "-x", "cu", "-c", path, "-o", obj]
+        fp = _fingerprint(cmd, [path] + headers)
+        if force or verbose or _stale(obj, stamp, fp):
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
-            jobs.append(cmd)
+            jobs.append((cmd, stamp, fp))
 
-    def run(cmd):
+    def run(job):
+        cmd, stamp, fp = job
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0 or verbose:
             sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
         if r.returncode != 0:
             raise RuntimeError("nvcc failed for " + cmd[-3])
+        if stamp:
+            with open(stamp, "w") as f:
+                f.write(fp)
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         list(ex.map(run, jobs))
-    if jobs or not os.path.exists(LIB):
-        run([NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC"])
+    # The library records what it was linked from in the same way.
+    link = [NVCC, *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC"]
+    lib_fp = hashlib.sha256(" ".join(link).encode())
+    for o in objs:
+        with open(o + ".stamp") as f:
+            lib_fp.update(f.read().encode())
+    lib_stamp = os.path.join(OBJDIR, "lib.stamp")
+    if jobs or _stale(LIB, lib_stamp, lib_fp.hexdigest()):
+        run((link, lib_stamp, lib_fp.hexdigest()))
     return LIB
 
 

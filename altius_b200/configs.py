@@ -105,15 +105,41 @@ def _linear(g: Graph, w: _W, x: int, din: int, dout: int) -> int:
     return g.op("Add", y, g.new_init(w(dout)))
 
 
-def _ln(g: Graph, w: _W, x: int, dim: int, eps: float) -> int:
-    return g.op("LayerNormalization", x, g.new_init(w(dim, mean=1.0)), g.new_init(w(dim)),
-                axis=-1, epsilon=eps, stash_type=1)
+def _f32(g: Graph, v: float) -> int:
+    return g.new_init(np.array(v, dtype=np.float32))
+
+
+def _ln(g: Graph, w: _W, x: int, dim: int, eps: float, fused: bool = True) -> int:
+    gamma, beta = g.new_init(w(dim, mean=1.0)), g.new_init(w(dim))
+    if fused:
+        return g.op("LayerNormalization", x, gamma, beta, axis=-1, epsilon=eps, stash_type=1)
+    # The nine nodes an opset < 17 export spells LayerNorm with, the pattern `fuse_layer_norm`
+    # recognises (crates/core/src/optimize/layer_norm_fusion.rs:9-15).
+    mean = g.op("ReduceMean", x, axes=[-1], keep_dims=True)
+    d = g.op("Sub", x, mean)
+    var = g.op("ReduceMean", g.op("Pow", d, _f32(g, 2.0)), axes=[-1], keep_dims=True)
+    n = g.op("Div", d, g.op("Sqrt", g.op("Add", var, _f32(g, eps))))
+    return g.op("Add", g.op("Mul", n, gamma), beta)
+
+
+def _gelu(g: Graph, x: int, fused: bool = True, form: str = "erf") -> int:
+    if fused:
+        return g.op("Gelu", x)
+    if form == "erf":
+        # x * 0.5 * (1 + erf(x / sqrt(2))) as exporters write it: the pattern of `fuse_gelu`
+        # (crates/core/src/optimize/gelu_fusion.rs:12-82).
+        e = g.op("Erf", g.op("Div", x, _f32(g, np.sqrt(2.0))))
+        return g.op("Mul", g.op("Mul", x, g.op("Add", e, _f32(g, 1.0))), _f32(g, 0.5))
+    # The tanh form: the pattern of `fuse_fast_gelu` (fast_gelu_fusion.rs:5-167).
+    c = g.op("Mul", g.op("Pow", x, _f32(g, 3.0)), _f32(g, 0.044715))
+    t = g.op("Tanh", g.op("Mul", g.op("Add", x, c), _f32(g, np.sqrt(2.0 / np.pi))))
+    return g.op("Mul", g.op("Mul", x, _f32(g, 0.5)), g.op("Add", t, _f32(g, 1.0)))
 
 
 def _encoder_layer(g: Graph, w: _W, x: int, B: int, T: int, D: int, H: int, mlp: int,
-                   eps: float) -> int:
+                   eps: float, fused: bool = True, gelu_form: str = "erf") -> int:
     hd = D // H
-    h = _ln(g, w, x, D, eps)
+    h = _ln(g, w, x, D, eps, fused)
     qkv = _linear(g, w, h, D, 3 * D)                                   # [B,T,3D]
     q, k, v = g.add_node("Split", [qkv, _i64(g, [D, D, D])], 3, axis=2)
 
@@ -133,20 +159,23 @@ def _encoder_layer(g: Graph, w: _W, x: int, B: int, T: int, D: int, H: int, mlp:
     o = g.op("Reshape", o, _i64(g, [B, T, D]))
     o = _linear(g, w, o, D, D)
     x = g.op("Add", x, o)
-    h = _ln(g, w, x, D, eps)
+    h = _ln(g, w, x, D, eps, fused)
     h = _linear(g, w, h, D, mlp)
-    h = g.op("Gelu", h)
+    h = _gelu(g, h, fused, gelu_form)
     h = _linear(g, w, h, mlp, D)
     return g.op("Add", x, h)
 
 
 def vision_transformer(batch: int, dim: int, depth: int, heads: int, mlp: int, n_prefix: int,
                        eps: float = 1e-6, n_classes: int = 1000, img: int = 224, patch: int = 16,
-                       seed: int = 0) -> Tuple[Model, Dict[str, np.ndarray]]:
+                       seed: int = 0, fused: bool = True, gelu_form: str = "erf"
+                       ) -> Tuple[Model, Dict[str, np.ndarray]]:
     """ViT / DeiT encoder: patch-embed Conv 16x16/16 -> tokens (+cls[, dist]) +
     pos-embed -> `depth` pre-LN layers -> LN -> class-token select -> Gemm.
     With two prefix tokens (DeiT distilled) the two heads' logits are averaged
-    (Add, Mul 0.5). Weights ~N(0, 0.02), LN gamma ~N(1, 0.02)."""
+    (Add, Mul 0.5). Weights ~N(0, 0.02), LN gamma ~N(1, 0.02). `fused=False` spells every
+    LayerNormalization and Gelu as the node chains a raw export has (the same weights: the
+    graph passes turn it back into the fused form)."""
     w = _W(seed, 0.02)
     B, D = batch, dim
     n_patch = (img // patch) ** 2
@@ -164,8 +193,8 @@ def vision_transformer(batch: int, dim: int, depth: int, heads: int, mlp: int, n
     t = g.op("Concat", prefix, t, axis=1)                              # [B,T,D]
     t = g.op("Add", t, g.new_init(w(1, T, D)))
     for _ in range(depth):
-        t = _encoder_layer(g, w, t, B, T, D, heads, mlp, eps)
-    t = _ln(g, w, t, D, eps)
+        t = _encoder_layer(g, w, t, B, T, D, heads, mlp, eps, fused, gelu_form)
+    t = _ln(g, w, t, D, eps, fused)
     logits = None
     for i in range(n_prefix):
         tok = g.op("Gather", t, g.new_init(np.array(i, dtype=np.int64)), axis=1)     # [B,D]
@@ -180,14 +209,14 @@ def vision_transformer(batch: int, dim: int, depth: int, heads: int, mlp: int, n
     return Model(g, 13), {"input": rng.standard_normal((B, 3, img, img)).astype(np.float32)}
 
 
-def vit_base_16(batch: int = 32, seed: int = 0, depth: int = 12):
+def vit_base_16(batch: int = 32, seed: int = 0, depth: int = 12, fused: bool = True, gelu_form: str = "erf"):
     """ViT-B/16: 197 tokens, dim 768, 12 heads, MLP 3072, LN eps 1e-6."""
-    return vision_transformer(batch, 768, depth, 12, 3072, 1, 1e-6, seed=seed)
+    return vision_transformer(batch, 768, depth, 12, 3072, 1, 1e-6, seed=seed, fused=fused, gelu_form=gelu_form)
 
 
-def deit_small_distilled_16(batch: int = 64, seed: int = 0, depth: int = 12):
+def deit_small_distilled_16(batch: int = 64, seed: int = 0, depth: int = 12, fused: bool = True):
     """DeiT-Small/16 distilled: 198 tokens, dim 384, 6 heads, MLP 1536."""
-    return vision_transformer(batch, 384, depth, 6, 1536, 2, 1e-6, seed=seed)
+    return vision_transformer(batch, 384, depth, 6, 1536, 2, 1e-6, seed=seed, fused=fused)
 
 
 # ---------------------------------------------------------------------------

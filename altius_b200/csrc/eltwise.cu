@@ -225,10 +225,47 @@ __global__ void where_kernel(int mode, const uint8_t* __restrict__ cond, const f
   else o[i] = cond[i % inner] ? __ldg(x + i) : __ldg(y);            // session.rs:966-987
 }
 
+// General broadcast forms: one thread per output element, offsets by mixed-radix decomposition.
+struct TernDev {
+  int rank;
+  int64_t dims[kMaxRank], c_str[kMaxRank], x_str[kMaxRank], y_str[kMaxRank];
+};
+__device__ __forceinline__ void tern_offsets(const TernDev& p, int64_t i, int64_t* co, int64_t* xo, int64_t* yo) {
+  int64_t c = 0, x = 0, y = 0;
+#pragma unroll 1
+  for (int d = p.rank - 1; d >= 0; --d) {
+    const int64_t q = i / p.dims[d], r = i - q * p.dims[d];
+    c += r * p.c_str[d]; x += r * p.x_str[d]; y += r * p.y_str[d];
+    i = q;
+  }
+  *co = c; *xo = x; *yo = y;
+}
+__global__ void greater_bcast_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                                     uint8_t* __restrict__ o, TernDev p, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int64_t co, xo, yo;
+  tern_offsets(p, i, &co, &xo, &yo);
+  o[i] = __ldg(x + xo) > __ldg(y + yo) ? 1 : 0;
+}
+__global__ void where_bcast_kernel(const uint8_t* __restrict__ cond, const float* __restrict__ x,
+                                   const float* __restrict__ y, float* __restrict__ o, TernDev p, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int64_t co, xo, yo;
+  tern_offsets(p, i, &co, &xo, &yo);
+  o[i] = cond[co] ? __ldg(x + xo) : __ldg(y + yo);
+}
+
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ o, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) o[i] = (TO)x[i];
+}
+template <typename TI>
+__global__ void cast_to_bool_kernel(const TI* __restrict__ x, uint8_t* __restrict__ o, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) o[i] = x[i] != (TI)0 ? 1 : 0;
 }
 __global__ void cast_f32_bool_kernel(const float* __restrict__ x, uint8_t* __restrict__ o,
                                      int64_t n) {
@@ -296,9 +333,61 @@ cudaError_t launch_where(int mode, const uint8_t* cond, const float* x, const fl
   return cudaGetLastError();
 }
 
+namespace {
+TernDev tern_dev(const TernaryParams& p) {
+  TernDev d;
+  d.rank = p.rank;
+  for (int i = 0; i < kMaxRank; ++i) {
+    d.dims[i] = i < p.rank ? p.dims[i] : 1;
+    d.c_str[i] = i < p.rank ? p.c_str[i] : 0;
+    d.x_str[i] = i < p.rank ? p.x_str[i] : 0;
+    d.y_str[i] = i < p.rank ? p.y_str[i] : 0;
+  }
+  return d;
+}
+}  // namespace
+
+cudaError_t launch_greater_bcast(const TernaryParams& p, const float* x, const float* y, uint8_t* out, cudaStream_t st) {
+  if (p.n == 0) return cudaSuccess;
+  greater_bcast_kernel<<<(unsigned)((p.n + 255) / 256), 256, 0, st>>>(x, y, out, tern_dev(p), p.n);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_where_bcast(const TernaryParams& p, const uint8_t* cond, const float* x, const float* y, float* out,
+                               cudaStream_t st) {
+  if (p.n == 0) return cudaSuccess;
+  where_bcast_kernel<<<(unsigned)((p.n + 255) / 256), 256, 0, st>>>(cond, x, y, out, tern_dev(p), p.n);
+  return cudaGetLastError();
+}
+
+namespace {
+template <typename TI>
+cudaError_t cast_from(int to, const TI* x, void* out, int64_t n, unsigned blocks, cudaStream_t st) {
+  switch (to) {
+    case 0: cast_to_bool_kernel<TI><<<blocks, 256, 0, st>>>(x, (uint8_t*)out, n); break;
+    case 1: cast_kernel<TI, float><<<blocks, 256, 0, st>>>(x, (float*)out, n); break;
+    case 2: cast_kernel<TI, int32_t><<<blocks, 256, 0, st>>>(x, (int32_t*)out, n); break;
+    case 3: cast_kernel<TI, int64_t><<<blocks, 256, 0, st>>>(x, (int64_t*)out, n); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_cast(int from, int to, const void* x, void* out, int64_t n, cudaStream_t st) {
   if (n == 0) return cudaSuccess;
   const unsigned blocks = (unsigned)((n + 255) / 256);
+  // Beyond the four pairs of the reference (below): every other pair of bool / f32 / i32 / i64.
+  const bool ref_pair = (from == 2 && to == 1) || (from == 3 && to == 2) || (from == 3 && to == 1) || (from == 1 && to == 0);
+  if (!ref_pair) {
+    switch (from) {
+      case 0: return cast_from<uint8_t>(to, (const uint8_t*)x, out, n, blocks, st);
+      case 1: return cast_from<float>(to, (const float*)x, out, n, blocks, st);
+      case 2: return cast_from<int32_t>(to, (const int32_t*)x, out, n, blocks, st);
+      case 3: return cast_from<int64_t>(to, (const int64_t*)x, out, n, blocks, st);
+      default: return cudaErrorInvalidValue;
+    }
+  }
   // session.rs:1350-1378: i32->f32, i64->i32, i64->f32, f32->bool
   if (from == 2 && to == 1)
     cast_kernel<int32_t, float><<<blocks, 256, 0, st>>>((const int32_t*)x, (float*)out, n);

@@ -85,6 +85,8 @@ struct TcEpilogue {
   const float* res; long long ldres, sres;
   uint2* c16_hi; uint2* c16_lo; long long ldc16;   // result as fp16 hi / lo halves (4 per uint2; ldc16 in halves), or null
   const float* acc_scale;   // device scalar the accumulators are multiplied by (B was scaled by its inverse), or null
+  const float* b_row_scale; long long b_row_scale_stride; int k_total;   // [K, N] operand: row k of B[bz] is multiplied by
+                                                                       // b_row_scale[bz * stride + k] while it is split, or null
   int* err;                 // error word: range of the split output
   int dbg;   // timing experiments only (0 in normal use)
 };
@@ -813,10 +815,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           if (MODE == TC_3X_SPLIT_B || MODE == TC_3X_SPLIT_B_MN) {   // elementwise: any tile layout
             float4* sb = reinterpret_cast<float4*>(b_hi(s));
             float4* dbp = reinterpret_cast<float4*>(b_lo(s));
+            // A per-row factor of the [K, N] operand (the squeeze-excite gate of the input planes
+            // of a pointwise convolution) is applied here, one fp32 multiply before the split:
+            // the same bits as a separate broadcast Mul in front of the GEMM. In the MN-major
+            // tile a float4 lies within one k-row: 128-byte rows, KB rows per 32-column box.
+            const float* rs = (MODE == TC_3X_SPLIT_B_MN && ep.b_row_scale)
+                                  ? ep.b_row_scale + (long long)(wk.tile / (tiles_n * tiles_m)) * ep.b_row_scale_stride
+                                  : nullptr;
 #pragma unroll
             for (int i = 0; i < L::kBBytes / 16 / kSplitThreads; ++i) {
               float4 hi, lo;
-              tf32_split(sb[i * kSplitThreads + t0], hi, lo);
+              float4 v = sb[i * kSplitThreads + t0];
+              if (MODE == TC_3X_SPLIT_B_MN && rs) {
+                const int k = kb * KB + ((i * kSplitThreads + t0) % (KB * 8)) / 8;
+                const float f = k < ep.k_total ? __ldg(rs + k) : 1.f;
+                v.x = __fmul_rn(v.x, f); v.y = __fmul_rn(v.y, f); v.z = __fmul_rn(v.z, f); v.w = __fmul_rn(v.w, f);
+              }
+              tf32_split(v, hi, lo);
               sb[i * kSplitThreads + t0] = hi;
               dbp[i * kSplitThreads + t0] = lo;
             }
@@ -1672,6 +1687,8 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
   ep.c16_hi = static_cast<uint2*>(q.c16_hi); ep.c16_lo = static_cast<uint2*>(q.c16_lo); ep.ldc16 = q.ldc16;
   ep.acc_scale = kmode == TC_F16X3 ? q.b16_inv_scale : nullptr;
+  ep.b_row_scale = q.b_row_scale; ep.b_row_scale_stride = q.b_row_scale_stride; ep.k_total = (int)q.k;
+  if (q.b_row_scale && kmode != TC_3X_SPLIT_B_MN) return cudaErrorInvalidValue;   // exists for the [K, N] operand only
   ep.err = err_word;
   if (q.c16_hi) {
     // Only the pair kernel's common epilogues (and the tail fix-up) write the split result.

@@ -67,7 +67,21 @@ cudaError_t launch_greater_scalar(const float* x, const float* y_scalar, uint8_t
 // mode 0: out = cond ? x[0] : y[i]; mode 1: out = cond[i % inner] ? x[i] : y[0]
 cudaError_t launch_where(int mode, const uint8_t* cond, const float* x, const float* y, float* out,
                          int64_t n, int64_t inner, cudaStream_t st);
-// from/to: 0 bool, 1 f32, 2 i32, 3 i64
+// NumPy-broadcast Greater and Where over a collapsed iteration space (as BinaryParams: dims and
+// element strides per operand, 0 = broadcast): the general forms beyond the two patterns of
+// the reference (ONNX semantics; comparisons and selections are exact).
+struct TernaryParams {
+  int rank;
+  int64_t dims[kMaxRank];
+  int64_t c_str[kMaxRank];
+  int64_t x_str[kMaxRank];
+  int64_t y_str[kMaxRank];
+  int64_t n;
+};
+cudaError_t launch_greater_bcast(const TernaryParams& p, const float* x, const float* y, uint8_t* out, cudaStream_t st);
+cudaError_t launch_where_bcast(const TernaryParams& p, const uint8_t* cond, const float* x, const float* y, float* out,
+                               cudaStream_t st);
+// from/to: 0 bool, 1 f32, 2 i32, 3 i64. Every pair (C conversion rules; to bool: x != 0).
 cudaError_t launch_cast(int from, int to, const void* x, void* out, int64_t n, cudaStream_t st);
 cudaError_t launch_batch_norm(const float* x, const float* scale, const float* bias,
                               const float* mean, const float* var, float* out, int64_t n,
@@ -76,8 +90,12 @@ cudaError_t launch_batch_norm(const float* x, const float* scale, const float* b
 // ---- row kernels (reductions over the last axis) ----------------------------
 // Softmax(x * scale) with the reference's polynomial exponential. `scale_mode`
 // 0: none, 1: multiply by *scale, 2: divide by *scale (scalar read on device).
+// With `mask` (bool, mask_rows x len, repeated over the rows) the scaled value is replaced by
+// *mask_else where the mask is false before the softmax: the Where(mask, x, c) of a masked
+// attention folded in (crates/session_interpreter/src/session.rs:958-987 computes that Where).
 cudaError_t launch_softmax(const float* x, float* out, int64_t rows, int64_t len, int scale_mode,
-                           const float* scale, cudaStream_t st);
+                           const float* scale, const uint8_t* mask, int64_t mask_rows, const float* mask_else,
+                           cudaStream_t st);
 
 // v = x; if (pre_bias) v += pre_bias[col]; if (gelu) v = Gelu(v);
 // if (residual) v = residual_first ? residual + v : v + residual;
@@ -178,6 +196,8 @@ struct GemmParams {
   void* c16_lo;             // halves [m, ldc16], for the GEMM that takes it as its pre-split A; or null
   int64_t ldc16;
   const float* b16_inv_scale;  // device scalar 2^-e when b16_hi / b16_lo hold B * 2^e; or null
+  const float* b_row_scale;    // tensor-core path with B given [K, N] only: row k of B[batch] is multiplied by
+  int64_t b_row_scale_stride;  // b_row_scale[batch * stride + k] (fp32, before the split); or null
   float alpha;
   float beta;               // applied to c_in (may alias c); 0: c_in not read
   const float* c_in; int64_t ldc_in; int64_t stride_c_in;

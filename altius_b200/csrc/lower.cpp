@@ -106,8 +106,11 @@ struct Plan {
   std::map<int, AttentionFusion> attention;  // Softmax node -> whole attention core
   std::map<int, Epilogue> epi;      // base node (MatMul/Gemm/Conv2d) -> epilogue
   std::map<int, int> softmax_scale; // Softmax node -> Mul/Div node folded in
+  std::map<int, int> softmax_mask;  // Softmax node -> Where(mask, x, c) node folded in
   std::map<int, LnFusion> ln;       // LayerNormalization node -> folded producers
   std::map<int, int> hardswish;     // Mul node -> HardSigmoid node folded in
+  struct SeGate { int x, gate; };
+  std::map<int, SeGate> se_gate;    // pointwise Conv2d node -> squeeze-excite Mul folded into its input
 };
 
 // Recognises `hs = HardSigmoid(t); m = Mul(t, hs)` hanging off value t whose only
@@ -355,15 +358,39 @@ void detect_epilogues(Ctx& c, Plan& plan) {
   }
 }
 
+// Softmax <- [Where(mask, ., c)] <- [Mul | Div by a scalar]: the masked, scaled softmax of an
+// attention block in one kernel. The mask is a bool tensor over the trailing dims of the scores
+// (broadcast over the leading ones: the interpreter's second Where pattern,
+// session.rs:958-987), `c` a scalar.
 void detect_softmax_scale(Ctx& c, Plan& plan) {
   for (int nid : c.s.order) {
     Node& n = c.node(nid);
     if (c.absorbed[nid] || n.op != AC_OP_SOFTMAX) continue;
-    const int x = n.inputs[0];
-    const int p = c.producer[x];
-    if (p < 0 || c.absorbed[p] || !c.single_use(x)) continue;
+    int x = n.inputs[0];
+    const Value& sv = c.val(x);
     const int64_t axis = n.ints.empty() ? -1 : n.ints[0];
-    if (!(axis == -1 || axis == c.val(x).rank - 1)) continue;   // left to lower_node, which rejects it
+    if (!(axis == -1 || axis == sv.rank - 1)) continue;   // left to lower_node, which rejects it
+    if (sv.elem_ty != AC_F32 || sv.rank < 1) continue;
+    int p = c.producer[x];
+    if (p >= 0 && !c.absorbed[p] && c.single_use(x) && c.node(p).op == AC_OP_WHERE) {
+      const Node& w = c.node(p);
+      const Value& cv = c.val(w.inputs[0]);
+      const Value& xv = c.val(w.inputs[1]);
+      const Value& yv = c.val(w.inputs[2]);
+      bool ok = cv.elem_ty == AC_BOOL && same_dims(xv, sv) && yv.numel() == 1 && xv.elem_ty == AC_F32 &&
+                yv.elem_ty == AC_F32 && cv.rank <= sv.rank && cv.rank >= 1;
+      // The mask's dims, leading 1s aside, are the trailing dims of the scores.
+      int lead = 0;
+      while (ok && lead < cv.rank - 1 && cv.dims[lead] == 1) ++lead;
+      for (int i = lead; ok && i < cv.rank; ++i) ok = cv.dims[i] == sv.dims[sv.rank - cv.rank + i];
+      if (ok) {
+        plan.softmax_mask[nid] = p;
+        c.absorbed[p] = 1;
+        x = w.inputs[1];
+        p = c.producer[x];
+      }
+    }
+    if (p < 0 || c.absorbed[p] || !c.single_use(x)) continue;
     Node& m = c.node(p);
     if (m.op != AC_OP_MUL && m.op != AC_OP_DIV) continue;
     const Value& a = c.val(m.inputs[0]);
@@ -450,6 +477,48 @@ void detect_hardswish(Ctx& c, Plan& plan) {
   }
 }
 
+// Squeeze-excite gate: Mul(x [N,C,H,W], g [N,C,1,1]) whose only user is a pointwise Conv2d that
+// the tensor-core kernel runs with the planes as its [K, N] operand. The multiply moves into
+// that kernel's operand split (one fp32 multiply per element, the bits of the separate Mul):
+// the gated feature map is never written or re-read.
+void detect_se_gate(Ctx& c, Plan& plan) {
+  const int mode = c.s.opt.gemm_mode;
+  if (mode == 1 || mode == 2) return;
+  for (int nid : c.s.order) {
+    const Node& m = c.node(nid);
+    if (c.absorbed[nid] || m.op != AC_OP_MUL) continue;
+    int x = -1, g = -1;
+    for (int k = 0; k < 2; ++k) {
+      const Value& a = c.val(m.inputs[k]);
+      const Value& b = c.val(m.inputs[1 - k]);
+      if (a.rank == 4 && b.rank == 4 && a.elem_ty == AC_F32 && b.elem_ty == AC_F32 && b.dims[0] == a.dims[0] &&
+          b.dims[1] == a.dims[1] && b.dims[2] == 1 && b.dims[3] == 1 && a.dims[2] * a.dims[3] > 1) {
+        x = m.inputs[k]; g = m.inputs[1 - k];
+      }
+    }
+    if (x < 0 || c.val(x).is_const || c.val(g).is_const) continue;
+    const int o = m.outputs[0];
+    if (!c.single_use(o)) continue;
+    const int cn = c.only_consumer(o);
+    const Node& conv = c.node(cn);
+    if (c.absorbed[cn] || conv.op != AC_OP_CONV2D || conv.inputs[0] != o) continue;
+    const Value& xv = c.val(x);
+    const Value& ov = c.val(conv.outputs[0]);
+    const int64_t hw = xv.dims[2] * xv.dims[3], ch = xv.dims[1];
+    const bool pointwise = conv.ints[0] == 1 && conv.ints[1] == 1 && conv.ints[2] == 1 && conv.ints[3] == 1 &&
+                           conv.ints[6] == 1 && conv.ints[7] == 0;
+    bool nopad = true;
+    for (int64_t k = 0; k < conv.ints[9]; ++k) nopad = nopad && conv.ints[10 + k] == 0;
+    const double flops = 2.0 * xv.dims[0] * ov.dims[1] * hw * ch;
+    // The conditions under which lower_conv / emit_gemm take the [K, N] tensor-core path.
+    if (!pointwise || !nopad || (hw % 4) != 0 || (ch % 4) != 0 || ch < 8 || flops < double(1 << 23) ||
+        xv.dims[0] > 65535 || !c.val(conv.inputs[1]).is_const)
+      continue;
+    plan.se_gate[cn] = Plan::SeGate{x, g};
+    c.absorbed[nid] = 1;
+  }
+}
+
 // ---- step construction ------------------------------------------------------------
 struct Emit {
   Ctx& c;
@@ -510,6 +579,30 @@ BinaryParams make_binary(int op, const Value& a, const Value& b, const Value& ou
     }
   }
   if (r == 0) { p.dims[0] = 1; p.a_str[0] = 0; p.b_str[0] = 0; r = 1; }
+  p.rank = r;
+  return p;
+}
+
+// Collapsed iteration space of three broadcast operands (condition, x, y) against `out`.
+TernaryParams make_ternary(const Value& out, const Value& cnd, const Value& x, const Value& y) {
+  int64_t cs[AC_MAX_RANK], xs[AC_MAX_RANK], ys[AC_MAX_RANK];
+  broadcast_strides(cnd, out, cs);
+  broadcast_strides(x, out, xs);
+  broadcast_strides(y, out, ys);
+  TernaryParams p{};
+  p.n = out.numel();
+  int r = 0;
+  for (int d = 0; d < out.rank; ++d) {
+    const int64_t dim = out.dims[d];
+    if (dim == 1) continue;
+    if (r > 0 && p.c_str[r - 1] == cs[d] * dim && p.x_str[r - 1] == xs[d] * dim && p.y_str[r - 1] == ys[d] * dim) {
+      p.dims[r - 1] *= dim;
+      p.c_str[r - 1] = cs[d]; p.x_str[r - 1] = xs[d]; p.y_str[r - 1] = ys[d];
+    } else {
+      p.dims[r] = dim; p.c_str[r] = cs[d]; p.x_str[r] = xs[d]; p.y_str[r] = ys[d]; ++r;
+    }
+  }
+  if (r == 0) { p.dims[0] = 1; r = 1; }
   p.rank = r;
   return p;
 }
@@ -635,7 +728,7 @@ void plan_presplit(Ctx& c, Plan& plan) {
 
 void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, int c_in, int bias_n,
                int bias_m, float alpha, float beta, float bias_scale, const Epilogue* e,
-               int64_t a_off = 0, int64_t b_off = 0, int64_t c_off = 0) {
+               int64_t a_off = 0, int64_t b_off = 0, int64_t c_off = 0, int b_row_scale = -1) {
   AcSession* s = em.s;
   GemmShape g = g_in;
   const int act = e ? e->act : ACT_NONE;
@@ -760,8 +853,10 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     ws_bytes = gemm_tc_workspace_bytes(g.m, g.n, g.k, g.batch, b16_hi >= 0 ? 2 : (b_lo >= 0 ? 0 : 1), pairs);
     if (ws_bytes) ws = new_value(em.c, (int64_t)(ws_bytes / 4), false);
   }
+  if (b_row_scale >= 0 && (!tc || g.tb || b16_hi >= 0 || b_lo >= 0))
+    fail(AC_ERR_INVALID, "internal: a row scale was planned for a GEMM that does not read its rhs as [K, N] tiles");
   std::vector<int> reads = {a_fp32_present ? a : -1, bsrc, b_plain, b_lo, b16_hi, b16_lo, b16_scale, a16_hi, a16_lo,
-                            c_in, bias_n, bias_m, res};
+                            c_in, bias_n, bias_m, res, b_row_scale};
   const char* kind = !tc ? "gemm_fp32_simt"
                      : (mode == 2 ? "gemm_tf32x1_tcgen05"
                                   : (b16_hi >= 0 ? (a16_hi >= 0 ? "gemm_f16x3_pair_tcgen05" : "gemm_f16x3_tcgen05")
@@ -790,6 +885,8 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.c16_lo = c16_lo >= 0 ? s->ptr(c16_lo) : nullptr;
     p.ldc16 = g.n;
     p.b16_inv_scale = b16_scale >= 0 ? s->fptr(b16_scale) : nullptr;
+    p.b_row_scale = b_row_scale >= 0 ? s->fptr(b_row_scale) : nullptr;
+    p.b_row_scale_stride = g.k;
     p.alpha = alpha; p.beta = c_in >= 0 ? beta : 0.f;
     p.c_in = c_in >= 0 ? s->fptr(c_in) + c_off : nullptr; p.ldc_in = g.ldc; p.stride_c_in = g.sc;
     p.bias_n = bias_n >= 0 ? s->fptr(bias_n) : nullptr;
@@ -798,7 +895,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.act = act; p.act_alpha = aa; p.act_beta = ab;
     p.residual = res >= 0 ? s->fptr(res) + c_off : nullptr; p.ld_res = g.ldc; p.stride_res = g.sc;
     if (tc && gemm_tc_supported(p)) return launch_gemm_tc(p, mode, s->err_word, st);
-    if (!p.a || !p.c || p.c16_hi) return cudaErrorInvalidValue;   // operands exist for the tensor-core kernel only
+    if (!p.a || !p.c || p.c16_hi || p.b_row_scale) return cudaErrorInvalidValue;   // operands exist for the tensor-core kernel only
     // The CUDA-core kernel multiplies the operand as given, not a TF32-rounded copy of it.
     if (b_lo >= 0) { p.b = s->fptr(b_plain) + b_off; p.b_lo = nullptr; }
     return launch_gemm_simt(p, st);
@@ -847,10 +944,11 @@ void lower_gemm(Emit& em, int nid, const Epilogue* e) {
   emit_gemm(em, n.op, g, a, b, out, c_in, bias_n, -1, alpha, beta, beta, e);
 }
 
-void lower_conv(Emit& em, int nid, const Epilogue* e) {
+void lower_conv(Emit& em, int nid, const Epilogue* e, const Plan::SeGate* gate = nullptr) {
   Node& n = em.c.node(nid);
   AcSession* s = em.s;
-  const int x = n.inputs[0], w = n.inputs[1];
+  // With a folded squeeze-excite gate the convolution reads the un-gated planes.
+  const int x = gate ? gate->x : n.inputs[0], w = n.inputs[1];
   int bias = n.inputs.size() > 2 ? n.inputs[2] : -1;
   if (e && e->bias >= 0) bias = e->bias;
   const int out = e ? e->out : n.outputs[0];
@@ -1004,7 +1102,10 @@ void lower_conv(Emit& em, int nid, const Epilogue* e) {
     const int64_t a_off = (int64_t)gi * ocg * kdim, b_off = (int64_t)gi * kdim * ohw,
                   c_off = (int64_t)gi * ocg * ohw;
     if (p.group == 1) {
-      emit_gemm(em, n.op, g, a_src, bsrc, out, -1, -1, bias, 1.f, 0.f, 1.f, &eg, a_off, b_off, c_off);
+      if (gate && (bsrc != x || rhs_transposed))
+        fail(AC_ERR_INVALID, "internal: a squeeze-excite gate was folded into a convolution that does not read its planes in place");
+      emit_gemm(em, n.op, g, a_src, bsrc, out, -1, -1, bias, 1.f, 0.f, 1.f, &eg, a_off, b_off, c_off,
+                gate ? gate->gate : -1);
     } else {
       if (bias >= 0 || eg.residual >= 0)
         fail(AC_ERR_UNSUPPORTED, "Conv2d: grouped (non-depthwise) convolution with bias");
@@ -1077,8 +1178,17 @@ void lower_node(Emit& em, Plan& plan, int nid) {
                          n.floats.size() > 1 ? n.floats[1] : 0.5f);
     case AC_OP_GREATER: {
       const int x = n.inputs[0], y = n.inputs[1], o = n.outputs[0];
-      if (!(V(y).numel() == 1 && V(y).rank <= 1))
-        fail(AC_ERR_UNSUPPORTED, "Greater: only a scalar rhs");  // session.rs:559
+      if (!(V(y).numel() == 1 && V(y).rank <= 1)) {
+        // The reference stops here (session.rs:559); the general form broadcasts as ONNX defines.
+        require_f32(V(x), "Greater");
+        require_f32(V(y), "Greater");
+        const TernaryParams tp = make_ternary(V(o), V(o), V(x), V(y));
+        em.add("greater_bcast", n.op, {x, y}, {o}, f32_bytes(V(x)) + f32_bytes(V(y)) + (double)V(o).bytes(), 0,
+               [=](cudaStream_t st) {
+                 return launch_greater_bcast(tp, s->fptr(x), s->fptr(y), static_cast<uint8_t*>(s->ptr(o)), st);
+               });
+        return;
+      }
       const int64_t cnt = V(x).numel();
       em.add("greater", n.op, {x, y}, {o}, 5.0 * cnt, 0, [=](cudaStream_t st) {
         return launch_greater_scalar(s->fptr(x), s->fptr(y), static_cast<uint8_t*>(s->ptr(o)), cnt, st);
@@ -1098,7 +1208,17 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         mode = 1;
         inner = ov.dims[2] * ov.dims[3];
       } else {
-        fail(AC_ERR_UNSUPPORTED, "Where: unsupported broadcasting pattern");
+        // Beyond the reference's two patterns: condition, x and y broadcast as ONNX defines.
+        if (cv.elem_ty != AC_BOOL) fail(AC_ERR_UNSUPPORTED, "Where: the condition must be a bool tensor");
+        require_f32(V(x), "Where");
+        require_f32(V(y), "Where");
+        const TernaryParams tp = make_ternary(ov, cv, V(x), V(y));
+        em.add("where_bcast", n.op, {cd, x, y}, {o}, (double)cv.bytes() + f32_bytes(V(x)) + f32_bytes(V(y)) + f32_bytes(ov), 0,
+               [=](cudaStream_t st) {
+                 return launch_where_bcast(tp, static_cast<const uint8_t*>(s->ptr(cd)), s->fptr(x), s->fptr(y),
+                                           s->fptr_mut(o), st);
+               });
+        return;
       }
       const int64_t cnt = ov.numel();
       em.add("where", n.op, {cd, x, y}, {o}, 9.0 * cnt, 0, [=](cudaStream_t st) {
@@ -1150,9 +1270,9 @@ void lower_node(Emit& em, Plan& plan, int nid) {
     case AC_OP_CAST: {
       const int x = n.inputs[0], o = n.outputs[0];
       const int from = V(x).elem_ty, to = (int)n.ints[0];
-      const bool ok = (from == AC_I32 && to == AC_F32) || (from == AC_I64 && to == AC_I32) ||
-                      (from == AC_I64 && to == AC_F32) || (from == AC_F32 && to == AC_BOOL);
-      if (!ok) fail(AC_ERR_UNSUPPORTED, "Cast: unsupported type pair");  // session.rs:1375-1376
+      // session.rs:1350-1378 has i32->f32, i64->i32, i64->f32 and f32->bool; every other pair of
+      // the four element types is converted as C does.
+      if (from < AC_BOOL || from > AC_I64 || to < AC_BOOL || to > AC_I64) fail(AC_ERR_UNSUPPORTED, "Cast: unsupported type pair");
       const int64_t cnt = V(x).numel();
       em.add("cast", n.op, {x}, {o}, (double)V(x).bytes() + V(o).bytes(), 0, [=](cudaStream_t st) {
         return launch_cast(from, to, s->ptr(x), s->ptr(o), cnt, st);
@@ -1219,7 +1339,14 @@ void lower_node(Emit& em, Plan& plan, int nid) {
       if (!(axis == -1 || axis == xv.rank - 1))
         fail(AC_ERR_UNSUPPORTED, "Softmax: last axis only");  // session.rs:999
       const int64_t len = xv.dims[xv.rank - 1], rows = xv.numel() / std::max<int64_t>(len, 1);
-      int mode = 0, scale = -1;
+      int mode = 0, scale = -1, mask = -1, mask_else = -1;
+      int64_t mask_rows = 1;
+      auto mk = plan.softmax_mask.find(nid);
+      if (mk != plan.softmax_mask.end()) {
+        const Node& w = c.node(mk->second);
+        mask = w.inputs[0]; x = w.inputs[1]; mask_else = w.inputs[2];
+        mask_rows = V(mask).numel() / std::max<int64_t>(len, 1);
+      }
       auto it = plan.softmax_scale.find(nid);
       if (it != plan.softmax_scale.end()) {
         Node& m = c.node(it->second);
@@ -1228,10 +1355,13 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         x = b_scalar ? m.inputs[0] : m.inputs[1];
         mode = m.op == AC_OP_MUL ? 1 : 2;
       }
-      em.add(mode ? "softmax_scaled" : "softmax", n.op, {x, scale}, {o}, 8.0 * rows * len, 0,
+      const char* kind = mask >= 0 ? (mode ? "softmax_scaled_masked" : "softmax_masked") : (mode ? "softmax_scaled" : "softmax");
+      em.add(kind, n.op, {x, scale, mask, mask_else}, {o}, 8.0 * rows * len + (mask >= 0 ? (double)V(mask).bytes() : 0.0), 0,
              [=](cudaStream_t st) {
                return launch_softmax(s->fptr(x), s->fptr_mut(o), rows, len, mode,
-                                     scale >= 0 ? s->fptr(scale) : nullptr, st);
+                                     scale >= 0 ? s->fptr(scale) : nullptr,
+                                     mask >= 0 ? static_cast<const uint8_t*>(s->ptr(mask)) : nullptr, mask_rows,
+                                     mask_else >= 0 ? s->fptr(mask_else) : nullptr, st);
              });
       return;
     }
@@ -1484,7 +1614,9 @@ void lower_node(Emit& em, Plan& plan, int nid) {
     }
     case AC_OP_CONV2D: {
       auto it = plan.epi.find(nid);
-      return lower_conv(em, nid, it == plan.epi.end() ? nullptr : &it->second);
+      auto sg = plan.se_gate.find(nid);
+      return lower_conv(em, nid, it == plan.epi.end() ? nullptr : &it->second,
+                        sg == plan.se_gate.end() ? nullptr : &sg->second);
     }
     default:
       fail(AC_ERR_UNSUPPORTED, std::string(op_name(n.op)) + ": Kernel not implemented");
@@ -1601,6 +1733,7 @@ void lower_graph(AcSession& s) {
       detect_softmax_scale(c, plan);
       detect_layer_norm(c, plan);
       detect_hardswish(c, plan);
+      detect_se_gate(c, plan);
       // Debug toggle: ALTIUS_CUDA_NO_FUSED_SPLIT=1 keeps a split kernel in front of every pair GEMM.
       if (!std::getenv("ALTIUS_CUDA_NO_FUSED_SPLIT")) plan_presplit(c, plan);
     }

@@ -41,16 +41,24 @@ __device__ __forceinline__ float pre_scale(float x, float s) {
 // ---- Softmax -----------------------------------------------------------------
 // compute_softmax, session.rs:990-1026 + fast_sum_exp, fast_math.rs:102-187:
 // m = max(row) ignoring NaN; e = exp_poly(max(x - m, -88.37626)); out = e * (1 / sum e).
-template <int VPT, int MODE>
+struct SoftmaxMask {
+  const uint8_t* mask;   // [mask_rows, len] or null
+  int64_t mask_rows;
+  const float* other;    // value where the mask is false
+};
+
+template <int VPT, int MODE, bool MASK>
 __global__ void __launch_bounds__(kThreads) softmax_warp(const float* __restrict__ x,
                                                          float* __restrict__ out, int64_t rows,
-                                                         int len, const float* __restrict__ scale) {
+                                                         int len, const float* __restrict__ scale, SoftmaxMask mk) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
   const float s = MODE ? __ldg(scale) : 1.f;
+  const float other = MASK ? __ldg(mk.other) : 0.f;
   for (int64_t row = warp; row < rows; row += nwarps) {
     const float* xr = x + row * len;
+    const uint8_t* mr = MASK ? mk.mask + (row % mk.mask_rows) * len : nullptr;
     float v[VPT];
     float m = CUDART_NAN_F;
 #pragma unroll
@@ -58,6 +66,7 @@ __global__ void __launch_bounds__(kThreads) softmax_warp(const float* __restrict
       const int c = lane + 32 * i;
       if (c < len) {
         v[i] = pre_scale<MODE>(__ldg(xr + c), s);
+        if (MASK) v[i] = mr[c] ? v[i] : other;     // Where(mask, x, other): a selection, exact
         m = fmaxf(v[i], m);
       }
     }
@@ -84,24 +93,30 @@ __global__ void __launch_bounds__(kThreads) softmax_warp(const float* __restrict
 
 // Rows longer than the register path holds: three passes over the row by one
 // warp (the re-reads hit L1/L2).
-template <int MODE>
+template <int MODE, bool MASK>
 __global__ void __launch_bounds__(kThreads) softmax_long(const float* __restrict__ x,
                                                          float* __restrict__ out, int64_t rows,
                                                          int64_t len,
-                                                         const float* __restrict__ scale) {
+                                                         const float* __restrict__ scale, SoftmaxMask mk) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
   const float s = MODE ? __ldg(scale) : 1.f;
+  const float other = MASK ? __ldg(mk.other) : 0.f;
   for (int64_t row = warp; row < rows; row += nwarps) {
     const float* xr = x + row * len;
+    const uint8_t* mr = MASK ? mk.mask + (row % mk.mask_rows) * len : nullptr;
     float* orow = out + row * len;
+    auto val = [&](int64_t c) {
+      const float v = pre_scale<MODE>(xr[c], s);
+      return MASK ? (mr[c] ? v : other) : v;
+    };
     float m = CUDART_NAN_F;
-    for (int64_t c = lane; c < len; c += 32) m = fmaxf(pre_scale<MODE>(xr[c], s), m);
+    for (int64_t c = lane; c < len; c += 32) m = fmaxf(val(c), m);
     m = warp_max(m);
     float sum = 0.f;
     for (int64_t c = lane; c < len; c += 32) {
-      const float e = exp_poly_softmax(__fsub_rn(pre_scale<MODE>(xr[c], s), m));
+      const float e = exp_poly_softmax(__fsub_rn(val(c), m));
       orow[c] = e;
       sum = __fadd_rn(sum, e);
     }
@@ -111,14 +126,14 @@ __global__ void __launch_bounds__(kThreads) softmax_long(const float* __restrict
   }
 }
 
-template <int MODE>
+template <int MODE, bool MASK>
 cudaError_t softmax_dispatch(const float* x, float* out, int64_t rows, int64_t len,
-                             const float* scale, cudaStream_t st) {
+                             const float* scale, SoftmaxMask mk, cudaStream_t st) {
   const int64_t blocks64 = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const unsigned blocks = (unsigned)(blocks64 > device_sm_count() * 64 ? device_sm_count() * 64 : blocks64);
   const int vpt = (int)((len + 31) / 32);
 #define AC_SM(V)                                                                         \
-  softmax_warp<V, MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, (int)len, scale)
+  softmax_warp<V, MODE, MASK><<<blocks, kThreads, 0, st>>>(x, out, rows, (int)len, scale, mk)
   if (vpt <= 1) AC_SM(1);
   else if (vpt <= 2) AC_SM(2);
   else if (vpt <= 4) AC_SM(4);
@@ -128,7 +143,7 @@ cudaError_t softmax_dispatch(const float* x, float* out, int64_t rows, int64_t l
   else if (vpt <= 16) AC_SM(16);
   else if (vpt <= 24) AC_SM(24);
   else if (vpt <= 32) AC_SM(32);
-  else softmax_long<MODE><<<blocks, kThreads, 0, st>>>(x, out, rows, len, scale);
+  else softmax_long<MODE, MASK><<<blocks, kThreads, 0, st>>>(x, out, rows, len, scale, mk);
 #undef AC_SM
   return cudaGetLastError();
 }
@@ -438,11 +453,20 @@ __global__ void __launch_bounds__(kThreads) max_all_stage(const float* __restric
 }  // namespace
 
 cudaError_t launch_softmax(const float* x, float* out, int64_t rows, int64_t len, int scale_mode,
-                           const float* scale, cudaStream_t st) {
+                           const float* scale, const uint8_t* mask, int64_t mask_rows, const float* mask_else,
+                           cudaStream_t st) {
   if (rows == 0 || len == 0) return cudaSuccess;
-  if (scale_mode == 1) return softmax_dispatch<1>(x, out, rows, len, scale, st);
-  if (scale_mode == 2) return softmax_dispatch<2>(x, out, rows, len, scale, st);
-  return softmax_dispatch<0>(x, out, rows, len, scale, st);
+  if (mask) {
+    if (mask_rows <= 0 || !mask_else) return cudaErrorInvalidValue;
+    const SoftmaxMask mk{mask, mask_rows, mask_else};
+    if (scale_mode == 1) return softmax_dispatch<1, true>(x, out, rows, len, scale, mk, st);
+    if (scale_mode == 2) return softmax_dispatch<2, true>(x, out, rows, len, scale, mk, st);
+    return softmax_dispatch<0, true>(x, out, rows, len, scale, mk, st);
+  }
+  const SoftmaxMask mk{nullptr, 1, nullptr};
+  if (scale_mode == 1) return softmax_dispatch<1, false>(x, out, rows, len, scale, mk, st);
+  if (scale_mode == 2) return softmax_dispatch<2, false>(x, out, rows, len, scale, mk, st);
+  return softmax_dispatch<0, false>(x, out, rows, len, scale, mk, st);
 }
 
 cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {

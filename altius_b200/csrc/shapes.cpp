@@ -170,9 +170,16 @@ void infer_shapes(AcSession& s) {
       case AC_OP_GREATER:
         set_shape(out(0), AC_BOOL, broadcast(in(0), in(1), "Greater"));
         break;
-      case AC_OP_WHERE:
-        set_shape(out(0), in(1).elem_ty, broadcast(in(1), in(2), "Where"));
+      case AC_OP_WHERE: {
+        // The reference broadcasts x with y (its two patterns keep the condition inside that
+        // shape); the condition takes part here as ONNX defines it.
+        Value xy;
+        const std::vector<int64_t> d = broadcast(in(1), in(2), "Where");
+        xy.rank = (int)d.size();
+        for (size_t i = 0; i < d.size(); ++i) xy.dims[i] = d[i];
+        set_shape(out(0), in(1).elem_ty, broadcast(xy, in(0), "Where"));
         break;
+      }
       case AC_OP_EXPAND: {
         // shape.rs:148-160: the output shape is the `shape` input, taken as it is.
         const Value& sh = in(1);
@@ -402,6 +409,9 @@ void infer_shapes(AcSession& s) {
         break;
       }
       case AC_OP_SHAPE:
+        // shape.rs:516-524 asserts start == 0 and no end.
+        if (n.ints.size() >= 2 && (n.ints[0] != 0 || n.ints[1] != 0))
+          fail(AC_ERR_UNSUPPORTED, "Shape: start / end are not supported");
         set_shape(out(0), AC_I64, {(int64_t)in(0).rank});
         break;
       case AC_OP_MATMUL: {

@@ -90,6 +90,9 @@ ABI_SYMBOLS = (
     "altius_cuda_schedule", "altius_cuda_profile", "altius_cuda_profile_reset", "altius_cuda_last_error",
     "altius_cuda_destroy", "altius_cuda_host_alloc", "altius_cuda_host_free",
     "altius_cuda_device_count", "altius_cuda_reduce_max_noalloc",
+    "altius_model_load_onnx", "altius_model_load_onnx_buffer", "altius_model_from_graph",
+    "altius_model_run_pass", "altius_model_optimize", "altius_model_graph", "altius_model_value_name",
+    "altius_model_lookup_named_value", "altius_model_destroy", "altius_cuda_create_from_onnx",
 )
 
 _lib = None
@@ -133,6 +136,19 @@ def load_library() -> ctypes.CDLL:
     lib.altius_cuda_host_alloc.argtypes = [ctypes.c_size_t, ctypes.POINTER(P)]
     lib.altius_cuda_host_free.argtypes = [P]
     lib.altius_cuda_reduce_max_noalloc.argtypes = [P, ctypes.c_int64, P, P]
+    lib.altius_model_load_onnx.argtypes = [ctypes.c_char_p, ctypes.POINTER(P)]
+    lib.altius_model_load_onnx_buffer.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(P)]
+    lib.altius_model_from_graph.argtypes = [ctypes.POINTER(AcGraphDesc), ctypes.POINTER(P)]
+    lib.altius_model_run_pass.argtypes = [P, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32)]
+    lib.altius_model_optimize.argtypes = [P]
+    lib.altius_model_graph.argtypes = [P, ctypes.POINTER(AcGraphDesc)]
+    lib.altius_model_value_name.argtypes = [P, ctypes.c_int32]
+    lib.altius_model_value_name.restype = ctypes.c_char_p
+    lib.altius_model_lookup_named_value.argtypes = [P, ctypes.c_char_p]
+    lib.altius_model_lookup_named_value.restype = ctypes.c_int32
+    lib.altius_model_destroy.argtypes = [P]
+    lib.altius_model_destroy.restype = None
+    lib.altius_cuda_create_from_onnx.argtypes = [ctypes.c_char_p, ctypes.POINTER(AcOptions), ctypes.POINTER(P)]
     _lib = lib
     return lib
 
@@ -192,11 +208,108 @@ def _attr_arrays(node: ir.Node):
     elif op == "LayerNormalization":
         ints = [a.get("axis", -1), a.get("stash_type", 1)]
         floats = [a.get("epsilon", 1e-5)]
+    elif op == "Shape":
+        end = a.get("end")
+        ints = [a.get("start", 0), 0 if end is None else 1, 0 if end is None else end]
     return ints, floats
 
 
+def attrs_from_arrays(op: str, ints: Sequence[int], floats: Sequence[float]) -> dict:
+    """Inverse of `_attr_arrays`: the attribute dictionary of an `ir.Node` from the flattened
+    arrays of the C ABI (a graph that comes back from the loader or from the passes)."""
+    ints, floats = list(ints), list(floats)
+    if op == "Conv2d":
+        npads = ints[9]
+        act = {0: None, 1: "Relu", 2: "HardSigmoid"}[ints[8]]
+        return dict(kernel_shape=ints[0:2], strides=ints[2:4], dilations=ints[4:6], group=ints[6],
+                    auto_pad="SAME_UPPER" if ints[7] else "NOTSET", activation=act,
+                    padding=ints[10:10 + npads], activation_alpha=floats[0], activation_beta=floats[1])
+    if op == "MaxPool":
+        npads = ints[5]
+        return dict(kernel_shape=ints[0:2], strides=ints[2:4], auto_pad="SAME_UPPER" if ints[4] else "NOTSET",
+                    padding=ints[6:6 + npads])
+    if op == "HardSigmoid":
+        return dict(alpha=floats[0], beta=floats[1])
+    if op == "LeakyReLU":
+        return dict(alpha=floats[0])
+    if op == "Resize":
+        return dict(mode="nearest" if ints[0] == 0 else "linear",
+                    coordinate_transformation_mode="asymmetric" if ints[1] == 0 else "half_pixel",
+                    nearest_mode="floor" if ints[2] == 0 else "round_prefer_floor")
+    if op in ("Softmax", "Flatten", "Concat", "Gather"):
+        return dict(axis=ints[0])
+    if op == "Cast":
+        return dict(to=ints[0])
+    if op == "Transpose":
+        return dict(perm=ints)
+    if op in ("Squeeze", "Unsqueeze"):
+        return dict(axes=ints) if ints else {}
+    if op in ("ReduceMax", "ReduceMean", "ReduceMin"):
+        return dict(keep_dims=bool(ints[0]), axes=ints[1:])
+    if op == "Split":
+        return dict(axis=ints[0], split=ints[1:])
+    if op == "Gemm":
+        return dict(trans_a=bool(ints[0]), trans_b=bool(ints[1]), alpha=floats[0], beta=floats[1])
+    if op == "BatchNormalization":
+        return dict(epsilon=floats[0])
+    if op == "LayerNormalization":
+        return dict(axis=ints[0], stash_type=ints[1], epsilon=floats[0])
+    if op == "Shape":
+        return dict(start=ints[0] if ints else 0, end=ints[2] if len(ints) > 2 and ints[1] else None)
+    return {}
+
+
+def graph_desc(model: ir.Model, device_inits: Optional[Dict[int, int]] = None):
+    """`AcGraphDesc` of an `ir.Model` plus the ctypes buffers that must outlive its use."""
+    g = model.graph
+    keep = []
+    values = (AcValueDesc * max(1, len(g.values)))()
+    for i, v in enumerate(g.values):
+        values[i].elem_ty = v.elem_ty
+        if v.shape is None:
+            values[i].rank = -1
+        else:
+            if len(v.shape) > AC_MAX_RANK:
+                raise SessionError(2, "rank above 8 is not supported")
+            values[i].rank = len(v.shape)
+            for k, d in enumerate(v.shape):
+                values[i].dims[k] = d
+    nodes = (AcNodeDesc * max(1, len(g.nodes)))()
+    for i, n in enumerate(g.nodes):
+        ints, floats = _attr_arrays(n)
+        ins = (ctypes.c_int32 * max(1, len(n.inputs)))(*n.inputs)
+        outs = (ctypes.c_int32 * max(1, len(n.outputs)))(*n.outputs)
+        ia = (ctypes.c_int64 * max(1, len(ints)))(*[int(x) for x in ints])
+        fa = (ctypes.c_float * max(1, len(floats)))(*[float(x) for x in floats])
+        keep += [ins, outs, ia, fa]
+        nodes[i].op = ir.OP_CODE[n.op]
+        nodes[i].n_inputs, nodes[i].inputs = len(n.inputs), ins
+        nodes[i].n_outputs, nodes[i].outputs = len(n.outputs), outs
+        nodes[i].n_ints, nodes[i].ints = len(ints), ia
+        nodes[i].n_floats, nodes[i].floats = len(floats), fa
+        nodes[i].name = n.name.encode() if n.name else None
+    inits = (AcInitDesc * max(1, len(g.inits)))()
+    for i, (vid, arr) in enumerate(g.inits.items()):
+        arr = np.ascontiguousarray(arr)
+        keep.append(arr)
+        inits[i].value = vid
+        if device_inits and vid in device_inits:
+            inits[i].location, inits[i].data = 1, device_inits[vid]
+        else:
+            inits[i].location, inits[i].data = 0, arr.ctypes.data
+        inits[i].bytes = arr.nbytes
+    run_inputs = [i for i in g.inputs if i not in g.inits]
+    gin = (ctypes.c_int32 * max(1, len(run_inputs)))(*run_inputs)
+    gout = (ctypes.c_int32 * max(1, len(g.outputs)))(*g.outputs)
+    desc = AcGraphDesc(model.opset_version, len(g.values), values, len(g.nodes), nodes,
+                       len(g.inits), inits, len(run_inputs), gin, len(g.outputs), gout)
+    keep += [values, nodes, inits, gin, gout]
+    return desc, keep, run_inputs
+
+
 class CudaSession:
-    """One session = one device, one stream, one arena; `run` is not re-entrant."""
+    """One session = one device, one stream, one arena. The run calls of one session are
+    serialised by a lock inside the library; distinct sessions run concurrently."""
 
     def __init__(self, model: ir.Model, device: int, enable_profiling: bool, use_cuda_graph: bool,
                  fuse: bool, gemm_mode: int, device_inits: Optional[Dict[int, int]] = None,
@@ -205,48 +318,7 @@ class CudaSession:
         self._lib = load_library()
         self._handle = ctypes.c_void_p()
         g = model.graph
-        keep = []  # ctypes buffers that must outlive the create call
-
-        values = (AcValueDesc * max(1, len(g.values)))()
-        for i, v in enumerate(g.values):
-            values[i].elem_ty = v.elem_ty
-            if v.shape is None:
-                values[i].rank = -1
-            else:
-                if len(v.shape) > AC_MAX_RANK:
-                    raise SessionError(2, "rank above 8 is not supported")
-                values[i].rank = len(v.shape)
-                for k, d in enumerate(v.shape):
-                    values[i].dims[k] = d
-        nodes = (AcNodeDesc * max(1, len(g.nodes)))()
-        for i, n in enumerate(g.nodes):
-            ints, floats = _attr_arrays(n)
-            ins = (ctypes.c_int32 * max(1, len(n.inputs)))(*n.inputs)
-            outs = (ctypes.c_int32 * max(1, len(n.outputs)))(*n.outputs)
-            ia = (ctypes.c_int64 * max(1, len(ints)))(*[int(x) for x in ints])
-            fa = (ctypes.c_float * max(1, len(floats)))(*[float(x) for x in floats])
-            keep += [ins, outs, ia, fa]
-            nodes[i].op = ir.OP_CODE[n.op]
-            nodes[i].n_inputs, nodes[i].inputs = len(n.inputs), ins
-            nodes[i].n_outputs, nodes[i].outputs = len(n.outputs), outs
-            nodes[i].n_ints, nodes[i].ints = len(ints), ia
-            nodes[i].n_floats, nodes[i].floats = len(floats), fa
-            nodes[i].name = n.name.encode() if n.name else None
-        inits = (AcInitDesc * max(1, len(g.inits)))()
-        for i, (vid, arr) in enumerate(g.inits.items()):
-            arr = np.ascontiguousarray(arr)
-            keep.append(arr)
-            inits[i].value = vid
-            if device_inits and vid in device_inits:
-                inits[i].location, inits[i].data = 1, device_inits[vid]
-            else:
-                inits[i].location, inits[i].data = 0, arr.ctypes.data
-            inits[i].bytes = arr.nbytes
-        run_inputs = [i for i in g.inputs if i not in g.inits]
-        gin = (ctypes.c_int32 * max(1, len(run_inputs)))(*run_inputs)
-        gout = (ctypes.c_int32 * max(1, len(g.outputs)))(*g.outputs)
-        desc = AcGraphDesc(model.opset_version, len(g.values), values, len(g.nodes), nodes,
-                           len(g.inits), inits, len(run_inputs), gin, len(g.outputs), gout)
+        desc, keep, run_inputs = graph_desc(model, device_inits)
         opt = AcOptions()
         opt.device = device
         opt.enable_profiling = int(enable_profiling)
@@ -289,6 +361,17 @@ class CudaSession:
             msg = self._lib.altius_cuda_last_error(self._handle)
             raise SessionError(rc, msg.decode() if msg else "run failed")
 
+    def _check_outputs(self, outputs):
+        """Caller-supplied output arrays are written by the library through raw pointers:
+        they must be what it expects (C-contiguous, writable, right dtype and shape)."""
+        if len(outputs) != len(self.output_ids):
+            raise SessionError(1, f"expected {len(self.output_ids)} outputs, got {len(outputs)}")
+        for o, (shape, dt) in zip(outputs, self.output_info):
+            if not isinstance(o, np.ndarray) or o.dtype != np.dtype(dt) or tuple(o.shape) != tuple(shape) \
+                    or not o.flags["C_CONTIGUOUS"] or not o.flags["WRITEABLE"]:
+                raise SessionError(2, f"output array must be a writable C-contiguous {np.dtype(dt).name} "
+                                      f"array of shape {tuple(shape)}")
+
     # -- run -------------------------------------------------------------------
     def run(self, inputs: Sequence[np.ndarray], outputs: Optional[List[np.ndarray]] = None
             ) -> List[np.ndarray]:
@@ -305,6 +388,8 @@ class CudaSession:
             arrs.append(a)
         if outputs is None:
             outputs = [np.empty(shape, dt) for shape, dt in self.output_info]
+        else:
+            self._check_outputs(outputs)
         ins = (ctypes.c_void_p * max(1, len(arrs)))(*[a.ctypes.data for a in arrs])
         outs = (ctypes.c_void_p * max(1, len(outputs)))(*[o.ctypes.data for o in outputs])
         self._check(self._lib.altius_cuda_run(self._handle, ins, outs))
@@ -328,6 +413,11 @@ class CudaSession:
             checked.append(row)
         if outputs is None:
             outputs = [[np.empty(shape, dt) for shape, dt in self.output_info] for _ in checked]
+        else:
+            if len(outputs) != len(checked):
+                raise SessionError(1, f"expected {len(checked)} output lists, got {len(outputs)}")
+            for row in outputs:
+                self._check_outputs(row)
         n = len(checked)
         flat_in = [a.ctypes.data for row in checked for a in row]
         flat_out = [o.ctypes.data for row in outputs for o in row]
@@ -450,8 +540,10 @@ class CudaSessionBuilder:
 
 
 class InferenceSession:
-    """`altius_py.InferenceSession` look-alike (crates/altius_py/altius_py/__init__.py:4-27).
-    `model` is an `ir.Model` (no `.onnx` loader is part of this backend)."""
+    """`altius_py.InferenceSession` look-alike (crates/altius_py/altius_py/__init__.py:4-27):
+    `InferenceSession("model.onnx", backend="cuda")` loads the file, applies the graph passes
+    altius_py applies (crates/altius_py/src/lib.rs:54-62) and builds the session. `model` may
+    also be an `ir.Model`; it goes through the same passes."""
 
     def __init__(self, model, enable_profile: bool = False, intra_op_num_threads: int = 1,
                  backend: str = "cuda", device: int = 0):
@@ -459,8 +551,12 @@ class InferenceSession:
             # altius_py raises PyRuntimeError for an unknown backend string
             # (crates/altius_py/src/lib.rs:64-88).
             raise RuntimeError(f"Unknown backend: {backend}")
-        if not isinstance(model, ir.Model):
-            raise TypeError("model must be an altius_b200.ir.Model")
+        from . import model_io
+        if isinstance(model, (str, os.PathLike)):
+            model = model_io.load(os.fspath(model))
+        elif not isinstance(model, ir.Model):
+            raise TypeError("model must be a path to an .onnx file or an altius_b200.ir.Model")
+        model = model_io.optimize(model)
         self.model = model
         self.session = (CudaSessionBuilder(model).with_device(device)
                         .with_intra_op_num_threads(intra_op_num_threads)

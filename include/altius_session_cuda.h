@@ -93,6 +93,7 @@ typedef struct AcValueDesc {
  *   GEMM     ints = trans_a, trans_b;  floats = alpha, beta
  *   BATCHNORMALIZATION floats = epsilon
  *   LAYERNORMALIZATION ints = axis, stash_type;  floats = epsilon
+ *   SHAPE    ints = start, has_end, end   (may be absent: start 0, no end)
  *
  * An absent optional input is value id -1. */
 typedef struct AcNodeDesc {
@@ -185,7 +186,8 @@ int altius_cuda_create(const AcGraphDesc *graph, const AcOptions *options, AcSes
 /* session.run(inputs): `ins[i]` / `outs[i]` are caller-owned HOST buffers of
  * the i-th graph input / output, sized by their (inferred) shapes. Copies
  * inputs to the device, replays the schedule, copies outputs back, and returns
- * after the outputs are complete. Not re-entrant for one session. Replaces
+ * after the outputs are complete. The run calls of one session (run, run_device,
+ * run_batches, time_device_runs) are serialised by a lock inside the session. Replaces
  * InterpreterSession::run, session.rs:66-134, in the calling convention of
  * session_clang's trampoline, translator.rs:499-503. */
 int altius_cuda_run(AcSession *s, const void *const *ins, void *const *outs);
@@ -266,6 +268,45 @@ int altius_cuda_reduce_max_noalloc(const float *d_x, int64_t n, float *d_out, vo
 
 /* Number of visible CUDA devices, or a negative AcStatus. */
 int altius_cuda_device_count(void);
+
+/* ---- the model object: loader and graph passes (host only) ------------------------------
+ * `Model` of the reference (crates/core/src/model.rs:13-17) as an opaque handle. */
+typedef struct AcModel AcModel;
+
+/* altius_core::onnx::load_onnx / load_onnx_from_buffer (crates/core/src/onnx/load.rs:55-64):
+ * operator table, attribute defaults and initializer types (f32 / i32 / i64 / bool, raw_data
+ * or typed arrays) as there (:170-361, :389-432); initializers are removed from the graph
+ * inputs (:143-148). A dynamic dimension of a graph input is loaded as -1 (and refused by
+ * altius_cuda_create, as shape inference refuses it in the reference). Additions: a Constant
+ * node becomes an initializer of its output value. Errors: AC_ERR_INVALID / AC_ERR_UNSUPPORTED
+ * with ModelLoadError's message from altius_cuda_last_error(NULL). */
+int altius_model_load_onnx(const char *path, AcModel **out);
+int altius_model_load_onnx_buffer(const void *buf, size_t len, AcModel **out);
+
+/* A model from a graph description (initializers are copied; they must be host memory). */
+int altius_model_from_graph(const AcGraphDesc *graph, AcModel **out);
+
+/* One graph pass; *n_rewrites (may be NULL) receives the number of patterns rewritten.
+ * pass 0 fuse_layer_norm     crates/core/src/optimize/layer_norm_fusion.rs:13-123
+ *      1 fuse_gelu           crates/core/src/optimize/gelu_fusion.rs:12-131
+ *      2 fuse_fast_gelu      crates/core/src/optimize/fast_gelu_fusion.rs:5-190
+ *      3 eliminate_identity  crates/core/src/optimize/identity_elim.rs:5-45 */
+int altius_model_run_pass(AcModel *m, int32_t pass, int32_t *n_rewrites);
+/* The four passes in the order altius_py runs them before it builds a session
+ * (crates/altius_py/src/lib.rs:54-62). */
+int altius_model_optimize(AcModel *m);
+
+/* The model as a graph description for altius_cuda_create. The pointers in *out belong to
+ * the model and stay valid until it is modified or destroyed. */
+int altius_model_graph(AcModel *m, AcGraphDesc *out);
+/* Name of a value (NULL: unnamed), and Model::lookup_named_value (-1: not found). */
+const char *altius_model_value_name(const AcModel *m, int32_t value);
+int32_t altius_model_lookup_named_value(const AcModel *m, const char *name);
+void altius_model_destroy(AcModel *m);
+
+/* load_onnx + the passes + builder.build() in one call: what
+ * `altius_py.InferenceSession(path, backend=...)` does (crates/altius_py/src/lib.rs:32-88). */
+int altius_cuda_create_from_onnx(const char *path, const AcOptions *options, AcSession **out);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

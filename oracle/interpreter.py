@@ -281,7 +281,9 @@ class InterpreterSession:
         if op == "Greater":
             x, y = _f32(ins[0]), _f32(ins[1])
             if not is_scalar(y.shape):
-                raise NotImplementedError("Greater: only a scalar rhs (session.rs:559)")
+                # session.rs:559 stops here. EXTENSION: ONNX Greater with NumPy broadcasting
+                # (a comparison: exact).
+                return [np.ascontiguousarray(np.greater(x, y))]
             out = np.empty(x.shape, np.uint8)
             L.or_greater_scalar(_fp(x), ctypes.c_float(float(y.reshape(-1)[0])),
                                 out.ctypes.data_as(c_u8p), x.size)
@@ -293,11 +295,14 @@ class InterpreterSession:
             out = np.empty(oshape, np.float32)
             if tuple(cond.shape) == tuple(y.shape) and is_scalar(x.shape):
                 L.or_where(0, cond.ctypes.data_as(c_u8p), _fp(x), _fp(y), _fp(out), out.size, 0)
-            else:
-                assert is_scalar(y.shape) and x.ndim == 4 and cond.ndim == 4 and \
-                    cond.shape[0] == 1 and cond.shape[1] == 1  # session.rs:958-964
+            elif is_scalar(y.shape) and x.ndim == 4 and cond.ndim == 4 and \
+                    cond.shape[0] == 1 and cond.shape[1] == 1 and cond.shape[2:] == tuple(oshape[2:]):  # session.rs:958-964
                 L.or_where(1, cond.ctypes.data_as(c_u8p), _fp(x), _fp(y), _fp(out), out.size,
                            oshape[2] * oshape[3])
+            else:
+                # EXTENSION beyond the reference's two patterns: ONNX Where with NumPy
+                # broadcasting of all three operands (a selection: exact).
+                return [np.ascontiguousarray(np.where(cond.view(np.bool_), x, y).astype(np.float32))]
             return [out]
         if op == "Cast":
             # session.rs:1350-1378: i32->f32, i64->i32, i64->f32, f32->bool
@@ -308,7 +313,14 @@ class InterpreterSession:
                 return [x.astype(table[(x.dtype, to)])]
             if x.dtype == np.float32 and to == 0:
                 return [x != 0.0]
-            raise NotImplementedError(f"cast {x.dtype} -> {to}")
+            # EXTENSION: the other pairs of bool / f32 / i32 / i64, converted as C does
+            # (towards zero for float -> integer; anything non-zero -> true).
+            target = {0: np.bool_, 1: np.float32, 2: np.int32, 3: np.int64}[to]
+            if to == 0:
+                return [x != 0]
+            if x.dtype == np.float32 and target in (np.int32, np.int64):
+                return [np.trunc(x).astype(target)]
+            return [x.astype(target)]
         if op == "Softmax":
             x = _f32(ins[0])
             axis = at.get("axis", -1)

@@ -697,3 +697,143 @@ def test_attention_writes_the_split_operand_of_the_projection(cuda_lib):
         sess.close()
     want = run_oracle(m, [qkv], sgemm="openblas")[0]
     assert (np.abs(got - want) <= _split_chain_bound(want, 0.3)).all()
+
+
+# ---- aliases and host-folded nodes (Squeeze / Unsqueeze / Identity / Shape) --------------------
+@pytest.mark.parametrize("opset", [11, 13])
+def test_squeeze_unsqueeze_identity_shape_nodes(cuda_lib, opset):
+    """Unsqueeze -> ReLU -> Squeeze -> Identity -> Flatten -> Reshape(shape = Shape(x)) -> Add:
+    the four alias operators and a Shape node evaluated on the host, with the axes as
+    attributes (opset 11) and as inputs (opset 13)."""
+    from altius_b200 import ir
+    x = RNG.standard_normal((2, 3, 4)).astype(np.float32)
+    g = ir.Graph()
+    xi = g.add_input("x", x.shape)
+    if opset >= 13:
+        ax = lambda v: [g.new_init(np.asarray(v, np.int64))]
+        u = g.op("Unsqueeze", xi, *ax([1]))
+        r = g.op("ReLU", u)
+        sq = g.op("Squeeze", r, *ax([1]))
+    else:
+        u = g.op("Unsqueeze", xi, axes=[1])
+        r = g.op("ReLU", u)
+        sq = g.op("Squeeze", r, axes=[1])
+    idn = g.op("Identity", sq)
+    flat = g.op("Flatten", idn, axis=1)
+    back = g.op("Reshape", flat, g.op("Shape", xi))
+    out = g.op("Add", back, xi)
+    g.outputs += [out, u]
+    m = ir.Model(g, opset)
+    got, want = both(m, [x])
+    assert got[0].shape == (2, 3, 4) and got[1].shape == (2, 1, 3, 4)
+    assert_bit_exact(got[0], want[0])
+    assert_bit_exact(got[1], want[1])
+    assert_bit_exact(got[0], np.maximum(x, 0) + x)
+
+
+def test_shape_node_as_a_graph_output_is_refused_or_right(cuda_lib):
+    """Shape with start / end attributes is what the reference's shape inference asserts against."""
+    from altius_b200 import ir
+    from altius_b200.session import CudaSessionBuilder, SessionError
+    g = ir.Graph()
+    xi = g.add_input("x", (2, 3))
+    g.outputs.append(g.op("Reshape", xi, g.op("Shape", xi, start=1)))
+    with pytest.raises(SessionError, match="Shape: start / end"):
+        CudaSessionBuilder(ir.Model(g, 15)).with_plan_only(True).build()
+
+
+# ---- general broadcasting of Where / Greater, every Cast pair (beyond the interpreter's patterns) ----
+@pytest.mark.parametrize("cshape,xshape,yshape", [((4, 1, 5), (1, 3, 5), (4, 3, 1)), ((3, 5), (2, 3, 5), (1,)),
+                                                   ((2, 1, 1, 7), (2, 3, 4, 7), (3, 1, 7)), ((6,), (6,), (6,))])
+def test_where_general_broadcast_bit_exact(cuda_lib, cshape, xshape, yshape):
+    cond = RNG.random(cshape) > 0.5
+    x = RNG.standard_normal(xshape).astype(np.float32)
+    y = RNG.standard_normal(yshape).astype(np.float32)
+    m = single_op_model("Where", [cond, x, y])
+    got, want = both(m, [cond, x, y])
+    assert_bit_exact(got[0], want[0])
+    assert_bit_exact(got[0], np.where(cond, x, y))
+
+
+@pytest.mark.parametrize("xshape,yshape", [((4, 3, 5), (3, 1)), ((2, 7), (2, 7)), ((5,), (3, 1, 5))])
+def test_greater_general_broadcast(cuda_lib, xshape, yshape):
+    x = RNG.integers(-2, 3, xshape).astype(np.float32)
+    y = RNG.integers(-2, 3, yshape).astype(np.float32)
+    m = single_op_model("Greater", [x, y])
+    got, want = both(m, [x, y])
+    assert got[0].dtype == np.bool_ and np.array_equal(got[0], want[0]) and np.array_equal(got[0], x > y)
+
+
+def test_cast_every_pair(cuda_lib):
+    from altius_b200 import ir
+    src = {ir.BOOL: np.array([True, False, True, True]), ir.F32: np.array([-2.7, 0.0, 3.9, 1e9], np.float32),
+           ir.I32: np.array([-3, 0, 7, 2 ** 30], np.int32), ir.I64: np.array([-3, 0, 7, 2 ** 40], np.int64)}
+    for frm, x in src.items():
+        for to in (ir.BOOL, ir.F32, ir.I32, ir.I64):
+            if frm == to or (frm == ir.I64 and to == ir.I32) or (frm == ir.F32 and to in (ir.I32,) ):
+                # out-of-range conversions are undefined in C; keep the values representable
+                x2 = np.clip(x, -1000, 1000).astype(x.dtype) if frm != ir.BOOL else x
+            else:
+                x2 = x
+            m = single_op_model("Cast", [x2], to=to)
+            got, want = both(m, [x2])
+            assert got[0].dtype == want[0].dtype and np.array_equal(got[0], want[0]), (frm, to)
+
+
+# ---- the two fusions of the metric's list that were still open ----------------------------------
+def test_scale_mask_softmax_is_one_kernel(cuda_lib):
+    """S * 0.125 -> Where(causal mask [1,1,T,T], ., -1e9) -> Softmax: one kernel; the same
+    bits as the three kernels (a selection is exact), within 1e-5 of the oracle."""
+    from altius_b200.session import CudaSessionBuilder
+    B, H, T = 3, 4, 197
+    sc = RNG.standard_normal((B, H, T, T)).astype(np.float32)
+    mask = np.tril(np.ones((T, T), bool))[None, None]
+
+    def build(g):
+        x = g.add_input("s", sc.shape)
+        m = g.op("Mul", x, g.new_init(np.array([0.125], np.float32)))
+        w = g.op("Where", g.new_init(mask), m, g.new_init(np.array(-1e9, np.float32)))
+        return [g.op("Softmax", w, axis=-1)]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["softmax_scaled_masked"]
+        got = sess.run([sc])[0]
+    finally:
+        sess.close()
+    unfused = run_cuda(m, [sc], fuse=False)[0]
+    assert_bit_exact(got, unfused)
+    want = run_oracle(m, [sc])[0]
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-9)
+    assert (got[..., 0, 1:] == 0).all() and np.allclose(got.sum(-1), 1, atol=1e-5)
+
+
+@pytest.mark.parametrize("c,hw,oc", [(72, 28, 40), (120, 28, 40), (480, 14, 112)])
+def test_squeeze_excite_gate_folds_into_the_pointwise_convolution(cuda_lib, c, hw, oc):
+    """x * gate[n, c, 1, 1] -> 1 x 1 Conv: the multiply happens inside the GEMM's operand split
+    (the gated map is never written); bit-identical to the unfused pair on the same kernel."""
+    from altius_b200.session import CudaSessionBuilder
+    n = 32
+    x = RNG.standard_normal((n, c, hw, hw)).astype(np.float32)
+    gate = RNG.random((n, c, 1, 1)).astype(np.float32)
+    w = (RNG.standard_normal((oc, c, 1, 1)) / np.sqrt(c)).astype(np.float32)
+    b = RNG.standard_normal(oc).astype(np.float32)
+
+    def build(g):
+        xi, gi = g.add_input("x", x.shape), g.add_input("g", gate.shape)
+        y = g.op("Conv2d", g.op("Mul", xi, gi), g.new_init(w), g.new_init(b), kernel_shape=[1, 1], strides=[1, 1],
+                 padding=[0, 0, 0, 0], dilations=[1, 1], group=1, auto_pad="")
+        return [y]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["gemm_tf32x3_tcgen05"]
+        got = sess.run([x, gate])[0]
+    finally:
+        sess.close()
+    unfused = run_cuda(m, [x, gate], fuse=False)[0]
+    assert_bit_exact(got, unfused)
+    want = run_oracle(m, [x, gate], sgemm="openblas")[0]
+    kk = np.abs(x * gate).reshape(n, c, -1)
+    bound = 1e-5 * np.abs(want) + 5e-6 * np.einsum("oc,nch->noh", np.abs(w[:, :, 0, 0]), kk).reshape(want.shape) + 1e-6
+    assert (np.abs(got - want) <= bound).all()

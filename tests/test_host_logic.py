@@ -21,7 +21,7 @@ def plan(model, fuse=True):
 
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "altius_session_cuda.h")).read()
-    declared = set(re.findall(r"\b(altius_cuda_\w+)\s*\(", header))
+    declared = set(re.findall(r"\b(altius_(?:cuda|model)_\w+)\s*\(", header))
     assert declared == set(session.ABI_SYMBOLS)
     lib = session.load_library()
     for name in declared:
@@ -77,7 +77,10 @@ def test_fusion_folds_the_expected_chains():
     model, _ = configs.mobilenet_v3_large(batch=1)
     kinds = collections.Counter(e["kind"] for e in plan(model).schedule())
     assert "unary_hard_sigmoid" not in kinds and "unary_relu" not in kinds and "binary_Add" not in kinds
-    assert kinds["binary_Mul"] == 8               # the squeeze-excite gates
+    # Squeeze-excite gates: folded into the pointwise convolution that follows where that one
+    # runs on the tensor cores with the planes as its [K, N] operand (large enough, plane size a
+    # multiple of four floats); the rest stay broadcast Mul kernels.
+    assert kinds["binary_Mul"] == 6
     assert kinds["conv_depthwise"] == 15
 
     # At the benchmark's batch the convolution GEMMs are large enough for the tensor cores:
@@ -88,6 +91,9 @@ def test_fusion_folds_the_expected_chains():
     steps = plan(model).schedule()
     kinds = collections.Counter(e["kind"] for e in steps)
     assert kinds["im2col"] == 1 and kinds["transpose_copy"] == 6
+    assert kinds["binary_Mul"] == 3                    # gates of the three 7 x 7 blocks (transposed planes)
+    assert plan(model, fuse=False).schedule().count is not None
+    assert collections.Counter(e["kind"] for e in plan(model, fuse=False).schedule())["binary_Mul"] >= 8
     assert kinds["gemm_tf32x3_tcgen05"] == 31          # the first layer and the 30 pointwise layers on planes
     assert kinds["gemm_f16x3_tcgen05"] == 12           # squeeze-excite, the 1 x 1 head convolution, the classifier
     assert kinds["gemm_fp32_simt"] == 6                # the smallest squeeze-excite products
