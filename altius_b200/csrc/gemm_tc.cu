@@ -469,35 +469,9 @@ __device__ __forceinline__ void epilogue_raw(float* ws_tile, float4* stage, uint
   }
 }
 
-// Adds the K-slices of the tail tiles in slice order and applies the epilogue.
-__global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ ws, TcEpilogue ep, int bm,
-                                                            int bn, int dp_tiles, int parts, int tiles_m,
-                                                            int tiles_n) {
-  const int tt = blockIdx.y;
-  const int t = dp_tiles + tt;
-  const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
-  const int e4 = blockIdx.x * 256 + threadIdx.x;          // float4 index inside the tile
-  if (e4 >= bm * bn / 4) return;
-  const int rl = e4 / (bn / 4), cl = (e4 % (bn / 4)) * 4;
-  const int row = tm * bm + rl, col0 = tn * bn + cl;
-  if (row >= ep.m || col0 >= ep.n) return;
-  const float* src = ws + (size_t)tt * parts * bm * bn + (size_t)rl * bn + cl;
-  // Slices are added in slice order; their loads are issued eight at a time so that the
-  // chain of additions does not also serialise the L2 round trips.
-  float4 acc = __ldg(reinterpret_cast<const float4*>(src));
-  auto add = [&](const float4& v) {
-    acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
-    acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
-  };
-  int p = 1;
-  for (; p + 8 <= parts; p += 8) {
-    float4 v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(src + (size_t)(p + j) * bm * bn));
-#pragma unroll
-    for (int j = 0; j < 8; ++j) add(v[j]);
-  }
-  for (; p < parts; ++p) add(__ldg(reinterpret_cast<const float4*>(src + (size_t)p * bm * bn)));
+// The epilogue of four consecutive elements of row `row` from column `col0` on (n % 4 == 0 when
+// the split result is written): what the tail fix-up applies to the summed K-slices.
+__device__ __forceinline__ void fixup_apply(const TcEpilogue& ep, int row, int col0, int bz, float4 acc) {
   float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
   const float* cin = (ep.cin && ep.beta != 0.f) ? ep.cin + (long long)bz * ep.scin : nullptr;
   const float* res = ep.res ? ep.res + (long long)bz * ep.sres : nullptr;
@@ -535,6 +509,38 @@ __global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restr
     // A tile's few K-sliced elements say nothing about the tensor being tiny: overflow only.
     if (split_seen(yv) & 1u) atomicCAS(ep.err, 0, kRangeCode);
   }
+}
+
+// Adds the K-slices of the tail tiles in slice order and applies the epilogue.
+__global__ void __launch_bounds__(256) gemm_tc_fixup_kernel(const float* __restrict__ ws, TcEpilogue ep, int bm,
+                                                            int bn, int dp_tiles, int parts, int tiles_m,
+                                                            int tiles_n) {
+  const int tt = blockIdx.y;
+  const int t = dp_tiles + tt;
+  const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
+  const int e4 = blockIdx.x * 256 + threadIdx.x;          // float4 index inside the tile
+  if (e4 >= bm * bn / 4) return;
+  const int rl = e4 / (bn / 4), cl = (e4 % (bn / 4)) * 4;
+  const int row = tm * bm + rl, col0 = tn * bn + cl;
+  if (row >= ep.m || col0 >= ep.n) return;
+  const float* src = ws + (size_t)tt * parts * bm * bn + (size_t)rl * bn + cl;
+  // Slices are added in slice order; their loads are issued eight at a time so that the
+  // chain of additions does not also serialise the L2 round trips.
+  float4 acc = __ldg(reinterpret_cast<const float4*>(src));
+  auto add = [&](const float4& v) {
+    acc.x = __fadd_rn(acc.x, v.x); acc.y = __fadd_rn(acc.y, v.y);
+    acc.z = __fadd_rn(acc.z, v.z); acc.w = __fadd_rn(acc.w, v.w);
+  };
+  int p = 1;
+  for (; p + 8 <= parts; p += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldg(reinterpret_cast<const float4*>(src + (size_t)(p + j) * bm * bn));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add(v[j]);
+  }
+  for (; p < parts; ++p) add(__ldg(reinterpret_cast<const float4*>(src + (size_t)p * bm * bn)));
+  fixup_apply(ep, row, col0, bz, acc);
 }
 
 // Shared-memory stage of the main loop. MT = 128-row sub-tiles per CTA tile.

@@ -123,6 +123,9 @@ cudaError_t launch_reduce_mean_last(const float* x, float* out, int64_t rows, in
                                     cudaStream_t st);
 cudaError_t launch_reduce_max_last(const float* x, float* out, int64_t rows, int64_t len,
                                    cudaStream_t st);
+// Both reductions of the same rows in one pass (sibling ReduceMean / ReduceMax nodes).
+cudaError_t launch_reduce_mean_max_last(const float* x, float* mean_out, float* max_out, int64_t rows, int64_t len,
+                                        cudaStream_t st);
 // Whole-tensor maximum; `partials` is scratch of reduce_max_all_scratch_elems(n) floats.
 int64_t reduce_max_all_scratch_elems(int64_t n);
 cudaError_t launch_reduce_max_all(const float* x, float* out, int64_t n, float* partials,

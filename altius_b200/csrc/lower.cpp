@@ -109,6 +109,7 @@ struct Plan {
   std::map<int, int> softmax_mask;  // Softmax node -> Where(mask, x, c) node folded in
   std::map<int, LnFusion> ln;       // LayerNormalization node -> folded producers
   std::map<int, int> hardswish;     // Mul node -> HardSigmoid node folded in
+  std::map<int, int> reduce_sibling; // ReduceMean node -> ReduceMax node of the same rows computed with it
   struct SeGate { int x, gate; };
   std::map<int, SeGate> se_gate;    // pointwise Conv2d node -> squeeze-excite Mul folded into its input
 };
@@ -516,6 +517,27 @@ void detect_se_gate(Ctx& c, Plan& plan) {
       continue;
     plan.se_gate[cn] = Plan::SeGate{x, g};
     c.absorbed[nid] = 1;
+  }
+}
+
+// ReduceMean and ReduceMax over the last axis of the same value: one pass over the rows.
+void detect_reduce_siblings(Ctx& c, Plan& plan) {
+  auto last_axis_only = [&](const Node& n) {
+    const Value& xv = c.val(n.inputs[0]);
+    if (n.ints.size() != 2 || xv.elem_ty != AC_F32 || xv.rank < 1) return false;
+    const int64_t ax = n.ints[1] < 0 ? n.ints[1] + xv.rank : n.ints[1];
+    return ax == xv.rank - 1;
+  };
+  for (int nid : c.s.order) {
+    const Node& n = c.node(nid);
+    if (c.absorbed[nid] || n.op != AC_OP_REDUCEMEAN || !last_axis_only(n)) continue;
+    for (int u : c.consumers[n.inputs[0]]) {
+      const Node& m = c.node(u);
+      if (u == nid || c.absorbed[u] || m.op != AC_OP_REDUCEMAX || m.inputs[0] != n.inputs[0] || !last_axis_only(m)) continue;
+      plan.reduce_sibling[nid] = u;
+      c.absorbed[u] = 1;
+      break;
+    }
   }
 }
 
@@ -1445,6 +1467,14 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         fail(AC_ERR_UNSUPPORTED, std::string(op_name(n.op)) + ": only the last axis is supported");
       const int64_t len = xv.dims[xv.rank - 1], rows = xv.numel() / std::max<int64_t>(len, 1);
       const bool mean = n.op == AC_OP_REDUCEMEAN;
+      auto sib = plan.reduce_sibling.find(nid);
+      if (mean && sib != plan.reduce_sibling.end()) {
+        const int o2 = c.node(sib->second).outputs[0];
+        em.add("reduce_mean_max", n.op, {x}, {o, o2}, 4.0 * rows * len + 8.0 * rows, 0, [=](cudaStream_t st) {
+          return launch_reduce_mean_max_last(s->fptr(x), s->fptr_mut(o), s->fptr_mut(o2), rows, len, st);
+        });
+        return;
+      }
       em.add(mean ? "reduce_mean" : "reduce_max", n.op, {x}, {o}, 4.0 * rows * len + 4.0 * rows, 0,
              [=](cudaStream_t st) {
                return mean ? launch_reduce_mean_last(s->fptr(x), s->fptr_mut(o), rows, len, st)
@@ -1734,6 +1764,7 @@ void lower_graph(AcSession& s) {
       detect_layer_norm(c, plan);
       detect_hardswish(c, plan);
       detect_se_gate(c, plan);
+      detect_reduce_siblings(c, plan);
       // Debug toggle: ALTIUS_CUDA_NO_FUSED_SPLIT=1 keeps a split kernel in front of every pair GEMM.
       if (!std::getenv("ALTIUS_CUDA_NO_FUSED_SPLIT")) plan_presplit(c, plan);
     }

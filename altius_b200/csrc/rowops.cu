@@ -190,9 +190,12 @@ __device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lan
 // only the current row in registers (no prefetch of the next one), which lets two or three
 // blocks share an SM.
 // SPLIT: the result is (also) written as fp16 hi / lo halves for the GEMM that consumes it.
-template <int NV, bool FUSED, bool GELU, bool SPLIT>
-__global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev p) {
-  constexpr bool PREFETCH = !FUSED;
+// RESX (1, 2): the residual operand is the chain's own input x, so it is taken from the row in
+// registers, float4 by float4, instead of being loaded and held as a second row: fewer live
+// registers, which buys a fourth block per SM (1) or the prefetch of the next row (2).
+template <int NV, bool FUSED, bool GELU, bool SPLIT, int RESX>
+__global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : 2) layer_norm_vec(LnDev p) {
+  constexpr bool PREFETCH = !FUSED || RESX == 2;
   unsigned seen = 0;
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -201,9 +204,10 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
   const float inv_n = __fdiv_rn(1.f, (float)p.len);
   int64_t row = warp;
   if (row >= p.rows) return;      // whole warps only: `warp` is uniform across the lanes
-  float4 v[NV], r[FUSED ? NV : 1];
+  constexpr bool LOAD_RES = FUSED && RESX == 0;
+  float4 v[NV], r[LOAD_RES ? NV : 1];
   float4 nv[PREFETCH ? NV : 1];
-  if (FUSED) ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
+  if (LOAD_RES) ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
   else ln_load_row<NV, false>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(v));
   while (true) {
     const int64_t next = row + nwarps;
@@ -218,6 +222,7 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
         if (FUSED) {
           // Same operations as ln_prologue, with the options tested per float4 (or at
           // compile time for the Gelu) instead of per element.
+          const float4 orig = v[i];
           if (p.pre_bias) {
             const float4 bv = __ldg(reinterpret_cast<const float4*>(p.pre_bias) + c);
             v[i].x = __fadd_rn(v[i].x, bv.x); v[i].y = __fadd_rn(v[i].y, bv.y);
@@ -228,9 +233,12 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
             const float2 hi = gelu_ref2(make_float2(v[i].z, v[i].w));
             v[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
           }
-          if (p.residual) {
-            v[i].x = __fadd_rn(v[i].x, r[i].x); v[i].y = __fadd_rn(v[i].y, r[i].y);
-            v[i].z = __fadd_rn(v[i].z, r[i].z); v[i].w = __fadd_rn(v[i].w, r[i].w);
+          if (RESX != 0) {
+            v[i].x = __fadd_rn(v[i].x, orig.x); v[i].y = __fadd_rn(v[i].y, orig.y);
+            v[i].z = __fadd_rn(v[i].z, orig.z); v[i].w = __fadd_rn(v[i].w, orig.w);
+          } else if (p.residual) {
+            v[i].x = __fadd_rn(v[i].x, r[LOAD_RES ? i : 0].x); v[i].y = __fadd_rn(v[i].y, r[LOAD_RES ? i : 0].y);
+            v[i].z = __fadd_rn(v[i].z, r[LOAD_RES ? i : 0].z); v[i].w = __fadd_rn(v[i].w, r[LOAD_RES ? i : 0].w);
           }
           if (p.sum_out) reinterpret_cast<float4*>(p.sum_out + row * p.len)[c] = v[i];
         }
@@ -280,8 +288,10 @@ __global__ void __launch_bounds__(kThreads, FUSED ? 3 : 2) layer_norm_vec(LnDev 
     if (PREFETCH) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) v[i] = nv[PREFETCH ? i : 0];
-    } else {
+    } else if (LOAD_RES) {
       ln_load_row<NV, true>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(r));
+    } else {
+      ln_load_row<NV, false>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(v));
     }
   }
   if (SPLIT) tc::split_report_warp(seen, p.err);
@@ -402,6 +412,47 @@ __global__ void __launch_bounds__(kThreads) reduce_last_vec(const float* __restr
   }
 }
 
+// ReduceMean and ReduceMax of the same rows in one pass over them (the two are siblings in
+// the tensor-op micrograph): same loads, same order of additions as reduce_last_vec.
+template <int NV>
+__global__ void __launch_bounds__(kThreads) reduce_mean_max_vec(const float* __restrict__ x, float* __restrict__ mean_out,
+                                                                float* __restrict__ max_out, int64_t rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+  constexpr int len = NV * 128;
+  const float inv_len = __fdiv_rn(1.0f, (float)len);
+  for (int64_t row = 2 * warp; row < rows; row += 2 * nwarps) {
+    const bool two = row + 1 < rows;
+    const float4* x0 = reinterpret_cast<const float4*>(x + row * len);
+    const float4* x1 = reinterpret_cast<const float4*>(x + (two ? row + 1 : row) * len);
+    float4 a[NV], b[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) a[j] = __ldg(x0 + lane + 32 * j);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) b[j] = __ldg(x1 + lane + 32 * j);
+    float s0 = 0.f, s1 = 0.f, m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      m0 = fmaxf(fmaxf(fmaxf(a[j].x, a[j].y), fmaxf(a[j].z, a[j].w)), m0);
+      m1 = fmaxf(fmaxf(fmaxf(b[j].x, b[j].y), fmaxf(b[j].z, b[j].w)), m1);
+      s0 = __fadd_rn(s0, __fadd_rn(__fadd_rn(a[j].x, a[j].y), __fadd_rn(a[j].z, a[j].w)));
+      s1 = __fadd_rn(s1, __fadd_rn(__fadd_rn(b[j].x, b[j].y), __fadd_rn(b[j].z, b[j].w)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s0 = __fadd_rn(s0, __shfl_xor_sync(0xffffffffu, s0, o));
+      s1 = __fadd_rn(s1, __shfl_xor_sync(0xffffffffu, s1, o));
+      m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+      m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
+    }
+    if (lane < 2 && (lane == 0 || two)) {
+      mean_out[row + lane] = __fmul_rn(lane == 0 ? s0 : s1, inv_len);
+      max_out[row + lane] = lane == 0 ? m0 : m1;
+    }
+  }
+}
+
 template <int MODE>
 cudaError_t reduce_last_dispatch(const float* x, float* out, int64_t rows, int64_t len,
                                  cudaStream_t st) {
@@ -487,14 +538,21 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
     const bool fused = q.pre_bias || q.residual || q.gelu || q.sum_out;
     // Two blocks of 8 warps per SM: several rows per warp, so the prefetch of the next
     // row overlaps the stores of the current one.
-    const int depth = fused ? 3 : 2;    // the fused variants are bound by arithmetic (measured: 1, 3, 4 are slower for the plain one)
+    // The residual is the chain's own input (x + f(x)): variant 1 or 2 (debug toggle
+    // ALTIUS_CUDA_LN_RESX=0|1|2 overrides the choice).
+    static const int resx_env = std::getenv("ALTIUS_CUDA_LN_RESX") ? std::atoi(std::getenv("ALTIUS_CUDA_LN_RESX")) : -1;
+    const int resx = (fused && q.residual && q.residual == q.x) ? (resx_env >= 0 ? resx_env : 1) : 0;
+    const int depth = fused ? (resx == 1 ? 4 : 3) : 2;    // blocks per SM (measured: 1, 3, 4 are slower for the plain one)
     const int64_t vcap = (int64_t)device_sm_count() * depth;
     const unsigned vblocks = blocks64 > vcap ? (unsigned)vcap : (unsigned)blocks64;
 #define AC_LN2(NVV, SP)                                                                     \
   do {                                                                                     \
-    if (fused && q.gelu) layer_norm_vec<NVV, true, true, SP><<<vblocks, kThreads, 0, st>>>(p);  \
-    else if (fused) layer_norm_vec<NVV, true, false, SP><<<vblocks, kThreads, 0, st>>>(p);      \
-    else layer_norm_vec<NVV, false, false, SP><<<vblocks, kThreads, 0, st>>>(p);                \
+    if (fused && q.gelu && resx == 1) layer_norm_vec<NVV, true, true, SP, 1><<<vblocks, kThreads, 0, st>>>(p);  \
+    else if (fused && q.gelu && resx == 2) layer_norm_vec<NVV, true, true, SP, 2><<<vblocks, kThreads, 0, st>>>(p);  \
+    else if (fused && q.gelu) layer_norm_vec<NVV, true, true, SP, 0><<<vblocks, kThreads, 0, st>>>(p);  \
+    else if (fused && resx) layer_norm_vec<NVV, true, false, SP, 1><<<vblocks, kThreads, 0, st>>>(p);   \
+    else if (fused) layer_norm_vec<NVV, true, false, SP, 0><<<vblocks, kThreads, 0, st>>>(p);      \
+    else layer_norm_vec<NVV, false, false, SP, 0><<<vblocks, kThreads, 0, st>>>(p);                \
   } while (0)
 #define AC_LN(NVV)                                                                         \
   do {                                                                                     \
@@ -523,6 +581,29 @@ cudaError_t launch_reduce_max_last(const float* x, float* out, int64_t rows, int
                                    cudaStream_t st) {
   return reduce_last_dispatch<1>(x, out, rows, len, st);
 }
+cudaError_t launch_reduce_mean_max_last(const float* x, float* mean_out, float* max_out, int64_t rows, int64_t len,
+                                        cudaStream_t st) {
+  if (rows == 0) return cudaSuccess;
+  if ((len % 128) == 0 && len <= 1024 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int64_t want = (rows + 2 * kWarpsPerBlock - 1) / (2 * kWarpsPerBlock);
+    const int64_t cap = (int64_t)device_sm_count() * 6;
+    const unsigned vb = (unsigned)(want > cap ? cap : want);
+    switch (len / 128) {
+      case 1: reduce_mean_max_vec<1><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      case 2: reduce_mean_max_vec<2><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      case 3: reduce_mean_max_vec<3><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      case 4: reduce_mean_max_vec<4><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      case 5: reduce_mean_max_vec<5><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      case 6: reduce_mean_max_vec<6><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      case 7: reduce_mean_max_vec<7><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+      default: reduce_mean_max_vec<8><<<vb, kThreads, 0, st>>>(x, mean_out, max_out, rows); break;
+    }
+    return cudaGetLastError();
+  }
+  cudaError_t e = reduce_last_dispatch<0>(x, mean_out, rows, len, st);
+  return e != cudaSuccess ? e : reduce_last_dispatch<1>(x, max_out, rows, len, st);
+}
+
 cudaError_t launch_gavg_pool(const float* x, float* out, int64_t planes, int64_t hw,
                              cudaStream_t st) {
   return reduce_last_dispatch<2>(x, out, planes, hw, st);

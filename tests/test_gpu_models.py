@@ -128,3 +128,20 @@ def test_sessions_on_two_devices_in_one_process(cuda_lib):
         finally:
             sess.close()
     assert_bit_exact(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("name,fn,kw", [
+    ("vit_b16_b32", configs.vit_base_16, dict(batch=32)),
+    ("deit_s16_b64", configs.deit_small_distilled_16, dict(batch=64)),
+    ("mobilenet_v3_b32", configs.mobilenet_v3_large, dict(batch=32)),
+])
+def test_models_at_the_benchmarked_batch(cuda_lib, name, fn, kw):
+    """The configurations at the batch the benchmark runs them at, through the default plan
+    (CTA-pair GEMMs with operands split by their producers, K-sliced tail tiles, the tcgen05
+    attention kernel, tensor-core convolutions), against the oracle with OpenBLAS sgemm on all
+    host threads: max absolute logit error 1e-3, identical top-1."""
+    model, feeds = fn(**kw)
+    x = list(feeds.values())
+    got = run_cuda(model, x)[0]
+    want = run_oracle(model, x, threads=0, sgemm="openblas")[0]
+    check_logits(got, want)
