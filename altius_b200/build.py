@@ -24,7 +24,7 @@ COMMON = (["-DAC_TC_BK=" + os.environ["AC_TC_BK"]] if "AC_TC_BK" in os.environ e
           "-Xcudafe", "--diag_suppress=177"]
 
 SOURCES = ["session.cu", "shapes.cpp", "lower.cpp", "eltwise.cu", "rowops.cu", "movement.cu",
-           "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "noalloc.cu",
+           "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "attention_tc.cu", "attention_tc16.cu", "noalloc.cu",
            "model.cpp", "onnx_load.cpp", "passes.cpp"]
 
 

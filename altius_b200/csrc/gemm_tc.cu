@@ -84,6 +84,7 @@ struct TcEpilogue {
   int act; float act_alpha, act_beta;
   const float* res; long long ldres, sres;
   uint2* c16_hi; uint2* c16_lo; long long ldc16;   // result as fp16 hi / lo halves (4 per uint2; ldc16 in halves), or null
+  int c16_fixed;            // the halves on the fixed scale (f16_split_fixed) instead of f16_split
   const float* acc_scale;   // device scalar the accumulators are multiplied by (B was scaled by its inverse), or null
   const float* b_row_scale; long long b_row_scale_stride; int k_total;   // [K, N] operand: row k of B[bz] is multiplied by
                                                                        // b_row_scale[bz * stride + k] while it is split, or null
@@ -101,18 +102,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   d |= (uint64_t)((8 * 64) >> 4) << 32;          // stride byte offset: 8 rows
   d |= (uint64_t)1 << 46;                        // descriptor version for this architecture
   d |= (uint64_t)4 << 61;                        // 64-byte swizzle
-  return d;
-}
-
-// K-major tile whose rows are 128 bytes (64 halves) with the 128-byte swizzle: 8-row groups
-// are 1024 bytes apart. A K-step of 16 halves advances the start address by 32 bytes.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;                        // leading byte offset (ignored for swizzled K-major)
-  d |= (uint64_t)((8 * 128) >> 4) << 32;         // stride byte offset: 8 rows
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
   return d;
 }
 
@@ -334,22 +323,49 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
   return released;
 }
 
-// The same epilogue for a kernel with sixteen epilogue warps and 2 KB of staging per warp: a
-// warp owns 32 rows x (NCH * 32) columns. The two accumulators of a 32-column chunk are fetched
-// with one wait; tensor memory goes back to the MMA warp as soon as the warp's last chunk has
-// left it. A chunk passes through the staging tile in halves of 16 columns (four lanes then
-// own one row's 64 contiguous bytes, eight rows per instruction). 16-byte slots are
-// XOR-swizzled by bits 1-2 of the row: writes (a lane per row) and reads (four lanes per row)
-// are both free of bank conflicts. (Draining all chunks into registers first, to release
-// tensor memory earlier, needs more than the 96 registers a thread of this kernel can have.)
+// The epilogue of the pair kernel that takes A pre-split: sixteen warps, a warp per tensor-memory
+// lane quarter and (NCH * 32)-column group, each with a shared-memory buffer for its whole
+// 32 x (NCH * 32) part of the result. Phase 1 copies that part out of tensor memory (the two
+// accumulators of a 32-column chunk are fetched with one wait, combined and scaled, and written
+// a row per lane) and hands tensor memory back to the MMA warp. Phase 2 -- bias, activation,
+// residual, the stores, the fp16 split for a consuming GEMM -- then runs under the next
+// tile's MMAs, reading the buffer four lanes per row (64 contiguous bytes of a row per
+// instruction and row). The 16-byte slots of a row are XOR-swizzled by the row so that both
+// the row-per-lane writes and the four-lanes-per-row reads are free of bank conflicts.
+__device__ __forceinline__ int epi_slot(int row, int j) { return j ^ (((row & 1) << 2) | ((row >> 1) & 3)); }
+
 template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
-__device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stage, uint32_t tmem_base, int q,
-                                              int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
-                                              Release&& release) {
-  bool released = false;
+__device__ __forceinline__ bool epilogue_buffered(const TcEpilogue& ep, float4* buf, uint32_t tmem_base, int q,
+                                                  int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
+                                                  Release&& release) {
+  constexpr int kRowVec = NCH * 8;                  // float4 slots per buffered row
   const float sc = acc_scale_of(ep);
   float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
+  __syncwarp();                                     // the previous tile's reads of the buffer are over
+#pragma unroll 1
+  for (int ci = 0; ci < NCH; ++ci) {
+    if (n0 + (cc0 + ci) * 32 >= ep.n) break;        // uniform across the warp
+    uint32_t v[32];
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32);
+    tc_ld_32x32_nowait(taddr, v);
+    if (D2OFF != 0) {
+      uint32_t w[32];
+      tc_ld_32x32_nowait(taddr + (uint32_t)D2OFF, w);
+      tc_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        v[j] = __float_as_uint(__fmul_rn(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])), sc));
+    } else {
+      tc_wait_ld();
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      buf[lane * kRowVec + epi_slot(lane, ci * 8 + j)] =
+          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                      __uint_as_float(v[4 * j + 3]));
+  }
+  const bool released = release();                  // includes a __syncwarp: the buffer is written
   const int c4 = lane & 3, rsub = lane >> 2;
   const int row_base = m0 + q * 32 + rsub;
   float bm[4];
@@ -358,84 +374,57 @@ __device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stag
     for (int i = 0; i < 4; ++i) bm[i] = row_base + 8 * i < ep.m ? __ldg(ep.bias_m + row_base + 8 * i) : 0.f;
   }
 #pragma unroll 1
-  for (int ci = 0; ci < NCH; ++ci) {
-    const int col0 = n0 + (cc0 + ci) * 32;
-    if (col0 >= ep.n) break;                       // uniform across the warp
-    uint32_t v[32];
-    {
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32);
-      tc_ld_32x32_nowait(taddr, v);
-      if (D2OFF != 0) {
-        uint32_t w[32];
-        tc_ld_32x32_nowait(taddr + (uint32_t)D2OFF, w);
-        tc_wait_ld();
+  for (int hh = 0; hh < 2 * NCH; ++hh) {            // halves of 16 columns
+    const int col = n0 + cc0 * 32 + 16 * hh + 4 * c4;
+    if (n0 + cc0 * 32 + 16 * hh >= ep.n) break;     // uniform across the warp
+    const bool col_ok = col < ep.n;                 // n % 4 == 0: the whole float4 is in range
+    float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+    float4 a[4], r[4];
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          v[j] = __float_as_uint(__fmul_rn(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])), sc));
-      } else {
-        tc_wait_ld();
+    for (int i = 0; i < 4; ++i) {
+      const int rl = 8 * i + rsub;
+      a[i] = buf[rl * kRowVec + epi_slot(rl, 4 * hh + c4)];
+      if (HAS_RES) {
+        const int row = row_base + 8 * i;
+        r[i] = (col_ok && row < ep.m)
+                   ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
+                   : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    if (ci + 1 == NCH || col0 + 32 >= ep.n) released = release();
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        stage[lane * 4 + (j ^ ((lane >> 1) & 3))] =
-            make_float4(__uint_as_float(v[16 * h + 4 * j]), __uint_as_float(v[16 * h + 4 * j + 1]),
-                        __uint_as_float(v[16 * h + 4 * j + 2]), __uint_as_float(v[16 * h + 4 * j + 3]));
-      __syncwarp();
-      const int col = col0 + 16 * h + 4 * c4;
-      const bool col_ok = col < ep.n;   // n % 4 == 0: the whole float4 is in range
-      float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
-      float4 a[4], r[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int rl = 8 * i + rsub;
-        a[i] = stage[rl * 4 + (c4 ^ ((rl >> 1) & 3))];
-        if (HAS_RES) {
-          const int row = row_base + 8 * i;
-          r[i] = (col_ok && row < ep.m)
-                     ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
-                     : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int i = 0; i < 4; ++i) {
+      float4 x = a[i];
+      if (BIAS == 1) {
+        x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
+        x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float4 x = a[i];
-        if (BIAS == 1) {
-          x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
-          x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
-        }
-        if (BIAS == 2) {
-          x.x = __fadd_rn(x.x, bm[i]); x.y = __fadd_rn(x.y, bm[i]);
-          x.z = __fadd_rn(x.z, bm[i]); x.w = __fadd_rn(x.w, bm[i]);
-        }
-        if (ACT == ACT_GELU) {
-          const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
-          x = make_float4(lo.x, lo.y, hi.x, hi.y);
-        } else if (ACT != ACT_NONE) {
-          const float al = ep.act_alpha, be = ep.act_beta;
-          x.x = apply_act(ACT, x.x, al, be); x.y = apply_act(ACT, x.y, al, be);
-          x.z = apply_act(ACT, x.z, al, be); x.w = apply_act(ACT, x.w, al, be);
-        }
-        if (HAS_RES) {
-          x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
-          x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
-        }
-        const int row = row_base + 8 * i;
-        if (col_ok && row < ep.m) {
-          if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
-          if (ep.c16_hi) {   // the GEMM that consumes this result takes it split (batch 1)
-            uint2 h, l;
-            f16_split(x, h, l);
-            const long long o = ((long long)row * ep.ldc16 + col) >> 2;
-            ep.c16_hi[o] = h;
-            ep.c16_lo[o] = l;
-            seen |= split_seen(x);
-          }
+      if (BIAS == 2) {
+        x.x = __fadd_rn(x.x, bm[i]); x.y = __fadd_rn(x.y, bm[i]);
+        x.z = __fadd_rn(x.z, bm[i]); x.w = __fadd_rn(x.w, bm[i]);
+      }
+      if (ACT == ACT_GELU) {
+        const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
+        x = make_float4(lo.x, lo.y, hi.x, hi.y);
+      } else if (ACT != ACT_NONE) {
+        const float al = ep.act_alpha, be = ep.act_beta;
+        x.x = apply_act(ACT, x.x, al, be); x.y = apply_act(ACT, x.y, al, be);
+        x.z = apply_act(ACT, x.z, al, be); x.w = apply_act(ACT, x.w, al, be);
+      }
+      if (HAS_RES) {
+        x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
+        x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
+      }
+      const int row = row_base + 8 * i;
+      if (col_ok && row < ep.m) {
+        if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
+        if (ep.c16_hi) {   // the GEMM that consumes this result takes it split (batch 1)
+          uint2 h, l;
+          if (ep.c16_fixed) { f16_split_fixed(x, h, l); seen |= split_seen_fixed(x); }
+          else { f16_split(x, h, l); seen |= split_seen(x); }
+          const long long o = ((long long)row * ep.ldc16 + col) >> 2;
+          ep.c16_hi[o] = h;
+          ep.c16_lo[o] = l;
         }
       }
     }
@@ -502,12 +491,12 @@ __device__ __forceinline__ void fixup_apply(const TcEpilogue& ep, int row, int c
   if (ep.c16_hi) {   // n is a multiple of 8 here: the whole float4 is in range
     uint2 h, l;
     const float4 yv = make_float4(y4[0], y4[1], y4[2], y4[3]);
-    f16_split(yv, h, l);
+    if (ep.c16_fixed) f16_split_fixed(yv, h, l); else f16_split(yv, h, l);
     const long long o = ((long long)row * ep.ldc16 + col0) >> 2;
     ep.c16_hi[o] = h;
     ep.c16_lo[o] = l;
     // A tile's few K-sliced elements say nothing about the tensor being tiny: overflow only.
-    if (split_seen(yv) & 1u) atomicCAS(ep.err, 0, kRangeCode);
+    if ((ep.c16_fixed ? split_seen_fixed(yv) : split_seen(yv)) & 1u) atomicCAS(ep.err, 0, kRangeCode);
   }
 }
 
@@ -960,9 +949,7 @@ __device__ __forceinline__ bool pair_get_work(const TcSched& sc, int w, TcWork* 
 // all four tiles of a stage come by TMA and no thread of the CTA touches them.
 template <int BN, bool PRE = false>
 struct PairSmem {
-  // K per stage: 32 (64-byte rows, 64-byte swizzle), or with PRE 64 (128-byte rows, 128-byte
-  // swizzle: half as many stages to signal, and the layout the tensor core fetches fastest)
-  static constexpr int kKb = PRE ? 64 : BK16;
+  static constexpr int kKb = BK16;                      // halves of K per stage: 64-byte rows, 64-byte swizzle
   static constexpr int kABytes = BM * kKb * 2;          // fp16 hi tile of A; the lo tile follows
   static constexpr int kBBytes = (BN / 2) * kKb * 2;    // this CTA's half of B: one of hi / lo
   static constexpr int kOffALo = kABytes;
@@ -971,8 +958,12 @@ struct PairSmem {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   // TMA brings B only (A goes global -> registers -> tiles), or everything (PRE)
   static constexpr int kTxBytes = 2 * kBBytes + (PRE ? 2 * kABytes : 0);
-  static constexpr int kStages = (200 * 1024) / kStageBytes;   // 6 at BN 256
-  static constexpr int kEpiBytes = kEpiWarps * 4096;
+  // PRE: sixteen epilogue warps with a buffer each for their whole 32 x (BN / 4) part of the
+  // accumulators (tensor memory is handed back as soon as it has been copied there, and the
+  // epilogue proper runs under the next tile's MMAs), which leaves room for three stages; the
+  // main loop is bound by the MMAs, not by the feed, and three stages (96 KB in flight) keep it so.
+  static constexpr int kEpiBytes = PRE ? 16 * 32 * (BN / 4) * 4 : kEpiWarps * 4096;
+  static constexpr int kStages = PRE ? 3 : (200 * 1024) / kStageBytes;   // 6 at BN 256 without PRE
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;              // D1 and D2, one accumulator set
   static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
@@ -1088,9 +1079,8 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
           if (it == 0) pair_stamp(dbg, 2);
           tc_fence_after();
-          auto mk = [](uint32_t a) { return PRE ? make_smem_desc_sw128(a) : make_smem_desc(a); };
-          const uint64_t da = mk(smem_u32(a_raw(s))), dal = mk(smem_u32(a_lo(s)));
-          const uint64_t db = mk(smem_u32(b_hi(s))), dbl = mk(smem_u32(b_lo(s)));
+          const uint64_t da = make_smem_desc(smem_u32(a_raw(s))), dal = make_smem_desc(smem_u32(a_lo(s)));
+          const uint64_t db = make_smem_desc(smem_u32(b_hi(s))), dbl = make_smem_desc(smem_u32(b_lo(s)));
           if (!(dbg & 256)) {   // one accumulator after the other within a stage: alternating between them
                                 // with every MMA cost 30 % of the tensor pipe's rate (dbg bit 256: the old order)
 #pragma unroll
@@ -1205,14 +1195,16 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   } else if (!PRE || warp < 16) {
     // ---------------- epilogue (each CTA its own 128 rows) ----------------
     // PRE: warps 0-15, a warp per lane quarter and quarter of the columns on the common
-    // epilogues (2 KB of staging each); the general and the K-slice epilogues are left to warps
-    // 8-15 with 4 KB each (the same 32 KB), the others only hand the accumulator back.
+    // epilogues; the general and the K-slice epilogues are left to warps 8-15 (half of the
+    // columns each), the others only hand the accumulator back.
     const int e = PRE ? warp : warp - kSplitWarps, q = e & 3;
     const int eo = PRE ? e - 8 : e;                                // index among the eight "old" warps
     const int cc0 = (eo >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // their 32-column chunks
     const int hc0 = (e >> 2) * (BN / 128);                        // PRE, common epilogues: 64 columns from chunk hc0
-    float4* stage = reinterpret_cast<float4*>(epi_smem + (eo < 0 ? 0 : eo) * 4096);
-    float4* stage_h = reinterpret_cast<float4*>(epi_smem + e * 2048);
+    // PRE: a buffer of 32 rows x BN / 4 floats per warp; the general and the K-slice epilogues
+    // (warps 8-15) use the first 4 KB of theirs as the staging tile.
+    float4* buf = reinterpret_cast<float4*>(epi_smem + (PRE ? e * (32 * (BN / 4) * 4) : 0));
+    float4* stage = PRE ? buf : reinterpret_cast<float4*>(epi_smem + e * 4096);
     const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
     const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !(ep.bias_m && ep.bias_n) &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
@@ -1248,17 +1240,14 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         return true;
       };
-      // The K-slice and general epilogues use the staging memory in 4 KB pieces that overlap
-      // the 2 KB pieces of the common epilogue: nobody may still be in the previous tile's.
-      if (PRE && (wk.raw >= 0 || key < 0)) asm volatile("bar.sync 2, 512;" ::: "memory");
       if (PRE && m0 < ep.m && wk.raw < 0) {
         switch (key) {
-          case 0: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 1: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 2: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 3: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, true>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_GELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_RELU, 1, false>(ep, stage_h, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 0: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 0, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 1: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 1, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 2: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 0, true>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 3: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 1, true>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_buffered<BN / 128, D2, ACT_GELU, 1, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_buffered<BN / 128, D2, ACT_RELU, 1, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
           default:
             if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1);
             break;
@@ -1409,16 +1398,12 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t k, int
   cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes,
                            (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * elem_bytes};
   cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
-  // 1128: the plain 128-byte swizzle (K-major tiles of 128-byte rows); 128: the same span with 32-byte atoms
-  const bool sw128_plain = swizzle == 1128;
-  if (sw128_plain) swizzle = 128;
   if (swizzle != 0 && box_k * elem_bytes != swizzle) return false;
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            sw128_plain ? CU_TENSOR_MAP_SWIZZLE_128B
-            : swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                             : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+            swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                           : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1613,7 +1598,7 @@ TcShape pick_shape(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, 
   // half of B (32 KB per stage), the pair's MMAs cost 128 clocks per SM; single accumulator set.
   const int pairs = allow_pairs ? pair_count() : 0;
   if (f16 && batch == 1 && (k % (allow_pairs == 2 ? 8 : 4)) == 0 && pairs > 0 && (!fbn || fbn == 256)) {
-    const int pkb = allow_pairs == 2 ? 64 : kbf;       // pre-split A: 64 halves of K per stage
+    const int pkb = kbf;
     const TcPlan pl = make_plan(m, n, k, batch, 256, 2, pkb, pairs);
     double rounds = (double)(pl.sc.dp_tiles / pairs) + (pl.sc.dp_tiles % pairs ? 1.0 : 0.0);
     if (pl.sc.tail_parts >= 2) rounds += 1.0 / pl.sc.tail_parts + 0.05;
@@ -1630,8 +1615,7 @@ bool gemm_tc_wants_presplit(int64_t m, int64_t n, int64_t k, int64_t batch) {
 
 size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, int allow_pairs) {
   const TcShape sh = pick_shape(m, n, k, batch, variant, allow_pairs);
-  const int kbf = sh.pair && allow_pairs == 2 ? 64 : (variant == 2 ? BK16 : BK);
-  return make_plan(m, n, k, batch, sh.bn, sh.mt, kbf, sh.pair ? pair_count() : 0).workspace_bytes;
+  return make_plan(m, n, k, batch, sh.bn, sh.mt, variant == 2 ? BK16 : BK, sh.pair ? pair_count() : 0).workspace_bytes;
 }
 
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
@@ -1657,15 +1641,14 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
     const int a_rows = sh.pair ? BM : sh.mt * BM, b_rows = sh.pair ? bn / 2 : bn;
     if (sh.pair && pre) {
       if ((q.lda16 % 8) != 0) return cudaErrorInvalidValue;
-      if (!make_map(&ma, q.a16_hi, 2, q.k, q.m, 1, q.lda16, 0, 64, BM, 1128)) return cudaErrorInvalidValue;
-      if (!make_map(&mal, q.a16_lo, 2, q.k, q.m, 1, q.lda16, 0, 64, BM, 1128)) return cudaErrorInvalidValue;
+      if (!make_map(&ma, q.a16_hi, 2, q.k, q.m, 1, q.lda16, 0, BK16, BM, 64)) return cudaErrorInvalidValue;
+      if (!make_map(&mal, q.a16_lo, 2, q.k, q.m, 1, q.lda16, 0, BK16, BM, 64)) return cudaErrorInvalidValue;
     } else {
       if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK16, a_rows, 0)) return cudaErrorInvalidValue;
       mal = ma;
     }
-    const int bbox = (sh.pair && pre) ? 64 : BK16, bsw = (sh.pair && pre) ? 1128 : 64;
-    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, bbox, b_rows, bsw)) return cudaErrorInvalidValue;
-    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, bbox, b_rows, bsw)) return cudaErrorInvalidValue;
+    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
+    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
   } else if (kmode == TC_3X_SPLIT_B_MN) {
     // B [K, N]: N is the contiguous dimension, boxes of 32 columns x BK k-rows.
     if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK, sh.mt * BM, 64)) return cudaErrorInvalidValue;
@@ -1692,6 +1675,7 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.act = q.act; ep.act_alpha = q.act_alpha; ep.act_beta = q.act_beta;
   ep.res = q.residual; ep.ldres = q.ld_res; ep.sres = q.stride_res;
   ep.c16_hi = static_cast<uint2*>(q.c16_hi); ep.c16_lo = static_cast<uint2*>(q.c16_lo); ep.ldc16 = q.ldc16;
+  ep.c16_fixed = q.c16_fixed;
   ep.acc_scale = kmode == TC_F16X3 ? q.b16_inv_scale : nullptr;
   ep.b_row_scale = q.b_row_scale; ep.b_row_scale_stride = q.b_row_scale_stride; ep.k_total = (int)q.k;
   if (q.b_row_scale && kmode != TC_3X_SPLIT_B_MN) return cudaErrorInvalidValue;   // exists for the [K, N] operand only
@@ -1708,8 +1692,7 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
     return cudaErrorInvalidValue;
   }
   ep.dbg = std::getenv("ALTIUS_CUDA_TC_DBG") ? std::atoi(std::getenv("ALTIUS_CUDA_TC_DBG")) : 0;
-  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, (sh.pair && pre) ? 64 : (kmode == TC_F16X3 ? BK16 : BK),
-                        sh.pair ? pair_count() : 0);
+  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, kmode == TC_F16X3 ? BK16 : BK, sh.pair ? pair_count() : 0);
   if (pl.sc.tail_parts >= 2 && (!q.workspace || q.workspace_bytes < pl.workspace_bytes)) {
     // No (or too small a) workspace: fall back to whole tiles only.
     pl.sc.dp_tiles = pl.sc.num_tiles;

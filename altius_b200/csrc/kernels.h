@@ -198,6 +198,8 @@ struct GemmParams {
   void* c16_hi;             // tensor-core pair kernel only: the result also (or only) as fp16 hi / lo
   void* c16_lo;             // halves [m, ldc16], for the GEMM that takes it as its pre-split A; or null
   int64_t ldc16;
+  int c16_fixed;            // 0: hi / lo as f16_split (lo scaled by 2^11); 1: both on the fixed scale 2^8
+                            // (f16_split_fixed), the operand format of the TMA-fed attention kernel
   const float* b16_inv_scale;  // device scalar 2^-e when b16_hi / b16_lo hold B * 2^e; or null
   const float* b_row_scale;    // tensor-core path with B given [K, N] only: row k of B[batch] is multiplied by
   int64_t b_row_scale_stride;  // b_row_scale[batch * stride + k] (fp32, before the split); or null
@@ -267,5 +269,22 @@ cudaError_t launch_attention(const AttentionParams& p, cudaStream_t st);
 // tcgen05 kernel: head_dim 64, 64 < tokens <= 256, 3xTF32 products.
 bool attention_tc_supported(const AttentionParams& p);
 cudaError_t launch_attention_tc(const AttentionParams& p, cudaStream_t st);
+
+// tcgen05 kernel fed by TMA: Q, K and V are column ranges of one [B, T, ld16] projection that its
+// GEMM wrote as two fp16 arrays on the fixed scale (GemmParams::c16_fixed); head_dim 64,
+// 64 < tokens <= 208. Head h of an operand starts at column col + 64 h.
+struct Attention16Params {
+  const void* qkv16_hi; const void* qkv16_lo;
+  int64_t ld16, q_col, k_col, v_col;
+  float* out; int64_t out_row_stride, out_batch_stride;   // out may be null when out16_hi / out16_lo are given
+  void* out16_hi; void* out16_lo;                         // the result as fp16 hi / lo halves (same strides), or null
+  int batch, heads, tokens, head_dim;
+  const float* scale; int scale_mode;                     // device scalar or null; 1: multiply, 2: divide
+  int* err_word;
+};
+bool attention_tc16_shape_ok(int head_dim, int tokens, int64_t ld16, int64_t q_col, int64_t k_col, int64_t v_col,
+                             int64_t out_row_stride, int64_t out_batch_stride);
+bool attention_tc16_supported(const Attention16Params& p);
+cudaError_t launch_attention_tc16(const Attention16Params& p, cudaStream_t st);
 
 }  // namespace ac

@@ -34,7 +34,9 @@ struct Ctx {
   // (scratch values `hi`, `lo`). `produced`: a step emitted so far writes the halves (the kernel
   // that computes the value, or a split kernel); `fp32_needed`: someone still reads the value
   // itself, so its producer writes it as well.
-  struct Split { int hi = -1, lo = -1; bool produced = false, fp32_needed = true; };
+  // `fixed`: the halves are on the fixed scale (f16_split_fixed), the operand format of the
+  // TMA-fed attention kernel, instead of f16_split's.
+  struct Split { int hi = -1, lo = -1; bool produced = false, fp32_needed = true, fixed = false; };
   std::map<int, Split> split;
   explicit Ctx(AcSession& s_) : s(s_) {}
 
@@ -734,16 +736,31 @@ void plan_presplit(Ctx& c, Plan& plan) {
     if (!presplit_applies(c.s, g, c.val(b).is_const, 0, 0)) continue;
     split_users[a]++;
   }
+  // The [B, T, 3D] projection in front of a fused attention core: its GEMM writes it on the fixed
+  // scale and the TMA-fed attention kernel reads Q, K and V from there (the Split node between
+  // them is the value's one consumer and is absorbed into the core).
+  std::map<int, int> fixed_users;
+  if (c.s.opt.gemm_mode == 0 && effective_pairs(c.s) == 2 && !std::getenv("ALTIUS_CUDA_NO_ATTENTION_TMA")) {
+    for (auto& kv : plan.attention) {
+      const AttentionFusion& f = kv.second;
+      const int src = f.q.src;
+      if (src != f.k.src || src != f.v.src || split_users.count(src) || c.val(src).is_const) continue;
+      if (!attention_tc16_shape_ok((int)f.q.hd, (int)f.q.T, f.q.C, f.q.col, f.k.col, f.v.col, f.q.H * f.q.hd,
+                                   f.q.T * f.q.H * f.q.hd))
+        continue;
+      split_users[src] = 1;
+      fixed_users[src] = 1;
+    }
+  }
   for (auto& kv : split_users) {
     const int a = kv.first;
     const Value& av = c.val(a);
-    const int64_t k = av.dims[av.rank - 1];
     const int64_t floats = av.numel() / 2;    // two halves per float of scratch; rows of k halves
-    (void)k;
     Ctx::Split sp;
     sp.hi = new_value(c, floats, false);
     sp.lo = new_value(c, floats, false);
     sp.fp32_needed = c.is_output[a] || (int)c.consumers[a].size() != kv.second;
+    sp.fixed = fixed_users.count(a) != 0;
     c.split[a] = sp;
   }
 }
@@ -831,7 +848,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
   if (tc && b16_hi >= 0 && presplit_applies(*s, g, true, a_off, b_off)) {
     lda16 = g.k;
     auto sp = em.c.split.find(a);
-    const bool planned = sp != em.c.split.end() && a_off == 0 && g.lda == g.k;
+    const bool planned = sp != em.c.split.end() && !sp->second.fixed && a_off == 0 && g.lda == g.k;
     if (planned) {
       a16_hi = sp->second.hi; a16_lo = sp->second.lo;
       a_fp32_present = sp->second.fp32_needed || !sp->second.produced;
@@ -858,13 +875,14 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
   // This GEMM's own result, when a later GEMM takes it pre-split and this one runs on the pair
   // kernel with an epilogue that can write the halves.
   int c16_hi = -1, c16_lo = -1;
-  bool c_fp32 = true;
+  bool c_fp32 = true, c16_fixed = false;
   {
     auto so = em.c.split.find(out);
     if (so != em.c.split.end() && !so->second.produced && a16_hi >= 0 && c_off == 0 && g.ldc == g.n && (g.n % 8) == 0 &&
         gemm_tc_can_split_output(act, bias_n >= 0, bias_m >= 0, c_in >= 0, alpha, bias_scale)) {
       c16_hi = so->second.hi; c16_lo = so->second.lo;
       c_fp32 = so->second.fp32_needed;
+      c16_fixed = so->second.fixed;
       so->second.produced = true;
     }
   }
@@ -906,6 +924,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.c16_hi = c16_hi >= 0 ? s->ptr(c16_hi) : nullptr;
     p.c16_lo = c16_lo >= 0 ? s->ptr(c16_lo) : nullptr;
     p.ldc16 = g.n;
+    p.c16_fixed = c16_fixed ? 1 : 0;
     p.b16_inv_scale = b16_scale >= 0 ? s->fptr(b16_scale) : nullptr;
     p.b_row_scale = b_row_scale >= 0 ? s->fptr(b_row_scale) : nullptr;
     p.b_row_scale_stride = g.k;
@@ -1336,6 +1355,25 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         std::vector<int> awrites;
         if (o_fp32) awrites.push_back(f.out);
         if (o16_hi >= 0) { awrites.push_back(o16_hi); awrites.push_back(o16_lo); }
+        // The projection was written on the fixed scale by its GEMM: the TMA-fed kernel.
+        auto si = c.split.find(f.q.src);
+        if (tc_attn && si != c.split.end() && si->second.fixed && si->second.produced && f.q.src == f.k.src &&
+            f.q.src == f.v.src) {
+          const int in_hi = si->second.hi, in_lo = si->second.lo;
+          em.add("attention_tma_tcgen05", n.op, {in_hi, in_lo, f.scale}, awrites, bytes, flops, [=](cudaStream_t st) {
+            Attention16Params p{};
+            p.qkv16_hi = s->ptr(in_hi); p.qkv16_lo = s->ptr(in_lo);
+            p.ld16 = C; p.q_col = f.q.col; p.k_col = f.k.col; p.v_col = f.v.col;
+            p.out = o_fp32 ? s->fptr_mut(f.out) : nullptr; p.out_row_stride = H * hd; p.out_batch_stride = T * H * hd;
+            p.out16_hi = o16_hi >= 0 ? s->ptr(o16_hi) : nullptr;
+            p.out16_lo = o16_lo >= 0 ? s->ptr(o16_lo) : nullptr;
+            p.batch = (int)B; p.heads = (int)H; p.tokens = (int)T; p.head_dim = (int)hd;
+            p.scale = f.scale >= 0 ? s->fptr(f.scale) : nullptr; p.scale_mode = f.scale_mode;
+            p.err_word = s->err_word;
+            return launch_attention_tc16(p, st);
+          });
+          return;
+        }
         em.add(tc_attn ? "attention_tcgen05" : "attention_fused", n.op, {f.q.src, f.k.src, f.v.src, f.scale}, awrites, bytes, flops,
                [=](cudaStream_t st) {
                  AttentionParams p{};

@@ -10,7 +10,7 @@
 namespace ac {
 namespace tc {
 
-constexpr uint32_t kWaitLimit = 1u << 24;    // polls before a wait gives up
+constexpr uint32_t kWaitLimit = 1u << 21;    // polls before a wait gives up
 // fp16 split: x = hi + lo * 2^-11 with lo kept scaled by 2^11 (out of the fp16 subnormals).
 constexpr float kLoScale = 2048.f, kLoUnscale = 1.f / 2048.f;
 
@@ -192,6 +192,36 @@ __device__ __forceinline__ unsigned split_seen(float4 v) {
 __device__ __forceinline__ void split_report_warp(unsigned seen, int* err) {
   const unsigned all = __reduce_or_sync(0xffffffffu, seen);
   if (((all & 1u) || ((all & 4u) && !(all & 2u))) && (threadIdx.x & 31) == 0) atomicCAS(err, 0, kRangeCode);
+}
+
+// ---- the fixed-scale split (operands of the TMA-fed attention kernel) ---------------------
+// X = x * 2^8; hi = rn_fp16(X); lo = rn_fp16(X - hi): both halves on ONE scale, so that the
+// three partial products of a split GEMM can share an accumulator. X - hi is exact in fp32;
+// lo is a normal fp16 (11 more bits of X) when |X| >= 2^-3 and has an absolute floor of 2^-25
+// below that: full precision for |x| in [2^-11, 255], a loss relative to the largest element
+// beside it of at most 2^-22 whenever a region holds one element of that size.
+constexpr float kFixedScale = 256.f, kFixedUnscale = 1.f / 256.f;
+__device__ __forceinline__ void f16_split_plain(float4 x, uint2& hi, uint2& lo) {
+  const __half2 h01 = __floats2half2_rn(x.x, x.y), h23 = __floats2half2_rn(x.z, x.w);
+  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+  const __half2 l01 = __floats2half2_rn(__fsub_rn(x.x, f01.x), __fsub_rn(x.y, f01.y));
+  const __half2 l23 = __floats2half2_rn(__fsub_rn(x.z, f23.x), __fsub_rn(x.w, f23.y));
+  hi.x = *reinterpret_cast<const uint32_t*>(&h01); hi.y = *reinterpret_cast<const uint32_t*>(&h23);
+  lo.x = *reinterpret_cast<const uint32_t*>(&l01); lo.y = *reinterpret_cast<const uint32_t*>(&l23);
+}
+__device__ __forceinline__ void f16_split_fixed(float4 x, uint2& hi, uint2& lo) {
+  f16_split_plain(make_float4(__fmul_rn(x.x, kFixedScale), __fmul_rn(x.y, kFixedScale),
+                              __fmul_rn(x.z, kFixedScale), __fmul_rn(x.w, kFixedScale)), hi, lo);
+}
+// As split_seen, for the fixed-scale split: bit 0 when x * 2^8 is beyond fp16, bit 1 an element
+// with |x * 2^8| >= 2^-3, bit 2 a non-zero element below that.
+__device__ __forceinline__ unsigned split_seen_fixed(float x) {
+  const float X = __fmul_rn(x, kFixedScale);
+  const unsigned ab = __float_as_uint(X) & 0x7FFFFFFFu;
+  return beyond_half(X) | (ab >= 0x3E000000u ? 2u : (ab != 0u ? 4u : 0u));
+}
+__device__ __forceinline__ unsigned split_seen_fixed(float4 v) {
+  return split_seen_fixed(v.x) | split_seen_fixed(v.y) | split_seen_fixed(v.z) | split_seen_fixed(v.w);
 }
 
 // Byte offset of 8-byte chunk `c8` (4 halves) of row `row` in a K-major fp16 tile with

@@ -2,29 +2,39 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).
-A step is one forward pass of ViT-B/16 (f32, batch 32 per GPU) over a synthetic
-~N(0,1) input with seeded ~N(0,0.02) weights. Rank 0 prints one JSON line:
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1). A step is one
+forward pass of ViT-B/16 (f32, batch 32 per GPU) over a synthetic ~N(0,1) input with seeded
+~N(0,0.02) weights. Rank 0 prints one JSON line:
 
-  value   images/s, whole job, inputs already resident in HBM, timed with CUDA
-          events on the session's stream (max over ranks);
-  e2e     images/s through the public API with page-locked HOST buffers: the H2D
-          copy of every step's images and the D2H copy of its logits are inside the
-          timed region. `CudaSession.run_batches` (a queue of batches: the copy of
-          step i+1 overlaps the kernels of step i); `e2e.sync_run` is the same with
-          one synchronous `CudaSession.run` per step;
-  roofline  the dominant kernel (the GEMM) from a per-kernel CUDA-event profile
-          taken in the same process, against the measured tensor peak;
-  hbm_kernels  the tensor-op micrograph (B=64) kernels' achieved GB/s against
-          the measured copy bandwidth -- the second half of the metric;
-  cpu_baseline  the CPU oracle (a port of the reference interpreter) timed on
-          the host cores on a bounded sample of the same workload.
+  value     images/s, whole job, inputs resident in HBM, CUDA events on the session's stream.
+            Blocks of exactly K steps (each bracketed by a barrier and a device synchronize, max
+            over ranks) are repeated until at least two seconds of timed work have passed: a B200
+            drops its clocks under the power cap after the first tenths of a second, so one short
+            block would be a burst figure. `value` is the median block, `blocks_ms` has them all,
+            `clocks` is sampled over the whole region and `ms_x_mhz` = ms_per_step x median SM MHz
+            lets runs at different clocks be compared;
+  e2e       images/s through the public API with page-locked HOST buffers: the H2D copy of every
+            step's images and the D2H copy of its logits are inside the timed region
+            (`CudaSession.run_batches`, a queue of batches: the copy of step i+1 overlaps the
+            kernels of step i); `e2e.sync_run` is the same with one synchronous `run` per step;
+  parity    max absolute logit error (and top-1 agreement) of the timed session's output against
+            the CPU oracle on the first two images of rank 0's shard (images are independent, so
+            the oracle's batch-2 run is exact for them);
+  roofline  the dominant kernel (the GEMM) from a per-kernel CUDA-event profile taken in the same
+            process, against the measured tensor peak;
+  configs   the other configurations of the metric: MNIST latency, MobileNetV3-Large batch 32,
+            DeiT-Small batch 64 (N = 1 only);
+  hbm_kernels  the tensor-op micrograph (B = 64) kernels' achieved GB/s against the measured copy
+            bandwidth -- the second half of the metric;
+  cpu_baseline, cpu_baseline_clang  the CPU oracle (a port of the reference interpreter) and a
+            restatement of the reference's generated-C backend, timed on the host cores.
 
-`--impl reference` times that CPU port instead (the reference itself is Rust
-and cannot be built offline), all host threads, same metric and config.
+`--impl reference` times the interpreter port instead (the reference itself is Rust and cannot
+be built offline), all host threads, same metric and config.
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -40,6 +50,7 @@ sys.path.insert(0, ROOT)
 PER_GPU_BATCH = 32
 WORKLOAD = "ViT-B/16 224x224 f32 forward, batch 32 per GPU (197 tokens, dim 768, 12 layers, 12 heads)"
 VIT_GFLOP_PER_IMAGE = 35.13
+MIN_TIMED_SECONDS = 2.0
 
 
 def measured_peaks():
@@ -52,8 +63,16 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
 
 
+def workload_config(world, gemm_mode=0):
+    """The `config` object: the same keys and values in both arms."""
+    return {"workload": WORKLOAD, "global_batch": world * PER_GPU_BATCH,
+            "parallelism": f"{world} batch-sharded replica(s), no per-inference collective",
+            "l2": "working set per step (weights + activations, > 340 MB) is larger than the 126 MB L2",
+            "gemm_mode": gemm_mode}
+
+
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, power and throttle reasons with nvidia-smi while the timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -75,9 +94,9 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -85,28 +104,32 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], {}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for stamp, line in self.lines:
+            if t_begin is not None and not (t_begin <= stamp <= t_end):
+                continue
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
                 sm.append(float(f[1]))
                 mx.append(float(f[2]))
+                power.append(float(f[3]))
             except ValueError:
                 continue
             for name, val in zip(names, f[5:9]):
                 if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+                    reasons[name] = reasons.get(name, 0) + 1
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_mhz_min": min(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "power_w_median": statistics.median(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons), "reason_samples": reasons}
 
 
 def host_threads():
-    """All host cores this process may use (torchrun presets OMP_NUM_THREADS=1, so the
-    OpenMP default cannot be trusted); also lifts numpy's BLAS pool to that count."""
+    """All host cores this process may use (torchrun presets OMP_NUM_THREADS=1, so the OpenMP
+    default cannot be trusted); also lifts numpy's BLAS pool to that count."""
     n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     try:
         from threadpoolctl import threadpool_limits
@@ -116,43 +139,64 @@ def host_threads():
     return n
 
 
-def time_cpu_port(target_seconds=12.0, batch=2, max_runs=50):
-    """The CPU oracle on a bounded sample: forward passes of ViT-B/16 at a small
-    batch, repeated for about `target_seconds`; all host threads; OpenBLAS sgemm
-    (numpy's) standing in for the reference's BLIS."""
+# ---- CPU arms (the oracle is the checker and the reported baseline, never the product) ----------
+def _oracle_session(batch, threads):
     from altius_b200 import configs
     from oracle import InterpreterSessionBuilder
-    threads = host_threads()
     model, feeds = configs.vit_base_16(batch=batch)
     sess = (InterpreterSessionBuilder(model).with_intra_op_num_threads(threads)
             .with_sgemm("openblas").build())
-    x = list(feeds.values())
-    sess.run(x)  # warm-up
+    return sess, list(feeds.values())
+
+
+def time_cpu_port():
+    """The CPU oracle at the benchmark's own batch: one warm-up at batch 2 (pages the library
+    in), then ONE timed forward pass of ViT-B/16 at batch 32 on all host threads (OpenBLAS sgemm
+    standing in for the reference's BLIS)."""
+    threads = host_threads()
+    warm, xw = _oracle_session(2, threads)
+    warm.run(xw)
+    sess, x = _oracle_session(PER_GPU_BATCH, threads)
     t0 = time.perf_counter()
-    runs = 0
-    while runs < max_runs:
-        sess.run(x)
-        runs += 1
-        if time.perf_counter() - t0 >= target_seconds:
-            break
+    sess.run(x)
     dt = time.perf_counter() - t0
-    return dict(value=batch * runs / dt, unit="images/s", cores=threads, kind="port",
-                sample=f"{runs} forward passes of ViT-B/16 at batch {batch} in {dt:.1f} s; "
-                       f"oracle port of the interpreter, OpenBLAS sgemm, {threads} threads"), dt / runs
+    return dict(value=PER_GPU_BATCH / dt, unit="images/s", cores=threads, kind="port",
+                sample=f"one forward pass of ViT-B/16 at batch {PER_GPU_BATCH} in {dt:.1f} s; oracle port of "
+                       f"the interpreter, OpenBLAS sgemm, {threads} threads")
+
+
+def time_cpu_clang():
+    """The reference's second CPU backend (session_clang: C generated per graph) as a
+    restatement: its kernel templates written out for the ViT graph, gcc -O3 -fopenmp. A
+    bounded sample (batch 4)."""
+    try:
+        from oracle import clang_port
+    except Exception as e:   # not built / not present
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+    threads = host_threads()
+    return clang_port.time_vit(batch=4, threads=threads)
 
 
 def reference_arm(args, rank):
+    """`--impl reference`: the interpreter port on the host cores, same metric and config. Every
+    step is a forward pass of ViT-B/16; the per-step batch is the benchmark's 32 when K such
+    steps fit into about two minutes, else the largest of 16 / 8 / 4 / 2 that does (the one
+    full batch-32 pass that decides this is reported in `cpu_baseline.sample`)."""
     if rank != 0:
         return
-    batch = 2
-    from altius_b200 import configs
-    from oracle import InterpreterSessionBuilder
     threads = host_threads()
-    model, feeds = configs.vit_base_16(batch=batch)
-    sess = (InterpreterSessionBuilder(model).with_intra_op_num_threads(threads)
-            .with_sgemm("openblas").build())
-    x = list(feeds.values())
-    for _ in range(args.warmup):
+    warm, xw = _oracle_session(2, threads)
+    warm.run(xw)
+    full, xf = _oracle_session(PER_GPU_BATCH, threads)
+    t0 = time.perf_counter()
+    full.run(xf)
+    t32 = time.perf_counter() - t0
+    budget = 120.0
+    batch = PER_GPU_BATCH
+    while batch > 2 and (args.steps + min(args.warmup, 1)) * t32 * batch / PER_GPU_BATCH > budget:
+        batch //= 2
+    sess, x = (full, xf) if batch == PER_GPU_BATCH else _oracle_session(batch, threads)
+    for _ in range(min(args.warmup, 1)):
         sess.run(x)
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -164,16 +208,18 @@ def reference_arm(args, rank):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample_per_step": f"{batch} images on the host CPU"},
+        "config": workload_config(max(args.gpus, 1), args.gemm_mode),
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": threads, "kind": "port",
-                         "sample": f"each step = ViT-B/16 forward at batch {batch}; CPU oracle port of "
-                                   f"the reference interpreter (the Rust reference cannot be built "
-                                   f"offline), OpenBLAS sgemm, {threads} threads"},
+                         "sample": f"each step = one ViT-B/16 forward at batch {batch} on the host CPU (one full "
+                                   f"batch-{PER_GPU_BATCH} pass took {t32:.1f} s = {PER_GPU_BATCH / t32:.2f} images/s); "
+                                   f"CPU oracle port of the reference interpreter (the Rust reference cannot be "
+                                   f"built offline), OpenBLAS sgemm, {threads} threads"},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
+# ---- the tensor-op micrograph: the HBM-bound half of the metric ---------------------------------
 def micrograph_hbm(device, peaks):
     """Per-kernel achieved HBM GB/s on the tensor-op micrograph at B=64. L2 is swept before
     every kernel (a 256 MB read), so each is timed cold and without another kernel's dirty
@@ -205,6 +251,118 @@ def micrograph_hbm(device, peaks):
     return out
 
 
+def _dominant_kernel(prof, runs, peaks):
+    """Shares per step kind and the roofline entry of the kind with the largest total time."""
+    total_ms = sum(p["total_ms"] for p in prof.values())
+    kernels = {k: {"share": round(p["total_ms"] / total_ms, 4),
+                   "ms_per_step": round(p["total_ms"] / runs, 4),
+                   "launches_per_step": p["launches"] // runs}
+               for k, p in sorted(prof.items(), key=lambda kv: -kv[1]["total_ms"])}
+    top_kind, tp = max(prof.items(), key=lambda kv: kv[1]["total_ms"])
+    if tp["flops"] > 0:
+        achieved = tp["flops"] / (tp["total_ms"] * 1e-3) / 1e12
+        # The fp16-split kernels issue fp16 MMAs (the rate of the measured bf16 GEMM), the TF32
+        # kernels run at half of it; both spend three MMAs per product, so `frac` tops out at 1/3.
+        f16 = "f16" in top_kind
+        peak = peaks["bf16_tflops_sustained"] / (1.0 if f16 else 2.0)
+        roofline = {"kernel": top_kind, "bound": "tensor", "achieved": round(achieved, 2),
+                    "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
+                    "traffic": None,
+                    "tensor_pipe_frac": round(3.0 * achieved / peak, 4),
+                    "peak_note": f"{peaks['source']} sustained bf16 cuBLAS TFLOP/s"
+                                 + ("" if f16 else " / 2 (no TF32 peak is measured)")
+                                 + "; achieved = algorithmic 2*M*N*K FLOPs / CUDA-event time; the kernel "
+                                   "issues three MMAs per product for fp32 fidelity, so frac tops out at "
+                                   "1/3 and tensor_pipe_frac = 3 * frac is the share of the tensor peak in use"}
+    else:
+        achieved = tp["bytes"] / (tp["total_ms"] * 1e-3) / 1e9
+        roofline = {"kernel": top_kind, "bound": "hbm", "achieved": round(achieved, 1),
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                    "traffic": None, "peak_note": f"{peaks['source']} copy bandwidth"}
+    return kernels, roofline
+
+
+def _profile_session(builder_fn, in_ptrs, out_ptrs, peaks, runs=4):
+    sess = builder_fn().with_profiling_enabled(True).build()
+    for it in range(runs + 2):
+        if it == 2:
+            sess.profile_reset()
+        sess.run_device(in_ptrs, out_ptrs)
+    prof = sess.profile()
+    sess.close()
+    return _dominant_kernel(prof, runs, peaks)
+
+
+def other_configs(device, peaks, gemm_mode, gemm_pairs):
+    """The metric's other configurations on one GPU: MNIST CNN latency at batch 1 (device
+    resident and through `run` with host buffers), MobileNetV3-Large at batch 32 and
+    DeiT-Small/16 distilled at batch 64 (images/s, inputs resident, at least 0.5 s of timed
+    work each), each with its per-kernel shares and the roofline entry of its dominant kernel."""
+    from altius_b200 import configs
+    from altius_b200.session import CudaSessionBuilder
+    import torch
+    dev = f"cuda:{device}"
+    out = {}
+    cases = [("mnist_cnn_b1", lambda: configs.mnist_cnn(seed=0), 1),
+             ("mobilenet_v3_large_b32", lambda: configs.mobilenet_v3_large(batch=32), 32),
+             ("deit_small_distilled_16_b64", lambda: configs.deit_small_distilled_16(batch=64), 64)]
+    for name, make, batch in cases:
+        model, feeds = make()
+
+        def builder():
+            return (CudaSessionBuilder(model).with_device(device).with_gemm_mode(gemm_mode)
+                    .with_gemm_pairs(gemm_pairs))
+        sess = builder().build()
+        ins = [torch.from_numpy(np.ascontiguousarray(v)).to(dev) for v in feeds.values()]
+        outs = [torch.empty(tuple(shape), dtype=torch.float32, device=dev) for shape, _ in sess.output_info]
+        ip, op = [t.data_ptr() for t in ins], [t.data_ptr() for t in outs]
+        for _ in range(5):
+            sess.run_device(ip, op)
+        torch.cuda.synchronize(device)
+        iters = 200 if batch == 1 else 20
+        ms, done = 0.0, 0
+        while ms < 500.0 and done < 100000:
+            ms += sess.time_device_runs(ip, op, iters)
+            done += iters
+        entry = {"batch": batch, "ms_per_run": round(ms / done, 5), "runs_timed": done,
+                 "images_per_s": round(batch * done / (ms * 1e-3), 1),
+                 "gpu_launches_per_run": sess.launches_per_run}
+        if batch == 1:
+            host_in = [np.ascontiguousarray(v) for v in feeds.values()]
+            for _ in range(20):
+                sess.run(host_in)
+            t0 = time.perf_counter()
+            for _ in range(500):
+                sess.run(host_in)
+            entry["latency_us_host_buffers"] = round((time.perf_counter() - t0) / 500 * 1e6, 2)
+            entry["latency_us_device_resident"] = round(1e3 * ms / done, 2)
+        sess.close()
+        entry["kernels"], entry["roofline"] = _profile_session(builder, ip, op, peaks)
+        out[name] = entry
+        del ins, outs
+    return out
+
+
+def parity_against_oracle(logits, x_host):
+    """The timed session's logits for the first two images of this rank's shard against the CPU
+    oracle run on those two images alone (the graph treats images independently)."""
+    from altius_b200 import configs
+    from oracle import InterpreterSessionBuilder
+    threads = host_threads()
+    model2, _ = configs.vit_base_16(batch=2, seed=0)
+    ref = (InterpreterSessionBuilder(model2).with_intra_op_num_threads(threads)
+           .with_sgemm("openblas").build().run([np.ascontiguousarray(x_host[:2])])[0]).astype(np.float64)
+    got = np.asarray(logits[:2], dtype=np.float64)
+    err = np.abs(got - ref)
+    return {"checked_images": 2, "batch_of_timed_run": int(logits.shape[0]),
+            "max_abs_logit_err": float(err.max()), "tolerance": 1e-3,
+            "logit_abs_max": float(np.abs(ref).max()),
+            "top1_agree": bool((got.argmax(-1) == ref.argmax(-1)).all()),
+            "within_tolerance": bool(err.max() <= 1e-3),
+            "finite": bool(np.isfinite(np.asarray(logits)).all()),
+            "checker": "CPU oracle (port of the reference interpreter), same seeded weights and inputs"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -212,9 +370,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--gemm-mode", type=int, default=0)
-    ap.add_argument("--gemm-pairs", type=int, default=0, help="AcOptions.gemm_pairs (0 default, 3: the one-CTA GEMM kernel only)")
+    ap.add_argument("--gemm-pairs", type=int, default=0,
+                    help="AcOptions.gemm_pairs (0 default, 3: the one-CTA GEMM kernel only)")
+    ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS)
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-micrograph", action="store_true")
+    ap.add_argument("--skip-configs", action="store_true")
+    ap.add_argument("--skip-parity", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -242,12 +404,16 @@ def main():
 
     # Every rank builds the same graph; rank 0's weights are broadcast once.
     model, _ = configs.vit_base_16(batch=PER_GPU_BATCH, seed=0)
-    builder = CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode).with_gemm_pairs(args.gemm_pairs)
+
+    def builder():
+        return (CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode)
+                .with_gemm_pairs(args.gemm_pairs))
+    b = builder()
     blob = None
     if distributed:
         blob, ptrs = replicas.broadcast_weights(model, dev, src=0)
-        builder = builder.with_device_initializers(ptrs)
-    sess = builder.build()
+        b = b.with_device_initializers(ptrs)
+    sess = b.build()
     del blob
 
     # This rank's shard of the global batch (seeded per rank).
@@ -273,6 +439,8 @@ def main():
         return float(t.item())
 
     # ---- device-resident throughput ("value") -------------------------------------
+    # Blocks of exactly K steps; every rank runs the same number of blocks (the decision to
+    # go on is taken from the max-over-ranks time, which all ranks hold).
     for _ in range(args.warmup):
         sess.run_device(in_ptrs, out_ptrs)
     sampler = ClockSampler(local_rank)
@@ -280,12 +448,18 @@ def main():
     time.sleep(0.4)                      # let nvidia-smi start sampling
     sess.run_device(in_ptrs, out_ptrs)   # and put the GPU under load before the first sample counts
     barrier()
-    n_before = len(sampler.lines)
-    ms = sess.time_device_runs(in_ptrs, out_ptrs, args.steps)
-    barrier()
-    sampler.lines = sampler.lines[max(n_before - 1, 0):] if len(sampler.lines) > n_before else sampler.lines[-2:]
-    clocks = sampler.stop()
-    ms = max_over_ranks(ms)
+    t_begin = time.perf_counter()
+    blocks_ms = []
+    while True:
+        barrier()
+        ms = sess.time_device_runs(in_ptrs, out_ptrs, args.steps)
+        barrier()
+        blocks_ms.append(max_over_ranks(ms))
+        if sum(blocks_ms) >= 1e3 * args.min_seconds or len(blocks_ms) >= 10000:
+            break
+    t_end = time.perf_counter()
+    clocks = sampler.stop(t_begin, t_end)
+    ms = statistics.median(blocks_ms)
     value = world * PER_GPU_BATCH * args.steps / (ms * 1e-3)
 
     # ---- end to end through the public API with host buffers ("e2e") ----------------
@@ -301,8 +475,9 @@ def main():
     sync_s = time.perf_counter() - t0
     barrier()
     e2e_sync = world * PER_GPU_BATCH * args.steps / max_over_ranks(sync_s)
-    queue_in = [[x_host]] * args.steps
-    queue_out = [[y_host]] * args.steps
+    e2e_steps = args.steps * max(1, int(math.ceil(len(blocks_ms) / 2)))   # about a second of work
+    queue_in = [[x_host]] * e2e_steps
+    queue_out = [[y_host]] * e2e_steps
     sess.run_batches(queue_in[:3], outputs=queue_out[:3])
     barrier()
     t0 = time.perf_counter()
@@ -310,9 +485,11 @@ def main():
     e2e_s = time.perf_counter() - t0
     barrier()
     e2e_s = max_over_ranks(e2e_s)
-    e2e = world * PER_GPU_BATCH * args.steps / e2e_s
+    e2e = world * PER_GPU_BATCH * e2e_steps / e2e_s
     logits = np.array(y_host)
-    launches = sess.launches_per_run * args.steps * world
+    timed_runs = args.steps * len(blocks_ms)
+    launches = sess.launches_per_run * timed_runs * world
+    launches_per_step = sess.launches_per_run
     sess.close()
 
     if rank != 0:
@@ -322,69 +499,47 @@ def main():
         return
 
     # ---- per-kernel profile of the same workload (rank 0) ---------------------------
-    prof_sess = (CudaSessionBuilder(model).with_device(local_rank).with_gemm_mode(args.gemm_mode).with_gemm_pairs(args.gemm_pairs)
-                 .with_profiling_enabled(True).build())
-    for it in range(6):
-        if it == 2:
-            prof_sess.profile_reset()
-        prof_sess.run_device(in_ptrs, out_ptrs)
-    prof = prof_sess.profile()
-    prof_sess.close()
-    total_ms = sum(p["total_ms"] for p in prof.values())
-    kernels = {k: {"share": round(p["total_ms"] / total_ms, 4),
-                   "ms_per_step": round(p["total_ms"] / 4, 4),
-                   "launches_per_step": p["launches"] // 4}
-               for k, p in sorted(prof.items(), key=lambda kv: -kv[1]["total_ms"])}
-    top = max(prof.items(), key=lambda kv: kv[1]["total_ms"])
-    top_kind, tp = top
-    if tp["flops"] > 0:
-        achieved = tp["flops"] / (tp["total_ms"] * 1e-3) / 1e12
-        # The fp16-split kernel issues fp16 MMAs (the rate of the measured bf16 GEMM), the TF32
-        # kernels run at half of it; both spend three MMAs per product, so `frac` tops out at 1/3.
-        f16 = "f16" in top_kind
-        peak = peaks["bf16_tflops_sustained"] / (1.0 if f16 else 2.0)
-        roofline = {"kernel": top_kind, "bound": "tensor", "achieved": round(achieved, 2),
-                    "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
-                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at the
-                    # QKV shape (M 6304, K 768, N 2304; algorithmic operand + result bytes 84.6 MB, of
-                    # which A, B and most of C stay in L2), from the ncu capture summarised in
-                    # profiles/gemm_f16x3_6304x768x2304.md
-                    "traffic": 50155264 if f16 else None,
-                    "tensor_pipe_frac": round(3.0 * achieved / peak, 4),
-                    "peak_note": f"{peaks['source']} sustained bf16 cuBLAS TFLOP/s"
-                                 + ("" if f16 else " / 2 (no TF32 peak is measured)")
-                                 + "; achieved = algorithmic 2*M*N*K FLOPs / CUDA-event time; the kernel "
-                                   "issues three MMAs per product for fp32 fidelity, so frac tops out at "
-                                   "1/3 and tensor_pipe_frac = 3 * frac is the share of the tensor peak in use"}
-    else:
-        achieved = tp["bytes"] / (tp["total_ms"] * 1e-3) / 1e9
-        roofline = {"kernel": top_kind, "bound": "hbm", "achieved": round(achieved, 1),
-                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
-                    "traffic": None, "peak_note": f"{peaks['source']} copy bandwidth"}
+    kernels, roofline = _profile_session(builder, in_ptrs, out_ptrs, peaks)
+    if roofline["bound"] == "tensor":
+        roofline["traffic_note"] = ("null: the ncu capture of this kernel is of one launch at the QKV shape "
+                                    "(M 6304, K 768, N 2304) from the kernel bench, not of this in-graph "
+                                    "launch mix; its DRAM bytes are in the committed profile summary")
 
+    sm = clocks.get("sm_mhz")
     line = {
         "metric": "ViT-B/16 images/s", "value": round(value, 2), "unit": "images/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": world * PER_GPU_BATCH,
-                   "parallelism": f"{world} batch-sharded replica(s), no per-inference collective",
-                   "l2": "working set per step (346 MB of weights + activations) is larger than the 126 MB L2",
-                   "gemm_mode": args.gemm_mode},
+        "config": workload_config(world, args.gemm_mode),
+        "timing": {"blocks": len(blocks_ms), "steps_per_block": args.steps,
+                   "timed_seconds": round(sum(blocks_ms) * 1e-3, 3),
+                   "value_is": "median block of K steps; max over ranks per block",
+                   "blocks_ms_per_step": [round(b / args.steps, 4) for b in blocks_ms[:64]],
+                   "first_block_images_per_s": round(world * PER_GPU_BATCH * args.steps / (blocks_ms[0] * 1e-3), 2),
+                   "last_block_images_per_s": round(world * PER_GPU_BATCH * args.steps / (blocks_ms[-1] * 1e-3), 2),
+                   "ms_x_mhz": round(ms / args.steps * sm, 1) if sm else None},
         "e2e": {"value": round(e2e, 2), "unit": "images/s",
                 "h2d_bytes_per_step": int(x_host.nbytes), "d2h_bytes_per_step": int(y_host.nbytes),
+                "steps": e2e_steps,
                 "api": "CudaSession.run_batches (pipelined queue of batches)", "sync_run": round(e2e_sync, 2)},
         "gpu_launches": int(launches),
+        "gpu_launches_per_step": int(launches_per_step),
         "clocks": clocks,
         "roofline": roofline,
         "algorithmic_tflops_whole_step": round(VIT_GFLOP_PER_IMAGE * value / 1e3, 2),
         "kernels": kernels,
         "logits_checksum": float(np.abs(logits).sum()),
     }
+    if not args.skip_parity:
+        line["parity"] = parity_against_oracle(logits, x_host)
     if not args.skip_micrograph:
         line["hbm_kernels"] = micrograph_hbm(local_rank, peaks)
+    if world == 1 and not args.skip_configs:
+        line["configs"] = other_configs(local_rank, peaks, args.gemm_mode, args.gemm_pairs)
     if world == 1 and not args.skip_cpu_baseline:
-        line["cpu_baseline"], _ = time_cpu_port()
+        line["cpu_baseline"] = time_cpu_port()
+        line["cpu_baseline_clang"] = time_cpu_clang()
     print(json.dumps(line), flush=True)
     if distributed:
         dist.barrier()

@@ -1,14 +1,16 @@
-"""Per-kernel microbenchmarks through the session's C ABI.
+"""Per-kernel microbenchmarks through the session's C ABI (a measurement harness beside
+bench.py, not part of the package).
 
-    python -m altius_b200.kernel_bench gemm 6304 768 2304 [--mode 0|1|2] [--iters 10] [--bias] [--gelu] [--residual]
-    python -m altius_b200.kernel_bench micrograph [--batch 64] [--no-fuse]
-    python -m altius_b200.kernel_bench attention 32 197 12     # batch, tokens, heads (head dim 64)
-    python -m altius_b200.kernel_bench conv 16 64 112 [--k 1] [--depthwise] [--batch 32]   # c_in, c_out, H = W
+    python kernel_bench.py gemm 6304 768 2304 [--mode 0|1|2] [--iters 10] [--bias] [--gelu] [--residual]
+    python kernel_bench.py micrograph [--batch 64] [--no-fuse]
+    python kernel_bench.py attention 32 197 12     # batch, tokens, heads (head dim 64)
+    python kernel_bench.py conv 16 64 112 [--k 1] [--depthwise] [--batch 32]   # c_in, c_out, H = W
 
 Builds a one-node (or micrograph) session with per-kernel CUDA-event profiling
 and prints, per kernel kind, the mean device time and the achieved algorithmic
 TFLOP/s or GB/s. Inputs live on the device; the weight of `gemm` is a constant
-(the form the models have). Used for the ncu captures under profiles/.
+(the form the models have). The event times include the host's launch latency of each step
+(the steps are launched one by one, not as a graph): compare variants, not absolutes.
 """
 import argparse
 import json
@@ -16,8 +18,11 @@ import sys
 
 import numpy as np
 
-from . import configs, ir
-from .session import CudaSessionBuilder
+import os
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from altius_b200 import configs, ir  # noqa: E402
+from altius_b200.session import CudaSessionBuilder  # noqa: E402
 
 
 def _run(model, feeds, mode, fuse, iters, cold=False, pairs=False):

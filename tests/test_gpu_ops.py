@@ -9,6 +9,8 @@ MaxPool and all data movement; max relative error 1e-5 for reductions and
 softmax (tree summation order differs from the oracle's 8-lane partial sums);
 rtol 1e-5 + atol 1e-5 for contractions (summation order is unspecified in the
 reference's BLIS)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -572,6 +574,91 @@ def test_fused_attention_core(cuda_lib, B, T, H, scale_op):
     np.testing.assert_allclose(unfused, want, rtol=1e-5, atol=1e-6)
 
 
+def _projection_attention_model(B, T, H, scale_op="Mul", w_scale=0.05, with_out_proj=True):
+    """x [B, T, D] -> MatMul + bias to [B, T, 3D] -> the attention core -> (MatMul): the shape
+    of a transformer layer between its LayerNormalization and its residual Add."""
+    hd, D = 64, 64 * H
+    rng = np.random.default_rng(1234 + T + H)
+    w_qkv = (w_scale * rng.standard_normal((D, 3 * D))).astype(np.float32)
+    b_qkv = (0.1 * rng.standard_normal(3 * D)).astype(np.float32)
+    w_o = (0.05 * rng.standard_normal((D, D))).astype(np.float32)
+
+    def build(g):
+        x = g.add_input("x", (B, T, D))
+        i64 = lambda v: g.new_init(np.asarray(v, np.int64))
+        qkv = g.op("Add", g.op("MatMul", x, g.new_init(w_qkv)), g.new_init(b_qkv))
+        q, k, v = g.add_node("Split", [qkv, i64([D, D, D])], 3, axis=2)
+
+        def heads(t):
+            t = g.op("Reshape", t, i64([B, T, H, hd]))
+            t = g.op("Transpose", t, perm=[0, 2, 1, 3])
+            return g.op("Reshape", t, i64([B * H, T, hd]))
+        q, k, v = heads(q), heads(k), heads(v)
+        s_ = g.op("MatMul", q, g.op("Transpose", k, perm=[0, 2, 1]))
+        s_ = g.op(scale_op, s_, g.new_init(np.array([hd ** -0.5 if scale_op == "Mul" else hd ** 0.5], np.float32)))
+        o = g.op("MatMul", g.op("Softmax", s_, axis=-1), v)
+        o = g.op("Reshape", o, i64([B, H, T, hd]))
+        o = g.op("Transpose", o, perm=[0, 2, 1, 3])
+        o = g.op("Reshape", o, i64([B, T, D]))
+        return [g.op("MatMul", o, g.new_init(w_o)) if with_out_proj else o]
+    return _chain_model(build)
+
+
+@pytest.mark.parametrize("B,T,H,scale_op,out_proj", [(32, 197, 12, "Mul", True), (32, 197, 12, "Div", False),
+                                                      (64, 198, 6, "Mul", True), (48, 100, 4, "Mul", False),
+                                                      (40, 128, 4, "Div", True), (33, 208, 4, "Mul", False),
+                                                      (37, 65, 4, "Mul", True), (44, 129, 4, "Mul", False)])
+def test_attention_fed_by_tma_from_the_projection_gemm(cuda_lib, B, T, H, scale_op, out_proj):
+    """The projection GEMM writes [B, T, 3D] as fp16 halves on the fixed scale and the attention
+    kernel takes Q, K and V from there by TMA (no fp32 copy of the projection exists): checked
+    against the oracle, and against the same session with that path switched off."""
+    from altius_b200.session import CudaSessionBuilder
+    D = 64 * H
+    m = _projection_attention_model(B, T, H, scale_op, with_out_proj=out_proj)
+    x = np.random.default_rng(T).standard_normal((B, T, D)).astype(np.float32)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        kinds = [e["kind"] for e in sess.schedule() if e["kind"] != "act_f16_split"]
+        assert kinds[:2] == ["gemm_f16x3_pair_tcgen05", "attention_tma_tcgen05"], kinds
+        got = sess.run([x])[0]
+    finally:
+        sess.close()
+    want = run_oracle(m, [x], sgemm="openblas")[0]
+    assert np.isfinite(got).all()
+    assert (np.abs(got - want) <= _split_chain_bound(want, 0.3)).all(), float(np.abs(got - want).max())
+    os.environ["ALTIUS_CUDA_NO_ATTENTION_TMA"] = "1"
+    try:
+        sess = CudaSessionBuilder(m).build()
+        try:
+            assert "attention_tcgen05" in [e["kind"] for e in sess.schedule()]
+            other = sess.run([x])[0]
+        finally:
+            sess.close()
+    finally:
+        del os.environ["ALTIUS_CUDA_NO_ATTENTION_TMA"]
+    assert (np.abs(got - other) <= _split_chain_bound(want, 0.3)).all()
+
+
+@pytest.mark.parametrize("case", ["beyond_the_fixed_scale", "all_tiny"])
+def test_attention_fed_by_tma_falls_back_when_the_projection_leaves_its_range(cuda_lib, case):
+    """The fixed scale holds |x| <= 255 with full precision down to 2^-11: a projection beyond
+    that (or one whose elements are all tiny) is reported by the GEMM that writes it, and the run
+    is repeated on the 3xTF32 plan."""
+    B, T, H = 32, 197, 4
+    m = _projection_attention_model(B, T, H, w_scale=40.0 if case == "beyond_the_fixed_scale" else 1e-7,
+                                    with_out_proj=False)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((B, T, 64 * H)).astype(np.float32)
+    if case == "all_tiny":
+        for i in list(m.graph.inits):
+            if m.graph.inits[i].shape == (3 * 64 * H,):
+                m.graph.inits[i] = (1e-6 * m.graph.inits[i]).astype(np.float32)     # the bias too
+    got = run_cuda(m, [x])[0]
+    want = run_oracle(m, [x], sgemm="openblas")[0]
+    assert np.isfinite(got).all()
+    np.testing.assert_allclose(got, want, rtol=2e-4, atol=2e-4 * np.abs(want).max())
+
+
 # ---- Resize / Expand (the interpreter's restricted patterns, session.rs:299-323, 1057-1132) ----
 @pytest.mark.parametrize("mode", ["nearest", "linear"])
 @pytest.mark.parametrize("ishape,oshape", [((2, 3, 7, 7), (2, 3, 14, 14)), ((1, 5, 16, 16), (1, 5, 8, 8)),
@@ -873,15 +960,15 @@ def test_gemm_error_on_the_models_shapes_is_measured(cuda_lib, m, k, n, record_p
     assert (np.abs(got - sg) <= 1e-5 * np.abs(sg) + 5e-6 * (np.abs(a) @ np.abs(w))).all()
 
 
-def test_tensor_memory_accumulation_bias_is_what_the_documentation_says(cuda_lib):
-    """All-positive operands, K = 3072: every partial sum is truncated the same way, so the
-    result comes out low. 1e-5 relative is not met in this worst case; the measured figure is
-    pinned between 1e-5 and 6e-5."""
-    a = RNG.random((512, 3072)).astype(np.float32) + 0.5
-    w = (RNG.random((3072, 256)).astype(np.float32) + 0.5) * 0.02
+@pytest.mark.parametrize("gemm_mode", [0, 3])
+def test_tensor_memory_accumulation_bias_is_what_the_documentation_says(cuda_lib, gemm_mode):
+    """All-positive operands, K = 3072, the MLP-2 shape: every partial sum in tensor memory is
+    rounded the same way, so the result is biased. The measured figure is printed and bounded."""
+    a = RNG.random((6304, 3072)).astype(np.float32) + 0.5
+    w = (RNG.random((3072, 768)).astype(np.float32) + 0.5) * 0.02
     model = single_op_model("MatMul", [a], [w])
-    got = run_cuda(model, [a])[0].astype(np.float64)
-    truth = a.astype(np.float64) @ w.astype(np.float64)
+    got = run_cuda(model, [a], gemm_mode=gemm_mode)[0][:256].astype(np.float64)
+    truth = a[:256].astype(np.float64) @ w.astype(np.float64)
     rel = (got - truth) / truth
-    print("all-positive K=3072: mean relative error", rel.mean(), "max |.|", np.abs(rel).max())
-    assert rel.mean() < 0 and 1e-6 < np.abs(rel).max() < 6e-5
+    print("all-positive K=3072, gemm_mode", gemm_mode, ": mean relative error", rel.mean(), "max |.|", np.abs(rel).max())
+    assert np.abs(rel).max() < 6e-5
