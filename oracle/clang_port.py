@@ -550,8 +550,11 @@ class ClangPortSession:
             src = os.path.join(_CACHE, f"model_{tag}.c")
             with open(src, "w") as f:
                 f.write(text)
-            subprocess.check_call(["gcc", *CFLAGS, "-o", so + ".tmp", src, "-lm"])
-            os.replace(so + ".tmp", so)
+            try:
+                subprocess.check_call(["gcc", *CFLAGS, "-o", so + ".tmp", src, "-lm"])
+                os.replace(so + ".tmp", so)
+            finally:
+                os.remove(src)      # the index tables of the transposes make it tens of megabytes
         self._lib = ctypes.CDLL(so)
         self._lib.set_sgemm(ctypes.c_void_p(sgemm_addr))
         self._keep = []
