@@ -67,7 +67,7 @@ struct AttnTcDev {
   const float* q; const float* k; const float* v;
   long long row_stride, batch_stride;
   float* out; long long out_row_stride, out_batch_stride;   // out may be null when o16_hi / o16_lo are given
-  uint2* o16_hi; uint2* o16_lo;   // the result split into fp16 hi / lo halves (same strides, in elements), or null
+  uint2* o16_hi; uint2* o16_lo;   // the result as fp16 halves on the fixed scale (f16_split_fixed; same strides, in elements), or null
   int heads, tokens;
   const float* scale; int scale_mode;   // 0 none, 1 multiply, 2 divide
   int* err;
@@ -464,10 +464,10 @@ __global__ void __launch_bounds__(kAtLaunch, 1) attention_tc_kernel(AttnTcDev p)
           if (p.out) *reinterpret_cast<float4*>(p.out + o) = y;
           if (p.o16_hi) {   // for the projection GEMM that takes this result as its pre-split A
             uint2 hh, ll;
-            f16_split(y, hh, ll);
+            f16_split_fixed(y, hh, ll);
             p.o16_hi[o >> 2] = hh;
             p.o16_lo[o >> 2] = ll;
-            seen_out |= split_seen(y);
+            seen_out |= split_seen_fixed(y);
           }
         }
       }

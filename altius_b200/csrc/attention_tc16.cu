@@ -55,7 +55,7 @@ constexpr uint32_t kS1Col = 224, kOCol = 448, kTmemCols = 512;
 
 struct Attn16Dev {
   float* out; long long out_row_stride, out_batch_stride;   // may be null when o16_hi / o16_lo are given
-  uint2* o16_hi; uint2* o16_lo;   // the result as fp16 hi / lo halves (f16_split), or null
+  uint2* o16_hi; uint2* o16_lo;   // the result as fp16 hi / lo halves on the fixed scale (f16_split_fixed), or null
   int heads, tokens, units;
   int q_col, k_col, v_col;        // first column of each operand in the [B, T, C] arrays
   const float* scale; int scale_mode;   // 0 none, 1 multiply, 2 divide
@@ -400,12 +400,12 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
           }
           if (p.o16_hi) {   // for the projection GEMM that takes this result as its pre-split A
             uint2 h0, l0, h1, l1;
-            f16_split(y0, h0, l0);
-            f16_split(y1, h1, l1);
+            f16_split_fixed(y0, h0, l0);
+            f16_split_fixed(y1, h1, l1);
             const long long o4 = (ob + 8 * j) >> 2;      // uint2 index; even: 16-byte aligned
             *reinterpret_cast<uint4*>(p.o16_hi + o4) = make_uint4(h0.x, h0.y, h1.x, h1.y);
             *reinterpret_cast<uint4*>(p.o16_lo + o4) = make_uint4(l0.x, l0.y, l1.x, l1.y);
-            seen_out |= split_seen(y0) | split_seen(y1);
+            seen_out |= split_seen_fixed(y0) | split_seen_fixed(y1);
           }
         }
       }

@@ -86,6 +86,7 @@ struct TcEpilogue {
   uint2* c16_hi; uint2* c16_lo; long long ldc16;   // result as fp16 hi / lo halves (4 per uint2; ldc16 in halves), or null
   int c16_fixed;            // the halves on the fixed scale (f16_split_fixed) instead of f16_split
   const float* acc_scale;   // device scalar the accumulators are multiplied by (B was scaled by its inverse), or null
+  float acc_scale_const;    // times this power of two (the inverse of the fixed scale of a pre-split A; else 1)
   const float* b_row_scale; long long b_row_scale_stride; int k_total;   // [K, N] operand: row k of B[bz] is multiplied by
                                                                        // b_row_scale[bz * stride + k] while it is split, or null
   int* err;                 // error word: range of the split output
@@ -136,9 +137,13 @@ __device__ __forceinline__ void load_acc(uint32_t taddr, uint32_t (&v)[32], floa
       v[j] = __float_as_uint(__fmul_rn(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])), sc));
   } else {
     tc_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__fmul_rn(__uint_as_float(v[j]), sc));   // sc is a power of two
   }
 }
-__device__ __forceinline__ float acc_scale_of(const TcEpilogue& ep) { return ep.acc_scale ? __ldg(ep.acc_scale) : 1.f; }
+__device__ __forceinline__ float acc_scale_of(const TcEpilogue& ep) {
+  return ep.acc_scale ? __fmul_rn(__ldg(ep.acc_scale), ep.acc_scale_const) : ep.acc_scale_const;
+}
 
 // Epilogue of one warp's 32 rows. The accumulator chunk arrives with one thread
 // per row (32 columns each); it goes through a 4 KB shared-memory tile so that
@@ -323,49 +328,20 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
   return released;
 }
 
-// The epilogue of the pair kernel that takes A pre-split: sixteen warps, a warp per tensor-memory
-// lane quarter and (NCH * 32)-column group, each with a shared-memory buffer for its whole
-// 32 x (NCH * 32) part of the result. Phase 1 copies that part out of tensor memory (the two
-// accumulators of a 32-column chunk are fetched with one wait, combined and scaled, and written
-// a row per lane) and hands tensor memory back to the MMA warp. Phase 2 -- bias, activation,
-// residual, the stores, the fp16 split for a consuming GEMM -- then runs under the next
-// tile's MMAs, reading the buffer four lanes per row (64 contiguous bytes of a row per
-// instruction and row). The 16-byte slots of a row are XOR-swizzled by the row so that both
-// the row-per-lane writes and the four-lanes-per-row reads are free of bank conflicts.
-__device__ __forceinline__ int epi_slot(int row, int j) { return j ^ (((row & 1) << 2) | ((row >> 1) & 3)); }
-
+// The epilogue of the pair kernel that takes A pre-split: sixteen warps with 2 KB of staging
+// each; a warp owns 32 rows x (NCH * 32) columns. Tensor memory goes back to the MMA warp as
+// soon as the warp's last chunk has left it. A chunk passes through the staging tile in halves
+// of 16 columns (four lanes then own one row's 64 contiguous bytes, eight rows per
+// instruction). 16-byte slots are XOR-swizzled by bits 1-2 of the row: writes (a lane per row)
+// and reads (four lanes per row) are both free of bank conflicts.
 template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
-__device__ __forceinline__ bool epilogue_buffered(const TcEpilogue& ep, float4* buf, uint32_t tmem_base, int q,
-                                                  int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
-                                                  Release&& release) {
-  constexpr int kRowVec = NCH * 8;                  // float4 slots per buffered row
+__device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stage, uint32_t tmem_base, int q,
+                                              int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
+                                              Release&& release) {
+  bool released = false;
   const float sc = acc_scale_of(ep);
   float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
-  __syncwarp();                                     // the previous tile's reads of the buffer are over
-#pragma unroll 1
-  for (int ci = 0; ci < NCH; ++ci) {
-    if (n0 + (cc0 + ci) * 32 >= ep.n) break;        // uniform across the warp
-    uint32_t v[32];
-    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32);
-    tc_ld_32x32_nowait(taddr, v);
-    if (D2OFF != 0) {
-      uint32_t w[32];
-      tc_ld_32x32_nowait(taddr + (uint32_t)D2OFF, w);
-      tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        v[j] = __float_as_uint(__fmul_rn(fmaf(__uint_as_float(w[j]), kLoUnscale, __uint_as_float(v[j])), sc));
-    } else {
-      tc_wait_ld();
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      buf[lane * kRowVec + epi_slot(lane, ci * 8 + j)] =
-          make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                      __uint_as_float(v[4 * j + 3]));
-  }
-  const bool released = release();                  // includes a __syncwarp: the buffer is written
   const int c4 = lane & 3, rsub = lane >> 2;
   const int row_base = m0 + q * 32 + rsub;
   float bm[4];
@@ -374,58 +350,150 @@ __device__ __forceinline__ bool epilogue_buffered(const TcEpilogue& ep, float4* 
     for (int i = 0; i < 4; ++i) bm[i] = row_base + 8 * i < ep.m ? __ldg(ep.bias_m + row_base + 8 * i) : 0.f;
   }
 #pragma unroll 1
-  for (int hh = 0; hh < 2 * NCH; ++hh) {            // halves of 16 columns
-    const int col = n0 + cc0 * 32 + 16 * hh + 4 * c4;
-    if (n0 + cc0 * 32 + 16 * hh >= ep.n) break;     // uniform across the warp
-    const bool col_ok = col < ep.n;                 // n % 4 == 0: the whole float4 is in range
-    float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
-    float4 a[4], r[4];
+  for (int ci = 0; ci < NCH; ++ci) {
+    const int col0 = n0 + (cc0 + ci) * 32;
+    if (col0 >= ep.n) break;                       // uniform across the warp
+    uint32_t v[32];
+    load_acc<D2OFF>(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32), v, sc);
+    if (ci + 1 == NCH || col0 + 32 >= ep.n) released = release();
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int rl = 8 * i + rsub;
-      a[i] = buf[rl * kRowVec + epi_slot(rl, 4 * hh + c4)];
-      if (HAS_RES) {
+    for (int h = 0; h < 2; ++h) {
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        stage[lane * 4 + (j ^ ((lane >> 1) & 3))] =
+            make_float4(__uint_as_float(v[16 * h + 4 * j]), __uint_as_float(v[16 * h + 4 * j + 1]),
+                        __uint_as_float(v[16 * h + 4 * j + 2]), __uint_as_float(v[16 * h + 4 * j + 3]));
+      __syncwarp();
+      const int col = col0 + 16 * h + 4 * c4;
+      const bool col_ok = col < ep.n;   // n % 4 == 0: the whole float4 is in range
+      float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+      float4 a[4], r[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rl = 8 * i + rsub;
+        a[i] = stage[rl * 4 + (c4 ^ ((rl >> 1) & 3))];
+        if (HAS_RES) {
+          const int row = row_base + 8 * i;
+          r[i] = (col_ok && row < ep.m)
+                     ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
+                     : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 x = a[i];
+        if (BIAS == 1) {
+          x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
+          x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
+        }
+        if (BIAS == 2) {
+          x.x = __fadd_rn(x.x, bm[i]); x.y = __fadd_rn(x.y, bm[i]);
+          x.z = __fadd_rn(x.z, bm[i]); x.w = __fadd_rn(x.w, bm[i]);
+        }
+        if (ACT == ACT_GELU) {
+          const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
+          x = make_float4(lo.x, lo.y, hi.x, hi.y);
+        } else if (ACT != ACT_NONE) {
+          const float al = ep.act_alpha, be = ep.act_beta;
+          x.x = apply_act(ACT, x.x, al, be); x.y = apply_act(ACT, x.y, al, be);
+          x.z = apply_act(ACT, x.z, al, be); x.w = apply_act(ACT, x.w, al, be);
+        }
+        if (HAS_RES) {
+          x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
+          x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
+        }
         const int row = row_base + 8 * i;
-        r[i] = (col_ok && row < ep.m)
-                   ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
-                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (col_ok && row < ep.m) {
+          if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
+          if (ep.c16_hi) {   // the kernel that consumes this result takes it split (batch 1)
+            uint2 h, l;
+            if (ep.c16_fixed) { f16_split_fixed(x, h, l); seen |= split_seen_fixed(x); }
+            else { f16_split(x, h, l); seen |= split_seen(x); }
+            const long long o = ((long long)row * ep.ldc16 + col) >> 2;
+            ep.c16_hi[o] = h;
+            ep.c16_lo[o] = l;
+          }
+        }
       }
     }
+  }
+  return released;
+}
+
+// The same epilogue without shared memory: a thread keeps its row's 32 columns of a chunk in
+// registers from tensor memory to the stores (128 contiguous bytes of fp32 per thread, or 64 of
+// each fp16 half). Stores are 16 bytes per lane on 32 different rows, which L2 merges into full
+// lines; in exchange the epilogue adds nothing to the shared-memory traffic of the operand
+// tiles (TMA writes and the tensor core's reads), which is what it competes with when it runs
+// under the next tile's MMAs.
+template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
+__device__ __forceinline__ bool epilogue_direct(const TcEpilogue& ep, uint32_t tmem_base, int q, int lane, int m0,
+                                                int n0, int bz, int cc0, unsigned& seen, Release&& release) {
+  static_assert(BIAS != 2, "per-row bias: the staged epilogues");
+  bool released = false;
+  const float sc = acc_scale_of(ep);
+  const int row = m0 + q * 32 + lane;
+  const bool row_ok = row < ep.m;
+  float* c = ep.c ? ep.c + (long long)bz * ep.sc + (long long)row * ep.ldc : nullptr;
+  const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres + (long long)row * ep.ldres : nullptr;
+#pragma unroll 1
+  for (int ci = 0; ci < NCH; ++ci) {
+    const int col0 = n0 + (cc0 + ci) * 32;
+    if (col0 >= ep.n) break;                       // uniform across the warp
+    uint32_t v[32];
+    load_acc<D2OFF>(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32), v, sc);
+    if (ci + 1 == NCH || col0 + 32 >= ep.n) released = release();
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float4 x = a[i];
+    for (int j = 0; j < 4; ++j) {                  // 8 columns at a time
+      const int col = col0 + 8 * j;
+      if (col >= ep.n) break;                      // n % 8 == 0 here: whole groups
+      float4 x0 = make_float4(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]), __uint_as_float(v[8 * j + 2]),
+                              __uint_as_float(v[8 * j + 3]));
+      float4 x1 = make_float4(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), __uint_as_float(v[8 * j + 6]),
+                              __uint_as_float(v[8 * j + 7]));
       if (BIAS == 1) {
-        x.x = __fadd_rn(x.x, bn.x); x.y = __fadd_rn(x.y, bn.y);
-        x.z = __fadd_rn(x.z, bn.z); x.w = __fadd_rn(x.w, bn.w);
-      }
-      if (BIAS == 2) {
-        x.x = __fadd_rn(x.x, bm[i]); x.y = __fadd_rn(x.y, bm[i]);
-        x.z = __fadd_rn(x.z, bm[i]); x.w = __fadd_rn(x.w, bm[i]);
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col + 4));
+        x0.x = __fadd_rn(x0.x, b0.x); x0.y = __fadd_rn(x0.y, b0.y); x0.z = __fadd_rn(x0.z, b0.z); x0.w = __fadd_rn(x0.w, b0.w);
+        x1.x = __fadd_rn(x1.x, b1.x); x1.y = __fadd_rn(x1.y, b1.y); x1.z = __fadd_rn(x1.z, b1.z); x1.w = __fadd_rn(x1.w, b1.w);
       }
       if (ACT == ACT_GELU) {
-        const float2 lo = gelu_ref2(make_float2(x.x, x.y)), hi = gelu_ref2(make_float2(x.z, x.w));
-        x = make_float4(lo.x, lo.y, hi.x, hi.y);
+        const float2 g0 = gelu_ref2(make_float2(x0.x, x0.y)), g1 = gelu_ref2(make_float2(x0.z, x0.w));
+        const float2 g2 = gelu_ref2(make_float2(x1.x, x1.y)), g3 = gelu_ref2(make_float2(x1.z, x1.w));
+        x0 = make_float4(g0.x, g0.y, g1.x, g1.y);
+        x1 = make_float4(g2.x, g2.y, g3.x, g3.y);
       } else if (ACT != ACT_NONE) {
         const float al = ep.act_alpha, be = ep.act_beta;
-        x.x = apply_act(ACT, x.x, al, be); x.y = apply_act(ACT, x.y, al, be);
-        x.z = apply_act(ACT, x.z, al, be); x.w = apply_act(ACT, x.w, al, be);
+        x0.x = apply_act(ACT, x0.x, al, be); x0.y = apply_act(ACT, x0.y, al, be);
+        x0.z = apply_act(ACT, x0.z, al, be); x0.w = apply_act(ACT, x0.w, al, be);
+        x1.x = apply_act(ACT, x1.x, al, be); x1.y = apply_act(ACT, x1.y, al, be);
+        x1.z = apply_act(ACT, x1.z, al, be); x1.w = apply_act(ACT, x1.w, al, be);
       }
+      if (!row_ok) continue;
       if (HAS_RES) {
-        x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
-        x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
+        const float4 r0 = __ldg(reinterpret_cast<const float4*>(res + col));
+        const float4 r1 = __ldg(reinterpret_cast<const float4*>(res + col + 4));
+        x0.x = __fadd_rn(x0.x, r0.x); x0.y = __fadd_rn(x0.y, r0.y); x0.z = __fadd_rn(x0.z, r0.z); x0.w = __fadd_rn(x0.w, r0.w);
+        x1.x = __fadd_rn(x1.x, r1.x); x1.y = __fadd_rn(x1.y, r1.y); x1.z = __fadd_rn(x1.z, r1.z); x1.w = __fadd_rn(x1.w, r1.w);
       }
-      const int row = row_base + 8 * i;
-      if (col_ok && row < ep.m) {
-        if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
-        if (ep.c16_hi) {   // the GEMM that consumes this result takes it split (batch 1)
-          uint2 h, l;
-          if (ep.c16_fixed) { f16_split_fixed(x, h, l); seen |= split_seen_fixed(x); }
-          else { f16_split(x, h, l); seen |= split_seen(x); }
-          const long long o = ((long long)row * ep.ldc16 + col) >> 2;
-          ep.c16_hi[o] = h;
-          ep.c16_lo[o] = l;
+      if (c) {
+        *reinterpret_cast<float4*>(c + col) = x0;
+        *reinterpret_cast<float4*>(c + col + 4) = x1;
+      }
+      if (ep.c16_hi) {   // the kernel that consumes this result takes it split (batch 1)
+        uint2 h0, l0, h1, l1;
+        if (ep.c16_fixed) {
+          f16_split_fixed(x0, h0, l0); f16_split_fixed(x1, h1, l1);
+          seen |= split_seen_fixed(x0) | split_seen_fixed(x1);
+        } else {
+          f16_split(x0, h0, l0); f16_split(x1, h1, l1);
+          seen |= split_seen(x0) | split_seen(x1);
         }
+        const long long o = ((long long)row * ep.ldc16 + col) >> 2;   // uint2 index, even: 16-byte aligned
+        *reinterpret_cast<uint4*>(ep.c16_hi + o) = make_uint4(h0.x, h0.y, h1.x, h1.y);
+        *reinterpret_cast<uint4*>(ep.c16_lo + o) = make_uint4(l0.x, l0.y, l1.x, l1.y);
       }
     }
   }
@@ -958,14 +1026,15 @@ struct PairSmem {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   // TMA brings B only (A goes global -> registers -> tiles), or everything (PRE)
   static constexpr int kTxBytes = 2 * kBBytes + (PRE ? 2 * kABytes : 0);
-  // PRE: sixteen epilogue warps with a buffer each for their whole 32 x (BN / 4) part of the
-  // accumulators (tensor memory is handed back as soon as it has been copied there, and the
-  // epilogue proper runs under the next tile's MMAs), which leaves room for three stages; the
-  // main loop is bound by the MMAs, not by the feed, and three stages (96 KB in flight) keep it so.
-  static constexpr int kEpiBytes = PRE ? 16 * 32 * (BN / 4) * 4 : kEpiWarps * 4096;
-  static constexpr int kStages = PRE ? 3 : (200 * 1024) / kStageBytes;   // 6 at BN 256 without PRE
+  // 32 KB of epilogue staging: 2 KB for each of the sixteen warps of the common epilogues (PRE),
+  // or 4 KB for each of the eight warps of the general ones.
+  static constexpr int kEpiBytes = kEpiWarps * 4096;
+  static constexpr int kStages = ((227 - 32) * 1024 - 1536) / kStageBytes;   // 6 at BN 256
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
-  static constexpr int kTmemCols = 2 * BN;              // D1 and D2, one accumulator set
+  // Without PRE: D1 and D2, one accumulator set. PRE: the operands are on fixed scales, the three
+  // partial products share ONE accumulator, and two sets alternate between consecutive tiles, so
+  // that a tile's epilogue runs under the next tile's MMAs.
+  static constexpr int kTmemCols = 2 * BN;
   static_assert(kDynBytes <= 227 * 1024, "shared memory per CTA");
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "tensor memory");
 };
@@ -987,7 +1056,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   using L = PairSmem<BN, PRE>;
   const int S = (dbg >> 8) > 0 && (dbg >> 8) < L::kStages ? (dbg >> 8) : L::kStages;   // experiment: fewer stages
   constexpr int KB = L::kKb;
-  constexpr int D2 = BN;                 // column offset of the cross-term accumulator
+  constexpr int D2 = PRE ? 0 : BN;       // column offset of the cross-term accumulator (none with PRE)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int SM = L::kStages;
@@ -996,9 +1065,9 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   uint64_t* full = bars;                 // this CTA's TMA bytes landed
   uint64_t* ready = bars + SM;            // leader's: both CTAs' fp16 tiles written (2 x 4 warps arrive)
   uint64_t* empty = bars + 2 * SM;        // this CTA's: the pair's MMAs that read the stage have completed
-  uint64_t* acc_full = bars + 3 * SM;     // this CTA's: accumulators complete
-  uint64_t* acc_empty = bars + 3 * SM + 1;   // leader's: drained by the 8 epilogue warps of the pair
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * SM + 2);
+  uint64_t* acc_full = bars + 3 * SM;     // [2] this CTA's: accumulator set complete (PRE uses both sets)
+  uint64_t* acc_empty = bars + 3 * SM + 2;   // [2] leader's: set drained by the epilogue warps of the pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * SM + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1019,8 +1088,10 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       mbar_init(&ready[s], PRE ? 2 : 2 * (kSplitThreads / 32));
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 2 * (PRE ? 16 : kEpiWarps)); // one arrival per epilogue warp of the pair
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 2 * (PRE ? 16 : kEpiWarps));   // one arrival per epilogue warp of the pair
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -1064,14 +1135,15 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     if (leader && lane == 0) {
       // fp32 accumulators, fp16 A and B (format 0), both K-major, N = BN, M = 256 over the pair.
       const uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-      const uint32_t acc_full_peer = map_to_cta(acc_full, 1);
       int it = 0, ti = 0;
       bool ok = true;
       TcWork wk;
       for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w, ++ti) {
-        // The eight epilogue warps must have drained the accumulators of the previous tile.
-        if (!mbar_wait(acc_empty, (ti & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
+        // The epilogue warps must have drained this accumulator set (PRE: the tile before last).
+        const int set = PRE ? (ti & 1) : 0, use = PRE ? (ti >> 1) : ti;
+        if (!mbar_wait(&acc_empty[set], (use & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
         tc_fence_after();
+        const uint32_t d1 = tmem_base + (uint32_t)(set * BN);
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -1081,45 +1153,33 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           tc_fence_after();
           const uint64_t da = make_smem_desc(smem_u32(a_raw(s))), dal = make_smem_desc(smem_u32(a_lo(s)));
           const uint64_t db = make_smem_desc(smem_u32(b_hi(s))), dbl = make_smem_desc(smem_u32(b_lo(s)));
-          if (!(dbg & 256)) {   // one accumulator after the other within a stage: alternating between them
-                                // with every MMA cost 30 % of the tensor pipe's rate (dbg bit 256: the old order)
+          if (PRE) {
+            // Operands on fixed scales: the cross terms go into the same accumulator.
+#pragma unroll
+            for (int kk = 0; kk < KB / 16; ++kk) {          // K-steps of 16 halves (32 bytes of a row)
+              const uint64_t off = (uint64_t)(kk * 2);
+              tc_mma_f16_pair(d1, dal + off, db + off, idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);   // a_lo * b_hi
+              tc_mma_f16_pair(d1, da + off, dbl + off, idesc, 1u);                                  // a_hi * b_lo
+              tc_mma_f16_pair(d1, da + off, db + off, idesc, 1u);                                   // a_hi * b_hi
+            }
+          } else {
+            // One accumulator after the other within a stage: alternating between them with every
+            // MMA cost 30 % of the tensor pipe's rate.
 #pragma unroll
             for (int kk = 0; kk < KB / 16; ++kk)
-              tc_mma_f16_pair(tmem_base, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16_pair(d1, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
 #pragma unroll
             for (int kk = 0; kk < KB / 16; ++kk) {
-              tc_mma_f16_pair(tmem_base + D2, dal + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
-              tc_mma_f16_pair(tmem_base + D2, da + (uint64_t)(kk * 2), dbl + (uint64_t)(kk * 2), idesc, 1u);
+              tc_mma_f16_pair(d1 + D2, dal + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);
+              tc_mma_f16_pair(d1 + D2, da + (uint64_t)(kk * 2), dbl + (uint64_t)(kk * 2), idesc, 1u);
             }
-          } else
-#pragma unroll
-          for (int kk = 0; kk < KB / 16; ++kk) {            // K-steps of 16 halves (32 bytes of a row)
-            const uint64_t off = (uint64_t)(kk * 32 >> 4);
-            const uint32_t acc = (kb > wk.k0 || kk > 0) ? 1u : 0u;
-            if (dbg & 1) continue;                                               // timing experiment: no MMAs
-            if (dbg & 32) { tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc); continue; }
-            if (dbg & 64) {
-              tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);
-              tc_mma_f16_pair(tmem_base, dal + off, db + off, idesc, 1u);
-              tc_mma_f16_pair(tmem_base, da + off, dbl + off, idesc, 1u);
-              continue;
-            }
-            if (dbg & 128) {
-              tc_mma_f16_pair(tmem_base + D2, dal + off, db + off, idesc, acc);
-              tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);
-              tc_mma_f16_pair(tmem_base + D2, da + off, dbl + off, idesc, 1u);
-              continue;
-            }
-            tc_mma_f16_pair(tmem_base, da + off, db + off, idesc, acc);          // a_hi * b_hi
-            tc_mma_f16_pair(tmem_base + D2, dal + off, db + off, idesc, acc);    // a_lo' * b_hi
-            tc_mma_f16_pair(tmem_base + D2, da + off, dbl + off, idesc, 1u);     // a_hi * b_lo'
           }
           tc_commit_pair(smem_u32(&empty[s]));      // the stage is free again in this CTA ...
           tc_commit_pair(map_to_cta(&empty[s], 1)); // ... and in the peer
         }
         if (ok) {
-          tc_commit_pair(smem_u32(acc_full));
-          tc_commit_pair(acc_full_peer);
+          tc_commit_pair(smem_u32(&acc_full[set]));
+          tc_commit_pair(map_to_cta(&acc_full[set], 1));
         }
         if (ti < 5) pair_stamp(dbg, 3 + ti);   // all MMAs of tile ti issued
       }
@@ -1195,17 +1255,14 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   } else if (!PRE || warp < 16) {
     // ---------------- epilogue (each CTA its own 128 rows) ----------------
     // PRE: warps 0-15, a warp per lane quarter and quarter of the columns on the common
-    // epilogues; the general and the K-slice epilogues are left to warps 8-15 (half of the
-    // columns each), the others only hand the accumulator back.
+    // epilogues (2 KB of staging each); the general and the K-slice epilogues are left to warps
+    // 8-15 with 4 KB each (the same 32 KB), the others only hand the accumulator back.
     const int e = PRE ? warp : warp - kSplitWarps, q = e & 3;
     const int eo = PRE ? e - 8 : e;                                // index among the eight "old" warps
     const int cc0 = (eo >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // their 32-column chunks
     const int hc0 = (e >> 2) * (BN / 128);                        // PRE, common epilogues: 64 columns from chunk hc0
-    // PRE: a buffer of 32 rows x BN / 4 floats per warp; the general and the K-slice epilogues
-    // (warps 8-15) use the first 4 KB of theirs as the staging tile.
-    float4* buf = reinterpret_cast<float4*>(epi_smem + (PRE ? e * (32 * (BN / 4) * 4) : 0));
-    float4* stage = PRE ? buf : reinterpret_cast<float4*>(epi_smem + e * 4096);
-    const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
+    float4* stage = reinterpret_cast<float4*>(epi_smem + (eo < 0 ? 0 : eo) * 4096);
+    float4* stage_h = reinterpret_cast<float4*>(epi_smem + e * 2048);
     const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !(ep.bias_m && ep.bias_n) &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
                         ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
@@ -1215,11 +1272,16 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     const int key = !simple ? -1 : ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2) | (ep.bias_m ? 64 : 0));
     int ti = 0;
     unsigned seen_out = 0;   // what this warp has seen of the results it wrote split (ep.c16_hi)
+    bool mixed = false;      // the previous tile used the staging memory in the other partition
+    bool dead = false;       // a wait of this warp has expired
     TcWork wk;
     for (int w = 0; pair_get_work(sc, w, &wk); ++w, ++ti) {
       const int t = wk.tile;
       const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
       const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
+      const int set = PRE ? (ti & 1) : 0, use = PRE ? (ti >> 1) : ti;
+      const uint32_t acc = tmem_base + (uint32_t)(set * BN);
+      const uint32_t acc_empty_leader = map_to_cta(&acc_empty[set], 0);
       if (PRE && ep.res && key >= 0 && wk.raw < 0) {
         // While the tile's MMAs run: pull this warp's 32 x 64 block of the residual into L2.
         const float* rp = ep.res + (long long)bz * ep.sres;
@@ -1230,7 +1292,15 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
             asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + (long long)row * ep.ldres + col));
         }
       }
-      if (!mbar_wait(acc_full, ti & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
+      // The K-slice and general epilogues use the staging memory in 4 KB pieces that overlap
+      // the 2 KB pieces of the common one: nobody may still be in a tile of the other kind. (A
+      // warp whose wait has expired keeps walking the tiles for these barriers alone, so that
+      // nobody is left waiting at one.)
+      const bool wide = wk.raw >= 0 || key < 0 || (key & 64);
+      if (PRE && (wide || mixed)) asm volatile("bar.sync 2, 512;" ::: "memory");
+      mixed = wide;
+      if (dead) continue;
+      if (!mbar_wait(&acc_full[set], use & 1)) { atomicExch(err, 4); *abort_flag = 1; dead = true; continue; }
       tc_fence_after();
       if (e == 0 && lane == 0 && ti < 3) pair_stamp(dbg, 8 + 2 * ti);     // accumulator of tile ti complete
       bool released = false;
@@ -1240,34 +1310,46 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         return true;
       };
-      if (PRE && m0 < ep.m && wk.raw < 0) {
+      if (PRE && m0 < ep.m && !wide && (ep.dbg & 512) == 0 && (ep.n % 8) == 0) {
         switch (key) {
-          case 0: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 0, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 1: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 1, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 2: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 0, true>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 3: released = epilogue_buffered<BN / 128, D2, ACT_NONE, 1, true>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_buffered<BN / 128, D2, ACT_GELU, 1, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_buffered<BN / 128, D2, ACT_RELU, 1, false>(ep, buf, tmem_base, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 0: released = epilogue_direct<BN / 128, D2, ACT_NONE, 0, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 1: released = epilogue_direct<BN / 128, D2, ACT_NONE, 1, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 2: released = epilogue_direct<BN / 128, D2, ACT_NONE, 0, true>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 3: released = epilogue_direct<BN / 128, D2, ACT_NONE, 1, true>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_direct<BN / 128, D2, ACT_GELU, 1, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_direct<BN / 128, D2, ACT_RELU, 1, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
           default:
-            if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1);
+            if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1);
+            break;
+        }
+      } else if (PRE && m0 < ep.m && !wide) {
+        switch (key) {
+          case 0: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 1: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 2: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, true>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 3: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, true>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_GELU, 1, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_RELU, 1, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          default:
+            if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1);
             break;
         }
       } else if (m0 < ep.m && eo >= 0) {
         if (wk.raw >= 0) {
-          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, tmem_base, q, lane, cc0, cc1, acc_scale_of(ep));
+          epilogue_raw<BN, D2>(workspace + ((size_t)wk.raw * 2 + rank) * BM * BN, stage, acc, q, lane, cc0, cc1, acc_scale_of(ep));
         } else
         switch (key) {
-          case 0: released = epilogue_fast<BN, D2, ACT_NONE, 0, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 1: released = epilogue_fast<BN, D2, ACT_NONE, 1, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 2: released = epilogue_fast<BN, D2, ACT_NONE, 0, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 3: released = epilogue_fast<BN, D2, ACT_NONE, 1, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, 1, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, 1, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 64: released = epilogue_fast<BN, D2, ACT_NONE, 2, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          case 64 | 2: released = epilogue_fast<BN, D2, ACT_NONE, 2, true>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case 64 | (ACT_RELU << 2): released = epilogue_fast<BN, D2, ACT_RELU, 2, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-        case 64 | (ACT_HARDSWISH << 2): released = epilogue_fast<BN, D2, ACT_HARDSWISH, 2, false>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1, release); break;
-          default: epilogue_generic<BN, D2>(ep, stage, tmem_base, q, lane, m0, n0, bz, cc0, cc1); break;
+          case 0: released = epilogue_fast<BN, D2, ACT_NONE, 0, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 1: released = epilogue_fast<BN, D2, ACT_NONE, 1, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 2: released = epilogue_fast<BN, D2, ACT_NONE, 0, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 3: released = epilogue_fast<BN, D2, ACT_NONE, 1, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_GELU, 1, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_fast<BN, D2, ACT_RELU, 1, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 64: released = epilogue_fast<BN, D2, ACT_NONE, 2, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 64 | 2: released = epilogue_fast<BN, D2, ACT_NONE, 2, true>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 64 | (ACT_RELU << 2): released = epilogue_fast<BN, D2, ACT_RELU, 2, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          case 64 | (ACT_HARDSWISH << 2): released = epilogue_fast<BN, D2, ACT_HARDSWISH, 2, false>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1, release); break;
+          default: epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1); break;
         }
       }
       if (!released) release();
@@ -1329,18 +1411,22 @@ __device__ __forceinline__ float weight_scale(unsigned absmax_bits) {
 // fp16 hi / lo split of a constant [rows, k] operand (row stride ld) into [rows, k8]
 // halves, columns k .. k8-1 zero. With `absmax` the operand is first scaled by weight_scale
 // (and *inv_scale receives the inverse). An element beyond fp16 leaves kRangeCode in *err.
+// `plain`: lo = rn(v - hi) on the scale of hi (the operands of the single-accumulator kernel: a
+// constant scaled to [2^13, 2^14), an activation on the fixed scale 2^8) instead of
+// rn((v - hi) * 2^11).
 __global__ void f16_split_kernel(const float* __restrict__ x, __half* __restrict__ hi, __half* __restrict__ lo,
                                  int64_t rows, int64_t k, int64_t ld, int64_t k8, int* err,
-                                 const unsigned* __restrict__ absmax, float* inv_scale) {
+                                 const unsigned* __restrict__ absmax, float* inv_scale, int plain) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const float sc = absmax ? weight_scale(*absmax) : 1.f;
+  const float sc = absmax ? weight_scale(*absmax) : (plain ? kFixedScale : 1.f);
   if (i == 0 && inv_scale) *inv_scale = __fdiv_rn(1.f, sc);
   if (i >= rows * k8) return;
   const int64_t r = i / k8, c = i % k8;
   const float v = c < k ? __fmul_rn(__ldg(x + r * ld + c), sc) : 0.f;
   const __half h = __float2half_rn(v);
   hi[i] = h;
-  lo[i] = __float2half_rn(__fmul_rn(__fsub_rn(v, __half2float(h)), kLoScale));
+  const float rest = __fsub_rn(v, __half2float(h));
+  lo[i] = __float2half_rn(plain ? rest : __fmul_rn(rest, kLoScale));
   if (beyond_half(v)) atomicCAS(err, 0, kRangeCode);
 }
 
@@ -1348,7 +1434,7 @@ __global__ void f16_split_kernel(const float* __restrict__ x, __half* __restrict
 // eight elements per thread (two 16-byte loads, one 16-byte store to each of hi and lo).
 __global__ void __launch_bounds__(256) f16_split_vec8_kernel(const float* __restrict__ x, uint4* __restrict__ hi,
                                                              uint4* __restrict__ lo, int64_t rows, int64_t k8th,
-                                                             int64_t ld, int* err) {
+                                                             int64_t ld, int* err, int fixed) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   unsigned seen = 0;
   if (i < rows * k8th) {
@@ -1356,11 +1442,17 @@ __global__ void __launch_bounds__(256) f16_split_vec8_kernel(const float* __rest
     const float4* src = reinterpret_cast<const float4*>(x + r * ld + c * 8);
     const float4 v0 = __ldg(src), v1 = __ldg(src + 1);
     uint2 h0, l0, h1, l1;
-    f16_split(v0, h0, l0);
-    f16_split(v1, h1, l1);
+    if (fixed) {
+      f16_split_fixed(v0, h0, l0);
+      f16_split_fixed(v1, h1, l1);
+      seen = split_seen_fixed(v0) | split_seen_fixed(v1);
+    } else {
+      f16_split(v0, h0, l0);
+      f16_split(v1, h1, l1);
+      seen = split_seen(v0) | split_seen(v1);
+    }
     hi[i] = make_uint4(h0.x, h0.y, h1.x, h1.y);
     lo[i] = make_uint4(l0.x, l0.y, l1.x, l1.y);
-    seen = split_seen(v0) | split_seen(v1);
   }
   // The block's 2048 elements: out of range, or non-zero values that are all tiny.
   const int over = __syncthreads_or(seen & 1u), big = __syncthreads_or(seen & 2u), tiny = __syncthreads_or(seen & 4u);
@@ -1639,6 +1731,8 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
     if (b_batched || (q.ldb16 % 8) != 0) return cudaErrorInvalidValue;
     // A pair's CTAs each load their own 128 rows of A and half of the B tile.
     const int a_rows = sh.pair ? BM : sh.mt * BM, b_rows = sh.pair ? bn / 2 : bn;
+    if (pre && (!sh.pair || !q.a16_fixed || !q.b16_plain)) return cudaErrorInvalidValue;   // the single-accumulator kernel's formats
+    if (!pre && q.b16_plain) return cudaErrorInvalidValue;
     if (sh.pair && pre) {
       if ((q.lda16 % 8) != 0) return cudaErrorInvalidValue;
       if (!make_map(&ma, q.a16_hi, 2, q.k, q.m, 1, q.lda16, 0, BK16, BM, 64)) return cudaErrorInvalidValue;
@@ -1677,6 +1771,7 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
   ep.c16_hi = static_cast<uint2*>(q.c16_hi); ep.c16_lo = static_cast<uint2*>(q.c16_lo); ep.ldc16 = q.ldc16;
   ep.c16_fixed = q.c16_fixed;
   ep.acc_scale = kmode == TC_F16X3 ? q.b16_inv_scale : nullptr;
+  ep.acc_scale_const = (kmode == TC_F16X3 && pre) ? kFixedUnscale : 1.f;   // A arrives on the fixed scale
   ep.b_row_scale = q.b_row_scale; ep.b_row_scale_stride = q.b_row_scale_stride; ep.k_total = (int)q.k;
   if (q.b_row_scale && kmode != TC_3X_SPLIT_B_MN) return cudaErrorInvalidValue;   // exists for the [K, N] operand only
   ep.err = err_word;
@@ -1717,7 +1812,7 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
 }
 
 cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, int64_t k, int64_t ld, int64_t k8,
-                             int* err_word, float* inv_scale, unsigned* absmax_scratch, cudaStream_t st) {
+                             int* err_word, float* inv_scale, unsigned* absmax_scratch, int plain, cudaStream_t st) {
   const int64_t n = rows * k8;
   if (n == 0) return cudaSuccess;
   if (inv_scale) {   // a constant operand: scaled by a power of two first
@@ -1727,18 +1822,18 @@ cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, i
     const int64_t blocks = std::min<int64_t>((rows * k + 255) / 256, 1184);
     absmax_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, rows, k, ld, absmax_scratch);
     f16_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, static_cast<__half*>(hi), static_cast<__half*>(lo),
-                                                                 rows, k, ld, k8, err_word, absmax_scratch, inv_scale);
+                                                                 rows, k, ld, k8, err_word, absmax_scratch, inv_scale, plain);
     return cudaGetLastError();
   }
   if (k8 == k && (k % 8) == 0 && (ld % 4) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(hi) & 15) == 0 && (reinterpret_cast<uintptr_t>(lo) & 15) == 0) {
     const int64_t n8 = n / 8;
     f16_split_vec8_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(x, static_cast<uint4*>(hi), static_cast<uint4*>(lo),
-                                                                       rows, k / 8, ld, err_word);
+                                                                       rows, k / 8, ld, err_word, plain);
     return cudaGetLastError();
   }
   f16_split_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, static_cast<__half*>(hi), static_cast<__half*>(lo),
-                                                               rows, k, ld, k8, err_word, nullptr, nullptr);
+                                                               rows, k, ld, k8, err_word, nullptr, nullptr, plain);
   return cudaGetLastError();
 }
 

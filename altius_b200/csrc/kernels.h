@@ -109,7 +109,7 @@ struct LayerNormParams {
   float* sum_out;          // [rows, len] or null
   float* out;              // may be null when out16_hi / out16_lo are given
   void* out16_hi;          // the result split for the fp16-split GEMM that consumes it: [rows, len]
-  void* out16_lo;          // halves each, hi = rn_fp16(y), lo = rn_fp16((y - hi) * 2^11); or null
+  void* out16_lo;          // halves each on the fixed scale: Y = y * 2^8, hi = rn_fp16(Y), lo = rn_fp16(Y - hi); or null
   int* err_word;           // receives kGemmRangeCode when the result does not fit that split
   int64_t rows;
   int64_t len;
@@ -199,7 +199,9 @@ struct GemmParams {
   void* c16_lo;             // halves [m, ldc16], for the GEMM that takes it as its pre-split A; or null
   int64_t ldc16;
   int c16_fixed;            // 0: hi / lo as f16_split (lo scaled by 2^11); 1: both on the fixed scale 2^8
-                            // (f16_split_fixed), the operand format of the TMA-fed attention kernel
+                            // (f16_split_fixed): what the kernels that take their operands by TMA read
+  int a16_fixed;            // a16_hi / a16_lo are on the fixed scale (required by the pair kernel that takes them)
+  int b16_plain;            // b16_lo = rn(v - hi) on the scale of b16_hi (the same kernel's format for B)
   const float* b16_inv_scale;  // device scalar 2^-e when b16_hi / b16_lo hold B * 2^e; or null
   const float* b_row_scale;    // tensor-core path with B given [K, N] only: row k of B[batch] is multiplied by
   int64_t b_row_scale_stride;  // b_row_scale[batch * stride + k] (fp32, before the split); or null
@@ -241,8 +243,11 @@ constexpr int kGemmRangeCode = 21;
 // largest magnitude into [2^13, 2^14), so that neither half meets the fp16 subnormals however
 // small the weights are; *inv_scale receives 2^-e for the GEMM's epilogue, `absmax_scratch` is
 // one device word of scratch. Null for activations (no scaling).
+// `plain` = 0: lo = rn((v - hi) * 2^11) (two accumulators in the GEMM); 1: lo = rn(v - hi) on the
+// scale of hi, and an activation is first multiplied by the fixed scale 2^8 -- the operand
+// formats of the single-accumulator pair kernel (GemmParams::a16_fixed, b16_plain).
 cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, int64_t k, int64_t ld, int64_t k8,
-                             int* err_word, float* inv_scale, unsigned* absmax_scratch, cudaStream_t st);
+                             int* err_word, float* inv_scale, unsigned* absmax_scratch, int plain, cudaStream_t st);
 // Whether the tensor-core pair kernel can write its result split (c16_hi / c16_lo) with this epilogue.
 bool gemm_tc_can_split_output(int act, bool bias_n, bool bias_m, bool c_in, float alpha, float bias_scale);
 // hi[i] = rn_tf32(x[i]); lo[i] = rn_tf32(x[i] - hi[i])

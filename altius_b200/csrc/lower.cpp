@@ -34,9 +34,8 @@ struct Ctx {
   // (scratch values `hi`, `lo`). `produced`: a step emitted so far writes the halves (the kernel
   // that computes the value, or a split kernel); `fp32_needed`: someone still reads the value
   // itself, so its producer writes it as well.
-  // `fixed`: the halves are on the fixed scale (f16_split_fixed), the operand format of the
-  // TMA-fed attention kernel, instead of f16_split's.
-  struct Split { int hi = -1, lo = -1; bool produced = false, fp32_needed = true, fixed = false; };
+  // The halves are on the fixed scale (f16_split_fixed): X = x * 2^8, hi = rn(X), lo = rn(X - hi).
+  struct Split { int hi = -1, lo = -1; bool produced = false, fp32_needed = true; };
   std::map<int, Split> split;
   explicit Ctx(AcSession& s_) : s(s_) {}
 
@@ -739,7 +738,6 @@ void plan_presplit(Ctx& c, Plan& plan) {
   // The [B, T, 3D] projection in front of a fused attention core: its GEMM writes it on the fixed
   // scale and the TMA-fed attention kernel reads Q, K and V from there (the Split node between
   // them is the value's one consumer and is absorbed into the core).
-  std::map<int, int> fixed_users;
   if (c.s.opt.gemm_mode == 0 && effective_pairs(c.s) == 2 && !std::getenv("ALTIUS_CUDA_NO_ATTENTION_TMA")) {
     for (auto& kv : plan.attention) {
       const AttentionFusion& f = kv.second;
@@ -749,7 +747,6 @@ void plan_presplit(Ctx& c, Plan& plan) {
                                    f.q.T * f.q.H * f.q.hd))
         continue;
       split_users[src] = 1;
-      fixed_users[src] = 1;
     }
   }
   for (auto& kv : split_users) {
@@ -760,7 +757,6 @@ void plan_presplit(Ctx& c, Plan& plan) {
     sp.hi = new_value(c, floats, false);
     sp.lo = new_value(c, floats, false);
     sp.fp32_needed = c.is_output[a] || (int)c.consumers[a].size() != kv.second;
-    sp.fixed = fixed_users.count(a) != 0;
     c.split[a] = sp;
   }
 }
@@ -807,10 +803,14 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       tc = mode != 2 && (g.ldb % 4) == 0 && (b_off % 4) == 0 && (g.sb % 4) == 0;
     }
   }
-  // mode 0 with a constant rhs: the fp16 split (hi, remainder * 2^11) prepared once, [N, K8] halves.
+  // mode 0 with a constant rhs: the fp16 split prepared once, [N, K8] halves: (hi, remainder * 2^11)
+  // for the kernels with two accumulators, (hi, remainder) for the CTA-pair kernel that takes A
+  // pre-split on the fixed scale and keeps one accumulator.
   int b16_hi = -1, b16_lo = -1, b16_scale = -1;
   int64_t ldb16 = 0;
-  if (tc && mode == 0 && em.c.val(b_use).is_const && g.tb && g.batch == 1 && b_off == 0) {
+  const bool b16_ok = tc && mode == 0 && em.c.val(b_use).is_const && g.tb && g.batch == 1 && b_off == 0;
+  const bool pre = b16_ok && presplit_applies(*s, g, true, a_off, b_off);
+  if (b16_ok) {
     ldb16 = (g.k + 7) / 8 * 8;
     const int64_t floats = g.n * ldb16 / 2;     // two halves per float of scratch
     b16_hi = new_value(em.c, floats, true);
@@ -823,7 +823,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     const int64_t nn = g.n, kk = g.k, ld = g.ldb, k8 = ldb16;
     em.add("weight_f16_split", op, {src}, {hi, lo, scv}, 4.0 * nn * kk + 4.0 * nn * k8, 0, [=](cudaStream_t st) {
       return launch_f16_split(s->fptr(src), s->fptr_mut(hi), s->fptr_mut(lo), nn, kk, ld, k8, s->err_word,
-                              s->fptr_mut(scv), reinterpret_cast<unsigned*>(s->fptr_mut(scv)) + 1, st);
+                              s->fptr_mut(scv), reinterpret_cast<unsigned*>(s->fptr_mut(scv)) + 1, pre ? 1 : 0, st);
     }, 3);
   }
   const int b_plain = b_use;   // the operand before any TF32 rounding
@@ -845,10 +845,10 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
   int a16_hi = -1, a16_lo = -1;
   int64_t lda16 = 0;
   bool a_fp32_present = true;
-  if (tc && b16_hi >= 0 && presplit_applies(*s, g, true, a_off, b_off)) {
+  if (pre) {
     lda16 = g.k;
     auto sp = em.c.split.find(a);
-    const bool planned = sp != em.c.split.end() && !sp->second.fixed && a_off == 0 && g.lda == g.k;
+    const bool planned = sp != em.c.split.end() && a_off == 0 && g.lda == g.k;
     if (planned) {
       a16_hi = sp->second.hi; a16_lo = sp->second.lo;
       a_fp32_present = sp->second.fp32_needed || !sp->second.produced;
@@ -862,7 +862,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
       const int64_t mm = g.m, kk = g.k, ld = g.lda, off = a_off;
       em.add("act_f16_split", op, {a}, {hi, lo}, 8.0 * mm * kk, 0, [=](cudaStream_t st) {
         return launch_f16_split(s->fptr(a) + off, s->fptr_mut(hi), s->fptr_mut(lo), mm, kk, ld, kk, s->err_word,
-                                nullptr, nullptr, st);
+                                nullptr, nullptr, 1, st);
       });
       if (planned) sp->second.produced = true;
     }
@@ -882,7 +882,7 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
         gemm_tc_can_split_output(act, bias_n >= 0, bias_m >= 0, c_in >= 0, alpha, bias_scale)) {
       c16_hi = so->second.hi; c16_lo = so->second.lo;
       c_fp32 = so->second.fp32_needed;
-      c16_fixed = so->second.fixed;
+      c16_fixed = true;
       so->second.produced = true;
     }
   }
@@ -913,6 +913,8 @@ void emit_gemm(Emit& em, int op, const GemmShape& g_in, int a, int b, int out, i
     p.a16_hi = a16_hi >= 0 ? s->ptr(a16_hi) : nullptr;
     p.a16_lo = a16_lo >= 0 ? s->ptr(a16_lo) : nullptr;
     p.lda16 = lda16;
+    p.a16_fixed = a16_hi >= 0 ? 1 : 0;
+    p.b16_plain = pre ? 1 : 0;
     p.m = g.m; p.n = g.n; p.k = g.k; p.batch = g.batch;
     p.a = a_fp32_present ? s->fptr(a) + a_off : nullptr; p.lda = g.lda; p.stride_a = g.sa; p.trans_a = g.ta;
     p.b = s->fptr(bsrc) + b_off; p.ldb = g.ldb; p.stride_b = g.sb; p.trans_b = g.tb;
@@ -1357,8 +1359,8 @@ void lower_node(Emit& em, Plan& plan, int nid) {
         if (o16_hi >= 0) { awrites.push_back(o16_hi); awrites.push_back(o16_lo); }
         // The projection was written on the fixed scale by its GEMM: the TMA-fed kernel.
         auto si = c.split.find(f.q.src);
-        if (tc_attn && si != c.split.end() && si->second.fixed && si->second.produced && f.q.src == f.k.src &&
-            f.q.src == f.v.src) {
+        if (tc_attn && si != c.split.end() && si->second.produced && f.q.src == f.k.src && f.q.src == f.v.src &&
+            attention_tc16_shape_ok((int)hd, (int)T, C, f.q.col, f.k.col, f.v.col, H * hd, T * H * hd)) {
           const int in_hi = si->second.hi, in_lo = si->second.lo;
           em.add("attention_tma_tcgen05", n.op, {in_hi, in_lo, f.scale}, awrites, bytes, flops, [=](cudaStream_t st) {
             Attention16Params p{};

@@ -189,7 +189,8 @@ __device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lan
 // The fused variants are bound by arithmetic (the Gelu above all), not by memory: they keep
 // only the current row in registers (no prefetch of the next one), which lets two or three
 // blocks share an SM.
-// SPLIT: the result is (also) written as fp16 hi / lo halves for the GEMM that consumes it.
+// SPLIT: the result is (also) written as fp16 hi / lo halves on the fixed scale (f16_split_fixed)
+// for the GEMM that consumes it.
 // RESX (1, 2): the residual operand is the chain's own input x, so it is taken from the row in
 // registers, float4 by float4, instead of being loaded and held as a second row: fewer live
 // registers, which buys a fourth block per SM (1) or the prefetch of the next row (2).
@@ -276,10 +277,10 @@ __global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : 2) lay
         if (!SPLIT || p.out) orow[c] = o;
         if (SPLIT) {
           uint2 h, l;
-          tc::f16_split(o, h, l);
+          tc::f16_split_fixed(o, h, l);
           p.hi[row * nvec + c] = h;
           p.lo[row * nvec + c] = l;
-          seen |= tc::split_seen(o);
+          seen |= tc::split_seen_fixed(o);
         }
       }
     }

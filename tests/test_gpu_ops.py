@@ -396,6 +396,45 @@ def test_fp16_split_falls_back_when_the_activations_are_all_tiny(cuda_lib, ascal
         sess.close()
 
 
+@pytest.mark.parametrize("case", ["unit", "up_to_200", "small_1e-2", "rows_of_mixed_size", "one_beyond_255", "all_tiny"])
+def test_presplit_gemm_on_the_fixed_scale(cuda_lib, case):
+    """The CTA-pair kernel takes A as fp16 halves on the fixed scale 2^8 (full precision for
+    |a| in [2^-11, 255]) and keeps one accumulator. In range: the usual bound. An element beyond
+    255, or a tile of A with nothing as large as 2^-11, is reported by the kernel that writes
+    the halves and the run is repeated on the 3xTF32 plan."""
+    from altius_b200.session import CudaSessionBuilder
+    rng = np.random.default_rng(99)
+    a = rng.standard_normal((6304, 768)).astype(np.float32)
+    if case == "up_to_200":
+        a = (a * (200.0 / np.abs(a).max())).astype(np.float32)
+    elif case == "small_1e-2":
+        a = (a * 1e-2).astype(np.float32)
+    elif case == "rows_of_mixed_size":
+        a = (a * np.exp2(-(np.arange(6304) % 10)).astype(np.float32)[:, None]).astype(np.float32)   # rows down to 2^-9
+    elif case == "one_beyond_255":
+        a[4000, 17] = 300.0
+    elif case == "all_tiny":
+        a = (a * 1e-5).astype(np.float32)
+    w = (0.05 * rng.standard_normal((768, 768))).astype(np.float32)
+    b = rng.standard_normal(768).astype(np.float32) * np.float32(1e-3 if case in ("small_1e-2", "all_tiny") else 1.0)
+
+    def build(g):
+        return [g.op("Add", g.op("MatMul", g.add_input("a", a.shape), g.new_init(w)), g.new_init(b))]
+    m = _chain_model(build)
+    sess = CudaSessionBuilder(m).build()
+    try:
+        assert [e["kind"] for e in sess.schedule()] == ["act_f16_split", "gemm_f16x3_pair_tcgen05"]
+        got = sess.run([a])[0]
+        falls_back = case in ("one_beyond_255", "all_tiny")
+        kinds = [e["kind"] for e in sess.schedule()]
+        assert ("gemm_tf32x3_tcgen05" in kinds) == falls_back, kinds
+    finally:
+        sess.close()
+    want = run_oracle(m, [a], sgemm="openblas")[0]
+    bound = 1e-5 * np.abs(want) + 5e-6 * (np.abs(a) @ np.abs(w) + np.abs(b))
+    assert (np.abs(got - want) <= bound).all(), float((np.abs(got - want) / bound).max())
+
+
 @pytest.mark.parametrize("ashape,bshape", [((2, 197, 768), (768, 2304)), ((394, 3072), (3072, 768)), ((1000, 768), (768, 768)),
                                             ((300, 100), (100, 72)), ((257, 36), (36, 513)), ((5000, 64), (64, 256)),
                                             ((6304, 768), (768, 768))])
