@@ -328,20 +328,42 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
   return released;
 }
 
-// The epilogue of the pair kernel that takes A pre-split: sixteen warps with 2 KB of staging
-// each; a warp owns 32 rows x (NCH * 32) columns. Tensor memory goes back to the MMA warp as
-// soon as the warp's last chunk has left it. A chunk passes through the staging tile in halves
-// of 16 columns (four lanes then own one row's 64 contiguous bytes, eight rows per
-// instruction). 16-byte slots are XOR-swizzled by bits 1-2 of the row: writes (a lane per row)
-// and reads (four lanes per row) are both free of bank conflicts.
-template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
-__device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stage, uint32_t tmem_base, int q,
-                                              int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
-                                              Release&& release) {
-  bool released = false;
+// The epilogue of the pair kernel that takes A pre-split: sixteen warps, a warp per tensor-memory
+// lane quarter and 64-column group, each with 4 KB of shared memory. Reading tensor memory
+// while MMAs write it is slow, so a warp first takes its whole 32 x 64 part out -- the second
+// 32-column chunk into its shared memory, the first into registers -- and hands tensor memory
+// back to the MMA warp; bias, activation, residual, the stores and the fp16 split for a
+// consuming kernel then run under the next tile's MMAs: the parked chunk first, then the one
+// from the registers through the same 4 KB. Shared memory is written a row per lane and read four
+// lanes per row (64 contiguous bytes of a row per instruction and row); the 16-byte slots of a
+// row are XOR-swizzled by the row so that neither side has bank conflicts.
+__device__ long long g_epi_stamps[8];   // debug aid: clock64 inside the epilogue of CTA 0, warp 0, tiles 0 and 1
+__device__ __forceinline__ int epi_slot(int row, int j) { return j ^ (((row & 1) << 2) | ((row >> 1) & 3)); }
+
+template <int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
+__device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* buf, uint32_t tmem_base, int q,
+                                                int lane, int m0, int n0, int bz, int cc0, unsigned& seen,
+                                                Release&& release, int stamp = -1) {
   const float sc = acc_scale_of(ep);
   float* c = ep.c ? ep.c + (long long)bz * ep.sc : nullptr;
   const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres : nullptr;
+  const bool have0 = n0 + cc0 * 32 < ep.n, have1 = n0 + (cc0 + 1) * 32 < ep.n;   // uniform across the warp
+  const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16);
+  auto to_buf = [&](const uint32_t (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      buf[lane * 8 + epi_slot(lane, j)] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                      __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+  };
+  uint32_t v[32];
+  __syncwarp();                                     // the previous tile's reads of the buffer are over
+  if (have1) {
+    load_acc<D2OFF>(trow + (uint32_t)((cc0 + 1) * 32), v, sc);
+    to_buf(v);
+  }
+  if (have0) load_acc<D2OFF>(trow + (uint32_t)(cc0 * 32), v, sc);
+  const bool released = release();                  // includes a __syncwarp: the buffer is written
+  if (stamp >= 0 && lane == 0) g_epi_stamps[stamp] = clock64();
   const int c4 = lane & 3, rsub = lane >> 2;
   const int row_base = m0 + q * 32 + rsub;
   float bm[4];
@@ -349,31 +371,19 @@ __device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stag
 #pragma unroll
     for (int i = 0; i < 4; ++i) bm[i] = row_base + 8 * i < ep.m ? __ldg(ep.bias_m + row_base + 8 * i) : 0.f;
   }
+  auto from_buf = [&](const int chunk) {            // bias, activation, residual, stores of one 32-column chunk
 #pragma unroll 1
-  for (int ci = 0; ci < NCH; ++ci) {
-    const int col0 = n0 + (cc0 + ci) * 32;
-    if (col0 >= ep.n) break;                       // uniform across the warp
-    uint32_t v[32];
-    load_acc<D2OFF>(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32), v, sc);
-    if (ci + 1 == NCH || col0 + 32 >= ep.n) released = release();
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        stage[lane * 4 + (j ^ ((lane >> 1) & 3))] =
-            make_float4(__uint_as_float(v[16 * h + 4 * j]), __uint_as_float(v[16 * h + 4 * j + 1]),
-                        __uint_as_float(v[16 * h + 4 * j + 2]), __uint_as_float(v[16 * h + 4 * j + 3]));
-      __syncwarp();
-      const int col = col0 + 16 * h + 4 * c4;
-      const bool col_ok = col < ep.n;   // n % 4 == 0: the whole float4 is in range
+    for (int hh = 0; hh < 2; ++hh) {                // halves of 16 columns
+      const int col = n0 + chunk * 32 + 16 * hh + 4 * c4;
+      if (n0 + chunk * 32 + 16 * hh >= ep.n) break; // uniform across the warp
+      const bool col_ok = col < ep.n;               // n % 4 == 0: the whole float4 is in range
       float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
       if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
       float4 a[4], r[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int rl = 8 * i + rsub;
-        a[i] = stage[rl * 4 + (c4 ^ ((rl >> 1) & 3))];
+        a[i] = buf[rl * 8 + epi_slot(rl, 4 * hh + c4)];
         if (HAS_RES) {
           const int row = row_base + 8 * i;
           r[i] = (col_ok && row < ep.m)
@@ -418,85 +428,19 @@ __device__ __forceinline__ bool epilogue_half(const TcEpilogue& ep, float4* stag
         }
       }
     }
+  };
+  if (have1) {
+    from_buf(cc0 + 1);
+    __syncwarp();                                   // everybody has read the parked chunk
   }
-  return released;
-}
-
-// The same epilogue without shared memory: a thread keeps its row's 32 columns of a chunk in
-// registers from tensor memory to the stores (128 contiguous bytes of fp32 per thread, or 64 of
-// each fp16 half). Stores are 16 bytes per lane on 32 different rows, which L2 merges into full
-// lines; in exchange the epilogue adds nothing to the shared-memory traffic of the operand
-// tiles (TMA writes and the tensor core's reads), which is what it competes with when it runs
-// under the next tile's MMAs.
-template <int NCH, int D2OFF, int ACT, int BIAS, bool HAS_RES, typename Release>
-__device__ __forceinline__ bool epilogue_direct(const TcEpilogue& ep, uint32_t tmem_base, int q, int lane, int m0,
-                                                int n0, int bz, int cc0, unsigned& seen, Release&& release) {
-  static_assert(BIAS != 2, "per-row bias: the staged epilogues");
-  bool released = false;
-  const float sc = acc_scale_of(ep);
-  const int row = m0 + q * 32 + lane;
-  const bool row_ok = row < ep.m;
-  float* c = ep.c ? ep.c + (long long)bz * ep.sc + (long long)row * ep.ldc : nullptr;
-  const float* res = HAS_RES ? ep.res + (long long)bz * ep.sres + (long long)row * ep.ldres : nullptr;
-#pragma unroll 1
-  for (int ci = 0; ci < NCH; ++ci) {
-    const int col0 = n0 + (cc0 + ci) * 32;
-    if (col0 >= ep.n) break;                       // uniform across the warp
-    uint32_t v[32];
-    load_acc<D2OFF>(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((cc0 + ci) * 32), v, sc);
-    if (ci + 1 == NCH || col0 + 32 >= ep.n) released = release();
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {                  // 8 columns at a time
-      const int col = col0 + 8 * j;
-      if (col >= ep.n) break;                      // n % 8 == 0 here: whole groups
-      float4 x0 = make_float4(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]), __uint_as_float(v[8 * j + 2]),
-                              __uint_as_float(v[8 * j + 3]));
-      float4 x1 = make_float4(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), __uint_as_float(v[8 * j + 6]),
-                              __uint_as_float(v[8 * j + 7]));
-      if (BIAS == 1) {
-        const float4 b0 = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
-        const float4 b1 = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col + 4));
-        x0.x = __fadd_rn(x0.x, b0.x); x0.y = __fadd_rn(x0.y, b0.y); x0.z = __fadd_rn(x0.z, b0.z); x0.w = __fadd_rn(x0.w, b0.w);
-        x1.x = __fadd_rn(x1.x, b1.x); x1.y = __fadd_rn(x1.y, b1.y); x1.z = __fadd_rn(x1.z, b1.z); x1.w = __fadd_rn(x1.w, b1.w);
-      }
-      if (ACT == ACT_GELU) {
-        const float2 g0 = gelu_ref2(make_float2(x0.x, x0.y)), g1 = gelu_ref2(make_float2(x0.z, x0.w));
-        const float2 g2 = gelu_ref2(make_float2(x1.x, x1.y)), g3 = gelu_ref2(make_float2(x1.z, x1.w));
-        x0 = make_float4(g0.x, g0.y, g1.x, g1.y);
-        x1 = make_float4(g2.x, g2.y, g3.x, g3.y);
-      } else if (ACT != ACT_NONE) {
-        const float al = ep.act_alpha, be = ep.act_beta;
-        x0.x = apply_act(ACT, x0.x, al, be); x0.y = apply_act(ACT, x0.y, al, be);
-        x0.z = apply_act(ACT, x0.z, al, be); x0.w = apply_act(ACT, x0.w, al, be);
-        x1.x = apply_act(ACT, x1.x, al, be); x1.y = apply_act(ACT, x1.y, al, be);
-        x1.z = apply_act(ACT, x1.z, al, be); x1.w = apply_act(ACT, x1.w, al, be);
-      }
-      if (!row_ok) continue;
-      if (HAS_RES) {
-        const float4 r0 = __ldg(reinterpret_cast<const float4*>(res + col));
-        const float4 r1 = __ldg(reinterpret_cast<const float4*>(res + col + 4));
-        x0.x = __fadd_rn(x0.x, r0.x); x0.y = __fadd_rn(x0.y, r0.y); x0.z = __fadd_rn(x0.z, r0.z); x0.w = __fadd_rn(x0.w, r0.w);
-        x1.x = __fadd_rn(x1.x, r1.x); x1.y = __fadd_rn(x1.y, r1.y); x1.z = __fadd_rn(x1.z, r1.z); x1.w = __fadd_rn(x1.w, r1.w);
-      }
-      if (c) {
-        *reinterpret_cast<float4*>(c + col) = x0;
-        *reinterpret_cast<float4*>(c + col + 4) = x1;
-      }
-      if (ep.c16_hi) {   // the kernel that consumes this result takes it split (batch 1)
-        uint2 h0, l0, h1, l1;
-        if (ep.c16_fixed) {
-          f16_split_fixed(x0, h0, l0); f16_split_fixed(x1, h1, l1);
-          seen |= split_seen_fixed(x0) | split_seen_fixed(x1);
-        } else {
-          f16_split(x0, h0, l0); f16_split(x1, h1, l1);
-          seen |= split_seen(x0) | split_seen(x1);
-        }
-        const long long o = ((long long)row * ep.ldc16 + col) >> 2;   // uint2 index, even: 16-byte aligned
-        *reinterpret_cast<uint4*>(ep.c16_hi + o) = make_uint4(h0.x, h0.y, h1.x, h1.y);
-        *reinterpret_cast<uint4*>(ep.c16_lo + o) = make_uint4(l0.x, l0.y, l1.x, l1.y);
-      }
-    }
+  if (stamp >= 0 && lane == 0) g_epi_stamps[stamp + 1] = clock64();
+  if (have0) {
+    to_buf(v);
+    __syncwarp();
+    if (stamp >= 0 && lane == 0) g_epi_stamps[stamp + 2] = clock64();
+    from_buf(cc0);
   }
+  if (stamp >= 0 && lane == 0) g_epi_stamps[stamp + 3] = clock64();
   return released;
 }
 
@@ -1026,10 +970,10 @@ struct PairSmem {
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   // TMA brings B only (A goes global -> registers -> tiles), or everything (PRE)
   static constexpr int kTxBytes = 2 * kBBytes + (PRE ? 2 * kABytes : 0);
-  // 32 KB of epilogue staging: 2 KB for each of the sixteen warps of the common epilogues (PRE),
-  // or 4 KB for each of the eight warps of the general ones.
-  static constexpr int kEpiBytes = kEpiWarps * 4096;
-  static constexpr int kStages = ((227 - 32) * 1024 - 1536) / kStageBytes;   // 6 at BN 256
+  // Epilogue memory: 4 KB per epilogue warp (PRE: sixteen of them; a parking place for half of
+  // the warp's accumulator part, or the staging tile of the general epilogues).
+  static constexpr int kEpiBytes = (PRE ? 16 : kEpiWarps) * 4096;
+  static constexpr int kStages = (227 * 1024 - kEpiBytes - 1536) / kStageBytes;   // BN 256: 5 with PRE, else 6
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   // Without PRE: D1 and D2, one accumulator set. PRE: the operands are on fixed scales, the three
   // partial products share ONE accumulator, and two sets alternate between consecutive tiles, so
@@ -1040,7 +984,7 @@ struct PairSmem {
 };
 
 // Debug aid (ALTIUS_CUDA_TC_DBG bit 0x1000): clock64 stamps of a few events per CTA.
-__device__ long long g_pair_stamps[160][16];
+__device__ long long g_pair_stamps[160][24];
 __device__ __forceinline__ void pair_stamp(int dbg, int slot) {
   if (dbg & 0x1000) g_pair_stamps[blockIdx.x][slot] = clock64();
 }
@@ -1140,7 +1084,8 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       TcWork wk;
       for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w, ++ti) {
         // The epilogue warps must have drained this accumulator set (PRE: the tile before last).
-        const int set = PRE ? (ti & 1) : 0, use = PRE ? (ti >> 1) : ti;
+        const bool two_sets = PRE && !(dbg & 1024);
+        const int set = two_sets ? (ti & 1) : 0, use = two_sets ? (ti >> 1) : ti;
         if (!mbar_wait(&acc_empty[set], (use & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t d1 = tmem_base + (uint32_t)(set * BN);
@@ -1261,8 +1206,10 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     const int eo = PRE ? e - 8 : e;                                // index among the eight "old" warps
     const int cc0 = (eo >> 2) * (BN / 64), cc1 = cc0 + BN / 64;   // their 32-column chunks
     const int hc0 = (e >> 2) * (BN / 128);                        // PRE, common epilogues: 64 columns from chunk hc0
-    float4* stage = reinterpret_cast<float4*>(epi_smem + (eo < 0 ? 0 : eo) * 4096);
-    float4* stage_h = reinterpret_cast<float4*>(epi_smem + e * 2048);
+    // 4 KB of shared memory per epilogue warp: the parking place of the common epilogues, the
+    // staging tile of the others.
+    float4* stage = reinterpret_cast<float4*>(epi_smem + e * 4096);
+    float4* park = stage;
     const bool simple = ep.alpha == 1.f && !(ep.cin && ep.beta != 0.f) && !(ep.bias_m && ep.bias_n) &&
                         ep.bias_scale == 1.f && (ep.ldc % 4) == 0 && (ep.n % 4) == 0 && (ep.sc % 4) == 0 &&
                         ((reinterpret_cast<uintptr_t>(ep.c) & 15) == 0) &&
@@ -1272,14 +1219,13 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
     const int key = !simple ? -1 : ((ep.bias_n ? 1 : 0) | (ep.res ? 2 : 0) | (ep.act << 2) | (ep.bias_m ? 64 : 0));
     int ti = 0;
     unsigned seen_out = 0;   // what this warp has seen of the results it wrote split (ep.c16_hi)
-    bool mixed = false;      // the previous tile used the staging memory in the other partition
-    bool dead = false;       // a wait of this warp has expired
     TcWork wk;
     for (int w = 0; pair_get_work(sc, w, &wk); ++w, ++ti) {
       const int t = wk.tile;
       const int tn = t % tiles_n, tm = (t / tiles_n) % tiles_m, bz = t / (tiles_n * tiles_m);
       const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
-      const int set = PRE ? (ti & 1) : 0, use = PRE ? (ti >> 1) : ti;
+      const bool two_sets = PRE && !(dbg & 1024);
+      const int set = two_sets ? (ti & 1) : 0, use = two_sets ? (ti >> 1) : ti;
       const uint32_t acc = tmem_base + (uint32_t)(set * BN);
       const uint32_t acc_empty_leader = map_to_cta(&acc_empty[set], 0);
       if (PRE && ep.res && key >= 0 && wk.raw < 0) {
@@ -1292,44 +1238,26 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
             asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + (long long)row * ep.ldres + col));
         }
       }
-      // The K-slice and general epilogues use the staging memory in 4 KB pieces that overlap
-      // the 2 KB pieces of the common one: nobody may still be in a tile of the other kind. (A
-      // warp whose wait has expired keeps walking the tiles for these barriers alone, so that
-      // nobody is left waiting at one.)
       const bool wide = wk.raw >= 0 || key < 0 || (key & 64);
-      if (PRE && (wide || mixed)) asm volatile("bar.sync 2, 512;" ::: "memory");
-      mixed = wide;
-      if (dead) continue;
-      if (!mbar_wait(&acc_full[set], use & 1)) { atomicExch(err, 4); *abort_flag = 1; dead = true; continue; }
+      if (!mbar_wait(&acc_full[set], use & 1)) { atomicExch(err, 4); *abort_flag = 1; break; }
       tc_fence_after();
       if (e == 0 && lane == 0 && ti < 3) pair_stamp(dbg, 8 + 2 * ti);     // accumulator of tile ti complete
       bool released = false;
+      const int estamp = ((dbg & 0x1000) && blockIdx.x == 0 && e == 0 && ti < 2) ? 4 * ti : -1;
       auto release = [&]() -> bool {     // all of this warp's tcgen05.ld have completed
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         return true;
       };
-      if (PRE && m0 < ep.m && !wide && (ep.dbg & 512) == 0 && (ep.n % 8) == 0) {
+      if (PRE && BN == 256 && m0 < ep.m && !wide) {
         switch (key) {
-          case 0: released = epilogue_direct<BN / 128, D2, ACT_NONE, 0, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 1: released = epilogue_direct<BN / 128, D2, ACT_NONE, 1, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 2: released = epilogue_direct<BN / 128, D2, ACT_NONE, 0, true>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 3: released = epilogue_direct<BN / 128, D2, ACT_NONE, 1, true>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_direct<BN / 128, D2, ACT_GELU, 1, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_direct<BN / 128, D2, ACT_RELU, 1, false>(ep, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          default:
-            if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1);
-            break;
-        }
-      } else if (PRE && m0 < ep.m && !wide) {
-        switch (key) {
-          case 0: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 1: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 2: released = epilogue_half<BN / 128, D2, ACT_NONE, 0, true>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case 3: released = epilogue_half<BN / 128, D2, ACT_NONE, 1, true>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_GELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_GELU, 1, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
-          case (ACT_RELU << 2) | 1: released = epilogue_half<BN / 128, D2, ACT_RELU, 1, false>(ep, stage_h, acc, q, lane, m0, n0, bz, hc0, seen_out, release); break;
+          case 0: released = epilogue_parked<D2, ACT_NONE, 0, false>(ep, park, acc, q, lane, m0, n0, bz, hc0, seen_out, release, estamp); break;
+          case 1: released = epilogue_parked<D2, ACT_NONE, 1, false>(ep, park, acc, q, lane, m0, n0, bz, hc0, seen_out, release, estamp); break;
+          case 2: released = epilogue_parked<D2, ACT_NONE, 0, true>(ep, park, acc, q, lane, m0, n0, bz, hc0, seen_out, release, estamp); break;
+          case 3: released = epilogue_parked<D2, ACT_NONE, 1, true>(ep, park, acc, q, lane, m0, n0, bz, hc0, seen_out, release, estamp); break;
+          case (ACT_GELU << 2) | 1: released = epilogue_parked<D2, ACT_GELU, 1, false>(ep, park, acc, q, lane, m0, n0, bz, hc0, seen_out, release, estamp); break;
+          case (ACT_RELU << 2) | 1: released = epilogue_parked<D2, ACT_RELU, 1, false>(ep, park, acc, q, lane, m0, n0, bz, hc0, seen_out, release, estamp); break;
           default:
             if (eo >= 0) epilogue_generic<BN, D2>(ep, stage, acc, q, lane, m0, n0, bz, cc0, cc1);
             break;
@@ -1581,8 +1509,13 @@ cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap&
                                                                           pl.tiles_m, pl.tiles_n, workspace, err, dbg);
   if (dbg & 0x1000) {
     cudaStreamSynchronize(st);
-    static long long h[160][16];
+    static long long h[160][24];
     cudaMemcpyFromSymbol(h, g_pair_stamps, sizeof(h));
+    long long eh[8];
+    cudaMemcpyFromSymbol(eh, g_epi_stamps, sizeof(eh));
+    std::printf("epi stamps:");
+    for (int i = 0; i < 8; ++i) std::printf(" %lld", eh[i] - h[0][0]);
+    std::printf("\n");
     for (int c : {0, 1, 64, 65, 146, 147}) {
       if (c >= 2 * pl.grid) continue;
       std::printf("pair cta %3d:", c);
@@ -1838,7 +1771,7 @@ cudaError_t launch_f16_split(const float* x, void* hi, void* lo, int64_t rows, i
 }
 
 bool gemm_tc_can_split_output(int act, bool bias_n, bool bias_m, bool c_in, float alpha, float bias_scale) {
-  // The epilogues the pair kernel has compiled in with the split store (epilogue_half's callers).
+  // The epilogues the pair kernel has compiled in with the split store (epilogue_parked's callers).
   return !bias_m && !c_in && alpha == 1.f && bias_scale == 1.f && (act == ACT_NONE || (bias_n && (act == ACT_GELU || act == ACT_RELU)));
 }
 
