@@ -998,7 +998,8 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
                     const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_blo,
                     TcEpilogue ep, TcSched sc, int tiles_m, int tiles_n, float* workspace, int* err, int dbg) {
   using L = PairSmem<BN, PRE>;
-  const int S = (dbg >> 8) > 0 && (dbg >> 8) < L::kStages ? (dbg >> 8) : L::kStages;   // experiment: fewer stages
+  // Debug toggle: bits 16-19 of dbg, when set, use fewer stages of the ring.
+  const int S = ((dbg >> 16) & 15) > 0 && ((dbg >> 16) & 15) < L::kStages ? ((dbg >> 16) & 15) : L::kStages;
   constexpr int KB = L::kKb;
   constexpr int D2 = PRE ? 0 : BN;       // column offset of the cross-term accumulator (none with PRE)
   extern __shared__ uint8_t smem_raw[];
@@ -1019,7 +1020,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   const bool leader = rank == 0;
   if (threadIdx.x == 0) pair_stamp(dbg, 0);
 
-  auto pwait = [&](uint64_t* bar, uint32_t parity) { return (dbg & 4) ? mbar_wait_spin(bar, parity) : mbar_wait(bar, parity); };
+  auto pwait = [&](uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity); };
   auto a_raw = [&](int s) { return smem + s * L::kStageBytes; };    // fp16 hi tile of A
   auto a_lo = [&](int s) { return smem + s * L::kStageBytes + L::kOffALo; };
   auto b_hi = [&](int s) { return smem + s * L::kStageBytes + L::kOffBHi; };
@@ -1063,7 +1064,6 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!pwait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
-          if (dbg & 2) { mbar_arrive(&full[s]); continue; }   // timing experiment: no loads
           mbar_arrive_expect_tx(&full[s], L::kTxBytes);
           if (PRE) {   // this CTA's 128 rows of A, hi and lo (rows past M are zero-filled)
             tma_load_3d(a_raw(s), &tm_a, &full[s], kb * KB, m0, 0);

@@ -194,9 +194,12 @@ __device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lan
 // RESX (1, 2): the residual operand is the chain's own input x, so it is taken from the row in
 // registers, float4 by float4, instead of being loaded and held as a second row: fewer live
 // registers, which buys a fourth block per SM (1) or the prefetch of the next row (2).
-template <int NV, bool FUSED, bool GELU, bool SPLIT, int RESX>
-__global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : 2) layer_norm_vec(LnDev p) {
-  constexpr bool PREFETCH = !FUSED || RESX == 2;
+// PF: the next row of a warp is prefetched into registers under the current one (pays when a
+// warp walks many rows; with few rows per warp the registers are worth more as a second pair
+// of resident blocks).
+template <int NV, bool FUSED, bool GELU, bool SPLIT, int RESX, bool PF = (!FUSED || RESX == 2)>
+__global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : (PF ? 2 : 4)) layer_norm_vec(LnDev p) {
+  constexpr bool PREFETCH = PF;
   unsigned seen = 0;
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -543,7 +546,12 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
     // ALTIUS_CUDA_LN_RESX=0|1|2 overrides the choice).
     static const int resx_env = std::getenv("ALTIUS_CUDA_LN_RESX") ? std::atoi(std::getenv("ALTIUS_CUDA_LN_RESX")) : -1;
     const int resx = (fused && q.residual && q.residual == q.x) ? (resx_env >= 0 ? resx_env : 1) : 0;
-    const int depth = fused ? (resx == 1 ? 4 : 3) : 2;    // blocks per SM (measured: 1, 3, 4 are slower for the plain one)
+    // The plain kernel: with fewer than eight rows per warp at two blocks per SM, four blocks per
+    // SM without the prefetch (debug toggle ALTIUS_CUDA_LN_PF=0|1 overrides the choice).
+    static const int pf_env = std::getenv("ALTIUS_CUDA_LN_PF") ? std::atoi(std::getenv("ALTIUS_CUDA_LN_PF")) : -1;
+    const bool few_rows = blocks64 < (int64_t)device_sm_count() * 2 * 8;
+    const bool plain_pf = pf_env >= 0 ? pf_env != 0 : !few_rows;
+    const int depth = fused ? (resx == 1 ? 4 : 3) : (plain_pf ? 2 : 4);    // blocks per SM
     const int64_t vcap = (int64_t)device_sm_count() * depth;
     const unsigned vblocks = blocks64 > vcap ? (unsigned)vcap : (unsigned)blocks64;
 #define AC_LN2(NVV, SP)                                                                     \
@@ -553,7 +561,8 @@ cudaError_t launch_layer_norm(const LayerNormParams& q, cudaStream_t st) {
     else if (fused && q.gelu) layer_norm_vec<NVV, true, true, SP, 0><<<vblocks, kThreads, 0, st>>>(p);  \
     else if (fused && resx) layer_norm_vec<NVV, true, false, SP, 1><<<vblocks, kThreads, 0, st>>>(p);   \
     else if (fused) layer_norm_vec<NVV, true, false, SP, 0><<<vblocks, kThreads, 0, st>>>(p);      \
-    else layer_norm_vec<NVV, false, false, SP, 0><<<vblocks, kThreads, 0, st>>>(p);                \
+    else if (plain_pf) layer_norm_vec<NVV, false, false, SP, 0, true><<<vblocks, kThreads, 0, st>>>(p);     \
+    else layer_norm_vec<NVV, false, false, SP, 0, false><<<vblocks, kThreads, 0, st>>>(p);             \
   } while (0)
 #define AC_LN(NVV)                                                                         \
   do {                                                                                     \

@@ -265,6 +265,14 @@ def _dominant_kernel(prof, runs, peaks):
         # kernels run at half of it; both spend three MMAs per product, so `frac` tops out at 1/3.
         f16 = "f16" in top_kind
         peak = peaks["bf16_tflops_sustained"] / (1.0 if f16 else 2.0)
+        if "simt" in top_kind:
+            # A CUDA-core GEMM (shapes too small for the tensor-core kernels): against the nominal
+            # fp32 FMA rate, 148 SMs x 128 lanes x 2 FLOP x 1.965 GHz; such a case is launch-bound.
+            achieved = tp["flops"] / (tp["total_ms"] * 1e-3) / 1e12
+            return kernels, {"kernel": top_kind, "bound": "tensor", "achieved": round(achieved, 3), "peak": 74.5,
+                             "unit": "TFLOP/s", "frac": round(achieved / 74.5, 5), "traffic": None,
+                             "peak_note": "nominal fp32 FMA rate of the CUDA cores (not measured); this kernel does not "
+                                          "use the tensor cores and a case this small is bound by launch latency"}
         roofline = {"kernel": top_kind, "bound": "tensor", "achieved": round(achieved, 2),
                     "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
                     "traffic": None,

@@ -3,7 +3,10 @@ bench.py, not part of the package).
 
     python kernel_bench.py gemm 6304 768 2304 [--mode 0|1|2] [--iters 10] [--bias] [--gelu] [--residual]
     python kernel_bench.py micrograph [--batch 64] [--no-fuse]
-    python kernel_bench.py attention 32 197 12     # batch, tokens, heads (head dim 64)
+    python kernel_bench.py attention 32 197 12     # batch, tokens, heads (head dim 64): the core alone, fp32 operands
+    python kernel_bench.py layers 32 2             # batch, depth: ViT-B/16 encoder layers as in the model (the
+                                                   # CTA-pair GEMMs with their epilogues, the TMA-fed attention kernel,
+                                                   # the LayerNorm chains writing fp16 halves)
     python kernel_bench.py conv 16 64 112 [--k 1] [--depthwise] [--batch 32]   # c_in, c_out, H = W
 
 Builds a one-node (or micrograph) session with per-kernel CUDA-event profiling
@@ -52,7 +55,7 @@ def _run(model, feeds, mode, fuse, iters, cold=False, pairs=False):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "micrograph", "attention", "conv"])
+    ap.add_argument("what", choices=["gemm", "micrograph", "attention", "conv", "layers"])
     ap.add_argument("dims", nargs="*", type=int)
     ap.add_argument("--mode", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
@@ -120,6 +123,10 @@ def main(argv=None):
         o = g.op("Transpose", o, perm=[0, 2, 1, 3])
         g.outputs.append(g.op("Reshape", o, i64([B, T, D])))
         rows = _run(ir.Model(g, 13), [qkv], a.mode, not a.no_fuse, a.iters)
+    elif a.what == "layers":
+        batch, depth = a.dims
+        model, feeds = configs.vit_base_16(batch=batch, depth=depth)
+        rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters, pairs=a.pairs)
     else:
         model, feeds = configs.micrograph(batch=a.batch)
         rows = _run(model, list(feeds.values()), a.mode, not a.no_fuse, a.iters, cold=a.cold_l2)
