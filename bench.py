@@ -275,7 +275,7 @@ def _dominant_kernel(prof, runs, peaks):
                                           "use the tensor cores and a case this small is bound by launch latency"}
         roofline = {"kernel": top_kind, "bound": "tensor", "achieved": round(achieved, 2),
                     "peak": round(peak, 1), "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
-                    "traffic": None,
+                    "traffic": None, "traffic_note": "no ncu capture of this kernel kind on this workload",
                     "tensor_pipe_frac": round(3.0 * achieved / peak, 4),
                     "peak_note": f"{peaks['source']} sustained bf16 cuBLAS TFLOP/s"
                                  + ("" if f16 else " / 2 (no TF32 peak is measured)")
@@ -508,11 +508,15 @@ def main():
 
     # ---- per-kernel profile of the same workload (rank 0) ---------------------------
     kernels, roofline = _profile_session(builder, in_ptrs, out_ptrs, peaks)
-    if roofline["bound"] == "tensor":
-        roofline["traffic_note"] = ("null: the ncu capture of this kernel is of one launch at the QKV shape "
-                                    "(M 6304, K 768, N 2304) from the kernel bench, not of this in-graph "
-                                    "launch mix; its DRAM bytes are in the committed profile summary")
-
+    if roofline["kernel"] == "gemm_f16x3_pair_tcgen05":
+        # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of this kernel at the QKV shape
+        # (M 6304, K 768, N 2304 + bias) from the ncu capture of `kernel_bench.py gemm 6304 768 2304
+        # --bias`; the roofline's `achieved` averages the 49 launches of four shapes of a step.
+        roofline["traffic"] = 27078400 + 40230400
+        roofline["traffic_note"] = ("ncu capture of one launch at the QKV shape, not of this in-graph launch mix: "
+                                    "27.1 MB read + 40.2 MB written; algorithmic bytes of that launch 84.6 MB "
+                                    "(A halves 19.4, B halves 7.1, output halves 58.1, a third of the output "
+                                    "still in L2 when the kernel ends)")
     sm = clocks.get("sm_mhz")
     line = {
         "metric": "ViT-B/16 images/s", "value": round(value, 2), "unit": "images/s",
