@@ -106,6 +106,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+// K-major tile whose rows are 128 bytes (64 halves) with the 128-byte swizzle: 8-row groups
+// are 1024 bytes apart. A K-step of 16 halves advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                        // leading byte offset (ignored for swizzled K-major)
+  d |= (uint64_t)((8 * 128) >> 4) << 32;         // stride byte offset: 8 rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+  return d;
+}
+
 // Descriptor of an MN-major tile of 4-byte elements. The one layout the tensor core accepts
 // for them is the 128-byte swizzle with 32-byte atoms: 32 columns (128 bytes) x 4 k-rows form
 // a 512-byte atom in which the 32-byte quarter of a row is XORed with the row index; the
@@ -961,19 +973,25 @@ __device__ __forceinline__ bool pair_get_work(const TcSched& sc, int w, TcWork* 
 // all four tiles of a stage come by TMA and no thread of the CTA touches them.
 template <int BN, bool PRE = false>
 struct PairSmem {
-  static constexpr int kKb = BK16;                      // halves of K per stage: 64-byte rows, 64-byte swizzle
+  // Without PRE a stage holds all four tiles for 32 halves of K (64-byte rows, 64-byte swizzle).
+  // PRE: the ring's entries hold ONE operand's hi and lo tiles for 64 halves of K (rows of 128
+  // bytes, 128-byte swizzle: TMA then asks L2 for whole 128-byte lines, which the L2 -> SM path
+  // delivers about a fifth faster than twice as many 64-byte requests); the entries of a K-block
+  // are A's and then B's.
+  static constexpr int kKb = PRE ? 64 : BK16;
   static constexpr int kABytes = BM * kKb * 2;          // fp16 hi tile of A; the lo tile follows
   static constexpr int kBBytes = (BN / 2) * kKb * 2;    // this CTA's half of B: one of hi / lo
   static constexpr int kOffALo = kABytes;
   static constexpr int kOffBHi = 2 * kABytes;
   static constexpr int kOffBLo = kOffBHi + kBBytes;
-  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
-  // TMA brings B only (A goes global -> registers -> tiles), or everything (PRE)
-  static constexpr int kTxBytes = 2 * kBBytes + (PRE ? 2 * kABytes : 0);
+  static_assert(!PRE || kABytes == kBBytes, "entries of one size");
+  static constexpr int kStageBytes = PRE ? 2 * kABytes : 2 * kABytes + 2 * kBBytes;
+  // TMA brings B only (A goes global -> registers -> tiles); PRE: a whole entry
+  static constexpr int kTxBytes = PRE ? 2 * kABytes : 2 * kBBytes;
   // Epilogue memory: 4 KB per epilogue warp (PRE: sixteen of them; a parking place for half of
   // the warp's accumulator part, or the staging tile of the general epilogues).
   static constexpr int kEpiBytes = (PRE ? 16 : kEpiWarps) * 4096;
-  static constexpr int kStages = (227 * 1024 - kEpiBytes - 1536) / kStageBytes;   // BN 256: 5 with PRE, else 6
+  static constexpr int kStages = (227 * 1024 - kEpiBytes - 1536) / kStageBytes;   // BN 256: 5 entries with PRE, else 6 stages
   static constexpr int kDynBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   // Without PRE: D1 and D2, one accumulator set. PRE: the operands are on fixed scales, the three
   // partial products share ONE accumulator, and two sets alternate between consecutive tiles, so
@@ -1060,15 +1078,32 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
         const int tn = wk.tile % tiles_n;
         const int m0 = ((wk.tile / tiles_n) % tiles_m) * (2 * BM) + (int)rank * BM;
+        if (PRE) {
+          // Two ring entries per K-block of 64 halves: this CTA's 128 rows of A (hi, lo; rows past
+          // M are zero-filled), then its half of the B tile (hi, lo).
+          for (int kb = wk.k0; ok && kb < wk.k1; ++kb) {
+            for (int op = 0; op < 2; ++op, ++it) {
+              const int s = it % S;
+              const uint32_t ph = (it / S) & 1;
+              if (!pwait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
+              mbar_arrive_expect_tx(&full[s], L::kTxBytes);
+              uint8_t* e = smem + s * L::kStageBytes;
+              if (op == 0) {
+                tma_load_3d(e, &tm_a, &full[s], kb * KB, m0, 0);
+                tma_load_3d(e + L::kABytes, &tm_alo, &full[s], kb * KB, m0, 0);
+              } else {
+                tma_load_3d(e, &tm_b, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
+                tma_load_3d(e + L::kABytes, &tm_blo, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
+              }
+            }
+          }
+          continue;
+        }
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!pwait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
           mbar_arrive_expect_tx(&full[s], L::kTxBytes);
-          if (PRE) {   // this CTA's 128 rows of A, hi and lo (rows past M are zero-filled)
-            tma_load_3d(a_raw(s), &tm_a, &full[s], kb * KB, m0, 0);
-            tma_load_3d(a_lo(s), &tm_alo, &full[s], kb * KB, m0, 0);
-          }
           tma_load_3d(b_hi(s), &tm_b, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
           tma_load_3d(b_lo(s), &tm_blo, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
         }
@@ -1089,6 +1124,30 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
         if (!mbar_wait(&acc_empty[set], (use & 1) ^ 1)) { atomicExch(err, 5); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t d1 = tmem_base + (uint32_t)(set * BN);
+        if (PRE) {
+          for (int kb = wk.k0; kb < wk.k1; ++kb, it += 2) {
+            const int sa = it % S, sb = (it + 1) % S;          // the K-block's A entry and B entry
+            ok = pwait(&ready[sa], (it / S) & 1) && pwait(&ready[sb], ((it + 1) / S) & 1);
+            if (!ok) { atomicExch(err, 2); *abort_flag = 1; break; }
+            if (it == 0) pair_stamp(dbg, 2);
+            tc_fence_after();
+            const uint32_t ea = smem_u32(smem + sa * L::kStageBytes), eb = smem_u32(smem + sb * L::kStageBytes);
+            const uint64_t da = make_smem_desc_sw128(ea), dal = make_smem_desc_sw128(ea + L::kABytes);
+            const uint64_t db = make_smem_desc_sw128(eb), dbl = make_smem_desc_sw128(eb + L::kABytes);
+            // Operands on fixed scales: the cross terms go into the same accumulator.
+#pragma unroll
+            for (int kk = 0; kk < KB / 16; ++kk) {          // K-steps of 16 halves (32 bytes of a row)
+              const uint64_t off = (uint64_t)(kk * 2);
+              tc_mma_f16_pair(d1, dal + off, db + off, idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);   // a_lo * b_hi
+              tc_mma_f16_pair(d1, da + off, dbl + off, idesc, 1u);                                  // a_hi * b_lo
+              tc_mma_f16_pair(d1, da + off, db + off, idesc, 1u);                                   // a_hi * b_hi
+            }
+            tc_commit_pair(smem_u32(&empty[sa]));          // both entries are free again in this CTA ...
+            tc_commit_pair(map_to_cta(&empty[sa], 1));     // ... and in the peer
+            tc_commit_pair(smem_u32(&empty[sb]));
+            tc_commit_pair(map_to_cta(&empty[sb], 1));
+          }
+        } else
         for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1;
@@ -1098,16 +1157,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           tc_fence_after();
           const uint64_t da = make_smem_desc(smem_u32(a_raw(s))), dal = make_smem_desc(smem_u32(a_lo(s)));
           const uint64_t db = make_smem_desc(smem_u32(b_hi(s))), dbl = make_smem_desc(smem_u32(b_lo(s)));
-          if (PRE) {
-            // Operands on fixed scales: the cross terms go into the same accumulator.
-#pragma unroll
-            for (int kk = 0; kk < KB / 16; ++kk) {          // K-steps of 16 halves (32 bytes of a row)
-              const uint64_t off = (uint64_t)(kk * 2);
-              tc_mma_f16_pair(d1, dal + off, db + off, idesc, (kb > wk.k0 || kk > 0) ? 1u : 0u);   // a_lo * b_hi
-              tc_mma_f16_pair(d1, da + off, dbl + off, idesc, 1u);                                  // a_hi * b_lo
-              tc_mma_f16_pair(d1, da + off, db + off, idesc, 1u);                                   // a_hi * b_hi
-            }
-          } else {
+          {
             // One accumulator after the other within a stage: alternating between them with every
             // MMA cost 30 % of the tensor pipe's rate.
 #pragma unroll
@@ -1136,7 +1186,7 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       bool ok = true;
       TcWork wk;
       for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
-        for (int kb = wk.k0; kb < wk.k1; ++kb, ++it) {
+        for (int e = 2 * (wk.k1 - wk.k0); e > 0; --e, ++it) {     // two ring entries per K-block
           const int s = it % S;
           ok = pwait(&full[s], (it / S) & 1);
           if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
@@ -1418,12 +1468,16 @@ bool make_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t k, int
   cuuint64_t strides[2] = {(cuuint64_t)ld * elem_bytes,
                            (cuuint64_t)(batch > 1 && batch_stride > 0 ? batch_stride : rows * ld) * elem_bytes};
   cuuint32_t box[3] = {(cuuint32_t)box_k, (cuuint32_t)box_rows, 1};
+  // 1128: the plain 128-byte swizzle (K-major tiles of 128-byte rows); 128: the same span with 32-byte atoms
+  const bool sw128_plain = swizzle == 1128;
+  if (sw128_plain) swizzle = 128;
   if (swizzle != 0 && box_k * elem_bytes != swizzle) return false;
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                           : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
+            sw128_plain ? CU_TENSOR_MAP_SWIZZLE_128B
+            : swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                             : (swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1640,7 +1694,8 @@ bool gemm_tc_wants_presplit(int64_t m, int64_t n, int64_t k, int64_t batch) {
 
 size_t gemm_tc_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch, int variant, int allow_pairs) {
   const TcShape sh = pick_shape(m, n, k, batch, variant, allow_pairs);
-  return make_plan(m, n, k, batch, sh.bn, sh.mt, variant == 2 ? BK16 : BK, sh.pair ? pair_count() : 0).workspace_bytes;
+  const int kbf = sh.pair && allow_pairs == 2 ? 64 : (variant == 2 ? BK16 : BK);   // pre-split A: K-blocks of 64 halves
+  return make_plan(m, n, k, batch, sh.bn, sh.mt, kbf, sh.pair ? pair_count() : 0).workspace_bytes;
 }
 
 cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStream_t st) {
@@ -1668,14 +1723,15 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
     if (!pre && q.b16_plain) return cudaErrorInvalidValue;
     if (sh.pair && pre) {
       if ((q.lda16 % 8) != 0) return cudaErrorInvalidValue;
-      if (!make_map(&ma, q.a16_hi, 2, q.k, q.m, 1, q.lda16, 0, BK16, BM, 64)) return cudaErrorInvalidValue;
-      if (!make_map(&mal, q.a16_lo, 2, q.k, q.m, 1, q.lda16, 0, BK16, BM, 64)) return cudaErrorInvalidValue;
+      if (!make_map(&ma, q.a16_hi, 2, q.k, q.m, 1, q.lda16, 0, 64, BM, 1128)) return cudaErrorInvalidValue;
+      if (!make_map(&mal, q.a16_lo, 2, q.k, q.m, 1, q.lda16, 0, 64, BM, 1128)) return cudaErrorInvalidValue;
     } else {
       if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK16, a_rows, 0)) return cudaErrorInvalidValue;
       mal = ma;
     }
-    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
-    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, BK16, b_rows, 64)) return cudaErrorInvalidValue;
+    const int bbox = (sh.pair && pre) ? 64 : BK16, bsw = (sh.pair && pre) ? 1128 : 64;   // pre: K-blocks of 64 halves
+    if (!make_map(&mb, q.b16_hi, 2, q.k, q.n, 1, q.ldb16, 0, bbox, b_rows, bsw)) return cudaErrorInvalidValue;
+    if (!make_map(&mbl, q.b16_lo, 2, q.k, q.n, 1, q.ldb16, 0, bbox, b_rows, bsw)) return cudaErrorInvalidValue;
   } else if (kmode == TC_3X_SPLIT_B_MN) {
     // B [K, N]: N is the contiguous dimension, boxes of 32 columns x BK k-rows.
     if (!make_map(&ma, q.a, 4, q.k, q.m, a_batch, q.lda, q.stride_a, BK, sh.mt * BM, 64)) return cudaErrorInvalidValue;
@@ -1720,7 +1776,8 @@ cudaError_t launch_gemm_tc(const GemmParams& q, int mode, int* err_word, cudaStr
     return cudaErrorInvalidValue;
   }
   ep.dbg = std::getenv("ALTIUS_CUDA_TC_DBG") ? std::atoi(std::getenv("ALTIUS_CUDA_TC_DBG")) : 0;
-  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, kmode == TC_F16X3 ? BK16 : BK, sh.pair ? pair_count() : 0);
+  TcPlan pl = make_plan(q.m, q.n, q.k, q.batch, bn, sh.mt, (sh.pair && pre) ? 64 : (kmode == TC_F16X3 ? BK16 : BK),
+                        sh.pair ? pair_count() : 0);
   if (pl.sc.tail_parts >= 2 && (!q.workspace || q.workspace_bytes < pl.workspace_bytes)) {
     // No (or too small a) workspace: fall back to whole tiles only.
     pl.sc.dp_tiles = pl.sc.num_tiles;
