@@ -346,9 +346,10 @@ __device__ __forceinline__ bool epilogue_fast(const TcEpilogue& ep, float4* stag
 // 32-column chunk into its shared memory, the first into registers -- and hands tensor memory
 // back to the MMA warp; bias, activation, residual, the stores and the fp16 split for a
 // consuming kernel then run under the next tile's MMAs: the parked chunk first, then the one
-// from the registers through the same 4 KB. Shared memory is written a row per lane and read four
-// lanes per row (64 contiguous bytes of a row per instruction and row); the 16-byte slots of a
-// row are XOR-swizzled by the row so that neither side has bank conflicts.
+// from the registers through the same 4 KB. Shared memory is written a row per lane and read
+// eight lanes per row (the whole 128 bytes of a row of the chunk per instruction and row: the
+// global loads and stores that follow are whole 128-byte lines, or 64 bytes of each fp16 half);
+// the 16-byte slots of a row are XOR-swizzled by the row so that neither side has bank conflicts.
 __device__ long long g_epi_stamps[8];   // debug aid: clock64 inside the epilogue of CTA 0, warp 0, tiles 0 and 1
 __device__ __forceinline__ int epi_slot(int row, int j) { return j ^ (((row & 1) << 2) | ((row >> 1) & 3)); }
 
@@ -376,28 +377,26 @@ __device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* bu
   if (have0) load_acc<D2OFF>(trow + (uint32_t)(cc0 * 32), v, sc);
   const bool released = release();                  // includes a __syncwarp: the buffer is written
   if (stamp >= 0 && lane == 0) g_epi_stamps[stamp] = clock64();
-  const int c4 = lane & 3, rsub = lane >> 2;
-  const int row_base = m0 + q * 32 + rsub;
-  float bm[4];
-  if (BIAS == 2) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) bm[i] = row_base + 8 * i < ep.m ? __ldg(ep.bias_m + row_base + 8 * i) : 0.f;
-  }
+  // Eight lanes per row: 128 contiguous bytes of fp32 (64 of each fp16 half) per row and
+  // instruction, four rows per instruction, sixteen rows per pass.
+  const int c8 = lane & 7, r4 = lane >> 3;
   auto from_buf = [&](const int chunk) {            // bias, activation, residual, stores of one 32-column chunk
+    const int col = n0 + chunk * 32 + 4 * c8;
+    const bool col_ok = col < ep.n;                 // n % 4 == 0: the whole float4 is in range
+    float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
 #pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {                // halves of 16 columns
-      const int col = n0 + chunk * 32 + 16 * hh + 4 * c4;
-      if (n0 + chunk * 32 + 16 * hh >= ep.n) break; // uniform across the warp
-      const bool col_ok = col < ep.n;               // n % 4 == 0: the whole float4 is in range
-      float4 bn = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (BIAS == 1 && col_ok) bn = __ldg(reinterpret_cast<const float4*>(ep.bias_n + col));
+    for (int pass = 0; pass < 2; ++pass) {
+      const int row_base = m0 + q * 32 + 16 * pass + r4;
       float4 a[4], r[4];
+      float bm[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int rl = 8 * i + rsub;
-        a[i] = buf[rl * 8 + epi_slot(rl, 4 * hh + c4)];
+        const int rl = 16 * pass + 4 * i + r4;
+        a[i] = buf[rl * 8 + epi_slot(rl, c8)];
+        const int row = row_base + 4 * i;
+        if (BIAS == 2) bm[i] = row < ep.m ? __ldg(ep.bias_m + row) : 0.f;
         if (HAS_RES) {
-          const int row = row_base + 8 * i;
           r[i] = (col_ok && row < ep.m)
                      ? __ldg(reinterpret_cast<const float4*>(res + (long long)row * ep.ldres + col))
                      : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -426,7 +425,7 @@ __device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* bu
           x.x = __fadd_rn(x.x, r[i].x); x.y = __fadd_rn(x.y, r[i].y);
           x.z = __fadd_rn(x.z, r[i].z); x.w = __fadd_rn(x.w, r[i].w);
         }
-        const int row = row_base + 8 * i;
+        const int row = row_base + 4 * i;
         if (col_ok && row < ep.m) {
           if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
           if (ep.c16_hi) {   // the kernel that consumes this result takes it split (batch 1)
