@@ -1278,7 +1278,10 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       const uint32_t acc = tmem_base + (uint32_t)(set * BN);
       const uint32_t acc_empty_leader = map_to_cta(&acc_empty[set], 0);
       if (PRE && ep.res && key >= 0 && wk.raw < 0) {
-        // While the tile's MMAs run: pull this warp's 32 x 64 block of the residual into L2.
+        // While the tile's MMAs run: pull this warp's 32 x 64 block of the residual into L2 -- but
+        // not ahead of the kernel's first operand tiles (a thousand prefetches per SM issued at
+        // kernel entry delayed those by 5 K clocks): wait until the first K-block has landed.
+        if (ti == 0) (void)mbar_wait(&full[1], 0);
         const float* rp = ep.res + (long long)bz * ep.sres;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
