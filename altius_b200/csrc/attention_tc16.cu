@@ -60,7 +60,10 @@ struct Attn16Dev {
   int q_col, k_col, v_col;        // first column of each operand in the [B, T, C] arrays
   const float* scale; int scale_mode;   // 0 none, 1 multiply, 2 divide
   int* err;
+  long long* dbg;   // phase time stamps of CTA 0 when not null (debug toggle)
 };
+__device__ long long g_attn16_stamps[40];   // [0]: kernel entry; [1 + 6 item + k]: phase k of the item (first six items)
+#define AT16_STAMP(k) do { if (p.dbg && blockIdx.x == 0 && (warp & 7) == 0 && lane == 0 && i < 6) p.dbg[1 + 6 * i + (k)] = clock64(); } while (0)
 
 // K-major tile with rows of 128 bytes and the 128-byte swizzle: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k128(uint32_t saddr) {
@@ -162,6 +165,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
   const int my_units = ((int)p.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   const int n_items = my_units * n_tiles;
   bool ok = true;
+  if (p.dbg && blockIdx.x == 0 && tid == 0) p.dbg[0] = clock64();
 
   if (tid == 0) {
     for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
@@ -305,6 +309,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
       const int q0 = tile * QM;
       if (ok && !warp_mbar_wait(&s_full[g], (uint32_t)((i >> 1) & 1), lane)) { atomicExch(p.err, 41); ok = false; }
       tc_fence_after();
+      AT16_STAMP(0);
       // ---- pass 1: row maximum of the scaled scores ----
       float m = CUDART_NAN_F;
 #pragma unroll 1
@@ -330,7 +335,9 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
       // ---- pass 2: P = e * 2^13 as fp16 hi / lo into the ring, running sum ----
       const float m13 = __fsub_rn(m, 13.f);
       float sum = 0.f;
+      AT16_STAMP(1);
       if (ok && i >= 1 && !warp_mbar_wait(p2_turn, (uint32_t)((i - 1) & 1), lane)) { atomicExch(p.err, 44); ok = false; }
+      AT16_STAMP(2);
 #pragma unroll 1
       for (int bi = 0; bi < b_count; ++bi) {
         const int blk = b_begin + bi;
@@ -365,6 +372,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
         fence_proxy_async();
         if (ok) mbar_arrive(&ready[slot]);
       }
+      AT16_STAMP(3);
       // The score buffer has been read for the last time: the scores of item i + 2 may overwrite it.
       tc_fence_before();
       __syncwarp();
@@ -379,6 +387,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
       // ---- O = acc * (1 / sum) * 2^-8: this thread's row, 32 of the 64 columns ----
       if (ok && !warp_mbar_wait(o_full, (uint32_t)(i & 1), lane)) { atomicExch(p.err, 43); ok = false; }
       tc_fence_after();
+      AT16_STAMP(4);
       uint32_t o[32];
       tc_ld_32x32(trow + kOCol + (uint32_t)(hf * 32), o);
       tc_fence_before();
@@ -409,6 +418,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
           }
         }
       }
+      AT16_STAMP(5);
     }
     if (p.o16_hi) split_report_warp(seen_out, p.err);   // out of range, or all tiny
   }
@@ -502,7 +512,24 @@ cudaError_t launch_attention_tc16(const Attention16Params& p, cudaStream_t st) {
   d.q_col = (int)p.q_col; d.k_col = (int)p.k_col; d.v_col = (int)p.v_col;
   d.scale = p.scale; d.scale_mode = p.scale ? p.scale_mode : 0;
   d.err = p.err_word;
-  return p.tokens <= 128 ? launch16_nb<8>(p, d, st) : launch16_nb<13>(p, d, st);
+  d.dbg = nullptr;
+  // Debug toggle: ALTIUS_CUDA_ATTN_STAMPS=1 prints the phase clocks of CTA 0 after every launch
+  // (per item: scores complete, pass 1 done, turn for pass 2, pass 2 done, output complete, written).
+  static const bool stamps = std::getenv("ALTIUS_CUDA_ATTN_STAMPS") != nullptr;
+  if (stamps) cudaGetSymbolAddress(reinterpret_cast<void**>(&d.dbg), g_attn16_stamps);
+  const cudaError_t e = p.tokens <= 128 ? launch16_nb<8>(p, d, st) : launch16_nb<13>(p, d, st);
+  if (stamps && e == cudaSuccess) {
+    long long h[40];
+    cudaStreamSynchronize(st);
+    cudaMemcpyFromSymbol(h, g_attn16_stamps, sizeof(h));
+    std::fprintf(stderr, "attention_tc16 stamps:");
+    for (int i = 0; i < 6; ++i) {
+      std::fprintf(stderr, " |");
+      for (int k = 0; k < 6; ++k) std::fprintf(stderr, " %lld", h[1 + 6 * i + k] - h[0]);
+    }
+    std::fprintf(stderr, "\n");
+  }
+  return e;
 }
 
 }  // namespace ac
