@@ -95,15 +95,19 @@ __device__ __forceinline__ void ld16_issue(uint32_t taddr, uint32_t (&v)[16]) {
       : "memory");
 }
 
-// tcgen05.mma with the A operand in tensor memory: row r of A in lane r, 16 fp16 values of K
-// in 8 consecutive 32-bit columns (element 2c in the low half of column c).
-__device__ __forceinline__ void tc_mma_f16_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                              uint32_t accumulate) {
+// The three partial products of one 16-key chunk (lo * hi, hi * lo, hi * hi) in one statement:
+// tcgen05.mma with the A operand in tensor memory (row r of A in lane r, 16 fp16 values of K in
+// 8 consecutive 32-bit columns, element 2c in the low half of column c).
+__device__ __forceinline__ void tc_mma3_f16_ta(uint32_t d_tmem, uint32_t a_hi, uint32_t a_lo, uint64_t b_hi, uint64_t b_lo,
+                                               uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p, t;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "setp.eq.b32 t, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %3, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %4, %5, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %3, %5, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_hi), "r"(a_lo), "l"(b_hi), "l"(b_lo), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void st16_issue(uint32_t taddr, const uint32_t (&v)[16]) {
@@ -254,25 +258,30 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
         if (i >= 1 && !mbar_wait(&o_free[g ^ 1], (uint32_t)(((i - 1) >> 1) & 1))) { atomicExch(p.err, 38); ok = false; return; }
         AT16_MSTAMP(i, 3);
         const uint32_t pcol = tmem_base + (g ? kS1Col : 0u);
-        const uint32_t v_hi = smem_u32(v_base + vb * 2 * kKvHalfBytes);
+        const uint64_t v_desc = desc_mn128(smem_u32(v_base + vb * 2 * kKvHalfBytes));   // + 128 per chunk of 16 keys (2048 bytes)
+        // When the products are behind the softmax, all of P is there already: one test of each
+        // half's last stage (stages complete in order) replaces the waits stage by stage.
+        const uint32_t rpar = (uint32_t)((i >> 1) & 1);
+        const bool all_there = mbar_test(&ready[(g * 2) * 4 + (NB0 + 1) / 2 - 1], rpar) &&
+                               mbar_test(&ready[(g * 2 + 1) * 4 + (NB - NB0 + 1) / 2 - 1], rpar);
+        if (all_there) tc_fence_after();
         bool first = true;
 #pragma unroll 1
         for (int n = 0; n < 2 * kStages; ++n) {
           const int st = n >> 1, hf = n & 1;
           const int cnt = hf ? NB - NB0 : NB0;
           if (2 * st >= cnt) continue;
-          if (!mbar_wait(&ready[(g * 2 + hf) * 4 + st], (uint32_t)((i >> 1) & 1))) { atomicExch(p.err, 39); ok = false; return; }
-          tc_fence_after();
+          if (!all_there) {
+            if (!mbar_wait(&ready[(g * 2 + hf) * 4 + st], rpar)) { atomicExch(p.err, 39); ok = false; return; }
+            tc_fence_after();
+          }
           if (n == 0) AT16_MSTAMP(i, 4);
           const int c_end = 2 * st + 2 < cnt ? 2 * st + 2 : cnt;
           for (int c = 2 * st; c < c_end; ++c) {
             const int chunk = (hf ? NB0 : 0) + c;
             const uint32_t a_hi = pcol + (uint32_t)(16 * chunk), a_lo = a_hi + 8u;
-            const uint32_t va = v_hi + (uint32_t)(chunk * 16) * 128u;
-            const uint64_t b_hi = desc_mn128(va), b_lo = desc_mn128(va + kKvHalfBytes);
-            tc_mma_f16_ta(tmem_base + kOCol, a_lo, b_hi, idesc_o, first ? 0u : 1u);
-            tc_mma_f16_ta(tmem_base + kOCol, a_hi, b_lo, idesc_o, 1u);
-            tc_mma_f16_ta(tmem_base + kOCol, a_hi, b_hi, idesc_o, 1u);
+            const uint64_t b_hi = v_desc + (uint64_t)(chunk * 128), b_lo = b_hi + (uint64_t)(kKvHalfBytes >> 4);
+            tc_mma3_f16_ta(tmem_base + kOCol, a_hi, a_lo, b_hi, b_lo, idesc_o, first ? 0u : 1u);
             first = false;
           }
         }

@@ -43,6 +43,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
   return false;
 }
+// One non-blocking test of the phase with the given parity.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // The same with the non-blocking test_wait: the thread keeps polling instead of being suspended
 // by the hardware, which notices arrivals from another CTA of the cluster sooner.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
