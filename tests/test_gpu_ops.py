@@ -646,7 +646,9 @@ def _projection_attention_model(B, T, H, scale_op="Mul", w_scale=0.05, with_out_
 @pytest.mark.parametrize("B,T,H,scale_op,out_proj", [(32, 197, 12, "Mul", True), (32, 197, 12, "Div", False),
                                                       (64, 198, 6, "Mul", True), (48, 100, 4, "Mul", False),
                                                       (40, 128, 4, "Div", True), (33, 208, 4, "Mul", False),
-                                                      (37, 65, 4, "Mul", True), (44, 129, 4, "Mul", False)])
+                                                      (37, 65, 4, "Mul", True), (44, 129, 4, "Mul", False),
+                                                      # seven and eight units per CTA: every barrier wraps its parity
+                                                      (128, 100, 8, "Mul", False), (96, 197, 12, "Mul", False)])
 def test_attention_fed_by_tma_from_the_projection_gemm(cuda_lib, B, T, H, scale_op, out_proj):
     """The projection GEMM writes [B, T, 3D] as fp16 halves on the fixed scale and the attention
     kernel takes Q, K and V from there by TMA (no fp32 copy of the projection exists): checked
