@@ -317,7 +317,7 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
     const float sc = SMODE ? __ldg(p.scale) : 1.f;
     const float c1 = __fmul_rn(SMODE == 1 ? __fmul_rn(sc, kLog2e) : (SMODE == 2 ? __fdiv_rn(kLog2e, sc) : kLog2e),
                                kFixedUnscale * kFixedUnscale);
-    unsigned seen_out = 0;
+    float seen_max = 0.f;           // largest magnitude written as fixed-scale halves
 #pragma unroll 1
     for (int i = g; i < n_items; i += 2) {
       const int u = i / n_tiles, tile = i - u * n_tiles;
@@ -420,13 +420,13 @@ attention_tc16_kernel(const __grid_constant__ CUtensorMap tm_q_hi, const __grid_
             const long long o4 = (ob + 8 * j) >> 2;      // uint2 index; even: 16-byte aligned
             *reinterpret_cast<uint4*>(p.o16_hi + o4) = make_uint4(h0.x, h0.y, h1.x, h1.y);
             *reinterpret_cast<uint4*>(p.o16_lo + o4) = make_uint4(l0.x, l0.y, l1.x, l1.y);
-            seen_out |= split_seen_fixed(y0) | split_seen_fixed(y1);
+            seen_max = split_track(split_track(seen_max, y0), y1);
           }
         }
       }
       AT16_STAMP(5);
     }
-    if (p.o16_hi) split_report_warp(seen_out, p.err);   // out of range, or all tiny
+    if (p.o16_hi) split_report_warp(split_seen_fixed_of_max(seen_max), p.err);   // out of range, or all tiny
   }
   tc_fence_before();
   __syncthreads();

@@ -380,6 +380,7 @@ __device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* bu
   // Eight lanes per row: 128 contiguous bytes of fp32 (64 of each fp16 half) per row and
   // instruction, four rows per instruction, sixteen rows per pass.
   const int c8 = lane & 7, r4 = lane >> 3;
+  float seen_max = 0.f;                             // largest magnitude written as fixed-scale halves
   auto from_buf = [&](const int chunk) {            // bias, activation, residual, stores of one 32-column chunk
     const int col = n0 + chunk * 32 + 4 * c8;
     const bool col_ok = col < ep.n;                 // n % 4 == 0: the whole float4 is in range
@@ -430,7 +431,7 @@ __device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* bu
           if (c) *reinterpret_cast<float4*>(c + (long long)row * ep.ldc + col) = x;
           if (ep.c16_hi) {   // the kernel that consumes this result takes it split (batch 1)
             uint2 h, l;
-            if (ep.c16_fixed) { f16_split_fixed(x, h, l); seen |= split_seen_fixed(x); }
+            if (ep.c16_fixed) { f16_split_fixed(x, h, l); seen_max = split_track(seen_max, x); }
             else { f16_split(x, h, l); seen |= split_seen(x); }
             const long long o = ((long long)row * ep.ldc16 + col) >> 2;
             ep.c16_hi[o] = h;
@@ -452,6 +453,7 @@ __device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* bu
     from_buf(cc0);
   }
   if (stamp >= 0 && lane == 0) g_epi_stamps[stamp + 3] = clock64();
+  seen |= split_seen_fixed_of_max(seen_max);
   return released;
 }
 

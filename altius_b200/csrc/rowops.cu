@@ -200,7 +200,7 @@ __device__ __forceinline__ void ln_load_row(const LnDev& p, int64_t row, int lan
 template <int NV, bool FUSED, bool GELU, bool SPLIT, int RESX, bool PF = (!FUSED || RESX == 2)>
 __global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : (PF ? 2 : 4)) layer_norm_vec(LnDev p) {
   constexpr bool PREFETCH = PF;
-  unsigned seen = 0;
+  float seen_max = 0.f;           // largest magnitude written as fixed-scale halves
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -283,7 +283,7 @@ __global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : (PF ? 
           tc::f16_split_fixed(o, h, l);
           p.hi[row * nvec + c] = h;
           p.lo[row * nvec + c] = l;
-          seen |= tc::split_seen_fixed(o);
+          seen_max = tc::split_track(seen_max, o);
         }
       }
     }
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, FUSED ? (RESX == 1 ? 4 : 3) : (PF ? 
       ln_load_row<NV, false>(p, row, lane, nvec, v, reinterpret_cast<float4(&)[NV]>(v));
     }
   }
-  if (SPLIT) tc::split_report_warp(seen, p.err);
+  if (SPLIT) tc::split_report_warp(tc::split_seen_fixed_of_max(seen_max), p.err);
 }
 
 // Any length / alignment: one warp per row, values recomputed from global

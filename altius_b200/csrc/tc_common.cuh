@@ -232,6 +232,15 @@ __device__ __forceinline__ unsigned split_seen_fixed(float x) {
   const unsigned ab = __float_as_uint(X) & 0x7FFFFFFFu;
   return beyond_half(X) | (ab >= 0x3E000000u ? 2u : (ab != 0u ? 4u : 0u));
 }
+// The same verdict from the largest magnitude a thread has seen (one FMNMX per element instead
+// of the flag arithmetic; NaN is ignored by fmaxf as it is by beyond_half): beyond fp16 when
+// |x| > 65504 / 2^8, at least 2^-3 after scaling when |x| >= 2^-11, else non-zero and tiny.
+__device__ __forceinline__ float split_track(float m, float4 v) {
+  return fmaxf(fmaxf(fmaxf(m, fabsf(v.x)), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+__device__ __forceinline__ unsigned split_seen_fixed_of_max(float m) {
+  return (m > 255.875f ? 1u : 0u) | (m >= 0.00048828125f ? 2u : (m > 0.f ? 4u : 0u));
+}
 __device__ __forceinline__ unsigned split_seen_fixed(float4 v) {
   return split_seen_fixed(v.x) | split_seen_fixed(v.y) | split_seen_fixed(v.z) | split_seen_fixed(v.w);
 }
