@@ -1008,10 +1008,11 @@ __device__ __forceinline__ void pair_stamp(int dbg, int slot) {
   if (dbg & 0x1000) g_pair_stamps[blockIdx.x][slot] = clock64();
 }
 
-// PRE runs 19 warps: sixteen epilogue warps (no thread has to touch the operand tiles), the TMA
-// producer, the MMA issuer and the relay.
+// PRE runs 18 warps: sixteen epilogue warps (no thread has to touch the operand tiles), the TMA
+// producer and the MMA issuer. Both CTAs' loads count their bytes on the leader's `ready`
+// barriers, which is all the MMA thread waits for.
 template <int BN, bool PRE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PRE ? kThreads + 32 : kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
                     const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_alo,
                     const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_blo,
@@ -1048,8 +1049,8 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      // one arrival per splitter warp of the pair; PRE: one per CTA (its relay thread)
-      mbar_init(&ready[s], PRE ? 2 : 2 * (kSplitThreads / 32));
+      // one arrival per splitter warp of the pair; PRE: the leader's producer, with the bytes of both CTAs
+      mbar_init(&ready[s], PRE ? 1 : 2 * (kSplitThreads / 32));
       mbar_init(&empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -1087,14 +1088,15 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
               const int s = it % S;
               const uint32_t ph = (it / S) & 1;
               if (!pwait(&empty[s], ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; ok = false; break; }
-              mbar_arrive_expect_tx(&full[s], L::kTxBytes);
+              const uint32_t rdy = map_to_cta(&ready[s], 0);       // the leader's barrier of this entry
+              if (leader) mbar_arrive_expect_tx(&ready[s], 2 * L::kTxBytes);
               uint8_t* e = smem + s * L::kStageBytes;
               if (op == 0) {
-                tma_load_3d(e, &tm_a, &full[s], kb * KB, m0, 0);
-                tma_load_3d(e + L::kABytes, &tm_alo, &full[s], kb * KB, m0, 0);
+                tma_load_3d_pair(e, &tm_a, rdy, kb * KB, m0, 0);
+                tma_load_3d_pair(e + L::kABytes, &tm_alo, rdy, kb * KB, m0, 0);
               } else {
-                tma_load_3d(e, &tm_b, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
-                tma_load_3d(e + L::kABytes, &tm_blo, &full[s], kb * KB, tn * BN + (int)rank * (BN / 2), 0);
+                tma_load_3d_pair(e, &tm_b, rdy, kb * KB, tn * BN + (int)rank * (BN / 2), 0);
+                tma_load_3d_pair(e + L::kABytes, &tm_blo, rdy, kb * KB, tn * BN + (int)rank * (BN / 2), 0);
               }
             }
           }
@@ -1178,21 +1180,6 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
           tc_commit_pair(map_to_cta(&acc_full[set], 1));
         }
         if (ti < 5) pair_stamp(dbg, 3 + ti);   // all MMAs of tile ti issued
-      }
-    }
-  } else if (PRE && warp == kMmaWarp + 1) {
-    // ---------------- relay (PRE): this CTA's tiles have landed -> tell the leader ----------------
-    if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      TcWork wk;
-      for (int w = 0; ok && pair_get_work(sc, w, &wk); ++w) {
-        for (int e = 2 * (wk.k1 - wk.k0); e > 0; --e, ++it) {     // two ring entries per K-block
-          const int s = it % S;
-          ok = pwait(&full[s], (it / S) & 1);
-          if (!ok) { atomicExch(err, 3); *abort_flag = 1; break; }
-          mbar_arrive_cluster(map_to_cta(&ready[s], 0));
-        }
       }
     }
   } else if (!PRE && warp < kSplitWarps) {
@@ -1282,8 +1269,8 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
       if (PRE && ep.res && key >= 0 && wk.raw < 0) {
         // While the tile's MMAs run: pull this warp's 32 x 64 block of the residual into L2 -- but
         // not ahead of the kernel's first operand tiles (a thousand prefetches per SM issued at
-        // kernel entry delayed those by 5 K clocks): wait until the first K-block has landed.
-        if (ti == 0) (void)mbar_wait(&full[1], 0);
+        // kernel entry delayed those by 5 K clocks): wait until the first K-block has been used.
+        if (ti == 0) (void)mbar_wait(&empty[1], 0);
         const float* rp = ep.res + (long long)bz * ep.sres;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -1346,8 +1333,8 @@ gemm_tc_pair_kernel(const float* __restrict__ a_ptr, long long lda, int k_total,
   __syncthreads();
   if (*abort_flag != 0 && warp == kTmaWarp && lane == 0) {
     for (int s = 0; s < S; ++s) {        // copies that may still be in flight: a bounded time to land
-      (void)mbar_wait(&full[s], 0);
-      (void)mbar_wait(&full[s], 1);
+      (void)mbar_wait(PRE ? &ready[s] : &full[s], 0);
+      (void)mbar_wait(PRE ? &ready[s] : &full[s], 1);
     }
   }
   cluster_sync_all();                    // no CTA leaves while its peer may still signal it or read its B half
@@ -1563,7 +1550,7 @@ cudaError_t launch_pair(const float* a, long long lda, int k, const CUtensorMap&
   if (cudaError_t e0 = ensure_dynamic_smem(gemm_tc_pair_kernel<BN, PRE>, L::kDynBytes, &attr_done)) return e0;
   // pl.grid counts pairs; the cluster shape (2, 1, 1) is a compile-time attribute of the kernel.
   static const int dbg = std::getenv("ALTIUS_CUDA_TC_DBG") ? std::atoi(std::getenv("ALTIUS_CUDA_TC_DBG")) : 0;
-  gemm_tc_pair_kernel<BN, PRE><<<2 * pl.grid, PRE ? kThreads + 32 : kThreads, L::kDynBytes, st>>>(a, lda, k, ma, mal, mb, mbl, ep, pl.sc,
+  gemm_tc_pair_kernel<BN, PRE><<<2 * pl.grid, kThreads, L::kDynBytes, st>>>(a, lda, k, ma, mal, mb, mbl, ep, pl.sc,
                                                                           pl.tiles_m, pl.tiles_n, workspace, err, dbg);
   if (dbg & 0x1000) {
     cudaStreamSynchronize(st);
