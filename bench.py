@@ -512,9 +512,9 @@ def main():
         # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of this kernel at the QKV shape
         # (M 6304, K 768, N 2304 + bias) from the ncu capture of `kernel_bench.py gemm 6304 768 2304
         # --bias`; the roofline's `achieved` averages the 49 launches of four shapes of a step.
-        roofline["traffic"] = 27406848 + 39409920
+        roofline["traffic"] = 26996480 + 36545536
         roofline["traffic_note"] = ("ncu capture of one launch at the QKV shape, not of this in-graph launch mix: "
-                                    "27.4 MB read + 39.4 MB written; algorithmic bytes of that launch 84.6 MB "
+                                    "27.0 MB read + 36.5 MB written; algorithmic bytes of that launch 84.6 MB "
                                     "(A halves 19.4, B halves 7.1, output halves 58.1, a third of the output "
                                     "still in L2 when the kernel ends)")
     sm = clocks.get("sm_mhz")
