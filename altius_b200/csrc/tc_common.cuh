@@ -161,6 +161,17 @@ __device__ __forceinline__ void tc_ld_32x32_nowait(uint32_t taddr, uint32_t (&v)
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Sixteen columns of the warp's 32 lanes, without the wait.
+__device__ __forceinline__ void tc_ld_32x16_nowait(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+        "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 
 // Round to nearest (ties away from zero) to TF32's 10 mantissa bits, on the
 // integer ALU: cvt.rna.tf32.f32 gives the same bits but issues on the
