@@ -373,23 +373,24 @@ __device__ __forceinline__ bool epilogue_parked(const TcEpilogue& ep, float4* bu
   if (D2OFF == 0 && have0 && have1 && !(ep.dbg & 128)) {
     // One accumulator, both chunks there. A load of tensor memory issued behind the parking
     // stores waited 2.7 K clocks where the first one took 0.4 K: the kept chunk and the first
-    // half of the parked one are requested together, the second half behind four stores only.
+    // half of the parked one are requested together, the second half before the first is parked.
     uint32_t w[16];
     tc_ld_32x32_nowait(trow + (uint32_t)(cc0 * 32), v);
     tc_ld_32x16_nowait(trow + (uint32_t)((cc0 + 1) * 32), w);
     tc_wait_ld();
+    uint32_t w2[16];
+    tc_ld_32x16_nowait(trow + (uint32_t)((cc0 + 1) * 32 + 16), w2);
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       buf[lane * 8 + epi_slot(lane, j)] =
           make_float4(__fmul_rn(__uint_as_float(w[4 * j]), sc), __fmul_rn(__uint_as_float(w[4 * j + 1]), sc),
                       __fmul_rn(__uint_as_float(w[4 * j + 2]), sc), __fmul_rn(__uint_as_float(w[4 * j + 3]), sc));
-    tc_ld_32x16_nowait(trow + (uint32_t)((cc0 + 1) * 32 + 16), w);
     tc_wait_ld();
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       buf[lane * 8 + epi_slot(lane, 4 + j)] =
-          make_float4(__fmul_rn(__uint_as_float(w[4 * j]), sc), __fmul_rn(__uint_as_float(w[4 * j + 1]), sc),
-                      __fmul_rn(__uint_as_float(w[4 * j + 2]), sc), __fmul_rn(__uint_as_float(w[4 * j + 3]), sc));
+          make_float4(__fmul_rn(__uint_as_float(w2[4 * j]), sc), __fmul_rn(__uint_as_float(w2[4 * j + 1]), sc),
+                      __fmul_rn(__uint_as_float(w2[4 * j + 2]), sc), __fmul_rn(__uint_as_float(w2[4 * j + 3]), sc));
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__fmul_rn(__uint_as_float(v[j]), sc));   // sc is a power of two
   } else {
